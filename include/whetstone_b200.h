@@ -1,0 +1,122 @@
+/* Whetstone attention path for NVIDIA B200: entry points that have no
+ * counterpart in the engine's own kernel library.
+ *
+ * The engine runs one sequence with a contiguous KV cache on one GPU
+ * (crates/whetstone-core/src/engine.rs:264-286,
+ * crates/whetstone-kernels/src/decode.rs:162-212).  Batches, a paged cache and a
+ * KV sequence sharded over several GPUs are therefore additions; they follow the
+ * same rules as whetstone.h (plain C types, device pointers unless named _host,
+ * wst_status_t + wst_last_error, nothing allocated per call, launches on the
+ * calling thread's stream).
+ */
+
+#ifndef WHETSTONE_B200_EXT_H
+#define WHETSTONE_B200_EXT_H
+
+#include "whetstone.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------- plumbing */
+
+/* Library version, "major.minor.patch". */
+WST_API const char *wst_b200_version(void);
+
+/* Stream used by every later call of THIS thread (a cudaStream_t).  NULL
+ * restores the per-thread default stream, which is what the engine's library is
+ * compiled to use (crates/whetstone-kernels/build.rs:133-138). */
+WST_API wst_status_t wst_b200_set_stream(void *stream);
+
+/* Kernels bound every wait on a barrier; one that ran out of time records a
+ * nonzero code in a per-device word instead of hanging.  This synchronises the
+ * calling thread's stream, returns that word in *out_code and clears it. */
+WST_API wst_status_t wst_b200_device_error(uint32_t *out_code);
+
+/* Which kernel family the attention entry points use:
+ *   0 = automatic (default), 1 = force the portable CUDA-core kernel.
+ * A debugging aid for A/B checks; process-wide. */
+WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
+
+/* --------------------------------------------------------- RoPE table */
+
+/* cos/sin tables [max_seq][head_dim/2] float, angles evaluated in double on the
+ * host: the definition the engine uses (RopeTable::with_scaling,
+ * crates/whetstone-kernels/src/decode.rs:95-147).
+ *   scaling_kind 0: inv_freq[j] = theta^(-j/half)
+ *   scaling_kind 1: the Llama-3 piecewise schedule (decode.rs:64-86, 110-130)
+ *                   with factor / low_freq_factor / high_freq_factor /
+ *                   original_max_position
+ * Both outputs are HOST buffers of max_seq * head_dim/2 floats. */
+WST_API wst_status_t wst_rope_table_host(float *cos_host, float *sin_host, int32_t max_seq,
+                                 int32_t head_dim, double theta, int32_t scaling_kind,
+                                 double factor, double low_freq_factor,
+                                 double high_freq_factor, int32_t original_max_position);
+
+/* ------------------------------- decode over a KV sequence shard (multi-GPU) */
+
+/* Like wst_attn_decode over cache rows [0, *len), but stops before the
+ * normalisation: writes, per query head, the running maximum (natural-log
+ * units), the denominator and head_dim numerators -- the (m, l, acc) triple of
+ * cuda/attention.cu:50-55 -- so that shards of one sequence held by different
+ * GPUs can be combined after an all-gather.
+ *   len          device int32, rows of THIS cache that are valid (0 allowed;
+ *                clamped to [0, max_seq])
+ *   partials     scratch of wst_attn_partial_floats() floats
+ *   out_partial  [n_q][head_dim + 2] float */
+WST_API wst_status_t wst_attn_decode_partial(const void *q, const void *k_cache, const void *v_cache,
+                                     void *partials, void *out_partial, int32_t n_q,
+                                     int32_t n_kv, int32_t head_dim, const void *len,
+                                     int32_t max_seq, float scale);
+
+/* Combines n_parts partial sets [n_parts][n_q][head_dim + 2] (as gathered from
+ * the shards) into out [n_q][head_dim] half: the merge of
+ * cuda/attention.cu:170-193 across GPUs instead of across slices. */
+WST_API wst_status_t wst_attn_merge_partials(const void *parts, void *out, int32_t n_parts,
+                                     int32_t n_q, int32_t head_dim);
+
+/* ------------------------------------------------ paged cache, many sequences */
+
+/* Paged KV pool: [n_pool_pages][n_kv][page_size][head_dim] half for K and for V.
+ * page_table [n_seq][max_pages] int32 maps (sequence, position / page_size) to
+ * a pool page.  Tokens of all sequences are packed token-major:
+ * sequence s owns tokens cu_tokens[s] .. cu_tokens[s+1]-1, which sit at cache
+ * positions seq_pos0[s] + j.  page_size must be 16. */
+
+/* Fused QK-norm + RoPE + append for a ragged batch (the batched form of
+ * wst_rope_cache_chunk).
+ *   qkv        [total_tokens][(n_q + 2*n_kv) * head_dim] float
+ *   cos/sin    [table_len][head_dim/2] float; positions are clamped to the table */
+WST_API wst_status_t wst_rope_cache_paged(void *qkv, void *k_pool, void *v_pool, const void *cos_tab,
+                                  const void *sin_tab, const void *page_table,
+                                  const void *seq_pos0, const void *cu_tokens, int32_t n_seq,
+                                  int32_t total_tokens, int32_t max_pages, int32_t page_size,
+                                  int32_t n_pool_pages, int32_t n_q, int32_t n_kv,
+                                  int32_t head_dim, int32_t table_len, const void *q_norm_w,
+                                  const void *k_norm_w, float eps);
+
+/* Ragged multi-token attention for speculative verification: token j of
+ * sequence s sees positions [0, seq_pos0[s] + j] of that sequence's pages (the
+ * batched, paged form of wst_attn_chunk).
+ *   max_tokens_per_seq  upper bound on cu_tokens[s+1]-cu_tokens[s]
+ *   max_len             upper bound on seq_pos0[s] + tokens of s (sizes the grid)
+ *   scratch             wst_attn_verify_scratch_floats() floats
+ *   out                 [total_tokens][n_q * head_dim] half */
+WST_API wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_pool, const void *v_pool,
+                                   const void *page_table, const void *seq_pos0,
+                                   const void *cu_tokens, void *scratch, void *out,
+                                   int32_t n_seq, int32_t total_tokens,
+                                   int32_t max_tokens_per_seq, int32_t max_pages,
+                                   int32_t page_size, int32_t n_pool_pages, int32_t n_q,
+                                   int32_t n_kv, int32_t head_dim, int32_t max_len,
+                                   float scale);
+
+WST_API int64_t wst_attn_verify_scratch_floats(int32_t n_seq, int32_t max_tokens_per_seq, int32_t n_q,
+                                       int32_t n_kv, int32_t head_dim, int32_t max_len);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* WHETSTONE_B200_EXT_H */

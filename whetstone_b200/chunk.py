@@ -1,0 +1,60 @@
+"""Multi-token side of the attention path: the checked wrappers the engine keeps
+in crates/whetstone-kernels/src/chunk.rs (`rope_cache` :140-201, `attn`
+:207-254), over this library's C ABI.  Used for chunked prefill and for
+speculative verification (a chunk of 1 + drafts tokens at pos0 = current pos).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ._ffi import ShapeError, check, lib
+from .decode import KvCache, QkNorm, RopeTable, _ptr, _require_cuda, norm_ptrs, use_torch_stream
+
+
+def rope_cache(qkv: torch.Tensor, cache: KvCache, table: RopeTable, n_q: int, pos0: int, n: int,
+               qk_norm: QkNorm | None = None) -> None:
+    """Rotary embedding (+ QK-norm) and KV append for n positions from pos0."""
+    hd = cache.head_dim
+    stride = (n_q + 2 * cache.n_kv) * hd
+    _require_cuda(qkv, "rope_cache_chunk: qkv", torch.float32)
+    if qkv.numel() < n * stride:
+        raise ShapeError(5, f"rope_cache_chunk: qkv[{qkv.numel()}] needs {n} * {stride}")
+    if table.half_dim != hd // 2 or table.max_seq < cache.max_seq:
+        raise ShapeError(5, "rope_cache_chunk: rotary table does not match the cache geometry")
+    if pos0 + n > cache.max_seq:
+        raise ShapeError(5, f"rope_cache_chunk: chunk [{pos0}, {pos0 + n}) runs past the "
+                            f"{cache.max_seq} token cache")
+    if qk_norm is not None and (qk_norm.q.numel() != hd or qk_norm.k.numel() != hd):
+        raise ShapeError(5, f"rope_cache_chunk: gains are q[{qk_norm.q.numel()}], "
+                            f"k[{qk_norm.k.numel()}]; both must be head_dim {hd}")
+    qw, kw, eps = norm_ptrs(qk_norm)
+    use_torch_stream()
+    check(lib.wst_rope_cache_chunk(_ptr(qkv), _ptr(cache.k), _ptr(cache.v), _ptr(table.cos),
+                                   _ptr(table.sin), n_q, cache.n_kv, hd, pos0, n,
+                                   cache.max_seq, qw, kw, eps))
+
+
+def attn(qkv: torch.Tensor, cache: KvCache, out: torch.Tensor, n_q: int, pos0: int,
+         n: int) -> None:
+    """Causal GQA attention: query j sees cache rows 0 ..= pos0+j."""
+    hd = cache.head_dim
+    stride = (n_q + 2 * cache.n_kv) * hd
+    _require_cuda(qkv, "attn_chunk: qkv", torch.float32)
+    _require_cuda(out, "attn_chunk: out", torch.float16)
+    if qkv.numel() < n * stride:
+        raise ShapeError(5, f"attn_chunk: qkv[{qkv.numel()}] needs {n} * {stride}")
+    if out.numel() < n * n_q * hd:
+        raise ShapeError(5, f"attn_chunk: out[{out.numel()}] needs {n} * {n_q} * {hd}")
+    if pos0 + n > cache.max_seq:
+        raise ShapeError(5, f"attn_chunk: chunk [{pos0}, {pos0 + n}) runs past the "
+                            f"{cache.max_seq} token cache")
+    scale = 1.0 / math.sqrt(hd)
+    use_torch_stream()
+    check(lib.wst_attn_chunk(_ptr(qkv), _ptr(cache.k), _ptr(cache.v), _ptr(out), n_q,
+                             cache.n_kv, hd, pos0, n, cache.max_seq, scale))
+
+
+__all__ = ["rope_cache", "attn"]

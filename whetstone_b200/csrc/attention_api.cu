@@ -1,0 +1,292 @@
+/* C-ABI entry points of the attention kernels: argument checks (same rules and
+ * messages' meaning as cuda/attention.cu:219-247 and cuda/chunk_ops.cu:267-291
+ * of the engine), kernel selection, and the small cross-GPU merge kernel. */
+
+#include <atomic>
+#include <mutex>
+
+#include "attn_prefill.cuh"
+#include "attn_rows.cuh"
+
+namespace wst {
+namespace {
+
+std::atomic<int> g_kernel_choice{0};
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+/* wst_attn_chunk has no scratch argument (the engine's chunk kernel never
+ * splits the sequence), but a handful of draft tokens against a long prefix
+ * must be split to fill the GPU.  The slices' triples go to a per-device
+ * workspace of fixed size, allocated by the first chunk call on that device --
+ * which, as for every lazily initialised part of this ABI, has to be an
+ * ordinary (not graph-captured) call.  Calls that overlap on the GPU from
+ * different streams would share it; the engine is single-stream. */
+constexpr long long kChunkWorkspaceFloats = 4ll << 20; /* 16 MiB */
+
+float *chunk_workspace() {
+  static float *ws[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ws[dev]) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(current_stream(), &cap);
+    if (cap != cudaStreamCaptureStatusNone) return nullptr;
+    void *p = nullptr;
+    if (cudaMalloc(&p, kChunkWorkspaceFloats * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    ws[dev] = static_cast<float *>(p);
+  }
+  return ws[dev];
+}
+
+int max_splits_for(int max_seq) {
+  int t = (max_seq + kRowsTile - 1) / kRowsTile;
+  if (t > kRowsMaxSplits) t = kRowsMaxSplits;
+  return t < 1 ? 1 : t;
+}
+
+/* Shared checks of the decode-shaped entry points. */
+wst_status_t check_decode_shape(const char *who, int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                int32_t max_seq) {
+  if (!(n_q > 0 && n_kv > 0 && head_dim > 0))
+    return fail(WST_ERR_INVALID_ARG, "%s: non-positive shape", who);
+  if (n_q % n_kv != 0)
+    return fail(WST_ERR_INVALID_ARG, "%s: query heads must be a multiple of key/value heads", who);
+  if (head_dim % 32 != 0)
+    return fail(WST_ERR_INVALID_ARG, "%s: head_dim must be a multiple of the warp size", who);
+  if (head_dim > 256) return fail(WST_ERR_INVALID_ARG, "%s: head_dim too large", who);
+  if (max_seq <= 0) return fail(WST_ERR_INVALID_ARG, "%s: empty cache", who);
+  return WST_OK;
+}
+
+wst_status_t decode_common(const char *who, const void *q, const void *k_cache,
+                           const void *v_cache, void *partials, void *out, int32_t n_q,
+                           int32_t n_kv, int32_t head_dim, const void *pos, int32_t max_seq,
+                           float scale, bool partial_out) {
+  RowsLaunch L;
+  L.name = who;
+  L.q = static_cast<const float *>(q);
+  L.q_tok_stride = 0;
+  L.k = static_cast<const __half *>(k_cache);
+  L.v = static_cast<const __half *>(v_cache);
+  L.max_seq = max_seq;
+  L.pos0_dev = static_cast<const int32_t *>(pos);
+  if (partial_out) {
+    L.pos0_bias = -1; /* `len` counts rows: the last visible one is len-1 */
+    L.clamp_pos0_nonneg = false;
+  } else {
+    L.clamp_pos0_nonneg = true; /* seq = max(*pos, 0) + 1 */
+  }
+  L.n_seq = 1;
+  L.n_tok = 1;
+  L.n_q = n_q;
+  L.n_kv = n_kv;
+  L.hd = head_dim;
+  L.scale = scale;
+  L.scratch = static_cast<float *>(partials);
+  L.scratch_floats = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 2);
+  L.max_len = max_seq;
+  L.out = out;
+  L.partial_out = partial_out;
+  if (g_kernel_choice.load() != 1 && rows_kernel_supports(n_q, n_kv, head_dim, k_cache, v_cache) &&
+      aligned16(q))
+    return launch_rows(L);
+  return launch_simple(L);
+}
+
+__global__ void merge_partials_kernel(const float *__restrict__ parts, __half *__restrict__ out,
+                                      int n_parts, int n_q, int hd) {
+  const int head = blockIdx.x;
+  const int stride = hd + 2;
+  float big = -INFINITY;
+  for (int g = 0; g < n_parts; ++g)
+    big = fmaxf(big, parts[(static_cast<long long>(g) * n_q + head) * stride]);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float num = 0.f, den = 0.f;
+    for (int g = 0; g < n_parts; ++g) {
+      const float *t = parts + (static_cast<long long>(g) * n_q + head) * stride;
+      if (t[0] == -INFINITY) continue; /* an empty shard contributes nothing */
+      const float f = expf(t[0] - big);
+      num = fmaf(t[2 + d], f, num);
+      den = fmaf(t[1], f, den);
+    }
+    out[static_cast<long long>(head) * hd + d] = __float2half_rn(den > 0.f ? num / den : 0.f);
+  }
+}
+
+}  // namespace
+}  // namespace wst
+
+using namespace wst;
+
+extern "C" wst_status_t wst_b200_set_kernel_choice(int32_t choice) {
+  WST_CHECK_ARG(choice == 0 || choice == 1, "wst_b200_set_kernel_choice: unknown choice");
+  g_kernel_choice.store(choice);
+  return WST_OK;
+}
+
+extern "C" int32_t wst_attn_partial_floats(int32_t n_q, int32_t head_dim, int32_t max_seq) {
+  if (n_q <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
+  const long long f = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 2);
+  return f > 0x7fffffffLL ? 0x7fffffff : static_cast<int32_t>(f);
+}
+
+extern "C" wst_status_t wst_attn_decode(const void *q, const void *k_cache, const void *v_cache,
+                                        void *partials, void *out, int32_t n_q, int32_t n_kv,
+                                        int32_t head_dim, const void *pos, int32_t max_seq,
+                                        float scale) {
+  WST_CHECK_ARG(q && k_cache && v_cache && out && pos && partials,
+                "wst_attn_decode: null pointer");
+  wst_status_t st = check_decode_shape("wst_attn_decode", n_q, n_kv, head_dim, max_seq);
+  if (st != WST_OK) return st;
+  return decode_common("wst_attn_decode", q, k_cache, v_cache, partials, out, n_q, n_kv,
+                       head_dim, pos, max_seq, scale, false);
+}
+
+extern "C" wst_status_t wst_attn_decode_partial(const void *q, const void *k_cache,
+                                                const void *v_cache, void *partials,
+                                                void *out_partial, int32_t n_q, int32_t n_kv,
+                                                int32_t head_dim, const void *len,
+                                                int32_t max_seq, float scale) {
+  WST_CHECK_ARG(q && k_cache && v_cache && out_partial && len && partials,
+                "wst_attn_decode_partial: null pointer");
+  wst_status_t st = check_decode_shape("wst_attn_decode_partial", n_q, n_kv, head_dim, max_seq);
+  if (st != WST_OK) return st;
+  return decode_common("wst_attn_decode_partial", q, k_cache, v_cache, partials, out_partial,
+                       n_q, n_kv, head_dim, len, max_seq, scale, true);
+}
+
+extern "C" wst_status_t wst_attn_merge_partials(const void *parts, void *out, int32_t n_parts,
+                                                int32_t n_q, int32_t head_dim) {
+  WST_CHECK_ARG(parts && out, "wst_attn_merge_partials: null pointer");
+  WST_CHECK_ARG(n_parts > 0 && n_q > 0 && head_dim > 0,
+                "wst_attn_merge_partials: non-positive shape");
+  const int threads = head_dim < 256 ? ((head_dim + 31) / 32) * 32 : 256;
+  merge_partials_kernel<<<n_q, threads, 0, current_stream()>>>(
+      static_cast<const float *>(parts), static_cast<__half *>(out), n_parts, n_q, head_dim);
+  WST_LAUNCHED("wst_attn_merge_partials");
+  return WST_OK;
+}
+
+extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
+                                       const void *v_cache, void *out, int32_t n_q,
+                                       int32_t n_kv, int32_t head_dim, int32_t pos0, int32_t n,
+                                       int32_t max_seq, float scale) {
+  WST_CHECK_ARG(qkv && k_cache && v_cache && out, "wst_attn_chunk: null pointer");
+  WST_CHECK_ARG(n_q > 0 && n_kv > 0 && head_dim > 0 && n > 0,
+                "wst_attn_chunk: non-positive shape");
+  WST_CHECK_ARG(n_q % n_kv == 0,
+                "wst_attn_chunk: query heads must be a multiple of key/value heads");
+  WST_CHECK_ARG(head_dim % 32 == 0, "wst_attn_chunk: head_dim must be a multiple of the warp size");
+  WST_CHECK_ARG(head_dim <= 256, "wst_attn_chunk: head_dim too large");
+  WST_CHECK_ARG(pos0 >= 0 && static_cast<long long>(pos0) + n <= max_seq,
+                "wst_attn_chunk: chunk runs past cache");
+
+  const int choice = g_kernel_choice.load();
+  const bool tc_ok = choice != 1 && rows_kernel_supports(n_q, n_kv, head_dim, k_cache, v_cache) &&
+                     aligned16(qkv);
+
+  if (tc_ok && prefill_kernel_supports(n_q, n_kv, head_dim, n)) {
+    PrefillLaunch P;
+    P.name = "wst_attn_chunk";
+    P.qkv = static_cast<const float *>(qkv);
+    P.q_tok_stride = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
+    P.k = static_cast<const __half *>(k_cache);
+    P.v = static_cast<const __half *>(v_cache);
+    P.out = static_cast<__half *>(out);
+    P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
+    P.pos0 = pos0; P.n = n; P.max_seq = max_seq; P.scale = scale;
+    return launch_prefill(P);
+  }
+
+  RowsLaunch L;
+  L.name = "wst_attn_chunk";
+  L.q = static_cast<const float *>(qkv);
+  L.q_tok_stride = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
+  L.k = static_cast<const __half *>(k_cache);
+  L.v = static_cast<const __half *>(v_cache);
+  L.max_seq = max_seq;
+  L.pos0_val = pos0;
+  L.n_seq = 1;
+  L.n_tok = n;
+  L.n_q = n_q;
+  L.n_kv = n_kv;
+  L.hd = head_dim;
+  L.scale = scale;
+  L.max_len = pos0 + n;
+  L.out = out;
+  if (!tc_ok) return launch_simple(L);
+  L.scratch = chunk_workspace();
+  L.scratch_floats = L.scratch ? kChunkWorkspaceFloats : 0;
+  return launch_rows(L);
+}
+
+extern "C" int64_t wst_attn_verify_scratch_floats(int32_t n_seq, int32_t max_tokens_per_seq,
+                                                  int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                                  int32_t max_len) {
+  if (n_seq <= 0 || max_tokens_per_seq <= 0 || n_q <= 0 || n_kv <= 0 || head_dim <= 0 ||
+      max_len <= 0 || n_q % n_kv != 0)
+    return 0;
+  /* every (sequence, KV head, row block) may be cut into the maximum number of
+   * slices; rows per block never exceed 64 */
+  const int gqa = n_q / n_kv;
+  const long long rows_total =
+      static_cast<long long>(n_seq) * n_kv *
+      (static_cast<long long>(max_tokens_per_seq) * gqa + 63);
+  return rows_total * max_splits_for(max_len) * (head_dim + 2);
+}
+
+extern "C" wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_pool,
+                                              const void *v_pool, const void *page_table,
+                                              const void *seq_pos0, const void *cu_tokens,
+                                              void *scratch, void *out, int32_t n_seq,
+                                              int32_t total_tokens, int32_t max_tokens_per_seq,
+                                              int32_t max_pages, int32_t page_size,
+                                              int32_t n_pool_pages, int32_t n_q, int32_t n_kv,
+                                              int32_t head_dim, int32_t max_len, float scale) {
+  WST_CHECK_ARG(qkv && k_pool && v_pool && page_table && seq_pos0 && cu_tokens && scratch && out,
+                "wst_attn_verify_paged: null pointer");
+  WST_CHECK_ARG(n_seq > 0 && total_tokens > 0 && max_tokens_per_seq > 0 && n_q > 0 && n_kv > 0,
+                "wst_attn_verify_paged: non-positive shape");
+  WST_CHECK_ARG(n_q % n_kv == 0,
+                "wst_attn_verify_paged: query heads must be a multiple of key/value heads");
+  WST_CHECK_ARG(page_size == 16, "wst_attn_verify_paged: page_size must be 16");
+  WST_CHECK_ARG(max_pages > 0 && n_pool_pages > 0 && max_len > 0,
+                "wst_attn_verify_paged: empty page table or pool");
+  WST_CHECK_ARG(static_cast<long long>(max_pages) * page_size >= max_len,
+                "wst_attn_verify_paged: page table shorter than max_len");
+  if (!rows_kernel_supports(n_q, n_kv, head_dim, k_pool, v_pool) || !aligned16(qkv))
+    return fail(WST_ERR_SHAPE,
+                "wst_attn_verify_paged: needs head_dim 64 or 128, at most 64 query heads per "
+                "KV head and 16-byte aligned buffers");
+  RowsLaunch L;
+  L.name = "wst_attn_verify_paged";
+  L.q = static_cast<const float *>(qkv);
+  L.q_tok_stride = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
+  L.k = static_cast<const __half *>(k_pool);
+  L.v = static_cast<const __half *>(v_pool);
+  L.paged = true;
+  L.max_seq = max_pages * page_size;
+  L.page_table = static_cast<const int32_t *>(page_table);
+  L.max_pages = max_pages;
+  L.n_pool_pages = n_pool_pages;
+  L.pos0_dev = static_cast<const int32_t *>(seq_pos0);
+  L.cu_tokens = static_cast<const int32_t *>(cu_tokens);
+  L.n_seq = n_seq;
+  L.n_tok = max_tokens_per_seq;
+  L.n_q = n_q;
+  L.n_kv = n_kv;
+  L.hd = head_dim;
+  L.scale = scale;
+  L.scratch = static_cast<float *>(scratch);
+  L.scratch_floats =
+      wst_attn_verify_scratch_floats(n_seq, max_tokens_per_seq, n_q, n_kv, head_dim, max_len);
+  L.max_len = max_len;
+  L.out = out;
+  return launch_rows(L);
+}

@@ -1,0 +1,29 @@
+/* Launch interface of the chunked-prefill attention kernel (kernel set 3):
+ * causal attention of a chunk of query tokens against the KV cache with both
+ * contractions on the 5th-generation tensor cores (tcgen05, accumulators in
+ * tensor memory, operands staged by TMA). */
+#pragma once
+
+#include "wst_common.cuh"
+
+namespace wst {
+
+struct PrefillLaunch {
+  const float *qkv = nullptr;  /* [n][q_tok_stride] fp32, q of head h at h*hd */
+  long long q_tok_stride = 0;
+  const __half *k = nullptr;   /* [n_kv][max_seq][hd] */
+  const __half *v = nullptr;
+  __half *out = nullptr;       /* [n][n_q*hd] */
+  int n_q = 0, n_kv = 0, hd = 0;
+  int pos0 = 0, n = 0, max_seq = 0;
+  float scale = 1.f;
+  const char *name = "attention";
+};
+
+/* True if the tcgen05 kernel takes this shape and the chunk is large enough
+ * for 128-row tiles to pay. */
+bool prefill_kernel_supports(int n_q, int n_kv, int hd, int n);
+
+wst_status_t launch_prefill(const PrefillLaunch &P);
+
+}  // namespace wst

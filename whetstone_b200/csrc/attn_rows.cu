@@ -1,0 +1,858 @@
+/* Kernel sets 2 and 4: split-KV attention of a small block of query rows against
+ * a long stretch of one KV head's cache -- batch-1 decode (rows = the heads of
+ * one GQA group), small chunks / speculative verification (rows = heads x draft
+ * tokens) and the ragged, paged form of the latter.
+ *
+ * The path is HBM-bound: every K and V byte of the visible prefix is needed
+ * exactly once.  So the design is built around that one stream:
+ *
+ *   - One CTA owns (sequence, KV head, row block, sequence slice) and serves ALL
+ *     query rows that share the KV head, so the cache is read from DRAM once, not
+ *     once per query head.
+ *   - A dedicated producer warp streams 64-position K and V tiles through a
+ *     multi-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte
+ *     swizzle) and mbarriers; ~128 KB are in flight per SM.
+ *   - Consumer warps each take 16 positions of a tile.  QK^T and PV are
+ *     mma.sync m16n8k16 (fp16 in, fp32 accumulate) because at ~7 query heads per
+ *     KV byte the CUDA cores could not keep up with HBM; the online softmax
+ *     state (running max, denominator) is fp32 and reduced with warp shuffles.
+ *   - The sequence is split over CTAs so that all SMs stream; each slice writes
+ *     an unnormalised (m, l, acc) triple and the LAST slice to finish (an atomic
+ *     ticket, nothing spins) merges them and writes the result.  One launch.
+ *
+ * Semantics follow cuda/attention.cu:57-193 (decode) and cuda/chunk_ops.cu:187-264
+ * (chunk: query j sees rows [0, pos0+j]) of the engine.
+ */
+
+#include "attn_rows.cuh"
+#include "tensor_map.cuh"
+#include "wst_ptx.cuh"
+
+#include <atomic>
+
+namespace wst {
+namespace {
+
+using namespace ptx;
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+/* Tickets for the "last slice merges" protocol: zero at load, reset to zero by
+ * the block that takes the last ticket.  A launch uses one slot. */
+constexpr int kTicketSlots = 32;
+constexpr int kTicketsPerSlot = 2048;
+__device__ unsigned int g_tickets[kTicketSlots * kTicketsPerSlot];
+
+struct RowsArgs {
+  const float *q;
+  long long q_tok_stride;
+  const int32_t *page_table;
+  int max_pages, n_pool_pages;
+  const int32_t *pos0_dev;
+  int pos0_bias, clamp_nonneg, pos0_val;
+  const int32_t *cu_tokens;
+  int n_tok;
+  int n_q, n_kv, gqa, max_seq;
+  float qscale; /* scale * log2(e): scores live in log2 units */
+  float *scratch;
+  unsigned int *tickets;
+  unsigned int *err_word;
+  void *out;
+  int partial_out;
+  int n_splits, n_rowblk, tpb, rows_cap;
+};
+
+template <int HD, int MT, int RG>
+struct Cfg {
+  static constexpr int BN = kRowsTile;
+  static constexpr int NH = HD / 64;             /* 64-column (128-byte) halves */
+  static constexpr int ROWS = 16 * MT * RG;
+  static constexpr int CWARPS = 4 * RG;
+  static constexpr int CTHREADS = CWARPS * 32;
+  static constexpr int THREADS = CTHREADS + 32;
+  static constexpr int HALF_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = 2 * NH * HALF_BYTES;
+  static constexpr int NSTAGE = HD == 128 ? 4 : 6;
+  static constexpr int Q_BYTES = NH * ROWS * 128;
+  static constexpr int NO = MT * (HD / 8) * 4;   /* output accumulators per thread */
+  static constexpr int NREG = NO + MT * 4;       /* + running max and sum */
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + Q_BYTES + 2 * NSTAGE * 8 + 64 + 1024;
+  static_assert(RG * 2 * NREG * 32 * 4 <= NSTAGE * STAGE_BYTES, "merge buffer must fit");
+  static_assert(ROWS * kRowsMaxSplits * 4 + ROWS * 8 <= NSTAGE * STAGE_BYTES, "weights must fit");
+};
+
+__device__ __forceinline__ void consumer_bar(int threads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
+template <int HD, int MT, int RG, bool PAGED>
+__global__ void __launch_bounds__(Cfg<HD, MT, RG>::THREADS, 1)
+attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
+                 const __grid_constant__ CUtensorMap vmap, const RowsArgs a) {
+  using C = Cfg<HD, MT, RG>;
+  constexpr int BN = C::BN, NH = C::NH, ROWS = C::ROWS, NSTAGE = C::NSTAGE;
+  constexpr int HALF_BYTES = C::HALF_BYTES, STAGE_BYTES = C::STAGE_BYTES;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / a.n_rowblk;
+  const int rb = blockIdx.y % a.n_rowblk;
+  const int s = blockIdx.z;
+
+  int tok_begin = 0, n_tok = a.n_tok;
+  if (a.cu_tokens) {
+    tok_begin = a.cu_tokens[s];
+    n_tok = a.cu_tokens[s + 1] - tok_begin;
+  }
+  const int tok0 = rb * a.tpb;
+  if (tok0 >= n_tok) return; /* ragged batch: this row block has no tokens */
+  const int ntok_blk = min(a.tpb, n_tok - tok0);
+  const int rows_valid = ntok_blk * a.gqa;
+
+  int pos0 = a.pos0_dev ? a.pos0_dev[s] + a.pos0_bias : a.pos0_val;
+  if (a.clamp_nonneg && pos0 < 0) pos0 = 0;
+  const int max_seq = a.max_seq;
+  auto limit_of = [pos0, max_seq](int tok) {
+    long long l = static_cast<long long>(pos0) + tok + 1;
+    l = l < 0 ? 0 : l;
+    return static_cast<int>(l < max_seq ? l : max_seq);
+  };
+  const int kv_end = limit_of(tok0 + ntok_blk - 1); /* rows [0, kv_end) are live data */
+  const int lim_min = limit_of(tok0);
+  const int n_tiles = (kv_end + BN - 1) / BN;
+  const int tile_lo = static_cast<int>(static_cast<long long>(split) * n_tiles / a.n_splits);
+  const int tile_hi = static_cast<int>(static_cast<long long>(split + 1) * n_tiles / a.n_splits);
+  const int my_tiles = tile_hi - tile_lo;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t *qsm = smem + NSTAGE * STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(qsm + C::Q_BYTES);
+  int *flags = reinterpret_cast<int *>(bars + 2 * NSTAGE);
+  const uint32_t stages_u32 = smem_u32(smem);
+  const uint32_t q_u32 = smem_u32(qsm);
+  const uint32_t full_u32 = smem_u32(bars);
+  const uint32_t empty_u32 = smem_u32(bars + NSTAGE);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSTAGE; ++i) {
+      mbar_init(full_u32 + 8 * i, 1);
+      mbar_init(empty_u32 + 8 * i, C::CWARPS);
+    }
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  /* ------------------------------------------------------------ producer */
+  if (warp == C::CWARPS) {
+    if (lane != 0) return;
+    tma_prefetch_desc(&kmap);
+    tma_prefetch_desc(&vmap);
+    for (int i = 0; i < my_tiles; ++i) {
+      const int stage = i % NSTAGE, round = i / NSTAGE;
+      if (i >= NSTAGE &&
+          !mbar_wait(empty_u32 + 8 * stage, (round - 1) & 1, a.err_word, 0x101u))
+        break;
+      const uint32_t full = full_u32 + 8 * stage;
+      mbar_arrive_expect_tx(full, STAGE_BYTES);
+      const int tile = tile_lo + i;
+      const uint32_t kdst = stages_u32 + stage * STAGE_BYTES;
+      const uint32_t vdst = kdst + NH * HALF_BYTES;
+      if constexpr (!PAGED) {
+        const int plane = s * a.n_kv + kvh;
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+          tma_load_3d(kdst + h * HALF_BYTES, &kmap, full, h * 64, tile * BN, plane);
+          tma_load_3d(vdst + h * HALF_BYTES, &vmap, full, h * 64, tile * BN, plane);
+        }
+      } else {
+#pragma unroll
+        for (int pg = 0; pg < BN / 16; ++pg) {
+          const int slot = tile * (BN / 16) + pg;
+          int page = slot < a.max_pages
+                         ? a.page_table[static_cast<long long>(s) * a.max_pages + slot]
+                         : -1;
+          /* an unmapped slot reads as zeros: coordinate just past the pool */
+          if (page < 0 || page >= a.n_pool_pages) page = a.n_pool_pages;
+#pragma unroll
+          for (int h = 0; h < NH; ++h) {
+            tma_load_4d(kdst + h * HALF_BYTES + pg * 16 * 128, &kmap, full, h * 64, 0, kvh, page);
+            tma_load_4d(vdst + h * HALF_BYTES + pg * 16 * 128, &vmap, full, h * 64, 0, kvh, page);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  /* ----------------------------------------------------------- consumers */
+  const int rg = warp >> 2; /* row group: rows [rg*16*MT, +16*MT) */
+  const int w = warp & 3;   /* positions [16w, 16w+16) of every tile */
+  const int ctid = threadIdx.x;
+
+  /* q -> fp16, pre-multiplied by scale*log2(e), swizzled like the K tiles. */
+  for (int idx = ctid; idx < ROWS * (HD / 8); idx += C::CTHREADS) {
+    const int row = idx / (HD / 8), ch = idx % (HD / 8);
+    uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows_valid) {
+      const int tok = tok_begin + tok0 + row / a.gqa;
+      const int head = kvh * a.gqa + row % a.gqa;
+      const float4 *src = reinterpret_cast<const float4 *>(
+          a.q + static_cast<long long>(tok) * a.q_tok_stride + static_cast<long long>(head) * HD +
+          ch * 8);
+      const float4 lo = __ldg(src), hi = __ldg(src + 1);
+      packed.x = pack_half2(lo.x * a.qscale, lo.y * a.qscale);
+      packed.y = pack_half2(lo.z * a.qscale, lo.w * a.qscale);
+      packed.z = pack_half2(hi.x * a.qscale, hi.y * a.qscale);
+      packed.w = pack_half2(hi.z * a.qscale, hi.w * a.qscale);
+    }
+    *reinterpret_cast<uint4 *>(qsm + (ch >> 3) * (ROWS * 128) + swz128(row, ch & 7)) = packed;
+  }
+  consumer_bar(C::CTHREADS);
+
+  int lim[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = rg * 16 * MT + mt * 16 + (lane >> 2) + hh * 8;
+      lim[mt][hh] = r < rows_valid ? limit_of(tok0 + r / a.gqa) : kv_end;
+    }
+
+  auto q_frag_addr = [&](int mt, int ks) {
+    const int row = rg * 16 * MT + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int chg = 2 * ks + (lane >> 4);
+    return q_u32 + (chg >> 3) * (ROWS * 128) + swz128(row, chg & 7);
+  };
+
+  uint32_t qf[MT == 1 ? HD / 16 : 1][4];
+  if constexpr (MT == 1) {
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      ldsm_x4(q_frag_addr(0, ks), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+  }
+
+  float m_run[MT][2], l_run[MT][2];
+  float o[MT][HD / 8][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[mt][nt][c] = 0.f;
+  }
+
+  for (int i = 0; i < my_tiles; ++i) {
+    const int stage = i % NSTAGE, round = i / NSTAGE;
+    if (!mbar_wait(full_u32 + 8 * stage, round & 1, a.err_word, 0x102u)) break;
+    const int tile = tile_lo + i;
+    const uint32_t kb = stages_u32 + stage * STAGE_BYTES;
+    const uint32_t vb = kb + NH * HALF_BYTES;
+
+    /* S = Q K^T for this warp's 16 positions */
+    float sacc[MT][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sacc[mt][nt][c] = 0.f;
+
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const int mi = lane >> 3;
+      const int prow = 16 * w + (mi >> 1) * 8 + (lane & 7);
+      const int chg = 2 * ks + (mi & 1);
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(kb + (chg >> 3) * HALF_BYTES + swz128(prow, chg & 7), b0, b1, b2, b3);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        if constexpr (MT == 1) {
+          mma_16816(sacc[0][0], qf[ks], b0, b1);
+          mma_16816(sacc[0][1], qf[ks], b2, b3);
+        } else {
+          uint32_t af[4];
+          ldsm_x4(q_frag_addr(mt, ks), af[0], af[1], af[2], af[3]);
+          mma_16816(sacc[mt][0], af, b0, b1);
+          mma_16816(sacc[mt][1], af, b2, b3);
+        }
+      }
+    }
+
+    /* causal / end-of-sequence mask: only tiles that reach past the smallest limit */
+    if (tile * BN + BN > lim_min) {
+      const int pbase = tile * BN + 16 * w + 2 * (lane & 3);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int p = pbase + nt * 8 + (c & 1);
+            if (p >= lim[mt][c >> 1]) sacc[mt][nt][c] = -INFINITY;
+          }
+    }
+
+    /* online softmax in fp32, two rows per thread per 16-row tile */
+    uint32_t pa[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        float mx = fmaxf(fmaxf(sacc[mt][0][2 * hh], sacc[mt][0][2 * hh + 1]),
+                         fmaxf(sacc[mt][1][2 * hh], sacc[mt][1][2 * hh + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[mt][hh], mx);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = ex2(m_run[mt][hh] - m_use);
+        m_run[mt][hh] = m_new;
+        float psum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const float p = ex2(sacc[mt][nt][2 * hh + c] - m_use);
+            sacc[mt][nt][2 * hh + c] = p;
+            psum += p;
+          }
+        l_run[mt][hh] = fmaf(l_run[mt][hh], corr, psum);
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; ++nt) {
+          o[mt][nt][2 * hh] *= corr;
+          o[mt][nt][2 * hh + 1] *= corr;
+        }
+      }
+      pa[mt][0] = pack_half2(sacc[mt][0][0], sacc[mt][0][1]);
+      pa[mt][1] = pack_half2(sacc[mt][0][2], sacc[mt][0][3]);
+      pa[mt][2] = pack_half2(sacc[mt][1][0], sacc[mt][1][1]);
+      pa[mt][3] = pack_half2(sacc[mt][1][2], sacc[mt][1][3]);
+    }
+
+    /* Rows past the live data may hold anything (even NaN bit patterns), and
+     * 0 * NaN is NaN: clear this warp's V rows beyond kv_end in the last tile. */
+    if (tile * BN + BN > kv_end) {
+      for (int idx = lane; idx < 16 * NH * 8; idx += 32) {
+        const int prow = 16 * w + idx / (NH * 8);
+        const int rest = idx % (NH * 8);
+        if (tile * BN + prow >= kv_end) {
+          asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(
+                           vb + (rest >> 3) * HALF_BYTES + prow * 128 + (rest & 7) * 16),
+                       "r"(0u)
+                       : "memory");
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+    }
+
+    /* O += P V */
+#pragma unroll
+    for (int jj = 0; jj < HD / 16; ++jj) {
+      const int mi = lane >> 3;
+      const int prow = 16 * w + (mi & 1) * 8 + (lane & 7);
+      const int chg = 2 * jj + (mi >> 1);
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_trans(vb + (chg >> 3) * HALF_BYTES + swz128(prow, chg & 7), b0, b1, b2, b3);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma_16816(o[mt][2 * jj], pa[mt], b0, b1);
+        mma_16816(o[mt][2 * jj + 1], pa[mt], b2, b3);
+      }
+    }
+
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_u32 + 8 * stage);
+  }
+
+  /* row sums live spread over the four lanes of a quad */
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float l = l_run[mt][hh];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      l_run[mt][hh] = l;
+    }
+
+  /* ---- combine the four warps of a row group (tree, through the idle ring) */
+  float *mbuf = reinterpret_cast<float *>(smem);
+  auto put_state = [&](int slot) {
+    float *dst = mbuf + static_cast<size_t>(slot) * C::NREG * 32 + lane;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int nt = 0; nt < HD / 8; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dst[((mt * (HD / 8) + nt) * 4 + c) * 32] = o[mt][nt][c];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        dst[(C::NO + mt * 2 + hh) * 32] = m_run[mt][hh];
+        dst[(C::NO + MT * 2 + mt * 2 + hh) * 32] = l_run[mt][hh];
+      }
+    }
+  };
+  auto take_state = [&](int slot) {
+    const float *src = mbuf + static_cast<size_t>(slot) * C::NREG * 32 + lane;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const float m_o = src[(C::NO + mt * 2 + hh) * 32];
+        const float l_o = src[(C::NO + MT * 2 + mt * 2 + hh) * 32];
+        const float m_new = fmaxf(m_run[mt][hh], m_o);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float c_me = ex2(m_run[mt][hh] - m_use);
+        const float c_ot = ex2(m_o - m_use);
+        m_run[mt][hh] = m_new;
+        l_run[mt][hh] = l_run[mt][hh] * c_me + l_o * c_ot;
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; ++nt)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int k = 2 * hh + c;
+            o[mt][nt][k] = o[mt][nt][k] * c_me + src[((mt * (HD / 8) + nt) * 4 + k) * 32] * c_ot;
+          }
+      }
+  };
+
+  consumer_bar(C::CTHREADS); /* every warp is done with the ring */
+  if (w >= 2) put_state(rg * 2 + (w - 2));
+  consumer_bar(C::CTHREADS);
+  if (w < 2) take_state(rg * 2 + w);
+  consumer_bar(C::CTHREADS);
+  if (w == 1) put_state(rg * 2);
+  consumer_bar(C::CTHREADS);
+  if (w == 0) take_state(rg * 2);
+
+  /* ---- write: final result (one slice) or this slice's triple */
+  const int unit = (s * a.n_kv + kvh) * a.n_rowblk + rb;
+  const bool single = a.n_splits == 1;
+  if (w == 0) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int r = rg * 16 * MT + mt * 16 + (lane >> 2) + hh * 8;
+        if (r >= rows_valid) continue;
+        const int col = 2 * (lane & 3);
+        if (single && !a.partial_out) {
+          const int tok = tok_begin + tok0 + r / a.gqa;
+          const int head = kvh * a.gqa + r % a.gqa;
+          const float inv = l_run[mt][hh] > 0.f ? 1.f / l_run[mt][hh] : 0.f;
+          __half *dst = static_cast<__half *>(a.out) +
+                        (static_cast<long long>(tok) * a.n_q + head) * HD + col;
+#pragma unroll
+          for (int nt = 0; nt < HD / 8; ++nt)
+            *reinterpret_cast<__half2 *>(dst + nt * 8) = __floats2half2_rn(
+                o[mt][nt][2 * hh] * inv, o[mt][nt][2 * hh + 1] * inv);
+        } else {
+          float *dst;
+          float m_out = m_run[mt][hh];
+          if (single) { /* partial_out: the caller's triple, natural-log units */
+            dst = static_cast<float *>(a.out) +
+                  static_cast<long long>(kvh * a.gqa + r % a.gqa) * (HD + 2);
+            m_out *= kLn2;
+          } else {
+            dst = a.scratch +
+                  ((static_cast<long long>(unit) * a.n_splits + split) * a.rows_cap + r) * (HD + 2);
+          }
+          if ((lane & 3) == 0) {
+            dst[0] = m_out;
+            dst[1] = l_run[mt][hh];
+          }
+#pragma unroll
+          for (int nt = 0; nt < HD / 8; ++nt)
+            *reinterpret_cast<float2 *>(dst + 2 + nt * 8 + col) =
+                make_float2(o[mt][nt][2 * hh], o[mt][nt][2 * hh + 1]);
+        }
+      }
+    if (!single) __threadfence();
+  }
+  if (single) return;
+
+  /* ---- ticket: the last slice of this unit to arrive merges all of them */
+  consumer_bar(C::CTHREADS);
+  if (ctid == 0) {
+    const unsigned int prev = atomicAdd(&a.tickets[unit], 1u);
+    const int last = prev == static_cast<unsigned int>(a.n_splits - 1);
+    if (last) a.tickets[unit] = 0u; /* everyone has arrived: leave it ready for the next launch */
+    flags[0] = last;
+  }
+  consumer_bar(C::CTHREADS);
+  if (!flags[0]) return;
+  __threadfence();
+
+  const int ns = a.n_splits;
+  float *wsm = reinterpret_cast<float *>(smem); /* [rows_valid][ns] weights */
+  float *row_m = wsm + ROWS * kRowsMaxSplits;   /* [ROWS] */
+  float *row_l = row_m + ROWS;
+  const float *base = a.scratch + static_cast<long long>(unit) * ns * a.rows_cap * (HD + 2);
+  auto triple = [&](int sp, int row) {
+    return base + (static_cast<long long>(sp) * a.rows_cap + row) * (HD + 2);
+  };
+  for (int idx = ctid; idx < rows_valid * ns; idx += C::CTHREADS) {
+    const int row = idx / ns, sp = idx % ns;
+    wsm[row * ns + sp] = __ldcg(triple(sp, row));
+  }
+  consumer_bar(C::CTHREADS);
+  for (int row = ctid; row < rows_valid; row += C::CTHREADS) {
+    float M = -INFINITY;
+    for (int sp = 0; sp < ns; ++sp) M = fmaxf(M, wsm[row * ns + sp]);
+    float den = 0.f;
+    for (int sp = 0; sp < ns; ++sp) {
+      const float m = wsm[row * ns + sp];
+      const float wgt = (m == -INFINITY) ? 0.f : ex2(m - M);
+      wsm[row * ns + sp] = wgt;
+      den = fmaf(wgt, __ldcg(triple(sp, row) + 1), den);
+    }
+    row_m[row] = M;
+    row_l[row] = den;
+  }
+  consumer_bar(C::CTHREADS);
+  for (int idx = ctid; idx < rows_valid * (HD / 2); idx += C::CTHREADS) {
+    const int row = idx / (HD / 2), c2 = idx % (HD / 2);
+    float ax = 0.f, ay = 0.f;
+#pragma unroll 4
+    for (int sp = 0; sp < ns; ++sp) {
+      const float wgt = wsm[row * ns + sp];
+      const float2 v = __ldcg(reinterpret_cast<const float2 *>(triple(sp, row) + 2) + c2);
+      ax = fmaf(wgt, v.x, ax);
+      ay = fmaf(wgt, v.y, ay);
+    }
+    const int head = kvh * a.gqa + row % a.gqa;
+    if (a.partial_out) {
+      float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (HD + 2);
+      if (c2 == 0) {
+        dst[0] = row_m[row] * kLn2;
+        dst[1] = row_l[row];
+      }
+      *reinterpret_cast<float2 *>(dst + 2 + 2 * c2) = make_float2(ax, ay);
+    } else {
+      const int tok = tok_begin + tok0 + row / a.gqa;
+      const float inv = row_l[row] > 0.f ? 1.f / row_l[row] : 0.f;
+      __half *dst =
+          static_cast<__half *>(a.out) + (static_cast<long long>(tok) * a.n_q + head) * HD;
+      *reinterpret_cast<__half2 *>(dst + 2 * c2) = __floats2half2_rn(ax * inv, ay * inv);
+    }
+  }
+}
+
+/* ------------------------------------------------- portable fallback kernel */
+
+/* One warp per (token, query head); eight lanes share a cache position, each
+ * holding an hd/8 slice of q and of the accumulator, so a warp sweeps four
+ * positions at a time.  CUDA cores only; natural-log softmax with expf. */
+struct SimpleArgs {
+  const float *q;
+  long long q_tok_stride;
+  const __half *k, *v;
+  int n_q, gqa, hd, max_seq, n_tok;
+  const int32_t *pos0_dev;
+  int pos0_bias, clamp_nonneg, pos0_val;
+  float scale;
+  void *out;
+  int partial_out;
+};
+
+template <int EPL> /* elements per lane = hd / 8, multiple of 4, <= 32 */
+__global__ void __launch_bounds__(128) attn_simple_kernel(const SimpleArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= a.n_tok * a.n_q) return;
+  const int tok = row / a.n_q, head = row % a.n_q;
+  const int kvh = head / a.gqa;
+  const int grp = lane >> 3, sub = lane & 7;
+
+  int pos0 = a.pos0_dev ? *a.pos0_dev + a.pos0_bias : a.pos0_val;
+  if (a.clamp_nonneg && pos0 < 0) pos0 = 0;
+  long long lim_ll = static_cast<long long>(pos0) + tok + 1;
+  lim_ll = lim_ll < 0 ? 0 : lim_ll;
+  const int limit = static_cast<int>(lim_ll < a.max_seq ? lim_ll : a.max_seq);
+
+  const int hd = a.hd;
+  const float *qp = a.q + static_cast<long long>(tok) * a.q_tok_stride +
+                    static_cast<long long>(head) * hd + sub * EPL;
+  float qv[EPL], acc[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    qv[e] = qp[e] * a.scale;
+    acc[e] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  const __half *kb = a.k + static_cast<long long>(kvh) * a.max_seq * hd + sub * EPL;
+  const __half *vb = a.v + static_cast<long long>(kvh) * a.max_seq * hd + sub * EPL;
+
+  for (int p0 = 0; p0 < limit; p0 += 4) {
+    const int p = p0 + grp;
+    const bool live = p < limit;
+    float part = 0.f;
+    if (live) {
+      const __half2 *kr = reinterpret_cast<const __half2 *>(kb + static_cast<long long>(p) * hd);
+#pragma unroll
+      for (int e = 0; e < EPL / 2; ++e) {
+        const float2 kk = __half22float2(kr[e]);
+        part = fmaf(qv[2 * e], kk.x, part);
+        part = fmaf(qv[2 * e + 1], kk.y, part);
+      }
+    }
+    part += __shfl_xor_sync(0xffffffffu, part, 1);
+    part += __shfl_xor_sync(0xffffffffu, part, 2);
+    part += __shfl_xor_sync(0xffffffffu, part, 4);
+    if (live) {
+      const float m_new = fmaxf(m, part);
+      const float corr = expf(m - m_new);
+      const float pw = expf(part - m_new);
+      l = l * corr + pw;
+      m = m_new;
+      const __half2 *vr = reinterpret_cast<const __half2 *>(vb + static_cast<long long>(p) * hd);
+#pragma unroll
+      for (int e = 0; e < EPL / 2; ++e) {
+        const float2 vv = __half22float2(vr[e]);
+        acc[2 * e] = fmaf(pw, vv.x, acc[2 * e] * corr);
+        acc[2 * e + 1] = fmaf(pw, vv.y, acc[2 * e + 1] * corr);
+      }
+    }
+  }
+
+  /* fold the four position groups together */
+#pragma unroll
+  for (int off = 8; off <= 16; off <<= 1) {
+    const float m_o = __shfl_xor_sync(0xffffffffu, m, off);
+    const float l_o = __shfl_xor_sync(0xffffffffu, l, off);
+    const float m_new = fmaxf(m, m_o);
+    const float c_me = m == -INFINITY ? 0.f : expf(m - m_new);
+    const float c_ot = m_o == -INFINITY ? 0.f : expf(m_o - m_new);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const float a_o = __shfl_xor_sync(0xffffffffu, acc[e], off);
+      acc[e] = acc[e] * c_me + a_o * c_ot;
+    }
+    l = l * c_me + l_o * c_ot;
+    m = m_new;
+  }
+  if (grp != 0) return;
+  if (a.partial_out) {
+    float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (hd + 2);
+    if (sub == 0) {
+      dst[0] = m;
+      dst[1] = l;
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) dst[2 + sub * EPL + e] = acc[e];
+  } else {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __half *dst = static_cast<__half *>(a.out) +
+                  (static_cast<long long>(tok) * a.n_q + head) * hd + sub * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) dst[e] = __float2half_rn(acc[e] * inv);
+  }
+}
+
+/* ------------------------------------------------------------ host side */
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+std::atomic<unsigned int> g_launch_counter{0};
+
+template <int HD, int MT, int RG, bool PAGED>
+wst_status_t launch_cfg(const RowsLaunch &L, const RowsArgs &args, const CUtensorMap &kmap,
+                        const CUtensorMap &vmap, dim3 grid) {
+  using C = Cfg<HD, MT, RG>;
+  auto kern = attn_rows_kernel<HD, MT, RG, PAGED>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  WST_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    WST_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  C::SMEM_BYTES));
+    configured_dev = dev;
+  }
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, current_stream()>>>(kmap, vmap, args);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(WST_ERR_CUDA, "%s (launch): %s (%s)", L.name, cudaGetErrorString(e),
+                cudaGetErrorName(e));
+  return WST_OK;
+}
+
+template <int HD, bool PAGED>
+wst_status_t launch_shape(const RowsLaunch &L, const RowsArgs &args, const CUtensorMap &kmap,
+                          const CUtensorMap &vmap, dim3 grid, int rows) {
+  if (rows == 16) return launch_cfg<HD, 1, 1, PAGED>(L, args, kmap, vmap, grid);
+  if (rows == 32) return launch_cfg<HD, 2, 1, PAGED>(L, args, kmap, vmap, grid);
+  return launch_cfg<HD, 2, 2, PAGED>(L, args, kmap, vmap, grid);
+}
+
+/* Rows a block carries for `n_tok` tokens of a GQA group of `gqa` heads. */
+int rows_for(int gqa, int n_tok) {
+  const long long want = static_cast<long long>(gqa) * n_tok;
+  if (want <= 16) return 16;
+  if (want <= 32) return 32;
+  return 64;
+}
+
+}  // namespace
+
+bool rows_kernel_supports(int n_q, int n_kv, int hd, const void *k, const void *v) {
+  if (hd != 64 && hd != 128) return false;
+  if (n_kv <= 0 || n_q % n_kv != 0 || n_q / n_kv > 64) return false;
+  return aligned16(k) && aligned16(v);
+}
+
+int rows_pick_splits(int n_units, int max_len, int sm_count) {
+  /* Few units (decode): one slice per SM.  Many units of uneven length (a
+   * ragged batch): slices of about 2048 positions, more blocks than SMs, and
+   * the block scheduler evens out the lengths. */
+  int splits = sm_count / (n_units > 0 ? n_units : 1);
+  const int by_len = (max_len + 2047) / 2048;
+  if (splits < by_len) splits = by_len;
+  const int tiles = (max_len + kRowsTile - 1) / kRowsTile;
+  if (splits > tiles) splits = tiles;
+  if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
+  if (splits < 1) splits = 1;
+  return splits;
+}
+
+long long rows_scratch_floats(int n_units_times_rows, int splits, int hd) {
+  return static_cast<long long>(n_units_times_rows) * splits * (hd + 2);
+}
+
+wst_status_t launch_rows(const RowsLaunch &L) {
+  DeviceFacts facts;
+  if (!device_facts(&facts)) return WST_ERR_CUDA;
+  if (facts.cc_major < 10)
+    return fail(WST_ERR_UNSUPPORTED_ARCH, "%s: this library is built for sm_100a only", L.name);
+
+  const int gqa = L.n_q / L.n_kv;
+  const int rows = rows_for(gqa, L.n_tok);
+  int tpb = rows / gqa; /* tokens per row block */
+  if (tpb > L.n_tok) tpb = L.n_tok;
+  const int n_rowblk = (L.n_tok + tpb - 1) / tpb;
+  const int n_units = L.n_seq * L.n_kv * n_rowblk;
+  const int rows_cap = tpb * gqa;
+
+  int splits = L.want_splits > 0 ? L.want_splits : rows_pick_splits(n_units, L.max_len, facts.sm_count);
+  if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
+  /* the slices must fit the caller's scratch and the ticket table */
+  while (splits > 1 &&
+         (!L.scratch || rows_scratch_floats(n_units * rows_cap, splits, L.hd) > L.scratch_floats))
+    --splits;
+  if (n_units > kTicketsPerSlot) splits = 1;
+
+  RowsArgs a{};
+  a.q = L.q;
+  a.q_tok_stride = L.q_tok_stride;
+  a.page_table = L.page_table;
+  a.max_pages = L.max_pages;
+  a.n_pool_pages = L.n_pool_pages;
+  a.pos0_dev = L.pos0_dev;
+  a.pos0_bias = L.pos0_bias;
+  a.clamp_nonneg = L.clamp_pos0_nonneg ? 1 : 0;
+  a.pos0_val = L.pos0_val;
+  a.cu_tokens = L.cu_tokens;
+  a.n_tok = L.n_tok;
+  a.n_q = L.n_q;
+  a.n_kv = L.n_kv;
+  a.gqa = gqa;
+  a.max_seq = L.max_seq;
+  a.qscale = L.scale * kLog2e;
+  a.scratch = L.scratch;
+  a.out = L.out;
+  a.partial_out = L.partial_out ? 1 : 0;
+  a.n_splits = splits;
+  a.n_rowblk = n_rowblk;
+  a.tpb = tpb;
+  a.rows_cap = rows_cap;
+  a.err_word = device_error_word();
+  if (!a.err_word) return WST_ERR_CUDA;
+  {
+    static thread_local unsigned int *ticket_base[64] = {};
+    int dev = 0;
+    WST_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(WST_ERR_CUDA, "%s: device ordinal out of range", L.name);
+    if (!ticket_base[dev]) {
+      void *p = nullptr;
+      WST_CUDA(cudaGetSymbolAddress(&p, g_tickets));
+      ticket_base[dev] = static_cast<unsigned int *>(p);
+    }
+    const unsigned int slot = g_launch_counter.fetch_add(1, std::memory_order_relaxed) % kTicketSlots;
+    a.tickets = ticket_base[dev] + static_cast<size_t>(slot) * kTicketsPerSlot;
+  }
+
+  CUtensorMap kmap, vmap;
+  KvMapKey key{};
+  key.d0 = static_cast<uint64_t>(L.hd);
+  if (L.paged) {
+    key.d1 = 16; key.d2 = static_cast<uint64_t>(L.n_kv); key.d3 = static_cast<uint64_t>(L.n_pool_pages);
+    key.b1 = 16; key.rank = 4;
+  } else {
+    key.d1 = static_cast<uint64_t>(L.max_seq);
+    key.d2 = static_cast<uint64_t>(L.n_kv) * L.n_seq; key.d3 = 1;
+    key.b1 = kRowsTile; key.rank = 3;
+  }
+  key.base = L.k;
+  wst_status_t st = cached_kv_tensor_map(&kmap, key);
+  if (st != WST_OK) return st;
+  key.base = L.v;
+  st = cached_kv_tensor_map(&vmap, key);
+  if (st != WST_OK) return st;
+
+  const dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(L.n_kv * n_rowblk),
+                  static_cast<unsigned>(L.n_seq));
+  if (L.hd == 128) {
+    return L.paged ? launch_shape<128, true>(L, a, kmap, vmap, grid, rows)
+                   : launch_shape<128, false>(L, a, kmap, vmap, grid, rows);
+  }
+  return L.paged ? launch_shape<64, true>(L, a, kmap, vmap, grid, rows)
+                 : launch_shape<64, false>(L, a, kmap, vmap, grid, rows);
+}
+
+wst_status_t launch_simple(const RowsLaunch &L) {
+  if (L.paged || L.n_seq != 1 || L.cu_tokens)
+    return fail(WST_ERR_SHAPE, "%s: the portable kernel takes one contiguous sequence", L.name);
+  if (L.hd % 32 != 0 || L.hd > 256 || L.hd <= 0)
+    return fail(WST_ERR_INVALID_ARG, "%s: head_dim must be a multiple of 32, at most 256", L.name);
+  SimpleArgs a{};
+  a.q = L.q;
+  a.q_tok_stride = L.q_tok_stride;
+  a.k = L.k;
+  a.v = L.v;
+  a.n_q = L.n_q;
+  a.gqa = L.n_q / L.n_kv;
+  a.hd = L.hd;
+  a.max_seq = L.max_seq;
+  a.n_tok = L.n_tok;
+  a.pos0_dev = L.pos0_dev;
+  a.pos0_bias = L.pos0_bias;
+  a.clamp_nonneg = L.clamp_pos0_nonneg ? 1 : 0;
+  a.pos0_val = L.pos0_val;
+  a.scale = L.scale;
+  a.out = L.out;
+  a.partial_out = L.partial_out ? 1 : 0;
+  const long long rows = static_cast<long long>(L.n_tok) * L.n_q;
+  const dim3 grid(static_cast<unsigned>((rows + 3) / 4)), block(128);
+  cudaStream_t st = current_stream();
+  switch (L.hd / 8) {
+    case 4: attn_simple_kernel<4><<<grid, block, 0, st>>>(a); break;
+    case 8: attn_simple_kernel<8><<<grid, block, 0, st>>>(a); break;
+    case 12: attn_simple_kernel<12><<<grid, block, 0, st>>>(a); break;
+    case 16: attn_simple_kernel<16><<<grid, block, 0, st>>>(a); break;
+    case 20: attn_simple_kernel<20><<<grid, block, 0, st>>>(a); break;
+    case 24: attn_simple_kernel<24><<<grid, block, 0, st>>>(a); break;
+    case 28: attn_simple_kernel<28><<<grid, block, 0, st>>>(a); break;
+    default: attn_simple_kernel<32><<<grid, block, 0, st>>>(a); break;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(WST_ERR_CUDA, "%s (launch): %s (%s)", L.name, cudaGetErrorString(e),
+                cudaGetErrorName(e));
+  return WST_OK;
+}
+
+}  // namespace wst

@@ -1,0 +1,64 @@
+/* Launch interface of the split-KV "row block" attention kernel (kernel sets 2
+ * and 4): a small block of query rows -- the heads of one GQA group for one or
+ * a few tokens -- against a long stretch of one KV head's cache.  Shared by the
+ * decode, small-chunk and paged-verify entry points. */
+#pragma once
+
+#include "wst_common.cuh"
+
+namespace wst {
+
+constexpr int kRowsTile = 64;       /* cache positions per pipeline stage */
+constexpr int kRowsMaxSplits = 64;  /* upper bound on sequence slices */
+
+struct RowsLaunch {
+  /* queries: q of (token t, head h) at q + t*q_tok_stride + h*hd, fp32 */
+  const float *q = nullptr;
+  long long q_tok_stride = 0;
+  /* cache: contiguous [n_seq][n_kv][max_seq][hd] (n_seq = 1 for the drop-in
+   * entry points) or the page pool [n_pool_pages][n_kv][16][hd] */
+  const __half *k = nullptr;
+  const __half *v = nullptr;
+  bool paged = false;
+  int max_seq = 0;        /* contiguous: rows per head; paged: max_pages*16 */
+  const int32_t *page_table = nullptr;
+  int max_pages = 0, n_pool_pages = 0;
+  /* positions: sequence s starts its tokens at pos0 = pos0_dev ? pos0_dev[s]
+   * (+ pos0_bias) : pos0_val; token j sees [0, clamp(pos0 + j + 1, 0, max_seq)) */
+  const int32_t *pos0_dev = nullptr;
+  int pos0_bias = 0;
+  bool clamp_pos0_nonneg = false;  /* decode cursor: max(*pos, 0) */
+  int pos0_val = 0;
+  /* tokens: cu_tokens ? ragged [n_seq+1] : n_tok for the single sequence */
+  const int32_t *cu_tokens = nullptr;
+  int n_seq = 1;
+  int n_tok = 1;          /* max tokens of any sequence */
+  int n_q = 0, n_kv = 0, hd = 0;
+  float scale = 1.f;
+  /* split scratch, floats: n_units * n_splits * rows_valid_max * (hd+2) */
+  float *scratch = nullptr;
+  long long scratch_floats = 0;
+  int want_splits = 0;    /* 0 = pick from the SM count */
+  int max_len = 0;        /* upper bound on any sequence's visible length */
+  /* output: fp16 [token][n_q*hd], or (partial mode) fp32 [n_q][hd+2] triples */
+  void *out = nullptr;
+  bool partial_out = false;
+  const char *name = "attention";
+};
+
+/* True if the tensor-core kernel can take this shape. */
+bool rows_kernel_supports(int n_q, int n_kv, int hd, const void *k, const void *v);
+
+/* Slices the kernel will use for a given shape on the current device. */
+int rows_pick_splits(int n_units, int max_len, int sm_count);
+
+/* Floats of scratch a launch with `splits` slices needs. */
+long long rows_scratch_floats(int n_units_times_rows, int splits, int hd);
+
+wst_status_t launch_rows(const RowsLaunch &L);
+
+/* Portable CUDA-core kernel for head widths the tensor-core kernel does not
+ * take (any head_dim % 32 == 0 up to 256, contiguous cache, no split). */
+wst_status_t launch_simple(const RowsLaunch &L);
+
+}  // namespace wst

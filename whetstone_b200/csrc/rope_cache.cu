@@ -1,0 +1,400 @@
+/* Kernel set 1: per-head RMSNorm (optional) + half-rotation RoPE + KV-cache
+ * append, for one token (wst_rope_cache), a chunk (wst_rope_cache_chunk) and a
+ * ragged batch over a paged cache (wst_rope_cache_paged).
+ *
+ * The work is pure HBM traffic (read the fused projection once, write q back,
+ * write two cache rows), so the layout is chosen for coalescing: one warp owns
+ * one (token, head) vector; lane l holds elements [l*E, l*E+E) of the first
+ * half and the same elements of the second half -- exactly the pairs the
+ * half-rotation couples -- so every load and store of a warp is one contiguous
+ * run, the norm's sum of squares is a warp shuffle reduction with no shared
+ * memory or block barrier, and a head never leaves registers.
+ *
+ * Semantics follow cuda/decode.cu:112-178 and cuda/chunk_ops.cu:101-150 of the
+ * engine: norm before rotation, per head, q and k with their own fp16 gains, v
+ * copied unrotated and un-normed; q written back in place as fp32; k and v
+ * narrowed to fp16 into cache row `pos`; positions clamped, never trusted.
+ */
+
+#include "wst_common.cuh"
+
+namespace wst {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+struct RopeArgs {
+  float *qkv;            /* [n_tokens][row_stride] */
+  __half *k_cache;       /* contiguous: [n_kv][max_seq][hd]; paged: the pool */
+  __half *v_cache;
+  const float *cos_tab;  /* [table_len][hd/2] */
+  const float *sin_tab;
+  const __half *q_gain;  /* [hd] or null */
+  const __half *k_gain;
+  const int32_t *pos_dev;     /* decode: device cursor, else null */
+  const int32_t *page_table;  /* paged only: [n_seq][max_pages] */
+  const int32_t *seq_pos0;    /* paged only: [n_seq] */
+  const int32_t *cu_tokens;   /* paged only: [n_seq + 1] */
+  int n_q, n_kv, hd;
+  int n_tokens;
+  int pos0;       /* chunk: position of token 0 */
+  int max_seq;    /* contiguous: rows per head */
+  int table_len;  /* rows in cos/sin */
+  int n_seq, max_pages, page_size, n_pool_pages;
+  float eps;
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int E>
+__device__ __forceinline__ void load_vec(const float *p, float (&x)[E]) {
+  if constexpr (E == 4) {
+    float4 t = *reinterpret_cast<const float4 *>(p);
+    x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+  } else if constexpr (E == 2) {
+    float2 t = *reinterpret_cast<const float2 *>(p);
+    x[0] = t.x; x[1] = t.y;
+  } else {
+    x[0] = *p;
+  }
+}
+
+template <int E>
+__device__ __forceinline__ void store_vec(float *p, const float (&x)[E]) {
+  if constexpr (E == 4) {
+    *reinterpret_cast<float4 *>(p) = make_float4(x[0], x[1], x[2], x[3]);
+  } else if constexpr (E == 2) {
+    *reinterpret_cast<float2 *>(p) = make_float2(x[0], x[1]);
+  } else {
+    *p = x[0];
+  }
+}
+
+template <int E>
+__device__ __forceinline__ void store_half_vec(__half *p, const float (&x)[E]) {
+  if constexpr (E == 4) {
+    __half2 a = __floats2half2_rn(x[0], x[1]);
+    __half2 b = __floats2half2_rn(x[2], x[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<uint32_t *>(&a);
+    t.y = *reinterpret_cast<uint32_t *>(&b);
+    *reinterpret_cast<uint2 *>(p) = t;
+  } else if constexpr (E == 2) {
+    *reinterpret_cast<__half2 *>(p) = __floats2half2_rn(x[0], x[1]);
+  } else {
+    *p = __float2half_rn(x[0]);
+  }
+}
+
+template <int E>
+__device__ __forceinline__ void load_gain(const __half *p, float (&g)[E]) {
+#pragma unroll
+  for (int e = 0; e < E; ++e) g[e] = __half2float(p[e]);
+}
+
+/* Where token `tok` lives: its cache position, and for the paged layout the
+ * element offset of its row 0 / head 0 in the pool (-1 = do not write). */
+struct TokenPlace {
+  int pos;             /* cache position (already clamped for contiguous) */
+  long long kv_base;   /* element offset of [kvh=0] row for this token, or -1 */
+  long long kv_head_stride;
+};
+
+template <bool PAGED>
+__device__ __forceinline__ TokenPlace place_token(const RopeArgs &a, int tok) {
+  TokenPlace t;
+  if constexpr (!PAGED) {
+    int p;
+    if (a.pos_dev) {
+      p = *a.pos_dev;
+      p = p < 0 ? 0 : p;
+    } else {
+      p = a.pos0 + tok;
+    }
+    p = p < a.max_seq - 1 ? p : a.max_seq - 1;
+    t.pos = p;
+    t.kv_base = static_cast<long long>(p) * a.hd;
+    t.kv_head_stride = static_cast<long long>(a.max_seq) * a.hd;
+  } else {
+    /* binary search: largest s with cu_tokens[s] <= tok */
+    int lo = 0, hi = a.n_seq - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (a.cu_tokens[mid] <= tok) lo = mid; else hi = mid - 1;
+    }
+    const int s = lo;
+    int p = a.seq_pos0[s] + (tok - a.cu_tokens[s]);
+    p = p < 0 ? 0 : p;
+    t.pos = p;
+    const int slot = p / a.page_size;
+    t.kv_base = -1;
+    t.kv_head_stride = static_cast<long long>(a.page_size) * a.hd;
+    if (slot < a.max_pages) {
+      const int page = a.page_table[static_cast<long long>(s) * a.max_pages + slot];
+      if (page >= 0 && page < a.n_pool_pages) {
+        t.kv_base = (static_cast<long long>(page) * a.n_kv * a.page_size + (p % a.page_size)) *
+                    a.hd;
+      }
+    }
+  }
+  return t;
+}
+
+/* Fast path: head_dim = 64 * E, everything in registers. */
+template <int E, bool PAGED>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rope_append_kernel(const RopeArgs a) {
+  constexpr int HD = 64 * E;
+  constexpr int HALF = HD / 2;
+  const int lane = threadIdx.x & 31;
+  const int heads = a.n_q + a.n_kv;
+  const long long unit =
+      static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (unit >= static_cast<long long>(a.n_tokens) * heads) return;
+  const int tok = static_cast<int>(unit / heads);
+  const int head = static_cast<int>(unit % heads);
+
+  const TokenPlace place = place_token<PAGED>(a, tok);
+  const int tpos = place.pos < a.table_len - 1 ? place.pos : a.table_len - 1;
+
+  float *row = a.qkv + static_cast<long long>(tok) * (a.n_q + 2 * a.n_kv) * HD;
+  const bool is_q = head < a.n_q;
+  const int kvh = head - a.n_q;
+  float *vec = is_q ? row + head * HD : row + (a.n_q + kvh) * HD;
+  const __half *gain = is_q ? a.q_gain : a.k_gain;
+
+  const int i0 = lane * E;
+  float x1[E], x2[E], c[E], s[E];
+  load_vec<E>(vec + i0, x1);
+  load_vec<E>(vec + HALF + i0, x2);
+  load_vec<E>(a.cos_tab + static_cast<long long>(tpos) * HALF + i0, c);
+  load_vec<E>(a.sin_tab + static_cast<long long>(tpos) * HALF + i0, s);
+
+  if (gain) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) ss = fmaf(x1[e], x1[e], fmaf(x2[e], x2[e], ss));
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / static_cast<float>(HD) + a.eps);
+    float g1[E], g2[E];
+    load_gain<E>(gain + i0, g1);
+    load_gain<E>(gain + HALF + i0, g2);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      x1[e] = x1[e] * inv * g1[e];
+      x2[e] = x2[e] * inv * g2[e];
+    }
+  }
+
+  float y1[E], y2[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    y1[e] = x1[e] * c[e] - x2[e] * s[e];
+    y2[e] = x2[e] * c[e] + x1[e] * s[e];
+  }
+
+  if (is_q) {
+    store_vec<E>(vec + i0, y1);
+    store_vec<E>(vec + HALF + i0, y2);
+    return;
+  }
+
+  if (place.kv_base < 0) return;
+  const long long slot = place.kv_base + static_cast<long long>(kvh) * place.kv_head_stride;
+  store_half_vec<E>(a.k_cache + slot + i0, y1);
+  store_half_vec<E>(a.k_cache + slot + HALF + i0, y2);
+
+  const float *vsrc = row + (a.n_q + a.n_kv + kvh) * HD;
+  float v1[E], v2[E];
+  load_vec<E>(vsrc + i0, v1);
+  load_vec<E>(vsrc + HALF + i0, v2);
+  store_half_vec<E>(a.v_cache + slot + i0, v1);
+  store_half_vec<E>(a.v_cache + slot + HALF + i0, v2);
+}
+
+/* Any even head_dim: two passes over the vector (the second hits L1). */
+template <bool PAGED>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rope_append_any_kernel(const RopeArgs a) {
+  const int hd = a.hd, half = hd >> 1;
+  const int lane = threadIdx.x & 31;
+  const int heads = a.n_q + a.n_kv;
+  const long long unit =
+      static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (unit >= static_cast<long long>(a.n_tokens) * heads) return;
+  const int tok = static_cast<int>(unit / heads);
+  const int head = static_cast<int>(unit % heads);
+
+  const TokenPlace place = place_token<PAGED>(a, tok);
+  const int tpos = place.pos < a.table_len - 1 ? place.pos : a.table_len - 1;
+  const float *ct = a.cos_tab + static_cast<long long>(tpos) * half;
+  const float *st = a.sin_tab + static_cast<long long>(tpos) * half;
+
+  float *row = a.qkv + static_cast<long long>(tok) * (a.n_q + 2 * a.n_kv) * hd;
+  const bool is_q = head < a.n_q;
+  const int kvh = head - a.n_q;
+  float *vec = is_q ? row + head * hd : row + (a.n_q + kvh) * hd;
+  const __half *gain = is_q ? a.q_gain : a.k_gain;
+
+  float inv = 1.f;
+  if (gain) {
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) ss = fmaf(vec[i], vec[i], ss);
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / static_cast<float>(hd) + a.eps);
+  }
+  const bool write_kv = !is_q && place.kv_base >= 0;
+  const long long slot =
+      write_kv ? place.kv_base + static_cast<long long>(kvh) * place.kv_head_stride : 0;
+  for (int i = lane; i < half; i += 32) {
+    float x1 = vec[i], x2 = vec[i + half];
+    if (gain) {
+      x1 = x1 * inv * __half2float(gain[i]);
+      x2 = x2 * inv * __half2float(gain[i + half]);
+    }
+    const float c = ct[i], s = st[i];
+    const float y1 = x1 * c - x2 * s;
+    const float y2 = x2 * c + x1 * s;
+    if (is_q) {
+      vec[i] = y1;
+      vec[i + half] = y2;
+    } else if (write_kv) {
+      a.k_cache[slot + i] = __float2half_rn(y1);
+      a.k_cache[slot + i + half] = __float2half_rn(y2);
+    }
+  }
+  if (write_kv) {
+    const float *vsrc = row + (a.n_q + a.n_kv + kvh) * hd;
+    for (int i = lane; i < hd; i += 32) a.v_cache[slot + i] = __float2half_rn(vsrc[i]);
+  }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <bool PAGED>
+wst_status_t launch_rope(const RopeArgs &a, const char *name) {
+  const long long units = static_cast<long long>(a.n_tokens) * (a.n_q + a.n_kv);
+  const long long blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (blocks > 0x7fffffffLL) return fail(WST_ERR_INVALID_ARG, "%s: too many tokens", name);
+  const dim3 grid(static_cast<unsigned>(blocks)), block(kWarpsPerBlock * 32);
+  cudaStream_t st = current_stream();
+  /* The vector path needs 16-byte aligned rows; fp32 rows of 64*E floats and
+   * cudaMalloc'd bases give that, an odd caller offset falls back. */
+  const bool vec_ok = aligned16(a.qkv) && aligned16(a.k_cache) && aligned16(a.v_cache) &&
+                      aligned16(a.cos_tab) && aligned16(a.sin_tab) &&
+                      (!a.q_gain || aligned16(a.q_gain)) && (!a.k_gain || aligned16(a.k_gain));
+  if (vec_ok && a.hd == 64) {
+    rope_append_kernel<1, PAGED><<<grid, block, 0, st>>>(a);
+  } else if (vec_ok && a.hd == 128) {
+    rope_append_kernel<2, PAGED><<<grid, block, 0, st>>>(a);
+  } else if (vec_ok && a.hd == 256) {
+    rope_append_kernel<4, PAGED><<<grid, block, 0, st>>>(a);
+  } else {
+    rope_append_any_kernel<PAGED><<<grid, block, 0, st>>>(a);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(WST_ERR_CUDA, "%s (launch): %s (%s)", name,
+                                    cudaGetErrorString(e), cudaGetErrorName(e));
+  return WST_OK;
+}
+
+}  // namespace
+}  // namespace wst
+
+using namespace wst;
+
+extern "C" wst_status_t wst_rope_cache(void *qkv, void *k_cache, void *v_cache,
+                                       const void *cos_tab, const void *sin_tab, int32_t n_q,
+                                       int32_t n_kv, int32_t head_dim, const void *pos,
+                                       int32_t max_seq, const void *q_norm_w,
+                                       const void *k_norm_w, float eps) {
+  WST_CHECK_ARG(qkv && k_cache && v_cache && cos_tab && sin_tab && pos,
+                "wst_rope_cache: null pointer");
+  WST_CHECK_ARG(n_q > 0 && n_kv > 0 && head_dim > 0, "wst_rope_cache: non-positive shape");
+  WST_CHECK_ARG(head_dim % 2 == 0, "wst_rope_cache: head_dim must be even");
+  WST_CHECK_ARG(max_seq > 0, "wst_rope_cache: empty cache");
+  WST_CHECK_ARG(head_dim / 2 <= 1024, "wst_rope_cache: head_dim/2 exceeds a block");
+  RopeArgs a{};
+  a.qkv = static_cast<float *>(qkv);
+  a.k_cache = static_cast<__half *>(k_cache);
+  a.v_cache = static_cast<__half *>(v_cache);
+  a.cos_tab = static_cast<const float *>(cos_tab);
+  a.sin_tab = static_cast<const float *>(sin_tab);
+  a.q_gain = static_cast<const __half *>(q_norm_w);
+  a.k_gain = static_cast<const __half *>(k_norm_w);
+  a.pos_dev = static_cast<const int32_t *>(pos);
+  a.n_q = n_q; a.n_kv = n_kv; a.hd = head_dim;
+  a.n_tokens = 1; a.pos0 = 0; a.max_seq = max_seq; a.table_len = max_seq;
+  a.eps = eps;
+  return launch_rope<false>(a, "wst_rope_cache");
+}
+
+extern "C" wst_status_t wst_rope_cache_chunk(void *qkv, void *k_cache, void *v_cache,
+                                             const void *cos_tab, const void *sin_tab,
+                                             int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                             int32_t pos0, int32_t n, int32_t max_seq,
+                                             const void *q_norm_w, const void *k_norm_w,
+                                             float eps) {
+  WST_CHECK_ARG(qkv && k_cache && v_cache && cos_tab && sin_tab,
+                "wst_rope_cache_chunk: null pointer");
+  WST_CHECK_ARG(n_q > 0 && n_kv > 0 && head_dim > 0 && n > 0,
+                "wst_rope_cache_chunk: non-positive shape");
+  WST_CHECK_ARG(head_dim % 2 == 0, "wst_rope_cache_chunk: head_dim must be even");
+  WST_CHECK_ARG(pos0 >= 0 && static_cast<long long>(pos0) + n <= max_seq,
+                "wst_rope_cache_chunk: chunk runs past the cache");
+  WST_CHECK_ARG(head_dim / 2 <= 1024, "wst_rope_cache_chunk: head_dim/2 exceeds a block");
+  RopeArgs a{};
+  a.qkv = static_cast<float *>(qkv);
+  a.k_cache = static_cast<__half *>(k_cache);
+  a.v_cache = static_cast<__half *>(v_cache);
+  a.cos_tab = static_cast<const float *>(cos_tab);
+  a.sin_tab = static_cast<const float *>(sin_tab);
+  a.q_gain = static_cast<const __half *>(q_norm_w);
+  a.k_gain = static_cast<const __half *>(k_norm_w);
+  a.pos_dev = nullptr;
+  a.n_q = n_q; a.n_kv = n_kv; a.hd = head_dim;
+  a.n_tokens = n; a.pos0 = pos0; a.max_seq = max_seq; a.table_len = max_seq;
+  a.eps = eps;
+  return launch_rope<false>(a, "wst_rope_cache_chunk");
+}
+
+extern "C" wst_status_t wst_rope_cache_paged(void *qkv, void *k_pool, void *v_pool,
+                                             const void *cos_tab, const void *sin_tab,
+                                             const void *page_table, const void *seq_pos0,
+                                             const void *cu_tokens, int32_t n_seq,
+                                             int32_t total_tokens, int32_t max_pages,
+                                             int32_t page_size, int32_t n_pool_pages,
+                                             int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                             int32_t table_len, const void *q_norm_w,
+                                             const void *k_norm_w, float eps) {
+  WST_CHECK_ARG(qkv && k_pool && v_pool && cos_tab && sin_tab && page_table && seq_pos0 &&
+                    cu_tokens,
+                "wst_rope_cache_paged: null pointer");
+  WST_CHECK_ARG(n_q > 0 && n_kv > 0 && head_dim > 0 && n_seq > 0 && total_tokens > 0,
+                "wst_rope_cache_paged: non-positive shape");
+  WST_CHECK_ARG(head_dim % 2 == 0, "wst_rope_cache_paged: head_dim must be even");
+  WST_CHECK_ARG(page_size == 16, "wst_rope_cache_paged: page_size must be 16");
+  WST_CHECK_ARG(max_pages > 0 && n_pool_pages > 0 && table_len > 0,
+                "wst_rope_cache_paged: empty page table, pool or RoPE table");
+  RopeArgs a{};
+  a.qkv = static_cast<float *>(qkv);
+  a.k_cache = static_cast<__half *>(k_pool);
+  a.v_cache = static_cast<__half *>(v_pool);
+  a.cos_tab = static_cast<const float *>(cos_tab);
+  a.sin_tab = static_cast<const float *>(sin_tab);
+  a.q_gain = static_cast<const __half *>(q_norm_w);
+  a.k_gain = static_cast<const __half *>(k_norm_w);
+  a.page_table = static_cast<const int32_t *>(page_table);
+  a.seq_pos0 = static_cast<const int32_t *>(seq_pos0);
+  a.cu_tokens = static_cast<const int32_t *>(cu_tokens);
+  a.n_q = n_q; a.n_kv = n_kv; a.hd = head_dim;
+  a.n_tokens = total_tokens; a.table_len = table_len;
+  a.n_seq = n_seq; a.max_pages = max_pages; a.page_size = page_size;
+  a.n_pool_pages = n_pool_pages;
+  a.eps = eps;
+  return launch_rope<true>(a, "wst_rope_cache_paged");
+}
