@@ -1,0 +1,503 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            (this library)
+    python bench.py --impl reference --gpus N --steps K ...  (numpy oracle on host cores)
+
+Prints ONE JSON line.  The headline workload is config c3 (Qwen2.5-7B-shaped
+long-context decode attention, context 32768, all 28 layers per step): the
+configuration the metric "decode attention us/layer and HBM GB/s at 32k context"
+is quoted on.  `value` is whole-job algorithmic bytes per second with inputs
+resident in HBM; `e2e` is the same step driven from pinned host buffers through
+the C ABI (H2D of each layer's qkv, RoPE/append, attention, D2H of the output).
+The other four configs are reported under "also" (prefill in TFLOP/s).
+
+With N > 1 (one process per GPU, torchrun) the KV sequence of c3 is sharded over
+the ranks: each rank runs the partial-softmax kernel on its shard, the
+(m, l, acc) triples are all-gathered with NCCL and merged.  Total work is fixed,
+so scaling is "strong".
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "decode_attn_hbm_gbs_ctx32k"
+UNIT = "GB/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel on
+# the c3 shape, from the ncu capture summarised in profiles/ (None until captured).
+NCU_DECODE_TRAFFIC_BYTES = None
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=float(d["hbm_gbs"]), tf_burst=float(d["bf16_tflops"]),
+                    tf_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    source="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(int(r[0]) for r in self.rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(self.rows[0][1]),
+                "reasons": reasons, "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------
+# reference arm / cpu baseline: the numpy oracle on the host cores
+# --------------------------------------------------------------------------
+
+def cpu_decode_sample(budget_s: float = 12.0, max_layers: int = 28):
+    """Times the oracle's decode attention on c3-shaped layers until the budget is
+    spent.  Returns (GB/s, layers timed, seconds)."""
+    from oracle import attention_oracle as orc
+    from whetstone_b200 import workloads as wl
+
+    s = wl.QWEN25_7B
+    ctx = wl.C3["context"]
+    nbytes = wl.decode_bytes(s.n_q, s.n_kv, s.head_dim, ctx)
+    q, k, v = wl.c3_layer(0)
+    done, spent = 0, 0.0
+    while done < max_layers and spent < budget_s:
+        t0 = time.perf_counter()
+        orc.decode_attention(q, k, v, ctx, s.scale)
+        spent += time.perf_counter() - t0
+        done += 1
+    return nbytes * done / spent / 1e9, done, spent
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = len(os.sched_getaffinity(0))
+    times = []
+    for i in range(args.warmup + args.steps):
+        gbs, layers, spent = cpu_decode_sample(budget_s=60.0, max_layers=1)
+        if i >= args.warmup:
+            times.append((gbs, layers, spent))
+    gbs = float(np.mean([t[0] for t in times]))
+    layers = times[0][1]
+    ms = float(np.mean([t[2] for t in times])) * 1e3
+    sample = (f"{layers} of 28 layers per step, float64 numpy (BLAS threads as configured), "
+              f"context 32768, fp16 cache widened to f64 inside the timed region")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": C3_NAME, "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+C3_NAME = ("c3: Qwen2.5-7B-shaped decode attention, batch 1, context 32768, 28 layers/step, "
+           "28 q / 4 kv heads, head_dim 128, fp16 KV cache")
+
+
+# --------------------------------------------------------------------------
+# this library
+# --------------------------------------------------------------------------
+
+def timed_graph(torch, fn, steps, warmup, dist=None):
+    """Captures fn() into a CUDA graph (after eager warm-up), replays it `steps`
+    times between CUDA events on the launching stream.  Returns seconds/step."""
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(graph):
+            fn()
+        run = graph.replay
+    except Exception as exc:  # capture is an optimisation, not a requirement
+        sys.stderr.write(f"[bench] graph capture failed ({exc}); timing eager launches\n")
+        torch.cuda.synchronize()
+        run = fn
+    for _ in range(max(warmup, 3)):
+        run()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        run()
+    t1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sec = t0.elapsed_time(t1) / 1e3 / steps
+    if dist is not None:
+        t = torch.tensor([sec], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    return sec
+
+
+def bench_c3(torch, args, rank, world, dist):
+    from whetstone_b200 import decode, workloads as wl
+
+    s = wl.QWEN25_7B
+    ctx = wl.C3["context"]
+    layers = s.layers
+    per = ctx // world                      # rows of the KV sequence on this rank
+    gen = torch.Generator(device="cuda").manual_seed(wl.C3["seed"] + rank)
+    table = decode.RopeTable(ctx, s.head_dim, s.theta)
+    caches, qkvs, outs = [], [], []
+    for _ in range(layers):
+        c = decode.KvCache(s.n_kv, s.n_q, s.head_dim, per)
+        c.k.copy_(torch.randn(c.k.shape, generator=gen, device="cuda", dtype=torch.float16))
+        c.v.copy_(torch.randn(c.v.shape, generator=gen, device="cuda", dtype=torch.float16))
+        caches.append(c)
+        qkvs.append(torch.randn(s.qkv_width, generator=gen, device="cuda",
+                                dtype=torch.float16).float())
+        outs.append(torch.zeros(s.n_q * s.head_dim, dtype=torch.float16, device="cuda"))
+    cursor = decode.DeviceCursor(per - 1)   # the new token is the shard's last row
+    length = torch.tensor([per], dtype=torch.int32, device="cuda")
+    launches_per_step = layers
+
+    if world == 1:
+        def step():
+            for i in range(layers):
+                decode.attn_decode(qkvs[i], caches[i], outs[i], s.n_q, cursor)
+    else:
+        mine = [torch.zeros((s.n_q, s.head_dim + 2), dtype=torch.float32, device="cuda")
+                for _ in range(layers)]
+        gathered = [torch.zeros((world, s.n_q, s.head_dim + 2), dtype=torch.float32,
+                                device="cuda") for _ in range(layers)]
+        launches_per_step = 2 * layers
+
+        def step():
+            for i in range(layers):
+                decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
+                dist.all_gather_into_tensor(gathered[i], mine[i])
+                decode.attn_merge_partials(gathered[i], outs[i], s.n_q, s.head_dim)
+
+    with ClockSampler(torch.cuda.current_device()) as clk:
+        sec = timed_graph(torch, step, args.steps, args.warmup, dist if world > 1 else None)
+    clocks = clk.summary()
+
+    bytes_layer = wl.decode_bytes(s.n_q, s.n_kv, s.head_dim, ctx)   # whole job, all ranks
+    value = bytes_layer * layers / sec / 1e9
+
+    # end to end: each layer's qkv comes from pinned host memory, the new token is
+    # appended (RoPE), attended, and the result goes back to the host
+    host_in = [q.cpu().pin_memory() for q in qkvs]
+    host_out = [torch.zeros(s.n_q * s.head_dim, dtype=torch.float16).pin_memory()
+                for _ in range(layers)]
+    if world == 1:
+        def step_e2e():
+            for i in range(layers):
+                qkvs[i].copy_(host_in[i], non_blocking=True)
+                decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cursor)
+                decode.attn_decode(qkvs[i], caches[i], outs[i], s.n_q, cursor)
+                host_out[i].copy_(outs[i], non_blocking=True)
+    else:
+        def step_e2e():
+            for i in range(layers):
+                qkvs[i].copy_(host_in[i], non_blocking=True)
+                if rank == world - 1:   # the shard that owns the newest position appends
+                    decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cursor)
+                decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
+                dist.all_gather_into_tensor(gathered[i], mine[i])
+                decode.attn_merge_partials(gathered[i], outs[i], s.n_q, s.head_dim)
+                host_out[i].copy_(outs[i], non_blocking=True)
+    sec_e2e = timed_graph(torch, step_e2e, args.steps, args.warmup, dist if world > 1 else None)
+    e2e = {"value": bytes_layer * layers / sec_e2e / 1e9, "unit": UNIT,
+           "h2d_bytes_per_step": layers * s.qkv_width * 4,
+           "d2h_bytes_per_step": layers * s.n_q * s.head_dim * 2,
+           "ms_per_step": sec_e2e * 1e3}
+
+    pk = peaks()
+    kernel_us = sec / layers * 1e6
+    achieved = bytes_layer / world / (sec / layers) / 1e9      # per GPU, per launch
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": achieved / pk["hbm"], "traffic": NCU_DECODE_TRAFFIC_BYTES,
+                "peak_source": pk["source"], "kernel": "attn_rows_kernel<128,1,1>",
+                "algorithmic_bytes_per_launch": bytes_layer // world,
+                "us_per_launch": kernel_us}
+    return dict(value=value, sec=sec, clocks=clocks, e2e=e2e, roofline=roofline,
+                launches=launches_per_step * args.steps,
+                extra={"us_per_layer": kernel_us, "tokens_per_s": 1.0 / sec})
+
+
+def bench_also(torch, args):
+    """Configs c1, c2, c4, c5 on one GPU, short runs; see whetstone_b200/workloads.py."""
+    from whetstone_b200 import chunk, decode, paged, workloads as wl
+    pk = peaks()
+    out = {}
+    gen = torch.Generator(device="cuda").manual_seed(7)
+
+    def randn16(shape):
+        return torch.randn(shape, generator=gen, device="cuda", dtype=torch.float16)
+
+    # ---- c1: 0.5B decode, append + attend, 24 layers
+    s = wl.QWEN25_05B
+    table = decode.RopeTable(wl.C1["max_seq"], s.head_dim, s.theta)
+    cur = decode.DeviceCursor(wl.C1["cached"])
+    caches, qkvs, outs = [], [], []
+    for _ in range(s.layers):
+        c = decode.KvCache(s.n_kv, s.n_q, s.head_dim, wl.C1["max_seq"])
+        c.k[:, : wl.C1["cached"]] = randn16((s.n_kv, wl.C1["cached"], s.head_dim))
+        c.v[:, : wl.C1["cached"]] = randn16((s.n_kv, wl.C1["cached"], s.head_dim))
+        caches.append(c)
+        qkvs.append(randn16((s.qkv_width,)).float())
+        outs.append(torch.zeros(s.n_q * s.head_dim, dtype=torch.float16, device="cuda"))
+
+    def c1_step():
+        for i in range(s.layers):
+            decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cur)
+            decode.attn_decode(qkvs[i], caches[i], outs[i], s.n_q, cur)
+    sec = timed_graph(torch, c1_step, args.steps, args.warmup)
+    out["c1_decode_0.5b"] = {"us_per_layer": sec / s.layers * 1e6,
+                             "note": "append + attention, 513 rows, latency-bound"}
+
+    # ---- c2: 0.5B chunked prefill, 2048 tokens = 8 chunks of 256, 24 layers
+    n, prompt = wl.C2["chunk"], wl.C2["prompt"]
+    table2 = decode.RopeTable(prompt, s.head_dim, s.theta)
+    caches = [decode.KvCache(s.n_kv, s.n_q, s.head_dim, prompt) for _ in range(s.layers)]
+    qkv_src = [randn16((prompt, s.qkv_width)).float() for _ in range(s.layers)]
+    qkv_buf = [torch.empty_like(q) for q in qkv_src]
+    outs = [torch.zeros(prompt * s.n_q * s.head_dim, dtype=torch.float16, device="cuda")
+            for _ in range(s.layers)]
+    flops_layer = sum(wl.prefill_flops(s.n_q, s.head_dim, c * n, n) for c in range(prompt // n))
+
+    def c2_rope():
+        for i in range(s.layers):
+            qkv_buf[i].copy_(qkv_src[i])
+            for c in range(prompt // n):
+                chunk.rope_cache(qkv_buf[i][c * n:(c + 1) * n], caches[i], table2, s.n_q, c * n, n)
+
+    def c2_attn():
+        for i in range(s.layers):
+            for c in range(prompt // n):
+                chunk.attn(qkv_buf[i][c * n:(c + 1) * n], caches[i],
+                           outs[i][c * n * s.n_q * s.head_dim:], s.n_q, c * n, n)
+    c2_rope()
+    sec = timed_graph(torch, c2_attn, args.steps, args.warmup)
+    tf = flops_layer * s.layers / sec / 1e12
+    out["c2_prefill_0.5b"] = {"tflops": tf, "ms_per_layer": sec / s.layers * 1e3,
+                              "frac_of_tensor_peak": tf / pk["tf_burst"],
+                              "flops_per_layer": flops_layer}
+    del caches, qkv_src, qkv_buf, outs
+
+    # ---- c4: Qwen3-8B prefill, 4 x 8192 tokens in 512-token chunks, QK-norm; a
+    # stated subset of layers is timed (every layer does identical work)
+    s4 = wl.QWEN3_8B
+    n4, prompt4, nseq = wl.C4["chunk"], wl.C4["prompt"], wl.C4["n_seq"]
+    lay4 = args.c4_layers
+    table4 = decode.RopeTable(prompt4, s4.head_dim, s4.theta)
+    gq, gk = (1 + 0.02 * randn16((s4.head_dim,)).float()).half(), \
+             (1 + 0.02 * randn16((s4.head_dim,)).float()).half()
+    norm = decode.QkNorm(gq, gk, wl.C4["eps"])
+    caches = [[decode.KvCache(s4.n_kv, s4.n_q, s4.head_dim, prompt4) for _ in range(nseq)]
+              for _ in range(lay4)]
+    pool = [randn16((n4, s4.qkv_width)).float() for _ in range(24)]   # 302 MB > L2
+    out4 = torch.zeros(n4 * s4.n_q * s4.head_dim, dtype=torch.float16, device="cuda")
+    chunks = prompt4 // n4
+    flops4 = nseq * sum(wl.prefill_flops(s4.n_q, s4.head_dim, c * n4, n4) for c in range(chunks))
+    # populate the caches once (keys must be finite for a meaningful run)
+    for l in range(lay4):
+        for q in range(nseq):
+            for c in range(chunks):
+                buf = pool[(q * chunks + c) % len(pool)].clone()
+                chunk.rope_cache(buf, caches[l][q], table4, s4.n_q, c * n4, n4, norm)
+    rope_bytes = n4 * s4.qkv_width * 4 + n4 * s4.n_q * s4.head_dim * 4 + \
+        2 * n4 * s4.n_kv * s4.head_dim * 2
+
+    def c4_attn():
+        for l in range(lay4):
+            for q in range(nseq):
+                for c in range(chunks):
+                    chunk.attn(pool[(q * chunks + c) % len(pool)], caches[l][q], out4, s4.n_q,
+                               c * n4, n4)
+
+    def c4_rope():
+        for l in range(lay4):
+            for q in range(nseq):
+                for c in range(chunks):
+                    chunk.rope_cache(pool[(q * chunks + c) % len(pool)], caches[l][q], table4,
+                                     s4.n_q, c * n4, n4, norm)
+    sec = timed_graph(torch, c4_attn, max(1, args.steps // 4), 3)
+    tf = flops4 * lay4 / sec / 1e12
+    sec_r = timed_graph(torch, c4_rope, max(1, args.steps // 4), 3)
+    rope_gbs = rope_bytes * lay4 * nseq * chunks / sec_r / 1e9
+    out["c4_prefill_qwen3_8b"] = {
+        "tflops": tf, "ms_per_layer": sec / lay4 * 1e3, "frac_of_tensor_peak": tf / pk["tf_burst"],
+        "flops_per_layer": flops4, "layers_timed": lay4, "layers_in_model": s4.layers,
+        "rope_append_gbs": rope_gbs, "rope_append_frac_of_hbm": rope_gbs / pk["hbm"]}
+    del caches, pool
+
+    # ---- c5: speculative verify, 16 sequences x 5 drafts, paged cache, 28 layers
+    s5 = wl.QWEN25_7B
+    lengths = wl.c5_lengths()
+    drafts = wl.C5["drafts"]
+    table_np, n_pages = wl.c5_page_table(lengths, drafts)
+    nseq5 = len(lengths)
+    total = nseq5 * drafts
+    max_len = int(lengths.max()) + drafts
+    lay5 = args.c5_layers
+    pcs = []
+    for _ in range(lay5):
+        pc = paged.PagedKvCache(n_pages, s5.n_kv, s5.head_dim, nseq5, table_np.shape[1])
+        pc.k.copy_(randn16(pc.k.shape))
+        pc.v.copy_(randn16(pc.v.shape))
+        pc.page_table.copy_(torch.from_numpy(table_np).cuda())
+        pcs.append(pc)
+    qkv5 = [randn16((total, s5.qkv_width)).float() for _ in range(lay5)]
+    out5 = torch.zeros(total * s5.n_q * s5.head_dim, dtype=torch.float16, device="cuda")
+    pos0 = torch.from_numpy(lengths).cuda()
+    cu = torch.arange(nseq5 + 1, dtype=torch.int32, device="cuda") * drafts
+    scratch = torch.zeros(paged.verify_scratch_floats(nseq5, drafts, s5.n_q, s5.n_kv,
+                                                      s5.head_dim, max_len),
+                          dtype=torch.float32, device="cuda")
+    rtab = decode.RopeTable(max_len, s5.head_dim, s5.theta)
+
+    def c5_step():
+        for l in range(lay5):
+            paged.rope_cache(qkv5[l], pcs[l], rtab, s5.n_q, pos0, cu, total)
+            paged.attn_verify(qkv5[l], pcs[l], out5, scratch, s5.n_q, pos0, cu, total, drafts,
+                              max_len)
+    sec = timed_graph(torch, c5_step, args.steps, args.warmup)
+    kv_bytes = int(2 * s5.n_kv * s5.head_dim * 2 * int((lengths.astype(np.int64) + drafts).sum()))
+    bytes5 = kv_bytes + total * s5.n_q * s5.head_dim * (4 + 2) + table_np.size * 4
+    gbs = bytes5 * lay5 / sec / 1e9
+    out["c5_verify_7b_paged"] = {"us_per_layer": sec / lay5 * 1e6, "hbm_gbs": gbs,
+                                 "frac_of_hbm_peak": gbs / pk["hbm"], "bytes_per_layer": bytes5,
+                                 "layers_timed": lay5, "layers_in_model": s5.layers,
+                                 "tokens_verified_per_s": total / (sec / lay5 * s5.layers)}
+    return out
+
+
+def run_ours(args):
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+
+    res = bench_c3(torch, args, rank, world, dist)
+    also = None
+    cpu = None
+    if world == 1 and not args.no_also:
+        also = bench_also(torch, args)
+    if world == 1 and rank == 0 and not args.no_cpu:
+        gbs, layers, spent = cpu_decode_sample()
+        cpu = {"value": gbs, "unit": UNIT, "cores": len(os.sched_getaffinity(0)), "kind": "port",
+               "sample": f"{layers} of 28 layers of c3 ({spent:.1f} s), float64 numpy oracle"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": res["sec"] * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {"workload": C3_NAME,
+                       "parallelism": "single GPU" if world == 1 else
+                       f"KV sequence sharded over {world} GPUs, NCCL all-gather of (m,l,acc) + merge",
+                       "l2": "inputs larger than L2: 1.88 GB of KV cache is streamed per step",
+                       "launch": "one CUDA graph per step"},
+            "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["launches"],
+            "roofline": res["roofline"],
+        }
+        line.update(res["extra"])
+        if cpu:
+            line["cpu_baseline"] = cpu
+        if also:
+            line["also"] = also
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-also", action="store_true", help="skip configs c1, c2, c4, c5")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--c4-layers", type=int, default=1)
+    ap.add_argument("--c5-layers", type=int, default=4)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
