@@ -67,7 +67,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                 "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -336,7 +336,7 @@ def bench_also(torch, args):
                 chunk.attn(qkv_buf[i][c * n:(c + 1) * n], caches[i],
                            outs[i][c * n * s.n_q * s.head_dim:], s.n_q, c * n, n)
     c2_rope()
-    sec = timed_graph(torch, c2_attn, args.steps, args.warmup)
+    sec = timed_graph(torch, c2_attn, min(args.steps, 50), args.warmup)
     tf = flops_layer * s.layers / sec / 1e12
     out["c2_prefill_0.5b"] = {"tflops": tf, "ms_per_layer": sec / s.layers * 1e3,
                               "frac_of_tensor_peak": tf / pk["tf_burst"],
@@ -380,9 +380,9 @@ def bench_also(torch, args):
                 for c in range(chunks):
                     chunk.rope_cache(pool[(q * chunks + c) % len(pool)], caches[l][q], table4,
                                      s4.n_q, c * n4, n4, norm)
-    sec = timed_graph(torch, c4_attn, max(1, args.steps // 4), 3)
+    sec = timed_graph(torch, c4_attn, max(1, min(args.steps, 20) // 4), 3)
     tf = flops4 * lay4 / sec / 1e12
-    sec_r = timed_graph(torch, c4_rope, max(1, args.steps // 4), 3)
+    sec_r = timed_graph(torch, c4_rope, max(1, min(args.steps, 20) // 4), 3)
     rope_gbs = rope_bytes * lay4 * nseq * chunks / sec_r / 1e9
     out["c4_prefill_qwen3_8b"] = {
         "tflops": tf, "ms_per_layer": sec / lay4 * 1e3, "frac_of_tensor_peak": tf / pk["tf_burst"],
@@ -420,7 +420,7 @@ def bench_also(torch, args):
             paged.rope_cache(qkv5[l], pcs[l], rtab, s5.n_q, pos0, cu, total)
             paged.attn_verify(qkv5[l], pcs[l], out5, scratch, s5.n_q, pos0, cu, total, drafts,
                               max_len)
-    sec = timed_graph(torch, c5_step, args.steps, args.warmup)
+    sec = timed_graph(torch, c5_step, min(args.steps, 50), args.warmup)
     kv_bytes = int(2 * s5.n_kv * s5.head_dim * 2 * int((lengths.astype(np.int64) + drafts).sum()))
     bytes5 = kv_bytes + total * s5.n_q * s5.head_dim * (4 + 2) + table_np.size * 4
     gbs = bytes5 * lay5 / sec / 1e9
@@ -485,7 +485,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip configs c1, c2, c4, c5")

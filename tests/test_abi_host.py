@@ -115,10 +115,10 @@ def test_typed_errors():
 
 
 def test_partial_floats_is_an_upper_bound_for_any_kv_head_count():
-    # n_q * max slices * (head_dim + 2); the slice count is capped by the tiles of max_seq
-    assert lib.wst_attn_partial_floats(28, 128, 32768) == 28 * 64 * 130
-    assert lib.wst_attn_partial_floats(14, 64, 1024) == 14 * 16 * 66
-    assert lib.wst_attn_partial_floats(14, 64, 8) == 14 * 1 * 66
+    # n_q * max slices * (head_dim + 4): numerators, max, denominator, 2 floats of padding
+    assert lib.wst_attn_partial_floats(28, 128, 32768) == 28 * 64 * 132
+    assert lib.wst_attn_partial_floats(14, 64, 1024) == 14 * 16 * 68
+    assert lib.wst_attn_partial_floats(14, 64, 8) == 14 * 1 * 68
     assert lib.wst_attn_partial_floats(0, 64, 8) == 0
 
 

@@ -89,7 +89,7 @@ wst_status_t decode_common(const char *who, const void *q, const void *k_cache,
   L.hd = head_dim;
   L.scale = scale;
   L.scratch = static_cast<float *>(partials);
-  L.scratch_floats = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 2);
+  L.scratch_floats = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 4);
   L.max_len = max_seq;
   L.out = out;
   L.partial_out = partial_out;
@@ -132,7 +132,7 @@ extern "C" wst_status_t wst_b200_set_kernel_choice(int32_t choice) {
 
 extern "C" int32_t wst_attn_partial_floats(int32_t n_q, int32_t head_dim, int32_t max_seq) {
   if (n_q <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
-  const long long f = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 2);
+  const long long f = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 4);
   return f > 0x7fffffffLL ? 0x7fffffff : static_cast<int32_t>(f);
 }
 
@@ -238,7 +238,7 @@ extern "C" int64_t wst_attn_verify_scratch_floats(int32_t n_seq, int32_t max_tok
   const long long rows_total =
       static_cast<long long>(n_seq) * n_kv *
       (static_cast<long long>(max_tokens_per_seq) * gqa + 63);
-  return rows_total * max_splits_for(max_len) * (head_dim + 2);
+  return rows_total * max_splits_for(max_len) * (head_dim + 4);
 }
 
 extern "C" wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_pool,

@@ -79,8 +79,15 @@ struct Cfg {
   static constexpr int NREG = NO + MT * 4;       /* + running max and sum */
   static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + Q_BYTES + 2 * NSTAGE * 8 + 64 + 1024;
   static_assert(RG * 2 * NREG * 32 * 4 <= NSTAGE * STAGE_BYTES, "merge buffer must fit");
-  static_assert(ROWS * kRowsMaxSplits * 4 + ROWS * 8 <= NSTAGE * STAGE_BYTES, "weights must fit");
+  static_assert(2 * ROWS * kRowsMaxSplits * 4 + ROWS * 8 <= NSTAGE * STAGE_BYTES, "weights must fit");
 };
+
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 __device__ __forceinline__ void consumer_bar(int threads) {
   asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
@@ -99,6 +106,33 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int kvh = blockIdx.y / a.n_rowblk;
   const int rb = blockIdx.y % a.n_rowblk;
   const int s = blockIdx.z;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t *qsm = smem + NSTAGE * STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(qsm + C::Q_BYTES);
+  int *flags = reinterpret_cast<int *>(bars + 2 * NSTAGE);
+  const uint32_t stages_u32 = smem_u32(smem);
+  const uint32_t q_u32 = smem_u32(qsm);
+  const uint32_t full_u32 = smem_u32(bars);
+  const uint32_t empty_u32 = smem_u32(bars + NSTAGE);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSTAGE; ++i) {
+      mbar_init(full_u32 + 8 * i, 1);
+      mbar_init(empty_u32 + 8 * i, C::CWARPS);
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&kmap);
+    tma_prefetch_desc(&vmap);
+  }
+  __syncthreads();
+
+  /* Everything above touches no global memory, so under programmatic dependent
+   * launch it overlaps the tail of the previous kernel in the stream.  From here
+   * on we read what that kernel may have written (cursor, q, cache rows). */
+  grid_dependency_wait();
 
   int tok_begin = 0, n_tok = a.n_tok;
   if (a.cu_tokens) {
@@ -125,31 +159,9 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int tile_hi = static_cast<int>(static_cast<long long>(split + 1) * n_tiles / a.n_splits);
   const int my_tiles = tile_hi - tile_lo;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = reinterpret_cast<uint8_t *>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t *qsm = smem + NSTAGE * STAGE_BYTES;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(qsm + C::Q_BYTES);
-  int *flags = reinterpret_cast<int *>(bars + 2 * NSTAGE);
-  const uint32_t stages_u32 = smem_u32(smem);
-  const uint32_t q_u32 = smem_u32(qsm);
-  const uint32_t full_u32 = smem_u32(bars);
-  const uint32_t empty_u32 = smem_u32(bars + NSTAGE);
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < NSTAGE; ++i) {
-      mbar_init(full_u32 + 8 * i, 1);
-      mbar_init(empty_u32 + 8 * i, C::CWARPS);
-    }
-    mbar_init_fence();
-  }
-  __syncthreads();
-
   /* ------------------------------------------------------------ producer */
   if (warp == C::CWARPS) {
     if (lane != 0) return;
-    tma_prefetch_desc(&kmap);
-    tma_prefetch_desc(&vmap);
     for (int i = 0; i < my_tiles; ++i) {
       const int stage = i % NSTAGE, round = i / NSTAGE;
       if (i >= NSTAGE &&
@@ -369,6 +381,10 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     if (lane == 0) mbar_arrive(empty_u32 + 8 * stage);
   }
 
+  /* The cache has been streamed: let the next kernel in the stream start its
+   * prologue while this one combines its slices. */
+  grid_launch_dependents();
+
   /* row sums live spread over the four lanes of a quad */
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -452,93 +468,124 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
             *reinterpret_cast<__half2 *>(dst + nt * 8) = __floats2half2_rn(
                 o[mt][nt][2 * hh] * inv, o[mt][nt][2 * hh + 1] * inv);
         } else {
-          float *dst;
+          /* (m, l, acc[HD]) for the caller (natural-log m), or a scratch row
+           * laid out acc[HD] | m | l | pad pad so that acc is 16-byte aligned */
+          float *acc_dst, *ml_dst;
           float m_out = m_run[mt][hh];
-          if (single) { /* partial_out: the caller's triple, natural-log units */
-            dst = static_cast<float *>(a.out) +
-                  static_cast<long long>(kvh * a.gqa + r % a.gqa) * (HD + 2);
+          if (single) {
+            ml_dst = static_cast<float *>(a.out) +
+                     static_cast<long long>(kvh * a.gqa + r % a.gqa) * (HD + 2);
+            acc_dst = ml_dst + 2;
             m_out *= kLn2;
           } else {
-            dst = a.scratch +
-                  ((static_cast<long long>(unit) * a.n_splits + split) * a.rows_cap + r) * (HD + 2);
+            acc_dst = a.scratch +
+                      ((static_cast<long long>(unit) * a.n_splits + split) * a.rows_cap + r) *
+                          (HD + 4);
+            ml_dst = acc_dst + HD;
           }
           if ((lane & 3) == 0) {
-            dst[0] = m_out;
-            dst[1] = l_run[mt][hh];
+            ml_dst[0] = m_out;
+            ml_dst[1] = l_run[mt][hh];
           }
 #pragma unroll
           for (int nt = 0; nt < HD / 8; ++nt)
-            *reinterpret_cast<float2 *>(dst + 2 + nt * 8 + col) =
+            *reinterpret_cast<float2 *>(acc_dst + nt * 8 + col) =
                 make_float2(o[mt][nt][2 * hh], o[mt][nt][2 * hh + 1]);
         }
       }
-    if (!single) __threadfence();
   }
   if (single) return;
 
-  /* ---- ticket: the last slice of this unit to arrive merges all of them */
+  /* ---- ticket: the last slice of this unit to arrive merges all of them.
+   * Writers store, the block barrier orders them before thread 0, whose fence +
+   * atomic publishes the whole block's rows (and, for the last arrival, makes
+   * every other block's rows visible before anyone here reads them). */
   consumer_bar(C::CTHREADS);
   if (ctid == 0) {
+    __threadfence();
     const unsigned int prev = atomicAdd(&a.tickets[unit], 1u);
     const int last = prev == static_cast<unsigned int>(a.n_splits - 1);
-    if (last) a.tickets[unit] = 0u; /* everyone has arrived: leave it ready for the next launch */
+    if (last) {
+      a.tickets[unit] = 0u; /* everyone has arrived: leave it ready for the next launch */
+      __threadfence();
+    }
     flags[0] = last;
   }
   consumer_bar(C::CTHREADS);
   if (!flags[0]) return;
-  __threadfence();
 
   const int ns = a.n_splits;
-  float *wsm = reinterpret_cast<float *>(smem); /* [rows_valid][ns] weights */
-  float *row_m = wsm + ROWS * kRowsMaxSplits;   /* [ROWS] */
+  constexpr int RS = HD + 4;                          /* floats per scratch row */
+  float *w_m = reinterpret_cast<float *>(smem);       /* [rows_valid][ns] max, then weight */
+  float *w_l = w_m + ROWS * kRowsMaxSplits;           /* [rows_valid][ns] denominators */
+  float *row_m = w_l + ROWS * kRowsMaxSplits;         /* [ROWS] */
   float *row_l = row_m + ROWS;
-  const float *base = a.scratch + static_cast<long long>(unit) * ns * a.rows_cap * (HD + 2);
-  auto triple = [&](int sp, int row) {
-    return base + (static_cast<long long>(sp) * a.rows_cap + row) * (HD + 2);
+  const float *base = a.scratch + static_cast<long long>(unit) * ns * a.rows_cap * RS;
+  auto scratch_row = [&](int sp, int row) {
+    return base + (static_cast<long long>(sp) * a.rows_cap + row) * RS;
   };
   for (int idx = ctid; idx < rows_valid * ns; idx += C::CTHREADS) {
     const int row = idx / ns, sp = idx % ns;
-    wsm[row * ns + sp] = __ldcg(triple(sp, row));
+    const float2 ml = __ldcg(reinterpret_cast<const float2 *>(scratch_row(sp, row) + HD));
+    w_m[row * ns + sp] = ml.x;
+    w_l[row * ns + sp] = ml.y;
   }
   consumer_bar(C::CTHREADS);
-  for (int row = ctid; row < rows_valid; row += C::CTHREADS) {
+  for (int row = warp; row < rows_valid; row += C::CWARPS) { /* one warp per row */
     float M = -INFINITY;
-    for (int sp = 0; sp < ns; ++sp) M = fmaxf(M, wsm[row * ns + sp]);
+    for (int sp = lane; sp < ns; sp += 32) M = fmaxf(M, w_m[row * ns + sp]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
     float den = 0.f;
-    for (int sp = 0; sp < ns; ++sp) {
-      const float m = wsm[row * ns + sp];
+    for (int sp = lane; sp < ns; sp += 32) {
+      const float m = w_m[row * ns + sp];
       const float wgt = (m == -INFINITY) ? 0.f : ex2(m - M);
-      wsm[row * ns + sp] = wgt;
-      den = fmaf(wgt, __ldcg(triple(sp, row) + 1), den);
+      w_m[row * ns + sp] = wgt;
+      den = fmaf(wgt, w_l[row * ns + sp], den);
     }
-    row_m[row] = M;
-    row_l[row] = den;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
+    if (lane == 0) {
+      row_m[row] = M;
+      row_l[row] = den;
+    }
   }
   consumer_bar(C::CTHREADS);
-  for (int idx = ctid; idx < rows_valid * (HD / 2); idx += C::CTHREADS) {
-    const int row = idx / (HD / 2), c2 = idx % (HD / 2);
-    float ax = 0.f, ay = 0.f;
-#pragma unroll 4
+  for (int idx = ctid; idx < rows_valid * (HD / 4); idx += C::CTHREADS) {
+    const int row = idx / (HD / 4), c4 = idx % (HD / 4);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 *src = reinterpret_cast<const float4 *>(scratch_row(0, row)) + c4;
+    const long long sp_stride = static_cast<long long>(a.rows_cap) * RS / 4;
+#pragma unroll 8
     for (int sp = 0; sp < ns; ++sp) {
-      const float wgt = wsm[row * ns + sp];
-      const float2 v = __ldcg(reinterpret_cast<const float2 *>(triple(sp, row) + 2) + c2);
-      ax = fmaf(wgt, v.x, ax);
-      ay = fmaf(wgt, v.y, ay);
+      const float wgt = w_m[row * ns + sp];
+      const float4 v = __ldcg(src + sp * sp_stride);
+      acc.x = fmaf(wgt, v.x, acc.x);
+      acc.y = fmaf(wgt, v.y, acc.y);
+      acc.z = fmaf(wgt, v.z, acc.z);
+      acc.w = fmaf(wgt, v.w, acc.w);
     }
     const int head = kvh * a.gqa + row % a.gqa;
     if (a.partial_out) {
       float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (HD + 2);
-      if (c2 == 0) {
+      if (c4 == 0) {
         dst[0] = row_m[row] * kLn2;
         dst[1] = row_l[row];
       }
-      *reinterpret_cast<float2 *>(dst + 2 + 2 * c2) = make_float2(ax, ay);
+      float2 *d2 = reinterpret_cast<float2 *>(dst + 2 + 4 * c4);
+      d2[0] = make_float2(acc.x, acc.y);
+      d2[1] = make_float2(acc.z, acc.w);
     } else {
       const int tok = tok_begin + tok0 + row / a.gqa;
       const float inv = row_l[row] > 0.f ? 1.f / row_l[row] : 0.f;
       __half *dst =
           static_cast<__half *>(a.out) + (static_cast<long long>(tok) * a.n_q + head) * HD;
-      *reinterpret_cast<__half2 *>(dst + 2 * c2) = __floats2half2_rn(ax * inv, ay * inv);
+      __half2 lo = __floats2half2_rn(acc.x * inv, acc.y * inv);
+      __half2 hi = __floats2half2_rn(acc.z * inv, acc.w * inv);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t *>(&lo);
+      packed.y = *reinterpret_cast<uint32_t *>(&hi);
+      *reinterpret_cast<uint2 *>(dst + 4 * c4) = packed;
     }
   }
 }
@@ -673,8 +720,18 @@ wst_status_t launch_cfg(const RowsLaunch &L, const RowsArgs &args, const CUtenso
                                   C::SMEM_BYTES));
     configured_dev = dev;
   }
-  kern<<<grid, C::THREADS, C::SMEM_BYTES, current_stream()>>>(kmap, vmap, args);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(C::THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = current_stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, kmap, vmap, args);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess)
     return fail(WST_ERR_CUDA, "%s (launch): %s (%s)", L.name, cudaGetErrorString(e),
                 cudaGetErrorName(e));
@@ -720,7 +777,7 @@ int rows_pick_splits(int n_units, int max_len, int sm_count) {
 }
 
 long long rows_scratch_floats(int n_units_times_rows, int splits, int hd) {
-  return static_cast<long long>(n_units_times_rows) * splits * (hd + 2);
+  return static_cast<long long>(n_units_times_rows) * splits * (hd + 4);
 }
 
 wst_status_t launch_rows(const RowsLaunch &L) {
@@ -740,6 +797,7 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   int splits = L.want_splits > 0 ? L.want_splits : rows_pick_splits(n_units, L.max_len, facts.sm_count);
   if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
   /* the slices must fit the caller's scratch and the ticket table */
+  if (!aligned16(L.scratch)) splits = 1; /* the merge reads scratch rows as float4 */
   while (splits > 1 &&
          (!L.scratch || rows_scratch_floats(n_units * rows_cap, splits, L.hd) > L.scratch_floats))
     --splits;
