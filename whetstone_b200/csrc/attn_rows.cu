@@ -16,9 +16,12 @@
  *     mma.sync m16n8k16 (fp16 in, fp32 accumulate) because at ~7 query heads per
  *     KV byte the CUDA cores could not keep up with HBM; the online softmax
  *     state (running max, denominator) is fp32 and reduced with warp shuffles.
- *   - The sequence is split over CTAs so that all SMs stream; each slice writes
- *     an unnormalised (m, l, acc) triple and the LAST slice to finish (an atomic
- *     ticket, nothing spins) merges them and writes the result.  One launch.
+ *   - The sequence is split over CTAs so that all SMs stream (slice s takes
+ *     tiles s, s + n, s + 2n, ...); each slice writes an unnormalised
+ *     (m, l, acc) row per query row, and a small second kernel -- launched with
+ *     programmatic stream serialization, so already resident when the last
+ *     slice ends -- merges them with every load in flight at once.  Nothing
+ *     spins and no counters persist between launches.
  *
  * Semantics follow cuda/attention.cu:57-193 (decode) and cuda/chunk_ops.cu:187-264
  * (chunk: query j sees rows [0, pos0+j]) of the engine.
@@ -28,7 +31,6 @@
 #include "tensor_map.cuh"
 #include "wst_ptx.cuh"
 
-#include <atomic>
 
 namespace wst {
 namespace {
@@ -38,11 +40,19 @@ using namespace ptx;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
-/* Tickets for the "last slice merges" protocol: zero at load, reset to zero by
- * the block that takes the last ticket.  A launch uses one slot. */
-constexpr int kTicketSlots = 32;
-constexpr int kTicketsPerSlot = 2048;
-__device__ unsigned int g_tickets[kTicketSlots * kTicketsPerSlot];
+/* Optional phase timestamps for tuning (compiled in only with -DWST_TRACE). */
+#ifdef WST_TRACE
+__device__ unsigned long long g_trace[4096 * 8];
+__device__ __forceinline__ void trace_stamp(int slot) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  const unsigned int b = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (b < 4096) g_trace[b * 8 + slot] = t;
+}
+#define WST_STAMP(slot) do { if (threadIdx.x == 0) trace_stamp(slot); } while (0)
+#else
+#define WST_STAMP(slot) do { } while (0)
+#endif
 
 struct RowsArgs {
   const float *q;
@@ -56,7 +66,6 @@ struct RowsArgs {
   int n_q, n_kv, gqa, max_seq;
   float qscale; /* scale * log2(e): scores live in log2 units */
   float *scratch;
-  unsigned int *tickets;
   unsigned int *err_word;
   void *out;
   int partial_out;
@@ -75,11 +84,10 @@ struct Cfg {
   static constexpr int STAGE_BYTES = 2 * NH * HALF_BYTES;
   static constexpr int NSTAGE = HD == 128 ? 4 : 6;
   static constexpr int Q_BYTES = NH * ROWS * 128;
-  static constexpr int NO = MT * (HD / 8) * 4;   /* output accumulators per thread */
-  static constexpr int NREG = NO + MT * 4;       /* + running max and sum */
   static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + Q_BYTES + 2 * NSTAGE * 8 + 64 + 1024;
-  static_assert(RG * 2 * NREG * 32 * 4 <= NSTAGE * STAGE_BYTES, "merge buffer must fit");
-  static_assert(2 * ROWS * kRowsMaxSplits * 4 + ROWS * 8 <= NSTAGE * STAGE_BYTES, "weights must fit");
+  /* the warp-combine dump [RG][4][16*MT][HD+4] floats reuses the ring and the q tile */
+  static_assert(RG * 4 * 16 * MT * (HD + 4) * 4 <= NSTAGE * STAGE_BYTES + Q_BYTES,
+                "combine buffer must fit");
 };
 
 __device__ __forceinline__ void grid_dependency_wait() {
@@ -87,6 +95,14 @@ __device__ __forceinline__ void grid_dependency_wait() {
 }
 __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void store_half4(__half *dst, float a, float b, float c, float d) {
+  __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t *>(&lo);
+  packed.y = *reinterpret_cast<uint32_t *>(&hi);
+  *reinterpret_cast<uint2 *>(dst) = packed;
 }
 
 __device__ __forceinline__ void consumer_bar(int threads) {
@@ -112,7 +128,6 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t *qsm = smem + NSTAGE * STAGE_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(qsm + C::Q_BYTES);
-  int *flags = reinterpret_cast<int *>(bars + 2 * NSTAGE);
   const uint32_t stages_u32 = smem_u32(smem);
   const uint32_t q_u32 = smem_u32(qsm);
   const uint32_t full_u32 = smem_u32(bars);
@@ -132,7 +147,53 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   /* Everything above touches no global memory, so under programmatic dependent
    * launch it overlaps the tail of the previous kernel in the stream.  From here
    * on we read what that kernel may have written (cursor, q, cache rows). */
+  WST_STAMP(0);
   grid_dependency_wait();
+  WST_STAMP(1);
+
+  /* Slice `split` owns tiles split, split + n_splits, split + 2 n_splits, ...:
+   * the first tiles of a slice do not depend on the sequence length, so for a
+   * single contiguous sequence the producer starts streaming them before the
+   * cursor has even been read (tiles past the live rows are loaded and ignored;
+   * they lie inside the cache allocation or read as zeros). */
+  const int ns = a.n_splits;
+  auto issue = [&](int i) {
+    const int stage = i % NSTAGE;
+    const uint32_t full = full_u32 + 8 * stage;
+    mbar_arrive_expect_tx(full, STAGE_BYTES);
+    const int tile = split + i * ns;
+    const uint32_t kdst = stages_u32 + stage * STAGE_BYTES;
+    const uint32_t vdst = kdst + NH * HALF_BYTES;
+    if constexpr (!PAGED) {
+      const int plane = s * a.n_kv + kvh;
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+        tma_load_3d(kdst + h * HALF_BYTES, &kmap, full, h * 64, tile * BN, plane);
+        tma_load_3d(vdst + h * HALF_BYTES, &vmap, full, h * 64, tile * BN, plane);
+      }
+    } else {
+#pragma unroll
+      for (int pg = 0; pg < BN / 16; ++pg) {
+        const int slot = tile * (BN / 16) + pg;
+        int page = slot < a.max_pages
+                       ? a.page_table[static_cast<long long>(s) * a.max_pages + slot]
+                       : -1;
+        /* an unmapped slot reads as zeros: coordinate just past the pool */
+        if (page < 0 || page >= a.n_pool_pages) page = a.n_pool_pages;
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+          tma_load_4d(kdst + h * HALF_BYTES + pg * 16 * 128, &kmap, full, h * 64, 0, kvh, page);
+          tma_load_4d(vdst + h * HALF_BYTES + pg * 16 * 128, &vmap, full, h * 64, 0, kvh, page);
+        }
+      }
+    }
+  };
+  int spec = 0; /* tiles issued ahead of knowing the sequence length */
+  if (!PAGED && a.cu_tokens == nullptr) {
+    while (spec < NSTAGE && static_cast<long long>(split + spec * ns) * BN < a.max_seq) ++spec;
+    if (warp == C::CWARPS && lane == 0)
+      for (int i = 0; i < spec; ++i) issue(i);
+  }
 
   int tok_begin = 0, n_tok = a.n_tok;
   if (a.cu_tokens) {
@@ -140,72 +201,16 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     n_tok = a.cu_tokens[s + 1] - tok_begin;
   }
   const int tok0 = rb * a.tpb;
-  if (tok0 >= n_tok) return; /* ragged batch: this row block has no tokens */
+  if (tok0 >= n_tok) return; /* ragged batch: this row block has no tokens (spec == 0 here) */
   const int ntok_blk = min(a.tpb, n_tok - tok0);
   const int rows_valid = ntok_blk * a.gqa;
 
-  int pos0 = a.pos0_dev ? a.pos0_dev[s] + a.pos0_bias : a.pos0_val;
-  if (a.clamp_nonneg && pos0 < 0) pos0 = 0;
-  const int max_seq = a.max_seq;
-  auto limit_of = [pos0, max_seq](int tok) {
-    long long l = static_cast<long long>(pos0) + tok + 1;
-    l = l < 0 ? 0 : l;
-    return static_cast<int>(l < max_seq ? l : max_seq);
-  };
-  const int kv_end = limit_of(tok0 + ntok_blk - 1); /* rows [0, kv_end) are live data */
-  const int lim_min = limit_of(tok0);
-  const int n_tiles = (kv_end + BN - 1) / BN;
-  const int tile_lo = static_cast<int>(static_cast<long long>(split) * n_tiles / a.n_splits);
-  const int tile_hi = static_cast<int>(static_cast<long long>(split + 1) * n_tiles / a.n_splits);
-  const int my_tiles = tile_hi - tile_lo;
+  const int32_t pos_raw = a.pos0_dev ? a.pos0_dev[s] : 0; /* issued now, used below */
 
-  /* ------------------------------------------------------------ producer */
-  if (warp == C::CWARPS) {
-    if (lane != 0) return;
-    for (int i = 0; i < my_tiles; ++i) {
-      const int stage = i % NSTAGE, round = i / NSTAGE;
-      if (i >= NSTAGE &&
-          !mbar_wait(empty_u32 + 8 * stage, (round - 1) & 1, a.err_word, 0x101u))
-        break;
-      const uint32_t full = full_u32 + 8 * stage;
-      mbar_arrive_expect_tx(full, STAGE_BYTES);
-      const int tile = tile_lo + i;
-      const uint32_t kdst = stages_u32 + stage * STAGE_BYTES;
-      const uint32_t vdst = kdst + NH * HALF_BYTES;
-      if constexpr (!PAGED) {
-        const int plane = s * a.n_kv + kvh;
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-          tma_load_3d(kdst + h * HALF_BYTES, &kmap, full, h * 64, tile * BN, plane);
-          tma_load_3d(vdst + h * HALF_BYTES, &vmap, full, h * 64, tile * BN, plane);
-        }
-      } else {
-#pragma unroll
-        for (int pg = 0; pg < BN / 16; ++pg) {
-          const int slot = tile * (BN / 16) + pg;
-          int page = slot < a.max_pages
-                         ? a.page_table[static_cast<long long>(s) * a.max_pages + slot]
-                         : -1;
-          /* an unmapped slot reads as zeros: coordinate just past the pool */
-          if (page < 0 || page >= a.n_pool_pages) page = a.n_pool_pages;
-#pragma unroll
-          for (int h = 0; h < NH; ++h) {
-            tma_load_4d(kdst + h * HALF_BYTES + pg * 16 * 128, &kmap, full, h * 64, 0, kvh, page);
-            tma_load_4d(vdst + h * HALF_BYTES + pg * 16 * 128, &vmap, full, h * 64, 0, kvh, page);
-          }
-        }
-      }
-    }
-    return;
-  }
-
-  /* ----------------------------------------------------------- consumers */
-  const int rg = warp >> 2; /* row group: rows [rg*16*MT, +16*MT) */
-  const int w = warp & 3;   /* positions [16w, 16w+16) of every tile */
-  const int ctid = threadIdx.x;
-
-  /* q -> fp16, pre-multiplied by scale*log2(e), swizzled like the K tiles. */
-  for (int idx = ctid; idx < ROWS * (HD / 8); idx += C::CTHREADS) {
+  /* q -> fp16, pre-multiplied by scale*log2(e), swizzled like the K tiles.  Done
+   * before the cursor value is first used, so that the two global round trips
+   * (cursor, q) overlap instead of following one another. */
+  for (int idx = threadIdx.x; warp < C::CWARPS && idx < ROWS * (HD / 8); idx += C::CTHREADS) {
     const int row = idx / (HD / 8), ch = idx % (HD / 8);
     uint4 packed = make_uint4(0u, 0u, 0u, 0u);
     if (row < rows_valid) {
@@ -222,6 +227,38 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     }
     *reinterpret_cast<uint4 *>(qsm + (ch >> 3) * (ROWS * 128) + swz128(row, ch & 7)) = packed;
   }
+
+  int pos0 = a.pos0_dev ? pos_raw + a.pos0_bias : a.pos0_val;
+  if (a.clamp_nonneg && pos0 < 0) pos0 = 0;
+  const int max_seq = a.max_seq;
+  auto limit_of = [pos0, max_seq](int tok) {
+    long long l = static_cast<long long>(pos0) + tok + 1;
+    l = l < 0 ? 0 : l;
+    return static_cast<int>(l < max_seq ? l : max_seq);
+  };
+  const int kv_end = limit_of(tok0 + ntok_blk - 1); /* rows [0, kv_end) are live data */
+  const int lim_min = limit_of(tok0);
+  const int n_tiles = (kv_end + BN - 1) / BN;
+  const int my_tiles = split < n_tiles ? (n_tiles - split + ns - 1) / ns : 0;
+
+  /* ------------------------------------------------------------ producer */
+  if (warp == C::CWARPS) {
+    if (lane != 0) return;
+    for (int i = spec; i < my_tiles; ++i) {
+      const int stage = i % NSTAGE, round = i / NSTAGE;
+      if (i >= NSTAGE &&
+          !mbar_wait(empty_u32 + 8 * stage, (round - 1) & 1, a.err_word, 0x101u))
+        break;
+      issue(i);
+    }
+    return;
+  }
+
+  /* ----------------------------------------------------------- consumers */
+  const int rg = warp >> 2; /* row group: rows [rg*16*MT, +16*MT) */
+  const int w = warp & 3;   /* positions [16w, 16w+16) of every tile */
+  const int ctid = threadIdx.x;
+
   consumer_bar(C::CTHREADS);
 
   int lim[MT][2];
@@ -261,7 +298,8 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   for (int i = 0; i < my_tiles; ++i) {
     const int stage = i % NSTAGE, round = i / NSTAGE;
     if (!mbar_wait(full_u32 + 8 * stage, round & 1, a.err_word, 0x102u)) break;
-    const int tile = tile_lo + i;
+    if (i == 0) WST_STAMP(2);
+    const int tile = split + i * ns;
     const uint32_t kb = stages_u32 + stage * STAGE_BYTES;
     const uint32_t vb = kb + NH * HALF_BYTES;
 
@@ -381,9 +419,15 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     if (lane == 0) mbar_arrive(empty_u32 + 8 * stage);
   }
 
+  /* Tiles that were streamed ahead but lie past this slice's share: wait for
+   * them to land, nothing may still be in flight when the ring is reused. */
+  for (int i = my_tiles; i < spec; ++i)
+    if (!mbar_wait(full_u32 + 8 * (i % NSTAGE), (i / NSTAGE) & 1, a.err_word, 0x103u)) break;
+
   /* The cache has been streamed: let the next kernel in the stream start its
-   * prologue while this one combines its slices. */
+   * prologue while this one combines its warps. */
   grid_launch_dependents();
+  WST_STAMP(3);
 
   /* row sums live spread over the four lanes of a quad */
 #pragma unroll
@@ -396,197 +440,197 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       l_run[mt][hh] = l;
     }
 
-  /* ---- combine the four warps of a row group (tree, through the idle ring) */
-  float *mbuf = reinterpret_cast<float *>(smem);
-  auto put_state = [&](int slot) {
-    float *dst = mbuf + static_cast<size_t>(slot) * C::NREG * 32 + lane;
+  /* ---- combine the four warps of each row group through the idle ring: every
+   * warp dumps its rows as [acc HD | m | l | pad pad], then each thread merges one
+   * (row, 4-column) cell of the four copies and stores it, coalesced. */
+  constexpr int DR = HD + 4;
+  constexpr int RPG = 16 * MT; /* rows per row group */
+  float *dump = reinterpret_cast<float *>(smem);
+  consumer_bar(C::CTHREADS); /* every warp is done with the ring */
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float *row = dump + (static_cast<size_t>(rg * 4 + w) * RPG + mt * 16 + (lane >> 2) + hh * 8) * DR;
 #pragma unroll
       for (int nt = 0; nt < HD / 8; ++nt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) dst[((mt * (HD / 8) + nt) * 4 + c) * 32] = o[mt][nt][c];
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        dst[(C::NO + mt * 2 + hh) * 32] = m_run[mt][hh];
-        dst[(C::NO + MT * 2 + mt * 2 + hh) * 32] = l_run[mt][hh];
+        *reinterpret_cast<float2 *>(row + nt * 8 + 2 * (lane & 3)) =
+            make_float2(o[mt][nt][2 * hh], o[mt][nt][2 * hh + 1]);
+      if ((lane & 3) == 0) {
+        row[HD] = m_run[mt][hh];
+        row[HD + 1] = l_run[mt][hh];
       }
     }
-  };
-  auto take_state = [&](int slot) {
-    const float *src = mbuf + static_cast<size_t>(slot) * C::NREG * 32 + lane;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const float m_o = src[(C::NO + mt * 2 + hh) * 32];
-        const float l_o = src[(C::NO + MT * 2 + mt * 2 + hh) * 32];
-        const float m_new = fmaxf(m_run[mt][hh], m_o);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        const float c_me = ex2(m_run[mt][hh] - m_use);
-        const float c_ot = ex2(m_o - m_use);
-        m_run[mt][hh] = m_new;
-        l_run[mt][hh] = l_run[mt][hh] * c_me + l_o * c_ot;
-#pragma unroll
-        for (int nt = 0; nt < HD / 8; ++nt)
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const int k = 2 * hh + c;
-            o[mt][nt][k] = o[mt][nt][k] * c_me + src[((mt * (HD / 8) + nt) * 4 + k) * 32] * c_ot;
-          }
-      }
-  };
+  consumer_bar(C::CTHREADS);
+  WST_STAMP(4);
 
-  consumer_bar(C::CTHREADS); /* every warp is done with the ring */
-  if (w >= 2) put_state(rg * 2 + (w - 2));
-  consumer_bar(C::CTHREADS);
-  if (w < 2) take_state(rg * 2 + w);
-  consumer_bar(C::CTHREADS);
-  if (w == 1) put_state(rg * 2);
-  consumer_bar(C::CTHREADS);
-  if (w == 0) take_state(rg * 2);
-
-  /* ---- write: final result (one slice) or this slice's triple */
   const int unit = (s * a.n_kv + kvh) * a.n_rowblk + rb;
-  const bool single = a.n_splits == 1;
-  if (w == 0) {
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int r = rg * 16 * MT + mt * 16 + (lane >> 2) + hh * 8;
-        if (r >= rows_valid) continue;
-        const int col = 2 * (lane & 3);
-        if (single && !a.partial_out) {
-          const int tok = tok_begin + tok0 + r / a.gqa;
-          const int head = kvh * a.gqa + r % a.gqa;
-          const float inv = l_run[mt][hh] > 0.f ? 1.f / l_run[mt][hh] : 0.f;
-          __half *dst = static_cast<__half *>(a.out) +
-                        (static_cast<long long>(tok) * a.n_q + head) * HD + col;
-#pragma unroll
-          for (int nt = 0; nt < HD / 8; ++nt)
-            *reinterpret_cast<__half2 *>(dst + nt * 8) = __floats2half2_rn(
-                o[mt][nt][2 * hh] * inv, o[mt][nt][2 * hh + 1] * inv);
-        } else {
-          /* (m, l, acc[HD]) for the caller (natural-log m), or a scratch row
-           * laid out acc[HD] | m | l | pad pad so that acc is 16-byte aligned */
-          float *acc_dst, *ml_dst;
-          float m_out = m_run[mt][hh];
-          if (single) {
-            ml_dst = static_cast<float *>(a.out) +
-                     static_cast<long long>(kvh * a.gqa + r % a.gqa) * (HD + 2);
-            acc_dst = ml_dst + 2;
-            m_out *= kLn2;
-          } else {
-            acc_dst = a.scratch +
-                      ((static_cast<long long>(unit) * a.n_splits + split) * a.rows_cap + r) *
-                          (HD + 4);
-            ml_dst = acc_dst + HD;
-          }
-          if ((lane & 3) == 0) {
-            ml_dst[0] = m_out;
-            ml_dst[1] = l_run[mt][hh];
-          }
-#pragma unroll
-          for (int nt = 0; nt < HD / 8; ++nt)
-            *reinterpret_cast<float2 *>(acc_dst + nt * 8 + col) =
-                make_float2(o[mt][nt][2 * hh], o[mt][nt][2 * hh + 1]);
-        }
-      }
-  }
-  if (single) return;
-
-  /* ---- ticket: the last slice of this unit to arrive merges all of them.
-   * Writers store, the block barrier orders them before thread 0, whose fence +
-   * atomic publishes the whole block's rows (and, for the last arrival, makes
-   * every other block's rows visible before anyone here reads them). */
-  consumer_bar(C::CTHREADS);
-  if (ctid == 0) {
-    __threadfence();
-    const unsigned int prev = atomicAdd(&a.tickets[unit], 1u);
-    const int last = prev == static_cast<unsigned int>(a.n_splits - 1);
-    if (last) {
-      a.tickets[unit] = 0u; /* everyone has arrived: leave it ready for the next launch */
-      __threadfence();
-    }
-    flags[0] = last;
-  }
-  consumer_bar(C::CTHREADS);
-  if (!flags[0]) return;
-
-  const int ns = a.n_splits;
-  constexpr int RS = HD + 4;                          /* floats per scratch row */
-  float *w_m = reinterpret_cast<float *>(smem);       /* [rows_valid][ns] max, then weight */
-  float *w_l = w_m + ROWS * kRowsMaxSplits;           /* [rows_valid][ns] denominators */
-  float *row_m = w_l + ROWS * kRowsMaxSplits;         /* [ROWS] */
-  float *row_l = row_m + ROWS;
-  const float *base = a.scratch + static_cast<long long>(unit) * ns * a.rows_cap * RS;
-  auto scratch_row = [&](int sp, int row) {
-    return base + (static_cast<long long>(sp) * a.rows_cap + row) * RS;
-  };
-  for (int idx = ctid; idx < rows_valid * ns; idx += C::CTHREADS) {
-    const int row = idx / ns, sp = idx % ns;
-    const float2 ml = __ldcg(reinterpret_cast<const float2 *>(scratch_row(sp, row) + HD));
-    w_m[row * ns + sp] = ml.x;
-    w_l[row * ns + sp] = ml.y;
-  }
-  consumer_bar(C::CTHREADS);
-  for (int row = warp; row < rows_valid; row += C::CWARPS) { /* one warp per row */
-    float M = -INFINITY;
-    for (int sp = lane; sp < ns; sp += 32) M = fmaxf(M, w_m[row * ns + sp]);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-    float den = 0.f;
-    for (int sp = lane; sp < ns; sp += 32) {
-      const float m = w_m[row * ns + sp];
-      const float wgt = (m == -INFINITY) ? 0.f : ex2(m - M);
-      w_m[row * ns + sp] = wgt;
-      den = fmaf(wgt, w_l[row * ns + sp], den);
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
-    if (lane == 0) {
-      row_m[row] = M;
-      row_l[row] = den;
-    }
-  }
-  consumer_bar(C::CTHREADS);
+  const bool single = ns == 1;
   for (int idx = ctid; idx < rows_valid * (HD / 4); idx += C::CTHREADS) {
-    const int row = idx / (HD / 4), c4 = idx % (HD / 4);
+    const int r = idx / (HD / 4), c4 = idx % (HD / 4);
+    const float *cell = dump + (static_cast<size_t>(r / RPG) * 4 * RPG + r % RPG) * DR;
+    float mw[4], M = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      mw[k] = cell[static_cast<size_t>(k) * RPG * DR + HD];
+      M = fmaxf(M, mw[k]);
+    }
+    const float m_use = M == -INFINITY ? 0.f : M;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 *src = reinterpret_cast<const float4 *>(scratch_row(0, row)) + c4;
-    const long long sp_stride = static_cast<long long>(a.rows_cap) * RS / 4;
-#pragma unroll 8
-    for (int sp = 0; sp < ns; ++sp) {
-      const float wgt = w_m[row * ns + sp];
-      const float4 v = __ldcg(src + sp * sp_stride);
+    float den = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float wgt = ex2(mw[k] - m_use);
+      const float4 v = *reinterpret_cast<const float4 *>(cell + static_cast<size_t>(k) * RPG * DR + 4 * c4);
       acc.x = fmaf(wgt, v.x, acc.x);
       acc.y = fmaf(wgt, v.y, acc.y);
       acc.z = fmaf(wgt, v.z, acc.z);
       acc.w = fmaf(wgt, v.w, acc.w);
+      den = fmaf(wgt, cell[static_cast<size_t>(k) * RPG * DR + HD + 1], den);
     }
-    const int head = kvh * a.gqa + row % a.gqa;
-    if (a.partial_out) {
+    const int head = kvh * a.gqa + r % a.gqa;
+    if (single && !a.partial_out) {
+      const int tok = tok_begin + tok0 + r / a.gqa;
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      store_half4(static_cast<__half *>(a.out) +
+                      (static_cast<long long>(tok) * a.n_q + head) * HD + 4 * c4,
+                  acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    } else if (single) { /* the caller's (m, l, acc) triple, natural-log m */
       float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (HD + 2);
       if (c4 == 0) {
-        dst[0] = row_m[row] * kLn2;
-        dst[1] = row_l[row];
+        dst[0] = M * kLn2;
+        dst[1] = den;
       }
-      float2 *d2 = reinterpret_cast<float2 *>(dst + 2 + 4 * c4);
-      d2[0] = make_float2(acc.x, acc.y);
-      d2[1] = make_float2(acc.z, acc.w);
-    } else {
-      const int tok = tok_begin + tok0 + row / a.gqa;
-      const float inv = row_l[row] > 0.f ? 1.f / row_l[row] : 0.f;
-      __half *dst =
-          static_cast<__half *>(a.out) + (static_cast<long long>(tok) * a.n_q + head) * HD;
-      __half2 lo = __floats2half2_rn(acc.x * inv, acc.y * inv);
-      __half2 hi = __floats2half2_rn(acc.z * inv, acc.w * inv);
-      uint2 packed;
-      packed.x = *reinterpret_cast<uint32_t *>(&lo);
-      packed.y = *reinterpret_cast<uint32_t *>(&hi);
-      *reinterpret_cast<uint2 *>(dst + 4 * c4) = packed;
+      reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[0] = make_float2(acc.x, acc.y);
+      reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[1] = make_float2(acc.z, acc.w);
+    } else { /* this slice's row for the merge kernel */
+      float *dst = a.scratch +
+                   ((static_cast<long long>(unit) * ns + split) * a.rows_cap + r) * DR;
+      *reinterpret_cast<float4 *>(dst + 4 * c4) = acc;
+      if (c4 == 0) *reinterpret_cast<float2 *>(dst + HD) = make_float2(M, den);
     }
+  }
+  WST_STAMP(5);
+}
+
+/* ---------------------------------------------------------- slice merge */
+
+/* Second kernel of a split launch: one block per (unit, row).  Launched with
+ * programmatic stream serialization, so its blocks are already resident when
+ * the last slice finishes; each warp takes a quarter of the slices with every
+ * load in flight at once (at most 16 per thread), so the merge costs about one
+ * memory round trip.  Same arithmetic as cuda/attention.cu:170-193, in log2
+ * units. */
+struct MergeArgs {
+  const float *scratch;
+  void *out;
+  const int32_t *cu_tokens;
+  int n_tok, n_q, n_kv, gqa;
+  int n_splits, n_rowblk, tpb, rows_cap;
+  int partial_out;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
+  constexpr int DR = HD + 4;
+  constexpr int LPR = HD / 4;      /* lanes that cover one row as float4 */
+  constexpr int SUB = 32 / LPR;    /* slice sub-groups inside a warp (1 or 2) */
+  constexpr int GROUPS = 4 * SUB;  /* slice groups per block */
+  constexpr int PER = kRowsMaxSplits / GROUPS;
+  __shared__ float4 s_acc[GROUPS][LPR];
+  __shared__ float s_m[GROUPS], s_l[GROUPS];
+
+  grid_launch_dependents();
+  grid_dependency_wait();
+
+  const int row = blockIdx.x, unit = blockIdx.y;
+  const int rb = unit % a.n_rowblk;
+  const int kvh = (unit / a.n_rowblk) % a.n_kv;
+  const int s = unit / (a.n_rowblk * a.n_kv);
+  int tok_begin = 0, n_tok = a.n_tok;
+  if (a.cu_tokens) {
+    tok_begin = a.cu_tokens[s];
+    n_tok = a.cu_tokens[s + 1] - tok_begin;
+  }
+  const int tok0 = rb * a.tpb;
+  if (tok0 >= n_tok) return;
+  const int ntok_blk = min(a.tpb, n_tok - tok0);
+  if (row >= ntok_blk * a.gqa) return;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = warp * SUB + lane / LPR, c4 = lane % LPR;
+  const int ns = a.n_splits;
+  const float *base = a.scratch + (static_cast<long long>(unit) * ns * a.rows_cap + row) * DR;
+  const long long sp_stride = static_cast<long long>(a.rows_cap) * DR;
+
+  float4 v[PER];
+  float2 ml[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int sp = group + i * GROUPS;
+    if (sp < ns) {
+      v[i] = __ldcg(reinterpret_cast<const float4 *>(base + sp * sp_stride) + c4);
+      ml[i] = __ldcg(reinterpret_cast<const float2 *>(base + sp * sp_stride + HD));
+    } else {
+      v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      ml[i] = make_float2(-INFINITY, 0.f);
+    }
+  }
+  float M = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) M = fmaxf(M, ml[i].x);
+  const float m_use = M == -INFINITY ? 0.f : M;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const float wgt = ex2(ml[i].x - m_use);
+    acc.x = fmaf(wgt, v[i].x, acc.x);
+    acc.y = fmaf(wgt, v[i].y, acc.y);
+    acc.z = fmaf(wgt, v[i].z, acc.z);
+    acc.w = fmaf(wgt, v[i].w, acc.w);
+    den = fmaf(wgt, ml[i].y, den);
+  }
+  s_acc[group][c4] = acc;
+  if (c4 == 0) {
+    s_m[group] = M;
+    s_l[group] = den;
+  }
+  __syncthreads();
+  if (threadIdx.x >= LPR) return;
+
+  float big = -INFINITY;
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) big = fmaxf(big, s_m[g]);
+  const float big_use = big == -INFINITY ? 0.f : big;
+  float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+  float dsum = 0.f;
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const float wgt = ex2(s_m[g] - big_use);
+    const float4 p = s_acc[g][threadIdx.x];
+    tot.x = fmaf(wgt, p.x, tot.x);
+    tot.y = fmaf(wgt, p.y, tot.y);
+    tot.z = fmaf(wgt, p.z, tot.z);
+    tot.w = fmaf(wgt, p.w, tot.w);
+    dsum = fmaf(wgt, s_l[g], dsum);
+  }
+  const int head = kvh * a.gqa + row % a.gqa;
+  const int col = 4 * threadIdx.x;
+  if (a.partial_out) {
+    float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (HD + 2);
+    if (threadIdx.x == 0) {
+      dst[0] = big * kLn2;
+      dst[1] = dsum;
+    }
+    reinterpret_cast<float2 *>(dst + 2 + col)[0] = make_float2(tot.x, tot.y);
+    reinterpret_cast<float2 *>(dst + 2 + col)[1] = make_float2(tot.z, tot.w);
+  } else {
+    const int tok = tok_begin + tok0 + row / a.gqa;
+    const float inv = dsum > 0.f ? 1.f / dsum : 0.f;
+    store_half4(static_cast<__half *>(a.out) + (static_cast<long long>(tok) * a.n_q + head) * HD +
+                    col,
+                tot.x * inv, tot.y * inv, tot.z * inv, tot.w * inv);
   }
 }
 
@@ -705,7 +749,24 @@ __global__ void __launch_bounds__(128) attn_simple_kernel(const SimpleArgs a) {
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-std::atomic<unsigned int> g_launch_counter{0};
+/* Launch with programmatic stream serialization: the kernel may become resident
+ * while its predecessor in the stream drains; it orders itself with
+ * griddepcontrol.wait. */
+template <typename Kern, typename... Args>
+cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = current_stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
+  return e == cudaSuccess ? cudaGetLastError() : e;
+}
 
 template <int HD, int MT, int RG, bool PAGED>
 wst_status_t launch_cfg(const RowsLaunch &L, const RowsArgs &args, const CUtensorMap &kmap,
@@ -720,18 +781,7 @@ wst_status_t launch_cfg(const RowsLaunch &L, const RowsArgs &args, const CUtenso
                                   C::SMEM_BYTES));
     configured_dev = dev;
   }
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(C::THREADS);
-  cfg.dynamicSmemBytes = C::SMEM_BYTES;
-  cfg.stream = current_stream();
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, kmap, vmap, args);
-  if (e == cudaSuccess) e = cudaGetLastError();
+  cudaError_t e = launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM_BYTES, kmap, vmap, args);
   if (e != cudaSuccess)
     return fail(WST_ERR_CUDA, "%s (launch): %s (%s)", L.name, cudaGetErrorString(e),
                 cudaGetErrorName(e));
@@ -755,6 +805,13 @@ int rows_for(int gqa, int n_tok) {
 }
 
 }  // namespace
+
+#ifdef WST_TRACE
+extern "C" __attribute__((visibility("default"))) int wst_b200_trace_read(unsigned long long *dst,
+                                                                         int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_trace, sizeof(unsigned long long) * n));
+}
+#endif
 
 bool rows_kernel_supports(int n_q, int n_kv, int hd, const void *k, const void *v) {
   if (hd != 64 && hd != 128) return false;
@@ -796,12 +853,11 @@ wst_status_t launch_rows(const RowsLaunch &L) {
 
   int splits = L.want_splits > 0 ? L.want_splits : rows_pick_splits(n_units, L.max_len, facts.sm_count);
   if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
-  /* the slices must fit the caller's scratch and the ticket table */
+  /* the slices must fit the caller's scratch */
   if (!aligned16(L.scratch)) splits = 1; /* the merge reads scratch rows as float4 */
   while (splits > 1 &&
          (!L.scratch || rows_scratch_floats(n_units * rows_cap, splits, L.hd) > L.scratch_floats))
     --splits;
-  if (n_units > kTicketsPerSlot) splits = 1;
 
   RowsArgs a{};
   a.q = L.q;
@@ -829,20 +885,6 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   a.rows_cap = rows_cap;
   a.err_word = device_error_word();
   if (!a.err_word) return WST_ERR_CUDA;
-  {
-    static thread_local unsigned int *ticket_base[64] = {};
-    int dev = 0;
-    WST_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return fail(WST_ERR_CUDA, "%s: device ordinal out of range", L.name);
-    if (!ticket_base[dev]) {
-      void *p = nullptr;
-      WST_CUDA(cudaGetSymbolAddress(&p, g_tickets));
-      ticket_base[dev] = static_cast<unsigned int *>(p);
-    }
-    const unsigned int slot = g_launch_counter.fetch_add(1, std::memory_order_relaxed) % kTicketSlots;
-    a.tickets = ticket_base[dev] + static_cast<size_t>(slot) * kTicketsPerSlot;
-  }
-
   CUtensorMap kmap, vmap;
   KvMapKey key{};
   key.d0 = static_cast<uint64_t>(L.hd);
@@ -864,11 +906,34 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   const dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(L.n_kv * n_rowblk),
                   static_cast<unsigned>(L.n_seq));
   if (L.hd == 128) {
-    return L.paged ? launch_shape<128, true>(L, a, kmap, vmap, grid, rows)
-                   : launch_shape<128, false>(L, a, kmap, vmap, grid, rows);
-  }
-  return L.paged ? launch_shape<64, true>(L, a, kmap, vmap, grid, rows)
+    st = L.paged ? launch_shape<128, true>(L, a, kmap, vmap, grid, rows)
+                 : launch_shape<128, false>(L, a, kmap, vmap, grid, rows);
+  } else {
+    st = L.paged ? launch_shape<64, true>(L, a, kmap, vmap, grid, rows)
                  : launch_shape<64, false>(L, a, kmap, vmap, grid, rows);
+  }
+  if (st != WST_OK || splits == 1) return st;
+
+  MergeArgs m{};
+  m.scratch = L.scratch;
+  m.out = L.out;
+  m.cu_tokens = L.cu_tokens;
+  m.n_tok = L.n_tok;
+  m.n_q = L.n_q;
+  m.n_kv = L.n_kv;
+  m.gqa = gqa;
+  m.n_splits = splits;
+  m.n_rowblk = n_rowblk;
+  m.tpb = tpb;
+  m.rows_cap = rows_cap;
+  m.partial_out = L.partial_out ? 1 : 0;
+  const dim3 mgrid(static_cast<unsigned>(rows_cap), static_cast<unsigned>(n_units));
+  cudaError_t e = L.hd == 128 ? launch_pdl(attn_merge_kernel<128>, mgrid, dim3(128), 0, m)
+                              : launch_pdl(attn_merge_kernel<64>, mgrid, dim3(128), 0, m);
+  if (e != cudaSuccess)
+    return fail(WST_ERR_CUDA, "%s (merge launch): %s (%s)", L.name, cudaGetErrorString(e),
+                cudaGetErrorName(e));
+  return WST_OK;
 }
 
 wst_status_t launch_simple(const RowsLaunch &L) {
