@@ -35,7 +35,10 @@ WST_API wst_status_t wst_b200_set_stream(void *stream);
 WST_API wst_status_t wst_b200_device_error(uint32_t *out_code);
 
 /* Which kernel family the attention entry points use:
- *   0 = automatic (default), 1 = force the portable CUDA-core kernel.
+ *   0 = automatic (default)
+ *   1 = force the portable CUDA-core kernel
+ *   2 = wst_attn_chunk: force the split-KV mma.sync kernel
+ *   3 = wst_attn_chunk: force the tcgen05 prefill kernel wherever it takes the shape
  * A debugging aid for A/B checks; process-wide. */
 WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
 

@@ -152,8 +152,9 @@ def test_decode_cursor_is_clamped():
                               orc.decode_attention(q, k, v, seq), f"cursor {raw}")
 
 
-def test_repeated_decode_calls_reuse_scratch_and_tickets():
-    """Back-to-back launches on one stream: the ticket table resets itself."""
+def test_repeated_decode_calls_share_scratch():
+    """Back-to-back launches on one stream reuse one split scratch: each launch
+    must be ordered after the merge of the one before it."""
     rng = np.random.default_rng(21)
     n_q, n_kv, hd, seq = 28, 4, 128, 3000
     cache = decode.KvCache(n_kv, n_q, hd, seq)
@@ -204,10 +205,17 @@ def test_partial_triples_merge_to_the_full_result(kernel_choice, shards):
 
 # -------------------------------------------- sets 3/4: chunk (contiguous)
 
+@pytest.fixture(params=[0, 1, 2, 3], ids=["auto", "portable", "splitkv", "tcgen05"])
+def chunk_kernel_choice(request):
+    check(lib.wst_b200_set_kernel_choice(request.param))
+    yield request.param
+    check(lib.wst_b200_set_kernel_choice(0))
+
+
 @pytest.mark.parametrize("n_q,n_kv,hd", [(14, 2, 64), (28, 4, 128), (32, 8, 128)])
 @pytest.mark.parametrize("pos0,n", [(0, 1), (0, 5), (0, 64), (20, 5), (1000, 5), (1000, 17),
-                                    (37, 130), (0, 257), (4000, 6)])
-def test_chunk_matches_oracle(kernel_choice, n_q, n_kv, hd, pos0, n):
+                                    (37, 130), (0, 257), (4000, 6), (100, 128), (511, 300)])
+def test_chunk_matches_oracle(chunk_kernel_choice, n_q, n_kv, hd, pos0, n):
     """append + causal attention of a chunk, prefix written by earlier appends."""
     rng = np.random.default_rng(pos0 * 7 + n + hd)
     theta = 1e6

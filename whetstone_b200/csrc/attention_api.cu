@@ -125,7 +125,7 @@ __global__ void merge_partials_kernel(const float *__restrict__ parts, __half *_
 using namespace wst;
 
 extern "C" wst_status_t wst_b200_set_kernel_choice(int32_t choice) {
-  WST_CHECK_ARG(choice == 0 || choice == 1, "wst_b200_set_kernel_choice: unknown choice");
+  WST_CHECK_ARG(choice >= 0 && choice <= 3, "wst_b200_set_kernel_choice: unknown choice");
   g_kernel_choice.store(choice);
   return WST_OK;
 }
@@ -191,7 +191,16 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
   const bool tc_ok = choice != 1 && rows_kernel_supports(n_q, n_kv, head_dim, k_cache, v_cache) &&
                      aligned16(qkv);
 
-  if (tc_ok && prefill_kernel_supports(n_q, n_kv, head_dim, n)) {
+  /* 128-row tcgen05 tiles when the chunk is large enough to fill the GPU with
+   * them (or the prefix is short enough that it does not matter); a few tokens
+   * against a long prefix go to the split-KV kernel instead. */
+  bool use_prefill = tc_ok && choice != 2 && prefill_kernel_supports(n_q, n_kv, head_dim, n);
+  if (use_prefill && choice != 3) {
+    const int gqa = n_q / n_kv;
+    const long long tiles = (static_cast<long long>(n) * gqa + 127) / 128 * n_kv;
+    use_prefill = tiles >= 32 || static_cast<long long>(pos0) + n <= 2048;
+  }
+  if (use_prefill) {
     PrefillLaunch P;
     P.name = "wst_attn_chunk";
     P.qkv = static_cast<const float *>(qkv);

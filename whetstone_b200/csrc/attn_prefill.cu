@@ -1,11 +1,487 @@
+/* Kernel set 3: causal chunked-prefill attention on the 5th-generation tensor
+ * cores.
+ *
+ * One CTA owns 128 query rows of one KV head -- rows are (token, head-in-group)
+ * pairs, token-major, so a tile covers 128/gqa consecutive tokens and all the
+ * query heads that share the KV head -- and walks the visible prefix in tiles of
+ * 128 cache positions.  Per tile:
+ *
+ *   S  = Q K^T   tcgen05.mma (M128 x N128 x K16 steps), fp16 operands from
+ *                128-byte-swizzled shared memory, fp32 accumulator in TENSOR MEMORY
+ *   softmax      128 threads, one query row each (a TMEM lane is a row, so row
+ *                max and row sum need no shuffles); fp32, exp2 with scale*log2(e)
+ *                folded into q; P is written back to shared memory as fp16
+ *   O' = P V     tcgen05.mma (M128 x N(head_dim) x K16 steps) into a second TMEM
+ *                buffer; the softmax threads fold O' into the running output they
+ *                keep in registers:  O = O * 2^(m_old - m_new) + O'
+ *
+ * Warp roles: warps 0-3 softmax/epilogue, warp 4 issues the MMAs (one elected
+ * lane), warp 5 feeds K and V tiles with TMA.  S and O' are double-buffered in
+ * tensor memory (512 columns), so QK^T of tile j+1 runs on the tensor cores
+ * while the CUDA cores do the softmax of tile j.  Every wait is bounded.
+ *
+ * Semantics: cuda/chunk_ops.cu:187-264 of the engine (query j sees cache rows
+ * [0, pos0 + j]; fp32 softmax state; fp16 output).
+ */
+
 #include "attn_prefill.cuh"
+#include "tensor_map.cuh"
+#include "wst_ptx.cuh"
 
 namespace wst {
+namespace {
 
-bool prefill_kernel_supports(int, int, int, int) { return false; }
+using namespace ptx;
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int HD>
+struct PCfg {
+  static constexpr int BM = 128;               /* query rows per CTA */
+  static constexpr int BN = 128;               /* cache positions per tile */
+  static constexpr int NH = HD / 64;           /* 128-byte column halves of a K/V/Q row */
+  static constexpr int HALF_BYTES = BN * 128;  /* one half of a tile: 128 rows x 128 B */
+  static constexpr int Q_BYTES = NH * HALF_BYTES;
+  static constexpr int KV_BYTES = NH * HALF_BYTES;
+  static constexpr int P_BYTES = 2 * HALF_BYTES; /* 128 rows x 128 positions fp16 */
+  static constexpr int NSTAGE = HD == 128 ? 2 : 3;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + NSTAGE * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + NSTAGE * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int NBAR = 4 * NSTAGE + 2 + 2 + 1 + 1 + 2 + 2 + 1;
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
+  static constexpr int THREADS = 192;
+  /* tensor-memory columns */
+  static constexpr int COL_S = 0;      /* two S buffers of BN fp32 columns */
+  static constexpr int COL_O = 2 * BN; /* two O' buffers of HD fp32 columns */
+  static constexpr int TMEM_COLS = 512;
+};
+
+struct PrefillArgs {
+  const float *q;
+  long long q_tok_stride;
+  __half *out;
+  int n_q, n_kv, gqa;
+  int pos0, n, max_seq;
+  int tpt;      /* tokens per 128-row tile = 128 / gqa */
+  int n_qtiles;
+  float qscale; /* scale * log2(e) */
+  unsigned int *err_word;
+};
+
+/* Shared-memory matrix descriptor for tcgen05.mma: 128-byte swizzle, tile base
+ * 1024-byte aligned, 8-row groups 1024 bytes apart. */
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((1024u >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46; /* descriptor version for sm_100 */
+  d |= 2ull << 61; /* SWIZZLE_128B */
+  return d;
+}
+
+/* Instruction descriptor, kind::f16: fp16 A and B, fp32 D, M x N tile. */
+__device__ __forceinline__ constexpr uint32_t umma_idesc(int m, int n, int b_mn_major) {
+  return (1u << 4) | (static_cast<uint32_t>(b_mn_major) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PCfg<HD>::THREADS, 1)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
+                    const __grid_constant__ CUtensorMap vmap, const PrefillArgs a) {
+  using C = PCfg<HD>;
+  constexpr int BN = C::BN, NH = C::NH, NSTAGE = C::NSTAGE;
+  constexpr int HALF_BYTES = C::HALF_BYTES, KV_BYTES = C::KV_BYTES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  auto bar = [bar0](int i) { return bar0 + 8u * i; };
+  /* barrier indices */
+  constexpr int K_FULL = 0, V_FULL = NSTAGE, K_EMPTY = 2 * NSTAGE, V_EMPTY = 3 * NSTAGE;
+  constexpr int S_FULL = 4 * NSTAGE, S_FREE = S_FULL + 2, P_READY = S_FREE + 2;
+  constexpr int P_FREE = P_READY + 1, OT_FULL = P_FREE + 1, OT_FREE = OT_FULL + 2;
+  constexpr int Q_READY = OT_FREE + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + C::OFF_BAR + C::NBAR * 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qtile = a.n_qtiles - 1 - blockIdx.x; /* longest prefixes first */
+  const int kvh = blockIdx.y;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSTAGE; ++i) {
+      mbar_init(bar(K_FULL + i), 1);
+      mbar_init(bar(V_FULL + i), 1);
+      mbar_init(bar(K_EMPTY + i), 1);
+      mbar_init(bar(V_EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(S_FREE + i), 128);
+      mbar_init(bar(OT_FULL + i), 1);
+      mbar_init(bar(OT_FREE + i), 128);
+    }
+    mbar_init(bar(P_READY), 128);
+    mbar_init(bar(P_FREE), 1);
+    mbar_init(bar(Q_READY), 128);
+    mbar_init_fence();
+    tma_prefetch_desc(&kmap);
+    tma_prefetch_desc(&vmap);
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  grid_dependency_wait();
+
+  /* rows of this tile: row r = (token tok0 + r / gqa, head kvh*gqa + r % gqa) */
+  const int tok0 = qtile * a.tpt;
+  const int ntok = min(a.tpt, a.n - tok0);
+  const int rows_valid = ntok * a.gqa;
+  const int kv_end = min(a.pos0 + tok0 + ntok, a.max_seq); /* live cache rows this tile sees */
+  const int lim_min = min(a.pos0 + tok0 + 1, a.max_seq);
+  const int n_tiles = (kv_end + BN - 1) / BN;
+
+  if (warp == 5) {
+    /* ------------------------------------------------------ TMA producer */
+    if (lane == 0) {
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j % NSTAGE, round = j / NSTAGE;
+        if (j >= NSTAGE && !mbar_wait(bar(K_EMPTY + st), (round - 1) & 1, a.err_word, 0x201u))
+          break;
+        mbar_arrive_expect_tx(bar(K_FULL + st), KV_BYTES);
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+          tma_load_3d(sbase + C::OFF_K + st * KV_BYTES + h * HALF_BYTES, &kmap, bar(K_FULL + st),
+                      h * 64, j * BN, kvh);
+        if (j >= NSTAGE && !mbar_wait(bar(V_EMPTY + st), (round - 1) & 1, a.err_word, 0x202u))
+          break;
+        mbar_arrive_expect_tx(bar(V_FULL + st), KV_BYTES);
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+          tma_load_3d(sbase + C::OFF_V + st * KV_BYTES + h * HALF_BYTES, &vmap, bar(V_FULL + st),
+                      h * 64, j * BN, kvh);
+      }
+    }
+  } else if (warp == 4) {
+    /* -------------------------------------------------------- MMA issuer */
+    constexpr uint32_t idesc_qk = umma_idesc(128, BN, 0);
+    constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
+    bool ok = mbar_wait(bar(Q_READY), 0, a.err_word, 0x210u);
+    tc_fence_after_sync();
+
+    auto issue_pv = [&](int i) -> bool {
+      const int st = i % NSTAGE;
+      if (!mbar_wait(bar(P_READY), i & 1, a.err_word, 0x211u)) return false;
+      if (!mbar_wait(bar(V_FULL + st), (i / NSTAGE) & 1, a.err_word, 0x212u)) return false;
+      if (i >= 2 && !mbar_wait(bar(OT_FREE + (i & 1)), ((i >> 1) - 1) & 1, a.err_word, 0x213u))
+        return false;
+      const uint32_t vb = sbase + C::OFF_V + st * KV_BYTES;
+      /* Cache rows past the live data can hold any bit pattern and 0 * NaN is
+       * NaN: clear them in the last tile before the tensor core reads V. */
+      if (i * BN + BN > kv_end) {
+        const int first = kv_end - i * BN;
+        for (int idx = first * (NH * 8) + lane; idx < BN * NH * 8; idx += 32) {
+          const int row = idx / (NH * 8), rest = idx % (NH * 8);
+          asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(
+                           vb + (rest >> 3) * HALF_BYTES + row * 128 + (rest & 7) * 16),
+                       "r"(0u)
+                       : "memory");
+        }
+        fence_async_smem();
+        __syncwarp();
+      }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t pb = sbase + C::OFF_P;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t ad = umma_desc(pb + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16);
+          const uint64_t bd = umma_desc(vb + kk * 2048, HALF_BYTES);
+          umma_ss_f16(tmem + C::COL_O + (i & 1) * HD, ad, bd, idesc_pv, kk > 0);
+        }
+        umma_commit(bar(V_EMPTY + st));
+        umma_commit(bar(P_FREE));
+        umma_commit(bar(OT_FULL + (i & 1)));
+      }
+      __syncwarp();
+      return true;
+    };
+
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int st = j % NSTAGE;
+      if (!mbar_wait(bar(K_FULL + st), (j / NSTAGE) & 1, a.err_word, 0x214u)) { ok = false; break; }
+      if (j >= 2 && !mbar_wait(bar(S_FREE + (j & 1)), ((j >> 1) - 1) & 1, a.err_word, 0x215u)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t qb = sbase + C::OFF_Q;
+        const uint32_t kb = sbase + C::OFF_K + st * KV_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_ss_f16(tmem + C::COL_S + (j & 1) * BN, umma_desc(qb + off, 16),
+                      umma_desc(kb + off, 16), idesc_qk, ks > 0);
+        }
+        umma_commit(bar(K_EMPTY + st));
+        umma_commit(bar(S_FULL + (j & 1)));
+      }
+      __syncwarp();
+      if (j >= 1 && !issue_pv(j - 1)) { ok = false; break; }
+    }
+    if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
+  } else {
+    /* ------------------------------------- softmax + output, one row each */
+    const int r = threadIdx.x; /* query row == TMEM lane */
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+
+    /* q row -> fp16 * scale * log2(e), in the K-major swizzled operand layout */
+    {
+      const bool valid = r < rows_valid;
+      const float *src = a.q + static_cast<long long>(tok0 + r / a.gqa) * a.q_tok_stride +
+                         static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD;
+#pragma unroll 4
+      for (int ch = 0; ch < HD / 8; ++ch) {
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) {
+          const float4 lo = __ldg(reinterpret_cast<const float4 *>(src + ch * 8));
+          const float4 hi = __ldg(reinterpret_cast<const float4 *>(src + ch * 8 + 4));
+          packed.x = pack_half2(lo.x * a.qscale, lo.y * a.qscale);
+          packed.y = pack_half2(lo.z * a.qscale, lo.w * a.qscale);
+          packed.z = pack_half2(hi.x * a.qscale, hi.y * a.qscale);
+          packed.w = pack_half2(hi.z * a.qscale, hi.w * a.qscale);
+        }
+        *reinterpret_cast<uint4 *>(smem + C::OFF_Q + (ch >> 3) * HALF_BYTES + swz128(r, ch & 7)) =
+            packed;
+      }
+      fence_async_smem();
+      mbar_arrive(bar(Q_READY));
+    }
+
+    const int lim = r < rows_valid ? min(a.pos0 + tok0 + r / a.gqa + 1, a.max_seq) : kv_end;
+    float o[HD];
+#pragma unroll
+    for (int c = 0; c < HD; ++c) o[c] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+    bool ok = true;
+
+    auto fold_output = [&](int i) -> bool { /* O = O * corr_i + O'(i) */
+      if (!mbar_wait(bar(OT_FULL + (i & 1)), (i >> 1) & 1, a.err_word, 0x221u)) return false;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + lane_base + C::COL_O + (i & 1) * HD + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c0 + e] = fmaf(o[c0 + e], corr_prev, __uint_as_float(v[e]));
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar(OT_FREE + (i & 1)));
+      return true;
+    };
+
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, a.err_word, 0x220u)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t s_addr = tmem + lane_base + C::COL_S + (j & 1) * BN;
+      const bool masked = j * BN + BN > lim_min;
+      const int lim_local = lim - j * BN; /* columns >= this are masked for this row */
+
+      /* pass 1: row maximum */
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c0, v);
+        tmem_ld_wait();
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c0 + e < lim_local) mx = fmaxf(mx, __uint_as_float(v[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = ex2(m_run - m_use);
+      m_run = m_new;
+
+      /* the tensor core must be done reading the previous P before it is overwritten */
+      if (j >= 1 && !mbar_wait(bar(P_FREE), (j - 1) & 1, a.err_word, 0x222u)) { ok = false; break; }
+
+      /* pass 2: p = 2^(s - m), row sum, fp16 P into the swizzled A-operand layout */
+      float psum = 0.f;
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c0, v);
+        tmem_ld_wait();
+        float p[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float x = ex2(__uint_as_float(v[e]) - m_use);
+          if (masked && c0 + e >= lim_local) x = 0.f;
+          p[e] = x;
+          psum += x;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 packed;
+          packed.x = pack_half2(p[8 * g + 0], p[8 * g + 1]);
+          packed.y = pack_half2(p[8 * g + 2], p[8 * g + 3]);
+          packed.z = pack_half2(p[8 * g + 4], p[8 * g + 5]);
+          packed.w = pack_half2(p[8 * g + 6], p[8 * g + 7]);
+          const int ch = c0 / 8 + g; /* 16-byte chunk index along the 128 positions */
+          *reinterpret_cast<uint4 *>(smem + C::OFF_P + (ch >> 3) * HALF_BYTES +
+                                     swz128(r, ch & 7)) = packed;
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar(S_FREE + (j & 1)));
+      fence_async_smem();
+      mbar_arrive(bar(P_READY));
+      l_run = fmaf(l_run, corr, psum);
+
+      if (j >= 1 && !fold_output(j - 1)) { ok = false; break; }
+      corr_prev = corr;
+    }
+    if (ok && n_tiles > 0) ok = fold_output(n_tiles - 1);
+    grid_launch_dependents();
+
+    if (ok && r < rows_valid) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __half *dst = a.out + (static_cast<long long>(tok0 + r / a.gqa) * a.n_q +
+                             (kvh * a.gqa + r % a.gqa)) * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 8) {
+        uint4 packed;
+        packed.x = pack_half2(o[c + 0] * inv, o[c + 1] * inv);
+        packed.y = pack_half2(o[c + 2] * inv, o[c + 3] * inv);
+        packed.z = pack_half2(o[c + 4] * inv, o[c + 5] * inv);
+        packed.w = pack_half2(o[c + 6] * inv, o[c + 7] * inv);
+        *reinterpret_cast<uint4 *>(dst + c) = packed;
+      }
+    }
+  }
+
+  /* common exit: every role gets here, then the allocating warp frees TMEM */
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int HD>
+wst_status_t launch_hd(const PrefillLaunch &P, const PrefillArgs &args, const CUtensorMap &kmap,
+                       const CUtensorMap &vmap, dim3 grid) {
+  using C = PCfg<HD>;
+  auto kern = attn_prefill_kernel<HD>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  WST_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    WST_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  C::SMEM_BYTES));
+    configured_dev = dev;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(C::THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = current_stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, kmap, vmap, args);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(WST_ERR_CUDA, "%s (launch): %s (%s)", P.name, cudaGetErrorString(e),
+                cudaGetErrorName(e));
+  return WST_OK;
+}
+
+}  // namespace
+
+bool prefill_kernel_supports(int n_q, int n_kv, int hd, int n) {
+  if (hd != 64 && hd != 128) return false;
+  if (n_kv <= 0 || n_q % n_kv != 0) return false;
+  const int gqa = n_q / n_kv;
+  if (gqa > 128) return false;
+  /* 128-row tiles pay once the chunk fills at least half of one */
+  return static_cast<long long>(n) * gqa >= 64;
+}
 
 wst_status_t launch_prefill(const PrefillLaunch &P) {
-  return fail(WST_ERR_SHAPE, "%s: prefill kernel not built", P.name);
+  DeviceFacts facts;
+  if (!device_facts(&facts)) return WST_ERR_CUDA;
+  if (facts.cc_major < 10)
+    return fail(WST_ERR_UNSUPPORTED_ARCH, "%s: this library is built for sm_100a only", P.name);
+  if (!aligned16(P.qkv) || !aligned16(P.k) || !aligned16(P.v) || !aligned16(P.out))
+    return fail(WST_ERR_INVALID_ARG, "%s: buffers must be 16-byte aligned", P.name);
+
+  PrefillArgs a{};
+  a.q = P.qkv;
+  a.q_tok_stride = P.q_tok_stride;
+  a.out = P.out;
+  a.n_q = P.n_q;
+  a.n_kv = P.n_kv;
+  a.gqa = P.n_q / P.n_kv;
+  a.pos0 = P.pos0;
+  a.n = P.n;
+  a.max_seq = P.max_seq;
+  a.tpt = 128 / a.gqa;
+  a.n_qtiles = (P.n + a.tpt - 1) / a.tpt;
+  a.qscale = P.scale * kLog2e;
+  a.err_word = device_error_word();
+  if (!a.err_word) return WST_ERR_CUDA;
+
+  CUtensorMap kmap, vmap;
+  KvMapKey key{};
+  key.d0 = static_cast<uint64_t>(P.hd);
+  key.d1 = static_cast<uint64_t>(P.max_seq);
+  key.d2 = static_cast<uint64_t>(P.n_kv);
+  key.d3 = 1;
+  key.b1 = 128;
+  key.rank = 3;
+  key.base = P.k;
+  wst_status_t st = cached_kv_tensor_map(&kmap, key);
+  if (st != WST_OK) return st;
+  key.base = P.v;
+  st = cached_kv_tensor_map(&vmap, key);
+  if (st != WST_OK) return st;
+
+  const dim3 grid(static_cast<unsigned>(a.n_qtiles), static_cast<unsigned>(P.n_kv));
+  return P.hd == 128 ? launch_hd<128>(P, a, kmap, vmap, grid)
+                     : launch_hd<64>(P, a, kmap, vmap, grid);
 }
 
 }  // namespace wst

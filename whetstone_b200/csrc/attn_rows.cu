@@ -191,8 +191,12 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   int spec = 0; /* tiles issued ahead of knowing the sequence length */
   if (!PAGED && a.cu_tokens == nullptr) {
     while (spec < NSTAGE && static_cast<long long>(split + spec * ns) * BN < a.max_seq) ++spec;
-    if (warp == C::CWARPS && lane == 0)
+    if (warp == C::CWARPS && lane == 0) {
       for (int i = 0; i < spec; ++i) issue(i);
+#ifdef WST_TRACE
+      trace_stamp(6);
+#endif
+    }
   }
 
   int tok_begin = 0, n_tok = a.n_tok;
@@ -210,22 +214,36 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   /* q -> fp16, pre-multiplied by scale*log2(e), swizzled like the K tiles.  Done
    * before the cursor value is first used, so that the two global round trips
    * (cursor, q) overlap instead of following one another. */
-  for (int idx = threadIdx.x; warp < C::CWARPS && idx < ROWS * (HD / 8); idx += C::CTHREADS) {
-    const int row = idx / (HD / 8), ch = idx % (HD / 8);
-    uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-    if (row < rows_valid) {
-      const int tok = tok_begin + tok0 + row / a.gqa;
-      const int head = kvh * a.gqa + row % a.gqa;
-      const float4 *src = reinterpret_cast<const float4 *>(
-          a.q + static_cast<long long>(tok) * a.q_tok_stride + static_cast<long long>(head) * HD +
-          ch * 8);
-      const float4 lo = __ldg(src), hi = __ldg(src + 1);
-      packed.x = pack_half2(lo.x * a.qscale, lo.y * a.qscale);
-      packed.y = pack_half2(lo.z * a.qscale, lo.w * a.qscale);
-      packed.z = pack_half2(hi.x * a.qscale, hi.y * a.qscale);
-      packed.w = pack_half2(hi.z * a.qscale, hi.w * a.qscale);
+  if (warp < C::CWARPS) {
+    constexpr int ITEMS = ROWS * (HD / 8) / C::CTHREADS; /* exact: 1, 2 or 4 */
+    static_assert(ITEMS * C::CTHREADS == ROWS * (HD / 8), "q tile must divide evenly");
+    float4 lo[ITEMS], hi[ITEMS];
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) { /* every load in flight before any is used */
+      const int idx = threadIdx.x + it * C::CTHREADS;
+      const int row = idx / (HD / 8), ch = idx % (HD / 8);
+      lo[it] = hi[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row < rows_valid) {
+        const int tok = tok_begin + tok0 + row / a.gqa;
+        const int head = kvh * a.gqa + row % a.gqa;
+        const float4 *src = reinterpret_cast<const float4 *>(
+            a.q + static_cast<long long>(tok) * a.q_tok_stride +
+            static_cast<long long>(head) * HD + ch * 8);
+        lo[it] = __ldg(src);
+        hi[it] = __ldg(src + 1);
+      }
     }
-    *reinterpret_cast<uint4 *>(qsm + (ch >> 3) * (ROWS * 128) + swz128(row, ch & 7)) = packed;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int idx = threadIdx.x + it * C::CTHREADS;
+      const int row = idx / (HD / 8), ch = idx % (HD / 8);
+      uint4 packed;
+      packed.x = pack_half2(lo[it].x * a.qscale, lo[it].y * a.qscale);
+      packed.y = pack_half2(lo[it].z * a.qscale, lo[it].w * a.qscale);
+      packed.z = pack_half2(hi[it].x * a.qscale, hi[it].y * a.qscale);
+      packed.w = pack_half2(hi[it].z * a.qscale, hi[it].w * a.qscale);
+      *reinterpret_cast<uint4 *>(qsm + (ch >> 3) * (ROWS * 128) + swz128(row, ch & 7)) = packed;
+    }
   }
 
   int pos0 = a.pos0_dev ? pos_raw + a.pos0_bias : a.pos0_val;
@@ -260,6 +278,7 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int ctid = threadIdx.x;
 
   consumer_bar(C::CTHREADS);
+  WST_STAMP(7);
 
   int lim[MT][2];
 #pragma unroll
