@@ -293,141 +293,149 @@ def bench_also(torch, args):
     def randn16(shape):
         return torch.randn(shape, generator=gen, device="cuda", dtype=torch.float16)
 
-    # ---- c1: 0.5B decode, append + attend, 24 layers
-    s = wl.QWEN25_05B
-    table = decode.RopeTable(wl.C1["max_seq"], s.head_dim, s.theta)
-    cur = decode.DeviceCursor(wl.C1["cached"])
-    caches, qkvs, outs = [], [], []
-    for _ in range(s.layers):
-        c = decode.KvCache(s.n_kv, s.n_q, s.head_dim, wl.C1["max_seq"])
-        c.k[:, : wl.C1["cached"]] = randn16((s.n_kv, wl.C1["cached"], s.head_dim))
-        c.v[:, : wl.C1["cached"]] = randn16((s.n_kv, wl.C1["cached"], s.head_dim))
-        caches.append(c)
-        qkvs.append(randn16((s.qkv_width,)).float())
-        outs.append(torch.zeros(s.n_q * s.head_dim, dtype=torch.float16, device="cuda"))
+    def want(tag):
+        return args.only in (None, tag)
 
-    def c1_step():
-        for i in range(s.layers):
-            decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cur)
-            decode.attn_decode(qkvs[i], caches[i], outs[i], s.n_q, cur)
-    sec = timed_graph(torch, c1_step, args.steps, args.warmup)
-    out["c1_decode_0.5b"] = {"us_per_layer": sec / s.layers * 1e6,
-                             "note": "append + attention, 513 rows, latency-bound"}
+    s = wl.QWEN25_05B
+
+    # ---- c1: 0.5B decode, append + attend, 24 layers
+    if want("c1"):
+        table = decode.RopeTable(wl.C1["max_seq"], s.head_dim, s.theta)
+        cur = decode.DeviceCursor(wl.C1["cached"])
+        caches, qkvs, outs = [], [], []
+        for _ in range(s.layers):
+            c = decode.KvCache(s.n_kv, s.n_q, s.head_dim, wl.C1["max_seq"])
+            c.k[:, : wl.C1["cached"]] = randn16((s.n_kv, wl.C1["cached"], s.head_dim))
+            c.v[:, : wl.C1["cached"]] = randn16((s.n_kv, wl.C1["cached"], s.head_dim))
+            caches.append(c)
+            qkvs.append(randn16((s.qkv_width,)).float())
+            outs.append(torch.zeros(s.n_q * s.head_dim, dtype=torch.float16, device="cuda"))
+
+        def c1_step():
+            for i in range(s.layers):
+                decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cur)
+                decode.attn_decode(qkvs[i], caches[i], outs[i], s.n_q, cur)
+        sec = timed_graph(torch, c1_step, args.steps, args.warmup)
+        out["c1_decode_0.5b"] = {"us_per_layer": sec / s.layers * 1e6,
+                                 "note": "append + attention, 513 rows, latency-bound"}
 
     # ---- c2: 0.5B chunked prefill, 2048 tokens = 8 chunks of 256, 24 layers
-    n, prompt = wl.C2["chunk"], wl.C2["prompt"]
-    table2 = decode.RopeTable(prompt, s.head_dim, s.theta)
-    caches = [decode.KvCache(s.n_kv, s.n_q, s.head_dim, prompt) for _ in range(s.layers)]
-    qkv_src = [randn16((prompt, s.qkv_width)).float() for _ in range(s.layers)]
-    qkv_buf = [torch.empty_like(q) for q in qkv_src]
-    outs = [torch.zeros(prompt * s.n_q * s.head_dim, dtype=torch.float16, device="cuda")
-            for _ in range(s.layers)]
-    flops_layer = sum(wl.prefill_flops(s.n_q, s.head_dim, c * n, n) for c in range(prompt // n))
+    if want("c2"):
+        n, prompt = wl.C2["chunk"], wl.C2["prompt"]
+        table2 = decode.RopeTable(prompt, s.head_dim, s.theta)
+        caches = [decode.KvCache(s.n_kv, s.n_q, s.head_dim, prompt) for _ in range(s.layers)]
+        qkv_src = [randn16((prompt, s.qkv_width)).float() for _ in range(s.layers)]
+        qkv_buf = [torch.empty_like(q) for q in qkv_src]
+        outs = [torch.zeros(prompt * s.n_q * s.head_dim, dtype=torch.float16, device="cuda")
+                for _ in range(s.layers)]
+        flops_layer = sum(wl.prefill_flops(s.n_q, s.head_dim, c * n, n) for c in range(prompt // n))
 
-    def c2_rope():
-        for i in range(s.layers):
-            qkv_buf[i].copy_(qkv_src[i])
-            for c in range(prompt // n):
-                chunk.rope_cache(qkv_buf[i][c * n:(c + 1) * n], caches[i], table2, s.n_q, c * n, n)
+        def c2_rope():
+            for i in range(s.layers):
+                qkv_buf[i].copy_(qkv_src[i])
+                for c in range(prompt // n):
+                    chunk.rope_cache(qkv_buf[i][c * n:(c + 1) * n], caches[i], table2, s.n_q, c * n, n)
 
-    def c2_attn():
-        for i in range(s.layers):
-            for c in range(prompt // n):
-                chunk.attn(qkv_buf[i][c * n:(c + 1) * n], caches[i],
-                           outs[i][c * n * s.n_q * s.head_dim:], s.n_q, c * n, n)
-    c2_rope()
-    sec = timed_graph(torch, c2_attn, min(args.steps, 50), args.warmup)
-    tf = flops_layer * s.layers / sec / 1e12
-    out["c2_prefill_0.5b"] = {"tflops": tf, "ms_per_layer": sec / s.layers * 1e3,
-                              "frac_of_tensor_peak": tf / pk["tf_burst"],
-                              "flops_per_layer": flops_layer}
-    del caches, qkv_src, qkv_buf, outs
+        def c2_attn():
+            for i in range(s.layers):
+                for c in range(prompt // n):
+                    chunk.attn(qkv_buf[i][c * n:(c + 1) * n], caches[i],
+                               outs[i][c * n * s.n_q * s.head_dim:], s.n_q, c * n, n)
+        c2_rope()
+        sec = timed_graph(torch, c2_attn, min(args.steps, 50), args.warmup)
+        tf = flops_layer * s.layers / sec / 1e12
+        out["c2_prefill_0.5b"] = {"tflops": tf, "ms_per_layer": sec / s.layers * 1e3,
+                                  "frac_of_tensor_peak": tf / pk["tf_burst"],
+                                  "flops_per_layer": flops_layer}
+        del caches, qkv_src, qkv_buf, outs
 
     # ---- c4: Qwen3-8B prefill, 4 x 8192 tokens in 512-token chunks, QK-norm; a
-    # stated subset of layers is timed (every layer does identical work)
-    s4 = wl.QWEN3_8B
-    n4, prompt4, nseq = wl.C4["chunk"], wl.C4["prompt"], wl.C4["n_seq"]
-    lay4 = args.c4_layers
-    table4 = decode.RopeTable(prompt4, s4.head_dim, s4.theta)
-    gq, gk = (1 + 0.02 * randn16((s4.head_dim,)).float()).half(), \
-             (1 + 0.02 * randn16((s4.head_dim,)).float()).half()
-    norm = decode.QkNorm(gq, gk, wl.C4["eps"])
-    caches = [[decode.KvCache(s4.n_kv, s4.n_q, s4.head_dim, prompt4) for _ in range(nseq)]
-              for _ in range(lay4)]
-    pool = [randn16((n4, s4.qkv_width)).float() for _ in range(24)]   # 302 MB > L2
-    out4 = torch.zeros(n4 * s4.n_q * s4.head_dim, dtype=torch.float16, device="cuda")
-    chunks = prompt4 // n4
-    flops4 = nseq * sum(wl.prefill_flops(s4.n_q, s4.head_dim, c * n4, n4) for c in range(chunks))
-    # populate the caches once (keys must be finite for a meaningful run)
-    for l in range(lay4):
-        for q in range(nseq):
-            for c in range(chunks):
-                buf = pool[(q * chunks + c) % len(pool)].clone()
-                chunk.rope_cache(buf, caches[l][q], table4, s4.n_q, c * n4, n4, norm)
-    rope_bytes = n4 * s4.qkv_width * 4 + n4 * s4.n_q * s4.head_dim * 4 + \
-        2 * n4 * s4.n_kv * s4.head_dim * 2
-
-    def c4_attn():
+    if want("c4"):
+        # stated subset of layers is timed (every layer does identical work)
+        s4 = wl.QWEN3_8B
+        n4, prompt4, nseq = wl.C4["chunk"], wl.C4["prompt"], wl.C4["n_seq"]
+        lay4 = args.c4_layers
+        table4 = decode.RopeTable(prompt4, s4.head_dim, s4.theta)
+        gq, gk = (1 + 0.02 * randn16((s4.head_dim,)).float()).half(), \
+                 (1 + 0.02 * randn16((s4.head_dim,)).float()).half()
+        norm = decode.QkNorm(gq, gk, wl.C4["eps"])
+        caches = [[decode.KvCache(s4.n_kv, s4.n_q, s4.head_dim, prompt4) for _ in range(nseq)]
+                  for _ in range(lay4)]
+        pool = [randn16((n4, s4.qkv_width)).float() for _ in range(24)]   # 302 MB > L2
+        out4 = torch.zeros(n4 * s4.n_q * s4.head_dim, dtype=torch.float16, device="cuda")
+        chunks = prompt4 // n4
+        flops4 = nseq * sum(wl.prefill_flops(s4.n_q, s4.head_dim, c * n4, n4) for c in range(chunks))
+        # populate the caches once (keys must be finite for a meaningful run)
         for l in range(lay4):
             for q in range(nseq):
                 for c in range(chunks):
-                    chunk.attn(pool[(q * chunks + c) % len(pool)], caches[l][q], out4, s4.n_q,
-                               c * n4, n4)
+                    buf = pool[(q * chunks + c) % len(pool)].clone()
+                    chunk.rope_cache(buf, caches[l][q], table4, s4.n_q, c * n4, n4, norm)
+        rope_bytes = n4 * s4.qkv_width * 4 + n4 * s4.n_q * s4.head_dim * 4 + \
+            2 * n4 * s4.n_kv * s4.head_dim * 2
 
-    def c4_rope():
-        for l in range(lay4):
-            for q in range(nseq):
-                for c in range(chunks):
-                    chunk.rope_cache(pool[(q * chunks + c) % len(pool)], caches[l][q], table4,
-                                     s4.n_q, c * n4, n4, norm)
-    sec = timed_graph(torch, c4_attn, max(1, min(args.steps, 20) // 4), 3)
-    tf = flops4 * lay4 / sec / 1e12
-    sec_r = timed_graph(torch, c4_rope, max(1, min(args.steps, 20) // 4), 3)
-    rope_gbs = rope_bytes * lay4 * nseq * chunks / sec_r / 1e9
-    out["c4_prefill_qwen3_8b"] = {
-        "tflops": tf, "ms_per_layer": sec / lay4 * 1e3, "frac_of_tensor_peak": tf / pk["tf_burst"],
-        "flops_per_layer": flops4, "layers_timed": lay4, "layers_in_model": s4.layers,
-        "rope_append_gbs": rope_gbs, "rope_append_frac_of_hbm": rope_gbs / pk["hbm"]}
-    del caches, pool
+        def c4_attn():
+            for l in range(lay4):
+                for q in range(nseq):
+                    for c in range(chunks):
+                        chunk.attn(pool[(q * chunks + c) % len(pool)], caches[l][q], out4, s4.n_q,
+                                   c * n4, n4)
+
+        def c4_rope():
+            for l in range(lay4):
+                for q in range(nseq):
+                    for c in range(chunks):
+                        chunk.rope_cache(pool[(q * chunks + c) % len(pool)], caches[l][q], table4,
+                                         s4.n_q, c * n4, n4, norm)
+        sec = timed_graph(torch, c4_attn, max(1, min(args.steps, 20) // 4), 3)
+        tf = flops4 * lay4 / sec / 1e12
+        sec_r = timed_graph(torch, c4_rope, max(1, min(args.steps, 20) // 4), 3)
+        rope_gbs = rope_bytes * lay4 * nseq * chunks / sec_r / 1e9
+        out["c4_prefill_qwen3_8b"] = {
+            "tflops": tf, "ms_per_layer": sec / lay4 * 1e3, "frac_of_tensor_peak": tf / pk["tf_burst"],
+            "flops_per_layer": flops4, "layers_timed": lay4, "layers_in_model": s4.layers,
+            "rope_append_gbs": rope_gbs, "rope_append_frac_of_hbm": rope_gbs / pk["hbm"]}
+        del caches, pool
 
     # ---- c5: speculative verify, 16 sequences x 5 drafts, paged cache, 28 layers
-    s5 = wl.QWEN25_7B
-    lengths = wl.c5_lengths()
-    drafts = wl.C5["drafts"]
-    table_np, n_pages = wl.c5_page_table(lengths, drafts)
-    nseq5 = len(lengths)
-    total = nseq5 * drafts
-    max_len = int(lengths.max()) + drafts
-    lay5 = args.c5_layers
-    pcs = []
-    for _ in range(lay5):
-        pc = paged.PagedKvCache(n_pages, s5.n_kv, s5.head_dim, nseq5, table_np.shape[1])
-        pc.k.copy_(randn16(pc.k.shape))
-        pc.v.copy_(randn16(pc.v.shape))
-        pc.page_table.copy_(torch.from_numpy(table_np).cuda())
-        pcs.append(pc)
-    qkv5 = [randn16((total, s5.qkv_width)).float() for _ in range(lay5)]
-    out5 = torch.zeros(total * s5.n_q * s5.head_dim, dtype=torch.float16, device="cuda")
-    pos0 = torch.from_numpy(lengths).cuda()
-    cu = torch.arange(nseq5 + 1, dtype=torch.int32, device="cuda") * drafts
-    scratch = torch.zeros(paged.verify_scratch_floats(nseq5, drafts, s5.n_q, s5.n_kv,
-                                                      s5.head_dim, max_len),
-                          dtype=torch.float32, device="cuda")
-    rtab = decode.RopeTable(max_len, s5.head_dim, s5.theta)
+    if want("c5"):
+        s5 = wl.QWEN25_7B
+        lengths = wl.c5_lengths()
+        drafts = wl.C5["drafts"]
+        table_np, n_pages = wl.c5_page_table(lengths, drafts)
+        nseq5 = len(lengths)
+        total = nseq5 * drafts
+        max_len = int(lengths.max()) + drafts
+        lay5 = args.c5_layers
+        pcs = []
+        for _ in range(lay5):
+            pc = paged.PagedKvCache(n_pages, s5.n_kv, s5.head_dim, nseq5, table_np.shape[1])
+            pc.k.copy_(randn16(pc.k.shape))
+            pc.v.copy_(randn16(pc.v.shape))
+            pc.page_table.copy_(torch.from_numpy(table_np).cuda())
+            pcs.append(pc)
+        qkv5 = [randn16((total, s5.qkv_width)).float() for _ in range(lay5)]
+        out5 = torch.zeros(total * s5.n_q * s5.head_dim, dtype=torch.float16, device="cuda")
+        pos0 = torch.from_numpy(lengths).cuda()
+        cu = torch.arange(nseq5 + 1, dtype=torch.int32, device="cuda") * drafts
+        scratch = torch.zeros(paged.verify_scratch_floats(nseq5, drafts, s5.n_q, s5.n_kv,
+                                                          s5.head_dim, max_len),
+                              dtype=torch.float32, device="cuda")
+        rtab = decode.RopeTable(max_len, s5.head_dim, s5.theta)
 
-    def c5_step():
-        for l in range(lay5):
-            paged.rope_cache(qkv5[l], pcs[l], rtab, s5.n_q, pos0, cu, total)
-            paged.attn_verify(qkv5[l], pcs[l], out5, scratch, s5.n_q, pos0, cu, total, drafts,
-                              max_len)
-    sec = timed_graph(torch, c5_step, min(args.steps, 50), args.warmup)
-    kv_bytes = int(2 * s5.n_kv * s5.head_dim * 2 * int((lengths.astype(np.int64) + drafts).sum()))
-    bytes5 = kv_bytes + total * s5.n_q * s5.head_dim * (4 + 2) + table_np.size * 4
-    gbs = bytes5 * lay5 / sec / 1e9
-    out["c5_verify_7b_paged"] = {"us_per_layer": sec / lay5 * 1e6, "hbm_gbs": gbs,
-                                 "frac_of_hbm_peak": gbs / pk["hbm"], "bytes_per_layer": bytes5,
-                                 "layers_timed": lay5, "layers_in_model": s5.layers,
-                                 "tokens_verified_per_s": total / (sec / lay5 * s5.layers)}
+        def c5_step():
+            for l in range(lay5):
+                paged.rope_cache(qkv5[l], pcs[l], rtab, s5.n_q, pos0, cu, total)
+                paged.attn_verify(qkv5[l], pcs[l], out5, scratch, s5.n_q, pos0, cu, total, drafts,
+                                  max_len)
+        sec = timed_graph(torch, c5_step, min(args.steps, 50), args.warmup)
+        kv_bytes = int(2 * s5.n_kv * s5.head_dim * 2 * int((lengths.astype(np.int64) + drafts).sum()))
+        bytes5 = kv_bytes + total * s5.n_q * s5.head_dim * (4 + 2) + table_np.size * 4
+        gbs = bytes5 * lay5 / sec / 1e9
+        out["c5_verify_7b_paged"] = {"us_per_layer": sec / lay5 * 1e6, "hbm_gbs": gbs,
+                                     "frac_of_hbm_peak": gbs / pk["hbm"], "bytes_per_layer": bytes5,
+                                     "layers_timed": lay5, "layers_in_model": s5.layers,
+                                     "tokens_verified_per_s": total / (sec / lay5 * s5.layers)}
     return out
 
 
@@ -447,10 +455,14 @@ def run_ours(args):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
 
+    if args.only not in (None, "c3"):
+        # a single secondary workload, for profiling: prints its own small JSON line
+        print(json.dumps({"only": args.only, "result": bench_also(torch, args)}))
+        return
     res = bench_c3(torch, args, rank, world, dist)
     also = None
     cpu = None
-    if world == 1 and not args.no_also:
+    if world == 1 and not args.no_also and args.only is None:
         also = bench_also(torch, args)
     if world == 1 and rank == 0 and not args.no_cpu:
         gbs, layers, spent = cpu_decode_sample()
@@ -490,6 +502,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip configs c1, c2, c4, c5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5"],
+                    help="run one workload only (c3 = the headline line without 'also')")
     ap.add_argument("--c4-layers", type=int, default=1)
     ap.add_argument("--c5-layers", type=int, default=4)
     args = ap.parse_args()

@@ -11,14 +11,16 @@
  *   softmax      128 threads, one query row each (a TMEM lane is a row, so row
  *                max and row sum need no shuffles); fp32, exp2 with scale*log2(e)
  *                folded into q; P is written back to shared memory as fp16
- *   O' = P V     tcgen05.mma (M128 x N(head_dim) x K16 steps) into a second TMEM
- *                buffer; the softmax threads fold O' into the running output they
- *                keep in registers:  O = O * 2^(m_old - m_new) + O'
+ *   O += P V     tcgen05.mma (M128 x N(head_dim) x K16 steps) accumulating in
+ *                tensor memory across tiles.  The exponent offset of a row is only
+ *                moved when its maximum grows by more than 2^8 ("lazy rescale");
+ *                then the row's owner multiplies its O lane in place
+ *                (tcgen05.ld / tcgen05.st) before the next PV is issued.
  *
  * Warp roles: warps 0-3 softmax/epilogue, warp 4 issues the MMAs (one elected
- * lane), warp 5 feeds K and V tiles with TMA.  S and O' are double-buffered in
- * tensor memory (512 columns), so QK^T of tile j+1 runs on the tensor cores
- * while the CUDA cores do the softmax of tile j.  Every wait is bounded.
+ * lane), warp 5 feeds K and V tiles with TMA.  S is double-buffered in tensor
+ * memory, so QK^T of tile j+1 runs on the tensor cores while the CUDA cores do
+ * the softmax of tile j.  Every wait is bounded.
  *
  * Semantics: cuda/chunk_ops.cu:187-264 of the engine (query j sees cache rows
  * [0, pos0 + j]; fp32 softmax state; fp16 output).
@@ -37,7 +39,6 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 template <int HD>
 struct PCfg {
-  static constexpr int BM = 128;               /* query rows per CTA */
   static constexpr int BN = 128;               /* cache positions per tile */
   static constexpr int NH = HD / 64;           /* 128-byte column halves of a K/V/Q row */
   static constexpr int HALF_BYTES = BN * 128;  /* one half of a tile: 128 rows x 128 B */
@@ -50,12 +51,12 @@ struct PCfg {
   static constexpr int OFF_V = OFF_K + NSTAGE * KV_BYTES;
   static constexpr int OFF_P = OFF_V + NSTAGE * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int NBAR = 4 * NSTAGE + 2 + 2 + 1 + 1 + 2 + 2 + 1;
+  static constexpr int NBAR = 4 * NSTAGE + 2 + 2 + 1 + 1 + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
   static constexpr int THREADS = 192;
   /* tensor-memory columns */
   static constexpr int COL_S = 0;      /* two S buffers of BN fp32 columns */
-  static constexpr int COL_O = 2 * BN; /* two O' buffers of HD fp32 columns */
+  static constexpr int COL_O = 2 * BN; /* the output accumulator, HD fp32 columns */
   static constexpr int TMEM_COLS = 512;
 };
 
@@ -89,6 +90,12 @@ __device__ __forceinline__ constexpr uint32_t umma_idesc(int m, int n, int b_mn_
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ void grid_dependency_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
@@ -113,8 +120,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   /* barrier indices */
   constexpr int K_FULL = 0, V_FULL = NSTAGE, K_EMPTY = 2 * NSTAGE, V_EMPTY = 3 * NSTAGE;
   constexpr int S_FULL = 4 * NSTAGE, S_FREE = S_FULL + 2, P_READY = S_FREE + 2;
-  constexpr int P_FREE = P_READY + 1, OT_FULL = P_FREE + 1, OT_FREE = OT_FULL + 2;
-  constexpr int Q_READY = OT_FREE + 2;
+  constexpr int PV_DONE = P_READY + 1, Q_READY = PV_DONE + 1;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + C::OFF_BAR + C::NBAR * 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,11 +137,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(S_FULL + i), 1);
       mbar_init(bar(S_FREE + i), 128);
-      mbar_init(bar(OT_FULL + i), 1);
-      mbar_init(bar(OT_FREE + i), 128);
     }
     mbar_init(bar(P_READY), 128);
-    mbar_init(bar(P_FREE), 1);
+    mbar_init(bar(PV_DONE), 1);
     mbar_init(bar(Q_READY), 128);
     mbar_init_fence();
     tma_prefetch_desc(&kmap);
@@ -192,8 +196,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       const int st = i % NSTAGE;
       if (!mbar_wait(bar(P_READY), i & 1, a.err_word, 0x211u)) return false;
       if (!mbar_wait(bar(V_FULL + st), (i / NSTAGE) & 1, a.err_word, 0x212u)) return false;
-      if (i >= 2 && !mbar_wait(bar(OT_FREE + (i & 1)), ((i >> 1) - 1) & 1, a.err_word, 0x213u))
-        return false;
       const uint32_t vb = sbase + C::OFF_V + st * KV_BYTES;
       /* Cache rows past the live data can hold any bit pattern and 0 * NaN is
        * NaN: clear them in the last tile before the tensor core reads V. */
@@ -216,11 +218,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint64_t ad = umma_desc(pb + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16);
           const uint64_t bd = umma_desc(vb + kk * 2048, HALF_BYTES);
-          umma_ss_f16(tmem + C::COL_O + (i & 1) * HD, ad, bd, idesc_pv, kk > 0);
+          umma_ss_f16(tmem + C::COL_O, ad, bd, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(bar(V_EMPTY + st));
-        umma_commit(bar(P_FREE));
-        umma_commit(bar(OT_FULL + (i & 1)));
+        umma_commit(bar(PV_DONE));
       }
       __syncwarp();
       return true;
@@ -279,110 +280,112 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     }
 
     const int lim = r < rows_valid ? min(a.pos0 + tok0 + r / a.gqa + 1, a.max_seq) : kv_end;
-    float o[HD];
-#pragma unroll
-    for (int c = 0; c < HD; ++c) o[c] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+    float m_ref = -INFINITY; /* exponent offset in use for this row (log2 units) */
+    float l_run = 0.f;
     bool ok = true;
-
-    auto fold_output = [&](int i) -> bool { /* O = O * corr_i + O'(i) */
-      if (!mbar_wait(bar(OT_FULL + (i & 1)), (i >> 1) & 1, a.err_word, 0x221u)) return false;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + C::COL_O + (i & 1) * HD + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) o[c0 + e] = fmaf(o[c0 + e], corr_prev, __uint_as_float(v[e]));
-      }
-      tc_fence_before_sync();
-      mbar_arrive(bar(OT_FREE + (i & 1)));
-      return true;
-    };
 
     for (int j = 0; j < n_tiles; ++j) {
       if (!mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, a.err_word, 0x220u)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t s_addr = tmem + lane_base + C::COL_S + (j & 1) * BN;
-      const bool masked = j * BN + BN > lim_min;
-      const int lim_local = lim - j * BN; /* columns >= this are masked for this row */
 
-      /* pass 1: row maximum */
-      float mx = -INFINITY;
+      /* the whole score row into registers, then hand the buffer back at once */
+      uint32_t sv[BN];
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c0, v);
-        tmem_ld_wait();
-        if (masked) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (c0 + e < lim_local) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        }
-      }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float corr = ex2(m_run - m_use);
-      m_run = m_new;
-
-      /* the tensor core must be done reading the previous P before it is overwritten */
-      if (j >= 1 && !mbar_wait(bar(P_FREE), (j - 1) & 1, a.err_word, 0x222u)) { ok = false; break; }
-
-      /* pass 2: p = 2^(s - m), row sum, fp16 P into the swizzled A-operand layout */
-      float psum = 0.f;
-#pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c0, v);
-        tmem_ld_wait();
-        float p[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float x = ex2(__uint_as_float(v[e]) - m_use);
-          if (masked && c0 + e >= lim_local) x = 0.f;
-          p[e] = x;
-          psum += x;
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 packed;
-          packed.x = pack_half2(p[8 * g + 0], p[8 * g + 1]);
-          packed.y = pack_half2(p[8 * g + 2], p[8 * g + 3]);
-          packed.z = pack_half2(p[8 * g + 4], p[8 * g + 5]);
-          packed.w = pack_half2(p[8 * g + 6], p[8 * g + 7]);
-          const int ch = c0 / 8 + g; /* 16-byte chunk index along the 128 positions */
-          *reinterpret_cast<uint4 *>(smem + C::OFF_P + (ch >> 3) * HALF_BYTES +
-                                     swz128(r, ch & 7)) = packed;
-        }
-      }
+      for (int c0 = 0; c0 < BN; c0 += 32)
+        tmem_ld_32x32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+      tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(bar(S_FREE + (j & 1)));
+
+      if (j * BN + BN > lim_min) { /* causal edge / end of sequence */
+        const int lim_local = lim - j * BN;
+#pragma unroll
+        for (int c = 0; c < BN; ++c)
+          if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN; c += 2)
+        mx = max3(mx, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+
+      /* Lazy rescale: keep the old offset unless some row of this warp outgrew
+       * it by more than 2^8 (p then stays <= 256, exact enough in fp16 and far
+       * from its range); the vote keeps the protocol warp-uniform. */
+      const bool grow = j == 0 || mx > m_ref + 8.f;
+      const bool warp_grow = __any_sync(0xffffffffu, grow);
+      const float m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+
+      float psum = 0.f;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) {
+        const float p = ex2(__uint_as_float(sv[c]) - m_use);
+        psum += p;
+        sv[c] = __float_as_uint(p);
+      }
+
+      /* PV of the previous tile must be finished: it reads P and writes O */
+      if (j >= 1 && !mbar_wait(bar(PV_DONE), (j - 1) & 1, a.err_word, 0x222u)) { ok = false; break; }
+
+#pragma unroll
+      for (int ch = 0; ch < BN / 8; ++ch) {
+        uint4 packed;
+        packed.x = pack_half2(__uint_as_float(sv[8 * ch + 0]), __uint_as_float(sv[8 * ch + 1]));
+        packed.y = pack_half2(__uint_as_float(sv[8 * ch + 2]), __uint_as_float(sv[8 * ch + 3]));
+        packed.z = pack_half2(__uint_as_float(sv[8 * ch + 4]), __uint_as_float(sv[8 * ch + 5]));
+        packed.w = pack_half2(__uint_as_float(sv[8 * ch + 6]), __uint_as_float(sv[8 * ch + 7]));
+        *reinterpret_cast<uint4 *>(smem + C::OFF_P + (ch >> 3) * HALF_BYTES + swz128(r, ch & 7)) =
+            packed;
+      }
+
+      if (warp_grow && j > 0) { /* move this warp's rows of O to the new offsets */
+        tc_fence_after_sync();
+        const float factor = ex2(m_ref - m_use); /* 1 for rows that did not move */
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + lane_base + C::COL_O + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
+          tmem_st_32x32(tmem + lane_base + C::COL_O + c0, v);
+        }
+        tmem_st_wait();
+        l_run *= factor;
+      }
+      m_ref = m_new;
+      l_run += psum;
+
+      tc_fence_before_sync();
       fence_async_smem();
       mbar_arrive(bar(P_READY));
-      l_run = fmaf(l_run, corr, psum);
-
-      if (j >= 1 && !fold_output(j - 1)) { ok = false; break; }
-      corr_prev = corr;
     }
-    if (ok && n_tiles > 0) ok = fold_output(n_tiles - 1);
     grid_launch_dependents();
 
-    if (ok && r < rows_valid) {
+    if (ok && n_tiles > 0)
+      ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, a.err_word, 0x223u);
+    if (ok) {
+      tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __half *dst = a.out + (static_cast<long long>(tok0 + r / a.gqa) * a.n_q +
                              (kvh * a.gqa + r % a.gqa)) * HD;
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
-        uint4 packed;
-        packed.x = pack_half2(o[c + 0] * inv, o[c + 1] * inv);
-        packed.y = pack_half2(o[c + 2] * inv, o[c + 3] * inv);
-        packed.z = pack_half2(o[c + 4] * inv, o[c + 5] * inv);
-        packed.w = pack_half2(o[c + 6] * inv, o[c + 7] * inv);
-        *reinterpret_cast<uint4 *>(dst + c) = packed;
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + lane_base + C::COL_O + c0, v);
+        tmem_ld_wait();
+        if (r < rows_valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 packed;
+            packed.x = pack_half2(__uint_as_float(v[8 * g + 0]) * inv, __uint_as_float(v[8 * g + 1]) * inv);
+            packed.y = pack_half2(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv);
+            packed.z = pack_half2(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv);
+            packed.w = pack_half2(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv);
+            *reinterpret_cast<uint4 *>(dst + c0 + 8 * g) = packed;
+          }
+        }
       }
     }
   }

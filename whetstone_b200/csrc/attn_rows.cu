@@ -191,12 +191,10 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   int spec = 0; /* tiles issued ahead of knowing the sequence length */
   if (!PAGED && a.cu_tokens == nullptr) {
     while (spec < NSTAGE && static_cast<long long>(split + spec * ns) * BN < a.max_seq) ++spec;
-    if (warp == C::CWARPS && lane == 0) {
-      for (int i = 0; i < spec; ++i) issue(i);
+    if (warp == C::CWARPS && lane < spec) issue(lane); /* one lane per stage, all at once */
 #ifdef WST_TRACE
-      trace_stamp(6);
+    if (warp == C::CWARPS && lane == 0) trace_stamp(6);
 #endif
-    }
   }
 
   int tok_begin = 0, n_tok = a.n_tok;
