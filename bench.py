@@ -232,7 +232,7 @@ def bench_c3(torch, args, rank, world, dist):
         def step():
             for i in range(layers):
                 decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
-                dist.all_gather_into_tensor(gathered[i], mine[i])
+                dist.all_gather_into_tensor(gathered[i].view(-1, s.head_dim + 2), mine[i])
                 decode.attn_merge_partials(gathered[i], outs[i], s.n_q, s.head_dim)
 
     with ClockSampler(torch.cuda.current_device()) as clk:
@@ -261,7 +261,7 @@ def bench_c3(torch, args, rank, world, dist):
                 if rank == world - 1:   # the shard that owns the newest position appends
                     decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cursor)
                 decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
-                dist.all_gather_into_tensor(gathered[i], mine[i])
+                dist.all_gather_into_tensor(gathered[i].view(-1, s.head_dim + 2), mine[i])
                 decode.attn_merge_partials(gathered[i], outs[i], s.n_q, s.head_dim)
                 host_out[i].copy_(outs[i], non_blocking=True)
     sec_e2e = timed_graph(torch, step_e2e, args.steps, args.warmup, dist if world > 1 else None)
