@@ -304,10 +304,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
         for (int c = 0; c < BN; ++c)
           if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
       }
-      float mx = -INFINITY;
+      /* four independent chains: one warp per scheduler has nothing else to
+       * hide the latency of a 64-deep dependent max (or add) chain behind */
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < BN; c += 2)
-        mx = max3(mx, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+      for (int c = 0; c < BN; c += 8)
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
 
       /* Lazy rescale: keep the old offset unless some row of this warp outgrew
        * it by more than 2^8 (p then stays <= 256, exact enough in fp16 and far
@@ -317,13 +322,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       const float m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
 
-      float psum = 0.f;
+      float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        const float p = ex2(__uint_as_float(sv[c]) - m_use);
-        psum += p;
-        sv[c] = __float_as_uint(p);
-      }
+      for (int c = 0; c < BN; c += 8)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float p = ex2(__uint_as_float(sv[c + k]) - m_use);
+          ps8[k] += p;
+          sv[c + k] = __float_as_uint(p);
+        }
+      const float psum = ((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7]));
 
       /* PV of the previous tile must be finished: it reads P and writes O */
       if (j >= 1 && !mbar_wait(bar(PV_DONE), (j - 1) & 1, a.err_word, 0x222u)) { ok = false; break; }
