@@ -1,0 +1,410 @@
+/* The reference's kernel tests for the attention path, written against the C++
+ * host layer (whetstone_b200/host/whetstone_host.hpp) the way the originals are
+ * written against the Rust one:
+ *
+ *   crates/whetstone-kernels/tests/decode_kernels.rs:91-410
+ *   crates/whetstone-kernels/tests/chunk_kernels.rs:263-360
+ *
+ * Same closed-form inputs, same LCG, same tolerances.  Prints one line per test
+ * and exits non-zero if any failed; needs a B200.
+ */
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "whetstone_host.hpp"
+
+using namespace whetstone;
+
+/* ---- fp16 <-> fp32 on the host (round to nearest even), like the `half` crate */
+static uint16_t f32_to_f16(float f) {
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  const uint32_t sign = (x >> 16) & 0x8000u;
+  int32_t exp = static_cast<int32_t>((x >> 23) & 0xff) - 127 + 15;
+  uint32_t man = x & 0x7fffffu;
+  if (((x >> 23) & 0xff) == 0xff) return static_cast<uint16_t>(sign | 0x7c00u | (man ? 0x200u : 0));
+  if (exp >= 31) return static_cast<uint16_t>(sign | 0x7c00u);
+  if (exp <= 0) {
+    if (exp < -10) return static_cast<uint16_t>(sign);
+    man |= 0x800000u;
+    const int shift = 14 - exp;
+    uint32_t half = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1), mid = 1u << (shift - 1);
+    if (rem > mid || (rem == mid && (half & 1))) ++half;
+    return static_cast<uint16_t>(sign | half);
+  }
+  uint32_t half = (static_cast<uint32_t>(exp) << 10) | (man >> 13);
+  const uint32_t rem = man & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (half & 1))) ++half;
+  return static_cast<uint16_t>(sign | half);
+}
+static float f16_to_f32(uint16_t h) {
+  const uint32_t sign = (h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1f, man = h & 0x3ffu, x;
+  if (exp == 0) {
+    if (man == 0) {
+      x = sign;
+    } else {
+      int e = -1;
+      do { ++e; man <<= 1; } while (!(man & 0x400u));
+      x = sign | ((127 - 15 - e) << 23) | ((man & 0x3ffu) << 13);
+    }
+  } else if (exp == 31) {
+    x = sign | 0x7f800000u | (man << 13);
+  } else {
+    x = sign | ((exp - 15 + 127) << 23) | (man << 13);
+  }
+  float f;
+  std::memcpy(&f, &x, 4);
+  return f;
+}
+static std::vector<uint16_t> f16v(const std::vector<float> &v) {
+  std::vector<uint16_t> o(v.size());
+  for (size_t i = 0; i < v.size(); ++i) o[i] = f32_to_f16(v[i]);
+  return o;
+}
+static std::vector<float> from_f16(const std::vector<uint16_t> &v) {
+  std::vector<float> o(v.size());
+  for (size_t i = 0; i < v.size(); ++i) o[i] = f16_to_f32(v[i]);
+  return o;
+}
+
+/* chunk_kernels.rs:31-39 */
+static std::vector<float> noise(size_t n, uint64_t seed) {
+  uint64_t s = seed * 6364136223846793005ull + 1ull;
+  std::vector<float> o(n);
+  for (auto &x : o) {
+    s = s * 6364136223846793005ull + 1442695040888963407ull;
+    x = static_cast<float>(s >> 33) / static_cast<float>(1ull << 31) - 1.0f;
+  }
+  return o;
+}
+
+struct Failure { std::string what; };
+#define REQUIRE(cond, msg) do { if (!(cond)) throw Failure{std::string(msg)}; } while (0)
+
+static std::vector<float> seq(size_t n, int mod, float div) {
+  std::vector<float> v(n);
+  for (size_t i = 0; i < n; ++i) v[i] = static_cast<float>(i % mod) / div - 1.0f;
+  return v;
+}
+static std::vector<float> cat3(const std::vector<float> &a, const std::vector<float> &b,
+                               const std::vector<float> &c) {
+  std::vector<float> o(a);
+  o.insert(o.end(), b.begin(), b.end());
+  o.insert(o.end(), c.begin(), c.end());
+  return o;
+}
+
+static void rope_uses_the_half_rotation_layout() {
+  const size_t n_q = 2, n_kv = 1, hd = 64, max_seq = 8, pos = 3;
+  const double theta = 1e6;
+  auto q = seq(n_q * hd, 31, 15.f), k = seq(n_kv * hd, 23, 11.f), v = seq(n_kv * hd, 19, 9.f);
+  RopeTable table(max_seq, hd, theta);
+  KvCache cache(n_kv, n_q, hd, max_seq);
+  auto qd = DeviceBuffer<float>::from_slice(cat3(q, k, v));
+  DeviceCursor cursor(static_cast<int32_t>(pos));
+  decode::rope_cache(qd, cache, table, n_q, cursor);
+  auto got = qd.to_vec();
+  const size_t half = hd / 2;
+  for (size_t h = 0; h < n_q; ++h)
+    for (size_t j = 0; j < half; ++j) {
+      const double inv = std::pow(theta, -static_cast<double>(j) / half);
+      const double s = std::sin(pos * inv), c = std::cos(pos * inv);
+      const double x1 = q[h * hd + j], x2 = q[h * hd + j + half];
+      REQUIRE(std::fabs(got[h * hd + j] - static_cast<float>(x1 * c - x2 * s)) < 1e-5f, "lo");
+      REQUIRE(std::fabs(got[h * hd + j + half] - static_cast<float>(x2 * c + x1 * s)) < 1e-5f, "hi");
+    }
+}
+
+static void qk_norm_is_per_head_and_precedes_the_rotation() {
+  const size_t n_q = 4, n_kv = 2, hd = 64, max_seq = 8, pos = 5;
+  const double theta = 1e6;
+  const float eps = 1e-6f;
+  auto q = seq(n_q * hd, 31, 15.f), k = seq(n_kv * hd, 23, 11.f), v = seq(n_kv * hd, 19, 9.f);
+  std::vector<float> gq(hd), gk(hd);
+  for (size_t i = 0; i < hd; ++i) {
+    gq[i] = 0.5f + static_cast<float>(i % 7) * 0.1f;
+    gk[i] = 1.5f - static_cast<float>(i % 5) * 0.2f;
+  }
+  auto gqd = DeviceBuffer<uint16_t>::from_slice(f16v(gq));
+  auto gkd = DeviceBuffer<uint16_t>::from_slice(f16v(gk));
+  RopeTable table(max_seq, hd, theta);
+  KvCache cache(n_kv, n_q, hd, max_seq);
+  auto qd = DeviceBuffer<float>::from_slice(cat3(q, k, v));
+  DeviceCursor cursor(static_cast<int32_t>(pos));
+  QkNorm norm{&gqd, &gkd, eps};
+  decode::rope_cache(qd, cache, table, n_q, cursor, &norm);
+  auto got = qd.to_vec();
+  const size_t half = hd / 2;
+  auto reference = [&](const std::vector<float> &src, const std::vector<float> &gain, size_t h,
+                       size_t j, float &w1, float &w2) {
+    double ms = 0;
+    for (size_t i = 0; i < hd; ++i) ms += static_cast<double>(src[h * hd + i]) * src[h * hd + i];
+    const double inv = 1.0 / std::sqrt(ms / hd + eps);
+    const double f = std::pow(theta, -static_cast<double>(j) / half);
+    const double s = std::sin(pos * f), c = std::cos(pos * f);
+    const double x1 = src[h * hd + j] * inv * f16_to_f32(f32_to_f16(gain[j]));
+    const double x2 = src[h * hd + j + half] * inv * f16_to_f32(f32_to_f16(gain[j + half]));
+    w1 = static_cast<float>(x1 * c - x2 * s);
+    w2 = static_cast<float>(x2 * c + x1 * s);
+  };
+  for (size_t h = 0; h < n_q; ++h)
+    for (size_t j = 0; j < half; ++j) {
+      float w1, w2;
+      reference(q, gq, h, j, w1, w2);
+      const float tol = 1e-4f * std::fmax(std::fmax(std::fabs(w1), std::fabs(w2)), 1.0f);
+      REQUIRE(std::fabs(got[h * hd + j] - w1) < tol, "q lo");
+      REQUIRE(std::fabs(got[h * hd + j + half] - w2) < tol, "q hi");
+    }
+  auto kc = from_f16(cache.keys().to_vec());
+  auto vc = from_f16(cache.values().to_vec());
+  for (size_t h = 0; h < n_kv; ++h) {
+    const size_t slot = (h * max_seq + pos) * hd;
+    for (size_t j = 0; j < half; ++j) {
+      float w1, w2;
+      reference(k, gk, h, j, w1, w2);
+      REQUIRE(std::fabs(kc[slot + j] - w1) < 3e-3f, "k lo");
+      REQUIRE(std::fabs(kc[slot + j + half] - w2) < 3e-3f, "k hi");
+    }
+    for (size_t j = 0; j < hd; ++j)
+      REQUIRE(std::fabs(vc[slot + j] - v[h * hd + j]) < 3e-3f, "v was modified");
+  }
+}
+
+static void qk_norm_with_unit_gain_on_a_unit_rms_head_is_the_identity() {
+  const size_t n_q = 2, n_kv = 1, hd = 64, max_seq = 8, pos = 2;
+  std::vector<float> q(n_q * hd), k(n_kv * hd);
+  for (size_t i = 0; i < q.size(); ++i) q[i] = i % 3 == 0 ? -1.f : 1.f;
+  for (size_t i = 0; i < k.size(); ++i) k[i] = i % 5 == 0 ? -1.f : 1.f;
+  auto v = seq(n_kv * hd, 19, 9.f);
+  auto ones = f16v(std::vector<float>(hd, 1.f));
+  auto gqd = DeviceBuffer<uint16_t>::from_slice(ones);
+  auto gkd = DeviceBuffer<uint16_t>::from_slice(ones);
+  RopeTable table(max_seq, hd, 1e6);
+  const auto qkv = cat3(q, k, v);
+  DeviceCursor cursor(static_cast<int32_t>(pos));
+  KvCache cache_off(n_kv, n_q, hd, max_seq), cache_on(n_kv, n_q, hd, max_seq);
+  auto off = DeviceBuffer<float>::from_slice(qkv);
+  decode::rope_cache(off, cache_off, table, n_q, cursor);
+  auto on = DeviceBuffer<float>::from_slice(qkv);
+  QkNorm norm{&gqd, &gkd, 0.f};
+  decode::rope_cache(on, cache_on, table, n_q, cursor, &norm);
+  auto a = off.to_vec(), b = on.to_vec();
+  for (size_t i = 0; i < a.size(); ++i) REQUIRE(std::fabs(a[i] - b[i]) < 1e-6f, "norm-on differs");
+}
+
+static void attention_over_one_position_returns_that_value() {
+  const size_t n_q = 14, n_kv = 2, hd = 64, max_seq = 32;
+  RopeTable table(max_seq, hd, 1e6);
+  KvCache cache(n_kv, n_q, hd, max_seq);
+  auto q = seq(n_q * hd, 29, 14.f), k = seq(n_kv * hd, 13, 6.f), v = seq(n_kv * hd, 17, 8.f);
+  auto qd = DeviceBuffer<float>::from_slice(cat3(q, k, v));
+  DeviceCursor cursor(0);
+  decode::rope_cache(qd, cache, table, n_q, cursor);
+  auto out = DeviceBuffer<uint16_t>::zeros(n_q * hd);
+  decode::attn_decode(qd, cache, out, n_q, cursor);
+  auto got = from_f16(out.to_vec());
+  for (size_t h = 0; h < n_q; ++h) {
+    const size_t kv = h / (n_q / n_kv);
+    for (size_t d = 0; d < hd; ++d)
+      REQUIRE(std::fabs(got[h * hd + d] - f16_to_f32(f32_to_f16(v[kv * hd + d]))) < 2e-3f, "value");
+  }
+}
+
+static void attention_over_two_positions_matches_an_explicit_softmax() {
+  const size_t n_q = 2, n_kv = 1, hd = 64, max_seq = 16, half = hd / 2;
+  const double theta = 1e6;
+  KvCache cache(n_kv, n_q, hd, max_seq);
+  RopeTable table(max_seq, hd, theta);
+  std::vector<std::vector<float>> ks, vs;
+  for (size_t p = 0; p < 2; ++p) {
+    std::vector<float> k(hd), v(hd);
+    for (size_t i = 0; i < hd; ++i) {
+      k[i] = static_cast<float>((i + 7 * p) % 11) / 5.f - 1.f;
+      v[i] = static_cast<float>((i + 3 * p) % 7) / 3.f - 1.f;
+    }
+    auto qd = DeviceBuffer<float>::from_slice(cat3(std::vector<float>(n_q * hd, 0.f), k, v));
+    DeviceCursor cursor(static_cast<int32_t>(p));
+    decode::rope_cache(qd, cache, table, n_q, cursor);
+    std::vector<float> kr(k);
+    for (size_t j = 0; j < half; ++j) {
+      const double inv = std::pow(theta, -static_cast<double>(j) / half);
+      const double s = std::sin(p * inv), c = std::cos(p * inv);
+      kr[j] = static_cast<float>(k[j] * c - k[j + half] * s);
+      kr[j + half] = static_cast<float>(k[j + half] * c + k[j] * s);
+    }
+    ks.push_back(kr);
+    vs.push_back(v);
+  }
+  std::vector<float> q(n_q * hd);
+  for (size_t i = 0; i < q.size(); ++i) q[i] = static_cast<float>(i % 5) / 2.f - 1.f;
+  auto qd = DeviceBuffer<float>::from_slice(q);
+  auto out = DeviceBuffer<uint16_t>::zeros(n_q * hd);
+  DeviceCursor at(1);
+  decode::attn_decode(qd, cache, out, n_q, at);
+  auto got = from_f16(out.to_vec());
+  const double scale = 1.0 / std::sqrt(static_cast<double>(hd));
+  for (size_t h = 0; h < n_q; ++h) {
+    double s[2];
+    for (size_t p = 0; p < 2; ++p) {
+      s[p] = 0;
+      for (size_t d = 0; d < hd; ++d)
+        s[p] += static_cast<double>(q[h * hd + d]) * f16_to_f32(f32_to_f16(ks[p][d]));
+      s[p] *= scale;
+    }
+    const double m = std::fmax(s[0], s[1]), e0 = std::exp(s[0] - m), e1 = std::exp(s[1] - m);
+    for (size_t d = 0; d < hd; ++d) {
+      const double want = (e0 * f16_to_f32(f32_to_f16(vs[0][d])) + e1 * f16_to_f32(f32_to_f16(vs[1][d]))) / (e0 + e1);
+      REQUIRE(std::fabs(got[h * hd + d] - want) < 3e-3, "two positions");
+    }
+  }
+}
+
+static void close(float got, float want, float tol, const char *what) {
+  REQUIRE(std::fabs(got - want) <= tol * std::fmax(std::fabs(want), 1.0f), what);
+}
+
+static void rope_and_attention_chunk_match_sequential_decode() {
+  const size_t n_q = 14, n_kv = 2, hd = 64, max_seq = 128, n = 9;
+  const size_t stride = (n_q + 2 * n_kv) * hd;
+  RopeTable rope(max_seq, hd, 1e6);
+  const auto all = noise(stride * n, 303);
+  KvCache cache_a(n_kv, n_q, hd, max_seq);
+  auto qkv_c = DeviceBuffer<float>::from_slice(all);
+  chunk::rope_cache(qkv_c, cache_a, rope, n_q, 0, n);
+  auto out_c = DeviceBuffer<uint16_t>::zeros(n * n_q * hd);
+  chunk::attn(qkv_c, cache_a, out_c, n_q, 0, n);
+  auto got = from_f16(out_c.to_vec());
+  KvCache cache_b(n_kv, n_q, hd, max_seq);
+  DeviceCursor cursor(0);
+  for (size_t j = 0; j < n; ++j) {
+    cursor.set(static_cast<int32_t>(j));
+    auto q1 = DeviceBuffer<float>::from_slice(std::vector<float>(all.begin() + j * stride, all.begin() + (j + 1) * stride));
+    decode::rope_cache(q1, cache_b, rope, n_q, cursor);
+    auto o1 = DeviceBuffer<uint16_t>::zeros(n_q * hd);
+    decode::attn_decode(q1, cache_b, o1, n_q, cursor);
+    auto want = from_f16(o1.to_vec());
+    for (size_t i = 0; i < n_q * hd; ++i) close(got[j * n_q * hd + i], want[i], 4e-3f, "attention token");
+  }
+}
+
+static void attention_chunk_resumes_mid_cache() {
+  const size_t n_q = 14, n_kv = 2, hd = 64, max_seq = 128, prefix = 20, n = 5;
+  const size_t stride = (n_q + 2 * n_kv) * hd;
+  RopeTable rope(max_seq, hd, 1e6);
+  const auto all = noise(stride * (prefix + n), 404);
+  KvCache cache_a(n_kv, n_q, hd, max_seq), cache_b(n_kv, n_q, hd, max_seq);
+  DeviceCursor cursor(0);
+  auto row = [&](size_t j) { return std::vector<float>(all.begin() + j * stride, all.begin() + (j + 1) * stride); };
+  for (size_t j = 0; j < prefix; ++j) {
+    cursor.set(static_cast<int32_t>(j));
+    for (KvCache *c : {&cache_a, &cache_b}) {
+      auto q1 = DeviceBuffer<float>::from_slice(row(j));
+      decode::rope_cache(q1, *c, rope, n_q, cursor);
+    }
+  }
+  auto qkv_c = DeviceBuffer<float>::from_slice(std::vector<float>(all.begin() + prefix * stride, all.end()));
+  chunk::rope_cache(qkv_c, cache_a, rope, n_q, prefix, n);
+  auto out_c = DeviceBuffer<uint16_t>::zeros(n * n_q * hd);
+  chunk::attn(qkv_c, cache_a, out_c, n_q, prefix, n);
+  auto got = from_f16(out_c.to_vec());
+  for (size_t j = 0; j < n; ++j) {
+    cursor.set(static_cast<int32_t>(prefix + j));
+    auto q1 = DeviceBuffer<float>::from_slice(row(prefix + j));
+    decode::rope_cache(q1, cache_b, rope, n_q, cursor);
+    auto o1 = DeviceBuffer<uint16_t>::zeros(n_q * hd);
+    decode::attn_decode(q1, cache_b, o1, n_q, cursor);
+    auto want = from_f16(o1.to_vec());
+    for (size_t i = 0; i < n_q * hd; ++i) close(got[j * n_q * hd + i], want[i], 4e-3f, "resumed attention token");
+  }
+}
+
+static void shape_errors_are_typed_and_launch_nothing() {
+  KvCache cache(2, 14, 64, 32);
+  RopeTable table(32, 64, 1e6);
+  auto qkv = DeviceBuffer<float>::zeros(17 * 64);
+  DeviceCursor cursor(0);
+  bool threw = false;
+  try {
+    decode::rope_cache(qkv, cache, table, 14, cursor);
+  } catch (const Error &e) {
+    threw = e.kind() == Error::Kind::Shape && std::string(e.what()).find("should be (14 + 2*2) * 64") != std::string::npos;
+  }
+  REQUIRE(threw, "wrong qkv length must raise a Shape error");
+  threw = false;
+  auto ok = DeviceBuffer<float>::zeros(4 * 18 * 64);
+  try {
+    chunk::rope_cache(ok, cache, table, 14, 30, 4);
+  } catch (const Error &e) {
+    threw = e.kind() == Error::Kind::Shape;
+  }
+  REQUIRE(threw, "chunk past the cache must raise a Shape error");
+  REQUIRE(wst_attn_decode(nullptr, nullptr, nullptr, nullptr, nullptr, 14, 2, 64, nullptr, 32, 0.125f) == WST_ERR_INVALID_ARG, "null pointers");
+}
+
+static void decode_step_replays_as_a_graph() {
+  /* src/decode.rs:543-607 / engine.rs:357-393: append + attend + advance captured once */
+  const size_t n_q = 14, n_kv = 2, hd = 64, max_seq = 64;
+  RopeTable table(max_seq, hd, 1e6);
+  KvCache cache(n_kv, n_q, hd, max_seq);
+  auto qkv = DeviceBuffer<float>::from_slice(noise((n_q + 2 * n_kv) * hd, 7));
+  auto out = DeviceBuffer<uint16_t>::zeros(n_q * hd);
+  DeviceCursor cursor(0);
+  auto step = [&] {
+    decode::rope_cache(qkv, cache, table, n_q, cursor);
+    decode::attn_decode(qkv, cache, out, n_q, cursor);
+    cursor.advance(max_seq);
+  };
+  Graph g = Graph::capture(step);   /* one eager step + one captured (not launched) */
+  REQUIRE(cursor.get() == 1, "capture must not execute");
+  for (int i = 0; i < 5; ++i) g.launch();
+  check(wst_stream_sync());
+  REQUIRE(cursor.get() == 6, "five replays advance the cursor five times");
+  auto o = from_f16(out.to_vec());
+  for (float x : o) REQUIRE(std::isfinite(x), "finite output");
+}
+
+int main() {
+  int32_t devices = 0;
+  if (wst_device_count(&devices) != WST_OK || devices == 0) {
+    std::printf("skip: no CUDA device\n");
+    return 0;
+  }
+  struct Case { const char *name; std::function<void()> fn; };
+  const Case cases[] = {
+      {"rope_uses_the_half_rotation_layout", rope_uses_the_half_rotation_layout},
+      {"qk_norm_is_per_head_and_precedes_the_rotation", qk_norm_is_per_head_and_precedes_the_rotation},
+      {"qk_norm_with_unit_gain_on_a_unit_rms_head_is_the_identity", qk_norm_with_unit_gain_on_a_unit_rms_head_is_the_identity},
+      {"attention_over_one_position_returns_that_value", attention_over_one_position_returns_that_value},
+      {"attention_over_two_positions_matches_an_explicit_softmax", attention_over_two_positions_matches_an_explicit_softmax},
+      {"rope_and_attention_chunk_match_sequential_decode", rope_and_attention_chunk_match_sequential_decode},
+      {"attention_chunk_resumes_mid_cache", attention_chunk_resumes_mid_cache},
+      {"shape_errors_are_typed_and_launch_nothing", shape_errors_are_typed_and_launch_nothing},
+      {"decode_step_replays_as_a_graph", decode_step_replays_as_a_graph},
+  };
+  int failed = 0;
+  for (const auto &c : cases) {
+    try {
+      c.fn();
+      std::printf("ok   %s\n", c.name);
+    } catch (const Failure &f) {
+      std::printf("FAIL %s: %s\n", c.name, f.what.c_str());
+      ++failed;
+    } catch (const std::exception &e) {
+      std::printf("FAIL %s: exception %s\n", c.name, e.what());
+      ++failed;
+    }
+  }
+  uint32_t code = 0;
+  if (wst_b200_device_error(&code) != WST_OK || code != 0) {
+    std::printf("FAIL device watchdog word = 0x%x\n", code);
+    ++failed;
+  }
+  std::printf("%d failed\n", failed);
+  return failed ? 1 : 0;
+}
