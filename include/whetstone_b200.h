@@ -79,6 +79,32 @@ WST_API wst_status_t wst_attn_decode_partial(const void *q, const void *k_cache,
 WST_API wst_status_t wst_attn_merge_partials(const void *parts, void *out, int32_t n_parts,
                                      int32_t n_q, int32_t head_dim);
 
+/* --------------------------------------------- decode without a scratch buffer */
+
+/* wst_attn_decode for callers that cannot provide (or allocate) the split
+ * scratch: same arguments minus `partials`, same result.  It has no counterpart
+ * in the engine's library.  Hosts that gave all their device memory to a pool
+ * at start-up, or that are in a phase where they may not call cudaMalloc, still
+ * need the sequence split to fill the GPU; here the slices' partial results go
+ * to an array built into the library (2 MiB of device memory per GPU, held from
+ * load to exit).
+ *
+ *   - Nothing is allocated or freed, on any call.
+ *   - Limit: n_q * min(64, ceil(max_seq / 64)) * (head_dim + 4) floats must not
+ *     exceed 524288 (e.g. 28 heads of 128 at any context: 236544).  Larger shapes
+ *     are refused with WST_ERR_INVALID_ARG; use wst_attn_decode for them.
+ *   - The first call on a device looks up the array's device address; make that
+ *     call an ordinary one, before any stream capture.
+ *   - All calls share the one array and it keeps whatever the last call left in
+ *     it.  Nothing in it has to start at zero -- every slot is written before
+ *     it is read within a call -- but two calls that overlap on the GPU (two
+ *     streams, two threads) would write over each other: run them one after
+ *     the other. */
+WST_API wst_status_t wst_attn_decode_noscratch(const void *q, const void *k_cache,
+                                               const void *v_cache, void *out, int32_t n_q,
+                                               int32_t n_kv, int32_t head_dim, const void *pos,
+                                               int32_t max_seq, float scale);
+
 /* ------------------------------------------------ paged cache, many sequences */
 
 /* Paged KV pool: [n_pool_pages][n_kv][page_size][head_dim] half for K and for V.

@@ -99,6 +99,37 @@ wst_status_t decode_common(const char *who, const void *q, const void *k_cache,
   return launch_simple(L);
 }
 
+/* Split scratch for wst_attn_decode_noscratch.  It lives in the library's own
+ * device image instead of coming from the caller: some hosts may not allocate
+ * device memory at all once they are running -- an engine that handed its whole
+ * budget to a pool at start-up, or code that is inside a region (a capture, a
+ * latency-critical loop) where cudaMalloc is off limits -- and the engine's
+ * decode entry point cannot run without a scratch buffer.  2 MiB per GPU that
+ * loads the library, held until the process exits.
+ *
+ * The array's NAME is only a host-side handle.  Its device address is asked for
+ * once per device, with that device current (cudaGetSymbolAddress), and that
+ * address is what the kernels receive. */
+constexpr long long kBuiltinScratchFloats = 512ll * 1024;
+static __device__ __align__(256) float g_builtin_scratch[kBuiltinScratchFloats];
+
+wst_status_t builtin_scratch(float **out) {
+  static float *ptrs[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  WST_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(WST_ERR_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_builtin_scratch);
+    if (e != cudaSuccess) return cuda_fail("cudaGetSymbolAddress(built-in scratch)", e);
+    ptrs[dev] = static_cast<float *>(p);
+  }
+  *out = ptrs[dev];
+  return WST_OK;
+}
+
 __global__ void merge_partials_kernel(const float *__restrict__ parts, __half *__restrict__ out,
                                       int n_parts, int n_q, int hd) {
   const int head = blockIdx.x;
@@ -146,6 +177,27 @@ extern "C" wst_status_t wst_attn_decode(const void *q, const void *k_cache, cons
   if (st != WST_OK) return st;
   return decode_common("wst_attn_decode", q, k_cache, v_cache, partials, out, n_q, n_kv,
                        head_dim, pos, max_seq, scale, false);
+}
+
+extern "C" wst_status_t wst_attn_decode_noscratch(const void *q, const void *k_cache,
+                                                  const void *v_cache, void *out, int32_t n_q,
+                                                  int32_t n_kv, int32_t head_dim,
+                                                  const void *pos, int32_t max_seq,
+                                                  float scale) {
+  WST_CHECK_ARG(q && k_cache && v_cache && out && pos, "wst_attn_decode_noscratch: null pointer");
+  wst_status_t st = check_decode_shape("wst_attn_decode_noscratch", n_q, n_kv, head_dim, max_seq);
+  if (st != WST_OK) return st;
+  const long long need = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 4);
+  if (need > kBuiltinScratchFloats)
+    return fail(WST_ERR_INVALID_ARG,
+                "wst_attn_decode_noscratch: this shape needs %lld floats of split scratch, the "
+                "built-in array holds %lld; use wst_attn_decode with a caller buffer",
+                need, kBuiltinScratchFloats);
+  float *scratch = nullptr;
+  st = builtin_scratch(&scratch);
+  if (st != WST_OK) return st;
+  return decode_common("wst_attn_decode_noscratch", q, k_cache, v_cache, scratch, out, n_q,
+                       n_kv, head_dim, pos, max_seq, scale, false);
 }
 
 extern "C" wst_status_t wst_attn_decode_partial(const void *q, const void *k_cache,
