@@ -27,6 +27,11 @@ def fill_bits(t: torch.Tensor, bits: int) -> None:
     t.view(torch.int16).fill_(np.array(bits, dtype=np.uint16).astype(np.int16).item())
 
 
+def fill_rows_from(t: torch.Tensor, bits: int, start: int) -> None:
+    """Same for rows [start:] of every head of a [heads][rows][dim] cache."""
+    t.view(torch.int16)[:, start:] = np.array(bits, dtype=np.uint16).astype(np.int16).item()
+
+
 def bits16(t: torch.Tensor) -> np.ndarray:
     return host(t.view(torch.int16)).view(np.uint16)
 
@@ -39,6 +44,20 @@ def assert_close_per_head(got: np.ndarray, want: np.ndarray, what: str,
     mx, cs = orc.error_stats(got, want)
     assert mx <= max_abs, f"{what}: max abs error {mx:.3e} > {max_abs}"
     assert cs >= min_cos, f"{what}: min cosine {cs:.6f} < {min_cos}"
+
+
+def assert_k_cache_matches(got_bits: np.ndarray, want_f64: np.ndarray, what: str) -> None:
+    """K rows against fp16(oracle).  The device rotates in fp32 from an fp32 table,
+    so a value may land on the neighbouring fp16 number (1 ulp); where the two
+    rotation terms cancel, the fp32 rounding of the terms (~1e-7 absolute) can be
+    several ulps of a tiny result, so an absolute 3e-6 is accepted there.  (The
+    reference's own test allows 3e-3 absolute, decode_kernels.rs:219.)"""
+    want_bits = want_f64.astype(np.float16).view(np.uint16)
+    ulp = f16_ulp_distance(got_bits, want_bits)
+    diff = np.abs(got_bits.view(np.float16).astype(np.float64) - want_f64)
+    bad = (ulp > 1) & (diff > 3e-6)
+    assert not bad.any(), (f"{what}: {int(bad.sum())} K values off; worst {diff[bad].max():.3e} "
+                           f"({int(ulp[bad].max())} ulp)")
 
 
 def f16_ulp_distance(a_bits: np.ndarray, b_bits: np.ndarray) -> np.ndarray:
