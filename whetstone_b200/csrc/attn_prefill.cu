@@ -6,11 +6,17 @@
  * query heads that share the KV head -- and walks the visible prefix in tiles of
  * 128 cache positions.  Per tile:
  *
- *   S  = Q K^T   tcgen05.mma (M128 x N128 x K16 steps), fp16 operands from
- *                128-byte-swizzled shared memory, fp32 accumulator in TENSOR MEMORY
+ *   S  = Q K^T   tcgen05.mma (M128 x N128 x K16 steps): Q is the A operand and
+ *                lives in TENSOR MEMORY for the whole kernel (written once with
+ *                tcgen05.st), K tiles are the B operand in 128-byte-swizzled
+ *                shared memory, the fp32 accumulator is in tensor memory
  *   softmax      128 threads, one query row each (a TMEM lane is a row, so row
  *                max and row sum need no shuffles); fp32, exp2 with scale*log2(e)
- *                folded into q; P is written back to shared memory as fp16
+ *                folded into q; P goes back into tensor memory as fp16 pairs
+ *                (tcgen05.st) and is the A operand of the next MMA, so neither Q
+ *                nor P ever crosses shared memory: per tile only K and V do
+ *                (TMA in, tensor core out), which is what shared-memory
+ *                bandwidth can sustain at the MMA rate
  *   O += P V     tcgen05.mma (M128 x N(head_dim) x K16 steps) accumulating in
  *                tensor memory across tiles.  The exponent offset of a row is only
  *                moved when its maximum grows by more than 2^8 ("lazy rescale");
@@ -42,22 +48,21 @@ struct PCfg {
   static constexpr int BN = 128;               /* cache positions per tile */
   static constexpr int NH = HD / 64;           /* 128-byte column halves of a K/V/Q row */
   static constexpr int HALF_BYTES = BN * 128;  /* one half of a tile: 128 rows x 128 B */
-  static constexpr int Q_BYTES = NH * HALF_BYTES;
   static constexpr int KV_BYTES = NH * HALF_BYTES;
-  static constexpr int P_BYTES = 2 * HALF_BYTES; /* 128 rows x 128 positions fp16 */
-  static constexpr int NSTAGE = HD == 128 ? 2 : 3;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int NSTAGE = HD == 128 ? 3 : 4;
+  static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + NSTAGE * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + NSTAGE * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_BAR = OFF_V + NSTAGE * KV_BYTES;
   static constexpr int NBAR = 4 * NSTAGE + 2 + 2 + 1 + 1 + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
   static constexpr int THREADS = 192;
   /* tensor-memory columns */
   static constexpr int COL_S = 0;      /* two S buffers of BN fp32 columns */
   static constexpr int COL_O = 2 * BN; /* the output accumulator, HD fp32 columns */
+  static constexpr int COL_P = 384;    /* P as the A operand of PV: 128 fp16 = 64 columns */
+  static constexpr int COL_Q = 448;    /* Q as the A operand of QK^T: HD fp16 = HD/2 columns */
   static constexpr int TMEM_COLS = 512;
+  static_assert(COL_O + HD <= COL_P && COL_Q + HD / 2 <= TMEM_COLS, "tensor-memory map");
 };
 
 struct PrefillArgs {
@@ -213,12 +218,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       tc_fence_after_sync();
       if (lane == 0) {
-        const uint32_t pb = sbase + C::OFF_P;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t ad = umma_desc(pb + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16);
           const uint64_t bd = umma_desc(vb + kk * 2048, HALF_BYTES);
-          umma_ss_f16(tmem + C::COL_O, ad, bd, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_f16(tmem + C::COL_O, tmem + C::COL_P + kk * 8, bd, idesc_pv,
+                      (i > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(bar(V_EMPTY + st));
         umma_commit(bar(PV_DONE));
@@ -236,12 +240,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       tc_fence_after_sync();
       if (lane == 0) {
-        const uint32_t qb = sbase + C::OFF_Q;
         const uint32_t kb = sbase + C::OFF_K + st * KV_BYTES;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_ss_f16(tmem + C::COL_S + (j & 1) * BN, umma_desc(qb + off, 16),
+          umma_ts_f16(tmem + C::COL_S + (j & 1) * BN, tmem + C::COL_Q + ks * 8,
                       umma_desc(kb + off, 16), idesc_qk, ks > 0);
         }
         umma_commit(bar(K_EMPTY + st));
@@ -256,26 +259,25 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     const int r = threadIdx.x; /* query row == TMEM lane */
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
 
-    /* q row -> fp16 * scale * log2(e), in the K-major swizzled operand layout */
+    /* q row -> fp16 * scale * log2(e), two per 32-bit column of this row's TMEM lane */
     {
       const bool valid = r < rows_valid;
       const float *src = a.q + static_cast<long long>(tok0 + r / a.gqa) * a.q_tok_stride +
                          static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD;
-#pragma unroll 4
-      for (int ch = 0; ch < HD / 8; ++ch) {
-        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-        if (valid) {
-          const float4 lo = __ldg(reinterpret_cast<const float4 *>(src + ch * 8));
-          const float4 hi = __ldg(reinterpret_cast<const float4 *>(src + ch * 8 + 4));
-          packed.x = pack_half2(lo.x * a.qscale, lo.y * a.qscale);
-          packed.y = pack_half2(lo.z * a.qscale, lo.w * a.qscale);
-          packed.z = pack_half2(hi.x * a.qscale, hi.y * a.qscale);
-          packed.w = pack_half2(hi.z * a.qscale, hi.w * a.qscale);
+#pragma unroll
+      for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+        uint32_t packed[32];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (valid) f = __ldg(reinterpret_cast<const float4 *>(src + 2 * (c0 + e)));
+          packed[e] = pack_half2(f.x * a.qscale, f.y * a.qscale);
+          packed[e + 1] = pack_half2(f.z * a.qscale, f.w * a.qscale);
         }
-        *reinterpret_cast<uint4 *>(smem + C::OFF_Q + (ch >> 3) * HALF_BYTES + swz128(r, ch & 7)) =
-            packed;
+        tmem_st_32x32(tmem + lane_base + C::COL_Q + c0, packed);
       }
-      fence_async_smem();
+      tmem_st_wait();
+      tc_fence_before_sync();
       mbar_arrive(bar(Q_READY));
     }
 
@@ -337,15 +339,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       if (j >= 1 && !mbar_wait(bar(PV_DONE), (j - 1) & 1, a.err_word, 0x222u)) { ok = false; break; }
 
 #pragma unroll
-      for (int ch = 0; ch < BN / 8; ++ch) {
-        uint4 packed;
-        packed.x = pack_half2(__uint_as_float(sv[8 * ch + 0]), __uint_as_float(sv[8 * ch + 1]));
-        packed.y = pack_half2(__uint_as_float(sv[8 * ch + 2]), __uint_as_float(sv[8 * ch + 3]));
-        packed.z = pack_half2(__uint_as_float(sv[8 * ch + 4]), __uint_as_float(sv[8 * ch + 5]));
-        packed.w = pack_half2(__uint_as_float(sv[8 * ch + 6]), __uint_as_float(sv[8 * ch + 7]));
-        *reinterpret_cast<uint4 *>(smem + C::OFF_P + (ch >> 3) * HALF_BYTES + swz128(r, ch & 7)) =
-            packed;
-      }
+      for (int c = 0; c < BN / 2; ++c)
+        sv[c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
+#pragma unroll
+      for (int c0 = 0; c0 < BN / 2; c0 += 32)
+        tmem_st_32x32(tmem + lane_base + C::COL_P + c0,
+                      *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
 
       if (warp_grow && j > 0) { /* move this warp's rows of O to the new offsets */
         tc_fence_after_sync();
@@ -365,8 +364,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       m_ref = m_new;
       l_run += psum;
 
+      tmem_st_wait();
       tc_fence_before_sync();
-      fence_async_smem();
       mbar_arrive(bar(P_READY));
     }
     grid_launch_dependents();
