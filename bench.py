@@ -359,41 +359,43 @@ def bench_also(torch, args):
         gq, gk = (1 + 0.02 * randn16((s4.head_dim,)).float()).half(), \
                  (1 + 0.02 * randn16((s4.head_dim,)).float()).half()
         norm = decode.QkNorm(gq, gk, wl.C4["eps"])
-        caches = [[decode.KvCache(s4.n_kv, s4.n_q, s4.head_dim, prompt4) for _ in range(nseq)]
-                  for _ in range(lay4)]
-        pool = [randn16((n4, s4.qkv_width)).float() for _ in range(24)]   # 302 MB > L2
-        out4 = torch.zeros(n4 * s4.n_q * s4.head_dim, dtype=torch.float16, device="cuda")
+        # one batched cache [4][8][8192][128] per layer; every chunk step is ONE launch
+        # over the 4 sequences (wst_rope_cache_chunk_batch / wst_attn_chunk_batch)
+        caches = [chunk.KvCacheBatch(nseq, s4.n_kv, s4.head_dim, prompt4) for _ in range(lay4)]
+        pool = [randn16((nseq, n4, s4.qkv_width)).float() for _ in range(8)]   # 403 MB > L2
+        out4 = torch.zeros(nseq * n4 * s4.n_q * s4.head_dim, dtype=torch.float16, device="cuda")
         chunks = prompt4 // n4
-        flops4 = nseq * sum(wl.prefill_flops(s4.n_q, s4.head_dim, c * n4, n4) for c in range(chunks))
+        starts = [torch.full((nseq,), c * n4, dtype=torch.int32, device="cuda")
+                  for c in range(chunks)]
+        flops4 = nseq * sum(wl.prefill_flops(s4.n_q, s4.head_dim, c * n4, n4)
+                            for c in range(chunks))
         # populate the caches once (keys must be finite for a meaningful run)
         for l in range(lay4):
-            for q in range(nseq):
-                for c in range(chunks):
-                    buf = pool[(q * chunks + c) % len(pool)].clone()
-                    chunk.rope_cache(buf, caches[l][q], table4, s4.n_q, c * n4, n4, norm)
+            for c in range(chunks):
+                buf = pool[c % len(pool)].clone()
+                chunk.rope_cache_batch(buf, caches[l], table4, s4.n_q, starts[c], n4, norm)
         rope_bytes = n4 * s4.qkv_width * 4 + n4 * s4.n_q * s4.head_dim * 4 + \
             2 * n4 * s4.n_kv * s4.head_dim * 2
 
         def c4_attn():
             for l in range(lay4):
-                for q in range(nseq):
-                    for c in range(chunks):
-                        chunk.attn(pool[(q * chunks + c) % len(pool)], caches[l][q], out4, s4.n_q,
-                                   c * n4, n4)
+                for c in range(chunks):
+                    chunk.attn_batch(pool[c % len(pool)], caches[l], out4, s4.n_q, starts[c], n4)
 
         def c4_rope():
             for l in range(lay4):
-                for q in range(nseq):
-                    for c in range(chunks):
-                        chunk.rope_cache(pool[(q * chunks + c) % len(pool)], caches[l][q], table4,
-                                         s4.n_q, c * n4, n4, norm)
+                for c in range(chunks):
+                    chunk.rope_cache_batch(pool[c % len(pool)], caches[l], table4, s4.n_q,
+                                           starts[c], n4, norm)
         sec = timed_graph(torch, c4_attn, max(1, min(args.steps, 20) // 4), 3)
         tf = flops4 * lay4 / sec / 1e12
         sec_r = timed_graph(torch, c4_rope, max(1, min(args.steps, 20) // 4), 3)
         rope_gbs = rope_bytes * lay4 * nseq * chunks / sec_r / 1e9
         out["c4_prefill_qwen3_8b"] = {
-            "tflops": tf, "ms_per_layer": sec / lay4 * 1e3, "frac_of_tensor_peak": tf / pk["tf_burst"],
+            "tflops": tf, "ms_per_layer": sec / lay4 * 1e3,
+            "frac_of_tensor_peak": tf / pk["tf_burst"],
             "flops_per_layer": flops4, "layers_timed": lay4, "layers_in_model": s4.layers,
+            "launch": "one batched launch per chunk step (4 sequences)",
             "rope_append_gbs": rope_gbs, "rope_append_frac_of_hbm": rope_gbs / pk["hbm"]}
         del caches, pool
 

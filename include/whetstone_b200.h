@@ -105,6 +105,30 @@ WST_API wst_status_t wst_attn_decode_noscratch(const void *q, const void *k_cach
                                                int32_t n_kv, int32_t head_dim, const void *pos,
                                                int32_t max_seq, float scale);
 
+/* ---------------------------------------- several sequences, contiguous caches */
+
+/* The chunk entry points for a batch of n_seq sequences that each process n
+ * tokens in this step (batched chunked prefill).  One launch covers the whole
+ * batch, so the GPU is filled by (sequence, KV head, query tile) units instead of
+ * one sequence's worth.  No counterpart in the engine, which runs one sequence.
+ *   qkv       [n_seq][n][(n_q + 2*n_kv) * head_dim] float
+ *   k_cache   [n_seq][n_kv][max_seq][head_dim] half (v_cache the same)
+ *   seq_pos0  device int32 [n_seq]: cache row of each sequence's first token;
+ *             rows are clamped to the cache like the single-sequence kernels do
+ *   out       [n_seq][n][n_q * head_dim] half
+ * Token j of sequence s sees rows [0, seq_pos0[s] + j] of its own cache. */
+WST_API wst_status_t wst_rope_cache_chunk_batch(void *qkv, void *k_cache, void *v_cache,
+                                                const void *cos_tab, const void *sin_tab,
+                                                const void *seq_pos0, int32_t n_seq, int32_t n_q,
+                                                int32_t n_kv, int32_t head_dim, int32_t n,
+                                                int32_t max_seq, const void *q_norm_w,
+                                                const void *k_norm_w, float eps);
+WST_API wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
+                                          const void *v_cache, void *out, const void *seq_pos0,
+                                          int32_t n_seq, int32_t n_q, int32_t n_kv,
+                                          int32_t head_dim, int32_t n, int32_t max_seq,
+                                          float scale);
+
 /* ------------------------------------------------ paged cache, many sequences */
 
 /* Paged KV pool: [n_pool_pages][n_kv][page_size][head_dim] half for K and for V.

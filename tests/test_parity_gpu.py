@@ -242,6 +242,59 @@ def test_chunk_matches_oracle(chunk_kernel_choice, n_q, n_kv, hd, pos0, n):
                           f"chunk {n_q}/{n_kv}/{hd} pos0 {pos0} n {n}")
 
 
+def _cache_view(batch, s_idx):
+    """One sequence of a KvCacheBatch as a single-sequence KvCache (no copy)."""
+    view = decode.KvCache.__new__(decode.KvCache)
+    view.k, view.v = batch.k[s_idx], batch.v[s_idx]
+    view.n_kv, view.head_dim, view.max_seq = batch.n_kv, batch.head_dim, batch.max_seq
+    view.partials = torch.zeros(1, dtype=torch.float32, device="cuda")
+    return view
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(14, 2, 64), (32, 8, 128)])
+@pytest.mark.parametrize("n", [5, 130])
+def test_chunk_batch_matches_oracle(chunk_kernel_choice, n_q, n_kv, hd, n):
+    """Three sequences at different positions in one launch (batched chunked prefill
+    and its few-token form), against the oracle per sequence."""
+    if chunk_kernel_choice == 1:
+        pytest.skip("the batched entry point has no portable-kernel form")
+    rng = np.random.default_rng(n * 3 + hd)
+    theta, starts = 1e6, [0, 100, 517]
+    n_seq, max_seq = len(starts), 700
+    width = (n_q + 2 * n_kv) * hd
+    batch = chunk.KvCacheBatch(n_seq, n_kv, hd, max_seq)
+    fill_bits(batch.k, NAN16)
+    fill_bits(batch.v, NAN16)
+    table = decode.RopeTable(max_seq, hd, theta)
+    prefix = []
+    for s_idx, p0 in enumerate(starts):
+        pre = workloads.f16_values(rng, (p0, width)) if p0 else np.zeros((0, width), np.float32)
+        if p0:
+            chunk.rope_cache(dev(pre), _cache_view(batch, s_idx), table, n_q, 0, p0)
+        prefix.append(pre)
+    qkv = workloads.f16_values(rng, (n_seq, n, width))
+    qd = dev(qkv)
+    pos0 = dev(np.asarray(starts, np.int32))
+    chunk.rope_cache_batch(qd, batch, table, n_q, pos0, n)
+    out = torch.zeros(n_seq * n * n_q * hd, dtype=torch.float16, device="cuda")
+    chunk.attn_batch(qd, batch, out, n_q, pos0, n)
+    got = host(out).astype(np.float64).reshape(n_seq, n, n_q, hd)
+    for s_idx, p0 in enumerate(starts):
+        k_all = np.zeros((p0 + n, n_kv, hd))
+        v_all = np.zeros((p0 + n, n_kv, hd))
+        if p0:
+            _, k_all[:p0], v_all[:p0] = orc.rope_append(prefix[s_idx], np.arange(p0), n_q, n_kv, hd,
+                                                        theta)
+        qr, k_all[p0:], v_all[p0:] = orc.rope_append(qkv[s_idx], p0 + np.arange(n), n_q, n_kv, hd,
+                                                     theta)
+        want = orc.attention_blocked(qr, k_all, v_all, p0 + 1 + np.arange(n))
+        assert_close_per_head(got[s_idx], want, f"batch seq {s_idx} pos0 {p0} n {n}")
+        vb = bits16(batch.v[s_idx])
+        assert np.array_equal(vb[:, p0:p0 + n],
+                              v_all[p0:].transpose(1, 0, 2).astype(np.float16).view(np.uint16))
+        assert np.all(vb[:, p0 + n:] == NAN16)
+
+
 def test_chunk_argument_errors_launch_nothing():
     cache = decode.KvCache(2, 14, 64, 32)
     qkv = torch.zeros(4 * 18 * 64, dtype=torch.float32, device="cuda")

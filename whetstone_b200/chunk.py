@@ -57,4 +57,57 @@ def attn(qkv: torch.Tensor, cache: KvCache, out: torch.Tensor, n_q: int, pos0: i
                              cache.n_kv, hd, pos0, n, cache.max_seq, scale))
 
 
-__all__ = ["rope_cache", "attn"]
+class KvCacheBatch:
+    """Caches of n_seq sequences in one allocation, ``[n_seq][n_kv][max_seq][head_dim]``
+    fp16 for K and V: what the batched chunk entry points take."""
+
+    def __init__(self, n_seq: int, n_kv: int, head_dim: int, max_seq: int,
+                 device: torch.device | str = "cuda"):
+        shape = (n_seq, n_kv, max_seq, head_dim)
+        self.k = torch.zeros(shape, dtype=torch.float16, device=device)
+        self.v = torch.zeros(shape, dtype=torch.float16, device=device)
+        self.n_seq, self.n_kv, self.head_dim, self.max_seq = n_seq, n_kv, head_dim, max_seq
+
+
+def rope_cache_batch(qkv: torch.Tensor, cache: KvCacheBatch, table: RopeTable, n_q: int,
+                     seq_pos0: torch.Tensor, n: int, qk_norm: QkNorm | None = None) -> None:
+    """rope_cache for n tokens of each of the batch's sequences (qkv [n_seq][n][width])."""
+    hd = cache.head_dim
+    stride = (n_q + 2 * cache.n_kv) * hd
+    _require_cuda(qkv, "rope_cache_chunk_batch: qkv", torch.float32)
+    _require_cuda(seq_pos0, "rope_cache_chunk_batch: seq_pos0", torch.int32)
+    if qkv.numel() < cache.n_seq * n * stride:
+        raise ShapeError(5, f"rope_cache_chunk_batch: qkv[{qkv.numel()}] needs "
+                            f"{cache.n_seq} * {n} * {stride}")
+    if seq_pos0.numel() != cache.n_seq:
+        raise ShapeError(5, "rope_cache_chunk_batch: seq_pos0 needs one entry per sequence")
+    if table.half_dim != hd // 2 or table.max_seq < cache.max_seq:
+        raise ShapeError(5, "rope_cache_chunk_batch: rotary table does not match the cache geometry")
+    if qk_norm is not None:
+        qk_norm.check(hd)
+    qw, kw, eps = norm_ptrs(qk_norm)
+    use_torch_stream()
+    check(lib.wst_rope_cache_chunk_batch(_ptr(qkv), _ptr(cache.k), _ptr(cache.v), _ptr(table.cos),
+                                         _ptr(table.sin), _ptr(seq_pos0), cache.n_seq, n_q,
+                                         cache.n_kv, hd, n, cache.max_seq, qw, kw, eps))
+
+
+def attn_batch(qkv: torch.Tensor, cache: KvCacheBatch, out: torch.Tensor, n_q: int,
+               seq_pos0: torch.Tensor, n: int) -> None:
+    """Causal attention of n tokens per sequence; out [n_seq][n][n_q*head_dim] fp16."""
+    hd = cache.head_dim
+    stride = (n_q + 2 * cache.n_kv) * hd
+    _require_cuda(qkv, "attn_chunk_batch: qkv", torch.float32)
+    _require_cuda(out, "attn_chunk_batch: out", torch.float16)
+    _require_cuda(seq_pos0, "attn_chunk_batch: seq_pos0", torch.int32)
+    if qkv.numel() < cache.n_seq * n * stride:
+        raise ShapeError(5, f"attn_chunk_batch: qkv[{qkv.numel()}] needs {cache.n_seq} * {n} * {stride}")
+    if out.numel() < cache.n_seq * n * n_q * hd:
+        raise ShapeError(5, f"attn_chunk_batch: out[{out.numel()}] needs {cache.n_seq} * {n} * {n_q} * {hd}")
+    use_torch_stream()
+    check(lib.wst_attn_chunk_batch(_ptr(qkv), _ptr(cache.k), _ptr(cache.v), _ptr(out),
+                                   _ptr(seq_pos0), cache.n_seq, n_q, cache.n_kv, hd, n,
+                                   cache.max_seq, 1.0 / math.sqrt(hd)))
+
+
+__all__ = ["rope_cache", "attn", "KvCacheBatch", "rope_cache_batch", "attn_batch"]

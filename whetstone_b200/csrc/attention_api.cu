@@ -287,6 +287,70 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
   return launch_rows(L);
 }
 
+extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
+                                             const void *v_cache, void *out,
+                                             const void *seq_pos0, int32_t n_seq, int32_t n_q,
+                                             int32_t n_kv, int32_t head_dim, int32_t n,
+                                             int32_t max_seq, float scale) {
+  WST_CHECK_ARG(qkv && k_cache && v_cache && out && seq_pos0, "wst_attn_chunk_batch: null pointer");
+  WST_CHECK_ARG(n_q > 0 && n_kv > 0 && head_dim > 0 && n > 0 && n_seq > 0,
+                "wst_attn_chunk_batch: non-positive shape");
+  WST_CHECK_ARG(n_q % n_kv == 0,
+                "wst_attn_chunk_batch: query heads must be a multiple of key/value heads");
+  WST_CHECK_ARG(n <= max_seq, "wst_attn_chunk_batch: chunk longer than the cache");
+  if (!rows_kernel_supports(n_q, n_kv, head_dim, k_cache, v_cache) || !aligned16(qkv) ||
+      !aligned16(out))
+    return fail(WST_ERR_SHAPE,
+                "wst_attn_chunk_batch: needs head_dim 64 or 128, at most 64 query heads per KV "
+                "head and 16-byte aligned buffers");
+  const long long q_stride = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
+  const int choice = g_kernel_choice.load();
+  bool use_prefill = choice != 2 && prefill_kernel_supports(n_q, n_kv, head_dim, n);
+  if (use_prefill && choice != 3) {
+    const int gqa = n_q / n_kv;
+    use_prefill = (static_cast<long long>(n) * gqa + 127) / 128 * n_kv * n_seq >= 32;
+  }
+  if (use_prefill) {
+    PrefillLaunch P;
+    P.name = "wst_attn_chunk_batch";
+    P.qkv = static_cast<const float *>(qkv);
+    P.q_tok_stride = q_stride;
+    P.q_seq_stride = q_stride * n;
+    P.k = static_cast<const __half *>(k_cache);
+    P.v = static_cast<const __half *>(v_cache);
+    P.out = static_cast<__half *>(out);
+    P.out_seq_stride = static_cast<long long>(n) * n_q * head_dim;
+    P.pos0_dev = static_cast<const int32_t *>(seq_pos0);
+    P.n_seq = n_seq;
+    P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
+    P.n = n; P.max_seq = max_seq; P.scale = scale;
+    return launch_prefill(P);
+  }
+  /* few tokens per sequence: the split-KV kernel, one grid over all sequences.
+   * Token t of sequence s sits at row s*n + t of qkv and out. */
+  RowsLaunch L;
+  L.name = "wst_attn_chunk_batch";
+  L.q = static_cast<const float *>(qkv);
+  L.q_tok_stride = q_stride;
+  L.k = static_cast<const __half *>(k_cache);
+  L.v = static_cast<const __half *>(v_cache);
+  L.max_seq = max_seq;
+  L.pos0_dev = static_cast<const int32_t *>(seq_pos0);
+  L.clamp_pos0_nonneg = true;
+  L.n_seq = n_seq;
+  L.n_tok = n;
+  L.tok_seq_stride = n;
+  L.n_q = n_q;
+  L.n_kv = n_kv;
+  L.hd = head_dim;
+  L.scale = scale;
+  L.max_len = max_seq;
+  L.out = out;
+  L.scratch = chunk_workspace();
+  L.scratch_floats = L.scratch ? kChunkWorkspaceFloats : 0;
+  return launch_rows(L);
+}
+
 extern "C" int64_t wst_attn_verify_scratch_floats(int32_t n_seq, int32_t max_tokens_per_seq,
                                                   int32_t n_q, int32_t n_kv, int32_t head_dim,
                                                   int32_t max_len) {

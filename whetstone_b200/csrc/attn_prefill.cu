@@ -67,8 +67,10 @@ struct PCfg {
 
 struct PrefillArgs {
   const float *q;
-  long long q_tok_stride;
+  long long q_tok_stride, q_seq_stride;
   __half *out;
+  long long out_seq_stride;
+  const int32_t *pos0_dev; /* per-sequence chunk start, or null: pos0 for all */
   int n_q, n_kv, gqa;
   int pos0, n, max_seq;
   int tpt;      /* tokens per 128-row tile = 128 / gqa */
@@ -131,6 +133,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qtile = a.n_qtiles - 1 - blockIdx.x; /* longest prefixes first */
   const int kvh = blockIdx.y;
+  const int seq = blockIdx.z;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) {
@@ -162,11 +165,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   grid_dependency_wait();
 
   /* rows of this tile: row r = (token tok0 + r / gqa, head kvh*gqa + r % gqa) */
+  const int pos0 = a.pos0_dev ? max(a.pos0_dev[seq], 0) : a.pos0;
+  const int plane = seq * a.n_kv + kvh; /* which [max_seq][hd] slab of the cache */
   const int tok0 = qtile * a.tpt;
   const int ntok = min(a.tpt, a.n - tok0);
   const int rows_valid = ntok * a.gqa;
-  const int kv_end = min(a.pos0 + tok0 + ntok, a.max_seq); /* live cache rows this tile sees */
-  const int lim_min = min(a.pos0 + tok0 + 1, a.max_seq);
+  const int kv_end = min(pos0 + tok0 + ntok, a.max_seq); /* live cache rows this tile sees */
+  const int lim_min = min(pos0 + tok0 + 1, a.max_seq);
   const int n_tiles = (kv_end + BN - 1) / BN;
 
   if (warp == 5) {
@@ -180,14 +185,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
         for (int h = 0; h < NH; ++h)
           tma_load_3d(sbase + C::OFF_K + st * KV_BYTES + h * HALF_BYTES, &kmap, bar(K_FULL + st),
-                      h * 64, j * BN, kvh);
+                      h * 64, j * BN, plane);
         if (j >= NSTAGE && !mbar_wait(bar(V_EMPTY + st), (round - 1) & 1, a.err_word, 0x202u))
           break;
         mbar_arrive_expect_tx(bar(V_FULL + st), KV_BYTES);
 #pragma unroll
         for (int h = 0; h < NH; ++h)
           tma_load_3d(sbase + C::OFF_V + st * KV_BYTES + h * HALF_BYTES, &vmap, bar(V_FULL + st),
-                      h * 64, j * BN, kvh);
+                      h * 64, j * BN, plane);
       }
     }
   } else if (warp == 4) {
@@ -262,7 +267,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     /* q row -> fp16 * scale * log2(e), two per 32-bit column of this row's TMEM lane */
     {
       const bool valid = r < rows_valid;
-      const float *src = a.q + static_cast<long long>(tok0 + r / a.gqa) * a.q_tok_stride +
+      const float *src = a.q + seq * a.q_seq_stride +
+                         static_cast<long long>(tok0 + r / a.gqa) * a.q_tok_stride +
                          static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD / 2; c0 += 32) {
@@ -281,7 +287,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       mbar_arrive(bar(Q_READY));
     }
 
-    const int lim = r < rows_valid ? min(a.pos0 + tok0 + r / a.gqa + 1, a.max_seq) : kv_end;
+    const int lim = r < rows_valid ? min(pos0 + tok0 + r / a.gqa + 1, a.max_seq) : kv_end;
     float m_ref = -INFINITY; /* exponent offset in use for this row (log2 units) */
     float l_run = 0.f;
     bool ok = true;
@@ -375,7 +381,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     if (ok) {
       tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __half *dst = a.out + (static_cast<long long>(tok0 + r / a.gqa) * a.n_q +
+      __half *dst = a.out + seq * a.out_seq_stride +
+                    (static_cast<long long>(tok0 + r / a.gqa) * a.n_q +
                              (kvh * a.gqa + r % a.gqa)) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -461,7 +468,10 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   PrefillArgs a{};
   a.q = P.qkv;
   a.q_tok_stride = P.q_tok_stride;
+  a.q_seq_stride = P.q_seq_stride;
   a.out = P.out;
+  a.out_seq_stride = P.out_seq_stride;
+  a.pos0_dev = P.pos0_dev;
   a.n_q = P.n_q;
   a.n_kv = P.n_kv;
   a.gqa = P.n_q / P.n_kv;
@@ -478,7 +488,7 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   KvMapKey key{};
   key.d0 = static_cast<uint64_t>(P.hd);
   key.d1 = static_cast<uint64_t>(P.max_seq);
-  key.d2 = static_cast<uint64_t>(P.n_kv);
+  key.d2 = static_cast<uint64_t>(P.n_kv) * P.n_seq;
   key.d3 = 1;
   key.b1 = 128;
   key.rank = 3;
@@ -489,7 +499,8 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   st = cached_kv_tensor_map(&vmap, key);
   if (st != WST_OK) return st;
 
-  const dim3 grid(static_cast<unsigned>(a.n_qtiles), static_cast<unsigned>(P.n_kv));
+  const dim3 grid(static_cast<unsigned>(a.n_qtiles), static_cast<unsigned>(P.n_kv),
+                  static_cast<unsigned>(P.n_seq));
   return P.hd == 128 ? launch_hd<128>(P, a, kmap, vmap, grid)
                      : launch_hd<64>(P, a, kmap, vmap, grid);
 }

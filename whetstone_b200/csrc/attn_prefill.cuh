@@ -16,6 +16,11 @@ struct PrefillLaunch {
   __half *out = nullptr;       /* [n][n_q*hd] */
   int n_q = 0, n_kv = 0, hd = 0;
   int pos0 = 0, n = 0, max_seq = 0;
+  /* batch: n_seq sequences with caches [n_seq][n_kv][max_seq][hd], qkv and out
+   * strided per sequence, chunk starts in device memory (null = pos0 for all) */
+  int n_seq = 1;
+  long long q_seq_stride = 0, out_seq_stride = 0;
+  const int32_t *pos0_dev = nullptr;
   float scale = 1.f;
   const char *name = "attention";
 };

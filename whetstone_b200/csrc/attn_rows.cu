@@ -62,7 +62,7 @@ struct RowsArgs {
   const int32_t *pos0_dev;
   int pos0_bias, clamp_nonneg, pos0_val;
   const int32_t *cu_tokens;
-  int n_tok;
+  int n_tok, tok_seq_stride;
   int n_q, n_kv, gqa, max_seq;
   float qscale; /* scale * log2(e): scores live in log2 units */
   float *scratch;
@@ -197,7 +197,7 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
 #endif
   }
 
-  int tok_begin = 0, n_tok = a.n_tok;
+  int tok_begin = s * a.tok_seq_stride, n_tok = a.n_tok;
   if (a.cu_tokens) {
     tok_begin = a.cu_tokens[s];
     n_tok = a.cu_tokens[s + 1] - tok_begin;
@@ -542,7 +542,7 @@ struct MergeArgs {
   const float *scratch;
   void *out;
   const int32_t *cu_tokens;
-  int n_tok, n_q, n_kv, gqa;
+  int n_tok, tok_seq_stride, n_q, n_kv, gqa;
   int n_splits, n_rowblk, tpb, rows_cap;
   int partial_out;
 };
@@ -564,7 +564,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
   const int rb = unit % a.n_rowblk;
   const int kvh = (unit / a.n_rowblk) % a.n_kv;
   const int s = unit / (a.n_rowblk * a.n_kv);
-  int tok_begin = 0, n_tok = a.n_tok;
+  int tok_begin = s * a.tok_seq_stride, n_tok = a.n_tok;
   if (a.cu_tokens) {
     tok_begin = a.cu_tokens[s];
     n_tok = a.cu_tokens[s + 1] - tok_begin;
@@ -888,6 +888,7 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   a.pos0_val = L.pos0_val;
   a.cu_tokens = L.cu_tokens;
   a.n_tok = L.n_tok;
+  a.tok_seq_stride = L.tok_seq_stride;
   a.n_q = L.n_q;
   a.n_kv = L.n_kv;
   a.gqa = gqa;
@@ -936,6 +937,7 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   m.out = L.out;
   m.cu_tokens = L.cu_tokens;
   m.n_tok = L.n_tok;
+  m.tok_seq_stride = L.tok_seq_stride;
   m.n_q = L.n_q;
   m.n_kv = L.n_kv;
   m.gqa = gqa;

@@ -33,6 +33,7 @@ struct RowsLaunch {
   const int32_t *cu_tokens = nullptr;
   int n_seq = 1;
   int n_tok = 1;          /* max tokens of any sequence */
+  int tok_seq_stride = 0; /* no cu_tokens: sequence s owns tokens [s*stride, s*stride + n_tok) */
   int n_q = 0, n_kv = 0, hd = 0;
   float scale = 1.f;
   /* split scratch, floats: n_units * n_splits * rows_valid_max * (hd+2) */

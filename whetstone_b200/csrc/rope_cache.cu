@@ -41,6 +41,7 @@ struct RopeArgs {
   int max_seq;    /* contiguous: rows per head */
   int table_len;  /* rows in cos/sin */
   int n_seq, max_pages, page_size, n_pool_pages;
+  int n_per_seq; /* contiguous batch: tokens per sequence (0 = single sequence) */
   float eps;
 };
 
@@ -109,7 +110,13 @@ __device__ __forceinline__ TokenPlace place_token(const RopeArgs &a, int tok) {
   TokenPlace t;
   if constexpr (!PAGED) {
     int p;
-    if (a.pos_dev) {
+    long long seq_base = 0;
+    if (a.n_per_seq > 0) { /* batch of contiguous caches [n_seq][n_kv][max_seq][hd] */
+      const int sq = tok / a.n_per_seq;
+      p = a.seq_pos0[sq] + (tok - sq * a.n_per_seq);
+      p = p < 0 ? 0 : p;
+      seq_base = static_cast<long long>(sq) * a.n_kv * a.max_seq * a.hd;
+    } else if (a.pos_dev) {
       p = *a.pos_dev;
       p = p < 0 ? 0 : p;
     } else {
@@ -117,7 +124,7 @@ __device__ __forceinline__ TokenPlace place_token(const RopeArgs &a, int tok) {
     }
     p = p < a.max_seq - 1 ? p : a.max_seq - 1;
     t.pos = p;
-    t.kv_base = static_cast<long long>(p) * a.hd;
+    t.kv_base = seq_base + static_cast<long long>(p) * a.hd;
     t.kv_head_stride = static_cast<long long>(a.max_seq) * a.hd;
   } else {
     /* binary search: largest s with cu_tokens[s] <= tok */
@@ -397,4 +404,33 @@ extern "C" wst_status_t wst_rope_cache_paged(void *qkv, void *k_pool, void *v_po
   a.n_pool_pages = n_pool_pages;
   a.eps = eps;
   return launch_rope<true>(a, "wst_rope_cache_paged");
+}
+
+extern "C" wst_status_t wst_rope_cache_chunk_batch(void *qkv, void *k_cache, void *v_cache,
+                                                   const void *cos_tab, const void *sin_tab,
+                                                   const void *seq_pos0, int32_t n_seq,
+                                                   int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                                   int32_t n, int32_t max_seq,
+                                                   const void *q_norm_w, const void *k_norm_w,
+                                                   float eps) {
+  WST_CHECK_ARG(qkv && k_cache && v_cache && cos_tab && sin_tab && seq_pos0,
+                "wst_rope_cache_chunk_batch: null pointer");
+  WST_CHECK_ARG(n_q > 0 && n_kv > 0 && head_dim > 0 && n > 0 && n_seq > 0,
+                "wst_rope_cache_chunk_batch: non-positive shape");
+  WST_CHECK_ARG(head_dim % 2 == 0, "wst_rope_cache_chunk_batch: head_dim must be even");
+  WST_CHECK_ARG(n <= max_seq, "wst_rope_cache_chunk_batch: chunk longer than the cache");
+  RopeArgs a{};
+  a.qkv = static_cast<float *>(qkv);
+  a.k_cache = static_cast<__half *>(k_cache);
+  a.v_cache = static_cast<__half *>(v_cache);
+  a.cos_tab = static_cast<const float *>(cos_tab);
+  a.sin_tab = static_cast<const float *>(sin_tab);
+  a.q_gain = static_cast<const __half *>(q_norm_w);
+  a.k_gain = static_cast<const __half *>(k_norm_w);
+  a.seq_pos0 = static_cast<const int32_t *>(seq_pos0);
+  a.n_q = n_q; a.n_kv = n_kv; a.hd = head_dim;
+  a.n_tokens = n_seq * n; a.max_seq = max_seq; a.table_len = max_seq;
+  a.n_seq = n_seq; a.n_per_seq = n;
+  a.eps = eps;
+  return launch_rope<false>(a, "wst_rope_cache_chunk_batch");
 }
