@@ -38,7 +38,8 @@ WST_API wst_status_t wst_b200_device_error(uint32_t *out_code);
  *   0 = automatic (default)
  *   1 = force the portable CUDA-core kernel
  *   2 = wst_attn_chunk: force the split-KV mma.sync kernel
- *   3 = wst_attn_chunk: force the tcgen05 prefill kernel wherever it takes the shape
+ *   3 = wst_attn_chunk: force the tcgen05 prefill kernel (one query tile per CTA)
+ *   4 = wst_attn_chunk: force the tcgen05 prefill kernel with two query tiles per CTA
  * A debugging aid for A/B checks; process-wide. */
 WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
 

@@ -205,7 +205,7 @@ def test_partial_triples_merge_to_the_full_result(kernel_choice, shards):
 
 # -------------------------------------------- sets 3/4: chunk (contiguous)
 
-@pytest.fixture(params=[0, 1, 2, 3], ids=["auto", "portable", "splitkv", "tcgen05"])
+@pytest.fixture(params=[0, 1, 2, 3, 4], ids=["auto", "portable", "splitkv", "tcgen05", "tcgen05pair"])
 def chunk_kernel_choice(request):
     check(lib.wst_b200_set_kernel_choice(request.param))
     yield request.param

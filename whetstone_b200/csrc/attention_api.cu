@@ -156,7 +156,7 @@ __global__ void merge_partials_kernel(const float *__restrict__ parts, __half *_
 using namespace wst;
 
 extern "C" wst_status_t wst_b200_set_kernel_choice(int32_t choice) {
-  WST_CHECK_ARG(choice >= 0 && choice <= 3, "wst_b200_set_kernel_choice: unknown choice");
+  WST_CHECK_ARG(choice >= 0 && choice <= 4, "wst_b200_set_kernel_choice: unknown choice");
   g_kernel_choice.store(choice);
   return WST_OK;
 }
@@ -247,7 +247,7 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
    * them (or the prefix is short enough that it does not matter); a few tokens
    * against a long prefix go to the split-KV kernel instead. */
   bool use_prefill = tc_ok && choice != 2 && prefill_kernel_supports(n_q, n_kv, head_dim, n);
-  if (use_prefill && choice != 3) {
+  if (use_prefill && choice != 3 && choice != 4) {
     const int gqa = n_q / n_kv;
     const long long tiles = (static_cast<long long>(n) * gqa + 127) / 128 * n_kv;
     use_prefill = tiles >= 32 || static_cast<long long>(pos0) + n <= 2048;
@@ -262,6 +262,7 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
     P.out = static_cast<__half *>(out);
     P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
     P.pos0 = pos0; P.n = n; P.max_seq = max_seq; P.scale = scale;
+    P.force_pair = choice == 4 ? 1 : (choice == 3 ? -1 : 0);
     return launch_prefill(P);
   }
 
@@ -306,7 +307,7 @@ extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cach
   const long long q_stride = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
   const int choice = g_kernel_choice.load();
   bool use_prefill = choice != 2 && prefill_kernel_supports(n_q, n_kv, head_dim, n);
-  if (use_prefill && choice != 3) {
+  if (use_prefill && choice != 3 && choice != 4) {
     const int gqa = n_q / n_kv;
     use_prefill = (static_cast<long long>(n) * gqa + 127) / 128 * n_kv * n_seq >= 32;
   }
@@ -324,6 +325,7 @@ extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cach
     P.n_seq = n_seq;
     P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
     P.n = n; P.max_seq = max_seq; P.scale = scale;
+    P.force_pair = choice == 4 ? 1 : (choice == 3 ? -1 : 0);
     return launch_prefill(P);
   }
   /* few tokens per sequence: the split-KV kernel, one grid over all sequences.

@@ -22,6 +22,7 @@ struct PrefillLaunch {
   long long q_seq_stride = 0, out_seq_stride = 0;
   const int32_t *pos0_dev = nullptr;
   float scale = 1.f;
+  int force_pair = 0; /* 0 = automatic, 1 = two query tiles per CTA, -1 = one */
   const char *name = "attention";
 };
 
