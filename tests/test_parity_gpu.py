@@ -214,7 +214,8 @@ def chunk_kernel_choice(request):
 
 @pytest.mark.parametrize("n_q,n_kv,hd", [(14, 2, 64), (28, 4, 128), (32, 8, 128)])
 @pytest.mark.parametrize("pos0,n", [(0, 1), (0, 5), (0, 64), (20, 5), (1000, 5), (1000, 17),
-                                    (37, 130), (0, 257), (4000, 6), (100, 128), (511, 300)])
+                                    (37, 130), (0, 257), (4000, 6), (100, 128), (511, 300),
+                                    (3000, 16)])
 def test_chunk_matches_oracle(chunk_kernel_choice, n_q, n_kv, hd, pos0, n):
     """append + causal attention of a chunk, prefix written by earlier appends."""
     rng = np.random.default_rng(pos0 * 7 + n + hd)
@@ -334,9 +335,19 @@ def build_paged_case(rng, shape, lengths, drafts, theta=1e6, with_nan=True):
     return cache, table_np, k_ctx, v_ctx
 
 
+@pytest.fixture(params=[0, 2], ids=["auto", "rows"])
+def verify_kernel_choice(request):
+    """0: the tcgen05 kernel over slices of the KV range when every query row of a
+    (sequence, KV head) fits one 128-row tile; 2: the mma.sync row-block kernel."""
+    check(lib.wst_b200_set_kernel_choice(request.param))
+    yield request.param
+    check(lib.wst_b200_set_kernel_choice(0))
+
+
 @pytest.mark.parametrize("lengths,drafts", [([100, 700, 16, 333], 5), ([1, 15, 17, 64, 65], 3),
-                                            ([2050, 1024], 5), ([40], 9)])
-def test_paged_verify_matches_oracle(lengths, drafts):
+                                            ([2050, 1024], 5), ([40], 9), ([5000, 129, 4100], 4),
+                                            ([300, 77], 20)])
+def test_paged_verify_matches_oracle(verify_kernel_choice, lengths, drafts):
     shape = workloads.QWEN25_7B
     n_q, n_kv, hd, theta = shape.n_q, shape.n_kv, shape.head_dim, 1e6
     rng = np.random.default_rng(sum(lengths))
@@ -374,7 +385,7 @@ def test_paged_verify_matches_oracle(lengths, drafts):
         assert_close_per_head(got[s], want, f"verify seq {s} (len {L})")
 
 
-def test_paged_verify_ragged_token_counts():
+def test_paged_verify_ragged_token_counts(verify_kernel_choice):
     """Sequences verify different numbers of draft tokens (cu_tokens is ragged)."""
     shape = workloads.QWEN25_7B
     n_q, n_kv, hd, theta = shape.n_q, shape.n_kv, shape.head_dim, 1e6

@@ -247,10 +247,16 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
    * them (or the prefix is short enough that it does not matter); a few tokens
    * against a long prefix go to the split-KV kernel instead. */
   bool use_prefill = tc_ok && choice != 2 && prefill_kernel_supports(n_q, n_kv, head_dim, n);
+  bool sliced = false;
   if (use_prefill && choice != 3 && choice != 4) {
     const int gqa = n_q / n_kv;
     const long long tiles = (static_cast<long long>(n) * gqa + 127) / 128 * n_kv;
-    use_prefill = tiles >= 32 || static_cast<long long>(pos0) + n <= 2048;
+    if (!(tiles >= 32 || static_cast<long long>(pos0) + n <= 2048)) {
+      /* more than one mma.sync row tile but at most one tcgen05 tile per KV head:
+       * the same kernel, one CTA per slice of the prefix */
+      sliced = n * gqa > 16 && prefill_split_supports(n_q, n_kv, head_dim, n);
+      use_prefill = sliced;
+    }
   }
   if (use_prefill) {
     PrefillLaunch P;
@@ -263,6 +269,18 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
     P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
     P.pos0 = pos0; P.n = n; P.max_seq = max_seq; P.scale = scale;
     P.force_pair = choice == 4 ? 1 : (choice == 3 ? -1 : 0);
+    if (sliced) {
+      DeviceFacts facts;
+      if (!device_facts(&facts)) return WST_ERR_CUDA;
+      P.scratch = chunk_workspace();
+      P.scratch_floats = P.scratch ? kChunkWorkspaceFloats : 0;
+      const int len = pos0 + n;
+      int splits = facts.sm_count / n_kv;
+      if (splits < (len + 2047) / 2048) splits = (len + 2047) / 2048;
+      if (splits > (len + 127) / 128) splits = (len + 127) / 128;
+      if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
+      P.n_splits = splits;
+    }
     return launch_prefill(P);
   }
 
@@ -316,11 +334,9 @@ extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cach
     P.name = "wst_attn_chunk_batch";
     P.qkv = static_cast<const float *>(qkv);
     P.q_tok_stride = q_stride;
-    P.q_seq_stride = q_stride * n;
     P.k = static_cast<const __half *>(k_cache);
     P.v = static_cast<const __half *>(v_cache);
     P.out = static_cast<__half *>(out);
-    P.out_seq_stride = static_cast<long long>(n) * n_q * head_dim;
     P.pos0_dev = static_cast<const int32_t *>(seq_pos0);
     P.n_seq = n_seq;
     P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
@@ -391,6 +407,41 @@ extern "C" wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_poo
     return fail(WST_ERR_SHAPE,
                 "wst_attn_verify_paged: needs head_dim 64 or 128, at most 64 query heads per "
                 "KV head and 16-byte aligned buffers");
+  if (g_kernel_choice.load() != 2 &&
+      prefill_split_supports(n_q, n_kv, head_dim, max_tokens_per_seq)) {
+    /* all query rows of a (sequence, KV head) unit fit one 128-row tcgen05 tile:
+     * one CTA per (slice of ~2048 positions, KV head, sequence) */
+    DeviceFacts facts;
+    if (!device_facts(&facts)) return WST_ERR_CUDA;
+    PrefillLaunch P;
+    P.name = "wst_attn_verify_paged";
+    P.qkv = static_cast<const float *>(qkv);
+    P.q_tok_stride = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
+    P.k = static_cast<const __half *>(k_pool);
+    P.v = static_cast<const __half *>(v_pool);
+    P.out = static_cast<__half *>(out);
+    P.pos0_dev = static_cast<const int32_t *>(seq_pos0);
+    P.cu_tokens = static_cast<const int32_t *>(cu_tokens);
+    P.page_table = static_cast<const int32_t *>(page_table);
+    P.max_pages = max_pages;
+    P.n_pool_pages = n_pool_pages;
+    P.n_seq = n_seq;
+    P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
+    P.n = max_tokens_per_seq;
+    P.max_seq = max_pages * page_size;
+    P.scale = scale;
+    P.scratch = static_cast<float *>(scratch);
+    P.scratch_floats =
+        wst_attn_verify_scratch_floats(n_seq, max_tokens_per_seq, n_q, n_kv, head_dim, max_len);
+    int splits = facts.sm_count / (n_seq * n_kv);
+    const int by_len = (max_len + 2047) / 2048;
+    if (splits < by_len) splits = by_len;
+    const int tiles = (max_len + 127) / 128;
+    if (splits > tiles) splits = tiles;
+    if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
+    P.n_splits = splits < 1 ? 1 : splits;
+    return launch_prefill(P);
+  }
   RowsLaunch L;
   L.name = "wst_attn_verify_paged";
   L.q = static_cast<const float *>(qkv);

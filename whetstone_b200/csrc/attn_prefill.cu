@@ -33,6 +33,7 @@
  */
 
 #include "attn_prefill.cuh"
+#include "attn_rows.cuh"
 #include "tensor_map.cuh"
 #include "wst_ptx.cuh"
 
@@ -68,11 +69,15 @@ struct PCfg {
 };
 
 struct PrefillArgs {
-  const float *q;
-  long long q_tok_stride, q_seq_stride;
-  __half *out;
-  long long out_seq_stride;
-  const int32_t *pos0_dev; /* per-sequence chunk start, or null: pos0 for all */
+  const float *q;            /* [token][q_tok_stride], sequence s owns tokens s*n .. or cu_tokens */
+  long long q_tok_stride;
+  __half *out;               /* [token][n_q*hd] */
+  float *scratch;            /* split mode: [unit][slice][rows_cap][hd+4] */
+  const int32_t *pos0_dev;   /* per-sequence chunk start, or null: pos0 for all */
+  const int32_t *cu_tokens;  /* ragged token ranges [n_seq+1], or null: n tokens each */
+  const int32_t *page_table; /* paged cache: [n_seq][max_pages] */
+  int max_pages, n_pool_pages;
+  int n_splits, rows_cap;
   int n_q, n_kv, gqa;
   int pos0, n, max_seq;
   int tpt;      /* tokens per 128-row tile = 128 / gqa */
@@ -112,7 +117,7 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-template <int HD>
+template <int HD, bool PAGED>
 __global__ void __launch_bounds__(PCfg<HD>::THREADS, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap, const PrefillArgs a) {
@@ -133,7 +138,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + C::OFF_BAR + C::NBAR * 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qtile = a.n_qtiles - 1 - blockIdx.x; /* longest prefixes first */
+  /* blockIdx.x is the query tile (longest prefixes first) or, when the KV range
+   * is cut into slices (few query rows against a long prefix), the slice */
+  const int ns = a.n_splits;
+  const int split = ns > 1 ? static_cast<int>(blockIdx.x) : 0;
+  const int qtile = ns > 1 ? 0 : a.n_qtiles - 1 - static_cast<int>(blockIdx.x);
   const int kvh = blockIdx.y;
   const int seq = blockIdx.z;
 
@@ -168,13 +177,22 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
 
   /* rows of this tile: row r = (token tok0 + r / gqa, head kvh*gqa + r % gqa) */
   const int pos0 = a.pos0_dev ? max(a.pos0_dev[seq], 0) : a.pos0;
-  const int plane = seq * a.n_kv + kvh; /* which [max_seq][hd] slab of the cache */
+  const int plane = seq * a.n_kv + kvh; /* which [max_seq][hd] slab of a contiguous cache */
+  int tok_begin = seq * a.n, n_tok = a.n; /* this sequence's tokens in qkv / out */
+  if (a.cu_tokens) {
+    tok_begin = a.cu_tokens[seq];
+    n_tok = a.cu_tokens[seq + 1] - tok_begin;
+  }
   const int tok0 = qtile * a.tpt;
-  const int ntok = min(a.tpt, a.n - tok0);
+  const int ntok = max(min(a.tpt, n_tok - tok0), 0);
+  const int tok_base = tok_begin + tok0;
   const int rows_valid = ntok * a.gqa;
-  const int kv_end = min(pos0 + tok0 + ntok, a.max_seq); /* live cache rows this tile sees */
+  const int kv_end = ntok > 0 ? min(pos0 + tok0 + ntok, a.max_seq) : 0; /* live rows seen */
   const int lim_min = min(pos0 + tok0 + 1, a.max_seq);
-  const int n_tiles = (kv_end + BN - 1) / BN;
+  const int all_tiles = (kv_end + BN - 1) / BN;
+  /* this CTA's tiles: split, split + ns, split + 2 ns, ... */
+  const int n_tiles = split < all_tiles ? (all_tiles - split + ns - 1) / ns : 0;
+  auto tile_of = [split, ns](int j) { return split + j * ns; };
 
   if (warp == 5) {
     /* ------------------------------------------------------ TMA producer */
@@ -183,18 +201,49 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
         const int st = j % NSTAGE, round = j / NSTAGE;
         if (j >= NSTAGE && !mbar_wait(bar(K_EMPTY + st), (round - 1) & 1, a.err_word, 0x201u))
           break;
-        mbar_arrive_expect_tx(bar(K_FULL + st), KV_BYTES);
+        const int jt = tile_of(j);
+        int pages[BN / 16];
+        if constexpr (PAGED) {
 #pragma unroll
-        for (int h = 0; h < NH; ++h)
-          tma_load_3d(sbase + C::OFF_K + st * KV_BYTES + h * HALF_BYTES, &kmap, bar(K_FULL + st),
-                      h * 64, j * BN, plane);
+          for (int pg = 0; pg < BN / 16; ++pg) {
+            const int slot = jt * (BN / 16) + pg;
+            int page = slot < a.max_pages
+                           ? a.page_table[static_cast<long long>(seq) * a.max_pages + slot]
+                           : -1;
+            /* an unmapped slot reads as zeros: coordinate just past the pool */
+            pages[pg] = (page < 0 || page >= a.n_pool_pages) ? a.n_pool_pages : page;
+          }
+        }
+        mbar_arrive_expect_tx(bar(K_FULL + st), KV_BYTES);
+        if constexpr (PAGED) {
+#pragma unroll
+          for (int pg = 0; pg < BN / 16; ++pg)
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+              tma_load_4d(sbase + C::OFF_K + st * KV_BYTES + h * HALF_BYTES + pg * 16 * 128, &kmap,
+                          bar(K_FULL + st), h * 64, 0, kvh, pages[pg]);
+        } else {
+#pragma unroll
+          for (int h = 0; h < NH; ++h)
+            tma_load_3d(sbase + C::OFF_K + st * KV_BYTES + h * HALF_BYTES, &kmap,
+                        bar(K_FULL + st), h * 64, jt * BN, plane);
+        }
         if (j >= NSTAGE && !mbar_wait(bar(V_EMPTY + st), (round - 1) & 1, a.err_word, 0x202u))
           break;
         mbar_arrive_expect_tx(bar(V_FULL + st), KV_BYTES);
+        if constexpr (PAGED) {
 #pragma unroll
-        for (int h = 0; h < NH; ++h)
-          tma_load_3d(sbase + C::OFF_V + st * KV_BYTES + h * HALF_BYTES, &vmap, bar(V_FULL + st),
-                      h * 64, j * BN, plane);
+          for (int pg = 0; pg < BN / 16; ++pg)
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+              tma_load_4d(sbase + C::OFF_V + st * KV_BYTES + h * HALF_BYTES + pg * 16 * 128, &vmap,
+                          bar(V_FULL + st), h * 64, 0, kvh, pages[pg]);
+        } else {
+#pragma unroll
+          for (int h = 0; h < NH; ++h)
+            tma_load_3d(sbase + C::OFF_V + st * KV_BYTES + h * HALF_BYTES, &vmap,
+                        bar(V_FULL + st), h * 64, jt * BN, plane);
+        }
       }
     }
   } else if (warp == 4) {
@@ -211,8 +260,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       const uint32_t vb = sbase + C::OFF_V + st * KV_BYTES;
       /* Cache rows past the live data can hold any bit pattern and 0 * NaN is
        * NaN: clear them in the last tile before the tensor core reads V. */
-      if (i * BN + BN > kv_end) {
-        const int first = kv_end - i * BN;
+      if (tile_of(i) * BN + BN > kv_end) {
+        const int first = kv_end - tile_of(i) * BN;
         for (int idx = first * (NH * 8) + lane; idx < BN * NH * 8; idx += 32) {
           const int row = idx / (NH * 8), rest = idx % (NH * 8);
           asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(
@@ -269,8 +318,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     /* q row -> fp16 * scale * log2(e), two per 32-bit column of this row's TMEM lane */
     {
       const bool valid = r < rows_valid;
-      const float *src = a.q + seq * a.q_seq_stride +
-                         static_cast<long long>(tok0 + r / a.gqa) * a.q_tok_stride +
+      const float *src = a.q + static_cast<long long>(tok_base + r / a.gqa) * a.q_tok_stride +
                          static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD / 2; c0 += 32) {
@@ -290,12 +338,24 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     }
 
     const int lim = r < rows_valid ? min(pos0 + tok0 + r / a.gqa + 1, a.max_seq) : kv_end;
+    /* A warp with no valid query row (a short last tile, or a handful of tokens
+     * against a long prefix) only keeps the barrier protocol going: its rows of
+     * S, P and O hold garbage that no other row depends on and nobody reads. */
+    const bool live = warp * 32 < rows_valid;
     float m_ref = -INFINITY; /* exponent offset in use for this row (log2 units) */
     float l_run = 0.f;
     bool ok = true;
 
     for (int j = 0; j < n_tiles; ++j) {
       if (!mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, a.err_word, 0x220u)) { ok = false; break; }
+      if (!live) {
+        mbar_arrive(bar(S_FREE + (j & 1)));
+        /* not before the previous tile's P has been consumed: an early arrival
+         * would be counted into the phase the live warps have not finished */
+        if (j >= 1 && !mbar_wait(bar(PV_DONE), (j - 1) & 1, a.err_word, 0x224u)) { ok = false; break; }
+        mbar_arrive(bar(P_READY));
+        continue;
+      }
       tc_fence_after_sync();
       const uint32_t s_addr = tmem + lane_base + C::COL_S + (j & 1) * BN;
 
@@ -308,8 +368,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       tc_fence_before_sync();
       mbar_arrive(bar(S_FREE + (j & 1)));
 
-      if (j * BN + BN > lim_min) { /* causal edge / end of sequence */
-        const int lim_local = lim - j * BN;
+      if (tile_of(j) * BN + BN > lim_min) { /* causal edge / end of sequence */
+        const int lim_local = lim - tile_of(j) * BN;
 #pragma unroll
         for (int c = 0; c < BN; ++c)
           if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
@@ -380,11 +440,38 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
 
     if (ok && n_tiles > 0)
       ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, a.err_word, 0x223u);
-    if (ok) {
+    if (ok && ns > 1) {
+      /* one slice of a split KV range: this row's (acc, m, l) for the merge kernel,
+       * acc[HD] | m | l | pad pad, log2 units (attn_rows.cu reads the same rows) */
+      tc_fence_after_sync();
+      if (live) {
+        const long long unit = static_cast<long long>(seq) * a.n_kv + kvh;
+        float *dst = a.scratch + ((unit * ns + split) * a.rows_cap + r) * (HD + 4);
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t v[32];
+          if (n_tiles > 0) { /* warp-uniform: the load is a warp-wide instruction */
+            tmem_ld_32x32(tmem + lane_base + C::COL_O + c0, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          if (r < rows_valid) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              *reinterpret_cast<uint4 *>(dst + c0 + e) =
+                  make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+          }
+        }
+        if (r < rows_valid)
+          *reinterpret_cast<float2 *>(dst + HD) =
+              make_float2(n_tiles > 0 ? m_ref : -INFINITY, l_run);
+      }
+    } else if (ok && live) {
       tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __half *dst = a.out + seq * a.out_seq_stride +
-                    (static_cast<long long>(tok0 + r / a.gqa) * a.n_q +
+      __half *dst = a.out + (static_cast<long long>(tok_base + r / a.gqa) * a.n_q +
                              (kvh * a.gqa + r % a.gqa)) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -629,8 +716,8 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     /* q row -> fp16 * scale * log2(e), in the K-major swizzled operand layout */
     {
       const bool valid = r < rows_valid;
-      const float *src = a.q + seq * a.q_seq_stride +
-                         static_cast<long long>(tok0[t] + r / a.gqa) * a.q_tok_stride +
+      const float *src = a.q +
+                         static_cast<long long>(seq * a.n + tok0[t] + r / a.gqa) * a.q_tok_stride +
                          static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD;
 #pragma unroll 4
       for (int ch = 0; ch < HD / 8; ++ch) {
@@ -739,8 +826,8 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     if (ok && rows_valid > 0) {
       tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __half *dst = a.out + seq * a.out_seq_stride +
-                    (static_cast<long long>(tok0[t] + r / a.gqa) * a.n_q +
+      __half *dst = a.out +
+                    (static_cast<long long>(seq * a.n + tok0[t] + r / a.gqa) * a.n_q +
                      (kvh * a.gqa + r % a.gqa)) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -772,23 +859,33 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <int HD, bool PAIR>
-wst_status_t launch_hd(const PrefillLaunch &P, const PrefillArgs &args, const CUtensorMap &kmap,
-                       const CUtensorMap &vmap, dim3 grid) {
-  using C = std::conditional_t<PAIR, P2Cfg<HD>, PCfg<HD>>;
-  auto kern = PAIR ? attn_prefill_pair_kernel<HD> : attn_prefill_kernel<HD>;
-  static thread_local int configured_dev = -1;
+template <class Cfg, class Kern>
+wst_status_t launch_kernel(const PrefillLaunch &P, Kern kern, const PrefillArgs &args,
+                           const CUtensorMap &kmap, const CUtensorMap &vmap, dim3 grid) {
+  /* the opt-in to > 48 KB of dynamic shared memory is per function and device */
+  static thread_local const void *configured_fn[8] = {};
+  static thread_local int configured_dev[8] = {};
   int dev = 0;
   WST_CUDA(cudaGetDevice(&dev));
-  if (configured_dev != dev) {
+  const void *fn = reinterpret_cast<const void *>(kern);
+  bool done = false;
+  int free_slot = -1;
+  for (int i = 0; i < 8; ++i) {
+    if (configured_fn[i] == fn && configured_dev[i] == dev) done = true;
+    if (!configured_fn[i] && free_slot < 0) free_slot = i;
+  }
+  if (!done) {
     WST_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  C::SMEM_BYTES));
-    configured_dev = dev;
+                                  Cfg::SMEM_BYTES));
+    if (free_slot >= 0) {
+      configured_fn[free_slot] = fn;
+      configured_dev[free_slot] = dev;
+    }
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(C::THREADS);
-  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.blockDim = dim3(Cfg::THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = current_stream();
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -814,6 +911,13 @@ bool prefill_kernel_supports(int n_q, int n_kv, int hd, int n) {
   return static_cast<long long>(n) * gqa >= 64;
 }
 
+bool prefill_split_supports(int n_q, int n_kv, int hd, int n_tok_max) {
+  if (hd != 64 && hd != 128) return false;
+  if (n_kv <= 0 || n_q % n_kv != 0) return false;
+  /* every query row of a (sequence, KV head) unit in one 128-row tile */
+  return static_cast<long long>(n_tok_max) * (n_q / n_kv) <= 128;
+}
+
 wst_status_t launch_prefill(const PrefillLaunch &P) {
   DeviceFacts facts;
   if (!device_facts(&facts)) return WST_ERR_CUDA;
@@ -825,10 +929,13 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   PrefillArgs a{};
   a.q = P.qkv;
   a.q_tok_stride = P.q_tok_stride;
-  a.q_seq_stride = P.q_seq_stride;
   a.out = P.out;
-  a.out_seq_stride = P.out_seq_stride;
+  a.scratch = P.scratch;
   a.pos0_dev = P.pos0_dev;
+  a.cu_tokens = P.cu_tokens;
+  a.page_table = P.page_table;
+  a.max_pages = P.max_pages;
+  a.n_pool_pages = P.n_pool_pages;
   a.n_q = P.n_q;
   a.n_kv = P.n_kv;
   a.gqa = P.n_q / P.n_kv;
@@ -841,14 +948,31 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   a.err_word = device_error_word();
   if (!a.err_word) return WST_ERR_CUDA;
 
+  /* slices of the KV range: only for a single query tile per unit */
+  int splits = P.n_splits > 0 ? P.n_splits : 1;
+  if (a.n_qtiles != 1) splits = 1;
+  a.rows_cap = P.n * a.gqa;
+  const long long units = static_cast<long long>(P.n_seq) * P.n_kv;
+  if (!P.scratch || !aligned16(P.scratch)) splits = 1;
+  while (splits > 1 && units * splits * a.rows_cap * (P.hd + 4) > P.scratch_floats) --splits;
+  a.n_splits = splits;
+
   CUtensorMap kmap, vmap;
   KvMapKey key{};
   key.d0 = static_cast<uint64_t>(P.hd);
-  key.d1 = static_cast<uint64_t>(P.max_seq);
-  key.d2 = static_cast<uint64_t>(P.n_kv) * P.n_seq;
-  key.d3 = 1;
-  key.b1 = 128;
-  key.rank = 3;
+  if (P.page_table) {
+    key.d1 = 16;
+    key.d2 = static_cast<uint64_t>(P.n_kv);
+    key.d3 = static_cast<uint64_t>(P.n_pool_pages);
+    key.b1 = 16;
+    key.rank = 4;
+  } else {
+    key.d1 = static_cast<uint64_t>(P.max_seq);
+    key.d2 = static_cast<uint64_t>(P.n_kv) * P.n_seq;
+    key.d3 = 1;
+    key.b1 = 128;
+    key.rank = 3;
+  }
   key.base = P.k;
   wst_status_t st = cached_kv_tensor_map(&kmap, key);
   if (st != WST_OK) return st;
@@ -862,14 +986,39 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
    * warpgroup shares that unit.  It is kept selectable because it halves the
    * K/V traffic from L2 and is the schedule that pays once part of the
    * exponentials moves to the FMA pipes. */
-  const bool pair = P.force_pair > 0;
-  const dim3 grid(static_cast<unsigned>(pair ? (a.n_qtiles + 1) / 2 : a.n_qtiles),
-                  static_cast<unsigned>(P.n_kv), static_cast<unsigned>(P.n_seq));
+  const bool pair = P.force_pair > 0 && splits == 1 && !P.page_table && !P.cu_tokens;
+  const unsigned gx = splits > 1 ? splits : (pair ? (a.n_qtiles + 1) / 2 : a.n_qtiles);
+  const dim3 grid(gx, static_cast<unsigned>(P.n_kv), static_cast<unsigned>(P.n_seq));
   if (pair)
-    return P.hd == 128 ? launch_hd<128, true>(P, a, kmap, vmap, grid)
-                       : launch_hd<64, true>(P, a, kmap, vmap, grid);
-  return P.hd == 128 ? launch_hd<128, false>(P, a, kmap, vmap, grid)
-                     : launch_hd<64, false>(P, a, kmap, vmap, grid);
+    st = P.hd == 128
+             ? launch_kernel<P2Cfg<128>>(P, attn_prefill_pair_kernel<128>, a, kmap, vmap, grid)
+             : launch_kernel<P2Cfg<64>>(P, attn_prefill_pair_kernel<64>, a, kmap, vmap, grid);
+  else if (P.page_table)
+    st = P.hd == 128
+             ? launch_kernel<PCfg<128>>(P, attn_prefill_kernel<128, true>, a, kmap, vmap, grid)
+             : launch_kernel<PCfg<64>>(P, attn_prefill_kernel<64, true>, a, kmap, vmap, grid);
+  else
+    st = P.hd == 128
+             ? launch_kernel<PCfg<128>>(P, attn_prefill_kernel<128, false>, a, kmap, vmap, grid)
+             : launch_kernel<PCfg<64>>(P, attn_prefill_kernel<64, false>, a, kmap, vmap, grid);
+  if (st != WST_OK || splits == 1) return st;
+
+  SplitMerge m;
+  m.scratch = P.scratch;
+  m.out = P.out;
+  m.cu_tokens = P.cu_tokens;
+  m.n_tok = P.n;
+  m.tok_seq_stride = P.cu_tokens ? 0 : P.n;
+  m.n_q = P.n_q;
+  m.n_kv = P.n_kv;
+  m.hd = P.hd;
+  m.n_splits = splits;
+  m.n_rowblk = 1;
+  m.tpb = P.n;
+  m.rows_cap = a.rows_cap;
+  m.n_units = static_cast<int>(units);
+  m.name = P.name;
+  return launch_split_merge(m);
 }
 
 }  // namespace wst

@@ -16,11 +16,21 @@ struct PrefillLaunch {
   __half *out = nullptr;       /* [n][n_q*hd] */
   int n_q = 0, n_kv = 0, hd = 0;
   int pos0 = 0, n = 0, max_seq = 0;
-  /* batch: n_seq sequences with caches [n_seq][n_kv][max_seq][hd], qkv and out
-   * strided per sequence, chunk starts in device memory (null = pos0 for all) */
+  /* batch: n_seq sequences with caches [n_seq][n_kv][max_seq][hd]; sequence s owns
+   * tokens s*n .. s*n+n-1 of qkv and out (or cu_tokens[s] .. cu_tokens[s+1]-1, with n
+   * the largest count); chunk starts in device memory (null = pos0 for all) */
   int n_seq = 1;
-  long long q_seq_stride = 0, out_seq_stride = 0;
   const int32_t *pos0_dev = nullptr;
+  const int32_t *cu_tokens = nullptr;
+  /* paged cache instead: pool [n_pool_pages][n_kv][16][hd], page_table [n_seq][max_pages],
+   * max_seq = max_pages * 16 */
+  const int32_t *page_table = nullptr;
+  int max_pages = 0, n_pool_pages = 0;
+  /* few query rows against a long prefix: cut the KV range into n_splits slices
+   * (needs n * gqa <= 128 and scratch of n_seq*n_kv*n_splits*n*gqa*(hd+4) floats) */
+  int n_splits = 0;
+  float *scratch = nullptr;
+  long long scratch_floats = 0;
   float scale = 1.f;
   int force_pair = 0; /* 0 = automatic, 1 = two query tiles per CTA, -1 = one */
   const char *name = "attention";
@@ -29,6 +39,9 @@ struct PrefillLaunch {
 /* True if the tcgen05 kernel takes this shape and the chunk is large enough
  * for 128-row tiles to pay. */
 bool prefill_kernel_supports(int n_q, int n_kv, int hd, int n);
+
+/* True if the sliced form (all query rows of a unit in one tile) takes the shape. */
+bool prefill_split_supports(int n_q, int n_kv, int hd, int n_tok_max);
 
 wst_status_t launch_prefill(const PrefillLaunch &P);
 

@@ -932,7 +932,7 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   }
   if (st != WST_OK || splits == 1) return st;
 
-  MergeArgs m{};
+  SplitMerge m;
   m.scratch = L.scratch;
   m.out = L.out;
   m.cu_tokens = L.cu_tokens;
@@ -940,17 +940,37 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   m.tok_seq_stride = L.tok_seq_stride;
   m.n_q = L.n_q;
   m.n_kv = L.n_kv;
-  m.gqa = gqa;
+  m.hd = L.hd;
   m.n_splits = splits;
   m.n_rowblk = n_rowblk;
   m.tpb = tpb;
   m.rows_cap = rows_cap;
-  m.partial_out = L.partial_out ? 1 : 0;
-  const dim3 mgrid(static_cast<unsigned>(rows_cap), static_cast<unsigned>(n_units));
-  cudaError_t e = L.hd == 128 ? launch_pdl(attn_merge_kernel<128>, mgrid, dim3(128), 0, m)
+  m.n_units = n_units;
+  m.partial_out = L.partial_out;
+  m.name = L.name;
+  return launch_split_merge(m);
+}
+
+wst_status_t launch_split_merge(const SplitMerge &S) {
+  MergeArgs m{};
+  m.scratch = S.scratch;
+  m.out = S.out;
+  m.cu_tokens = S.cu_tokens;
+  m.n_tok = S.n_tok;
+  m.tok_seq_stride = S.tok_seq_stride;
+  m.n_q = S.n_q;
+  m.n_kv = S.n_kv;
+  m.gqa = S.n_q / S.n_kv;
+  m.n_splits = S.n_splits;
+  m.n_rowblk = S.n_rowblk;
+  m.tpb = S.tpb;
+  m.rows_cap = S.rows_cap;
+  m.partial_out = S.partial_out ? 1 : 0;
+  const dim3 mgrid(static_cast<unsigned>(S.rows_cap), static_cast<unsigned>(S.n_units));
+  cudaError_t e = S.hd == 128 ? launch_pdl(attn_merge_kernel<128>, mgrid, dim3(128), 0, m)
                               : launch_pdl(attn_merge_kernel<64>, mgrid, dim3(128), 0, m);
   if (e != cudaSuccess)
-    return fail(WST_ERR_CUDA, "%s (merge launch): %s (%s)", L.name, cudaGetErrorString(e),
+    return fail(WST_ERR_CUDA, "%s (merge launch): %s (%s)", S.name, cudaGetErrorString(e),
                 cudaGetErrorName(e));
   return WST_OK;
 }

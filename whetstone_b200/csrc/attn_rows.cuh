@@ -58,6 +58,20 @@ long long rows_scratch_floats(int n_units_times_rows, int splits, int hd);
 
 wst_status_t launch_rows(const RowsLaunch &L);
 
+/* The slice merge on its own (the tcgen05 kernel's sliced form writes the same
+ * scratch rows: acc[hd] | m | l | 2 pad per query row, log2 units). */
+struct SplitMerge {
+  const float *scratch = nullptr;
+  void *out = nullptr;
+  const int32_t *cu_tokens = nullptr;
+  int n_tok = 1, tok_seq_stride = 0;
+  int n_q = 0, n_kv = 0, hd = 0;
+  int n_splits = 1, n_rowblk = 1, tpb = 1, rows_cap = 1, n_units = 1;
+  bool partial_out = false;
+  const char *name = "attention";
+};
+wst_status_t launch_split_merge(const SplitMerge &m);
+
 /* Portable CUDA-core kernel for head widths the tensor-core kernel does not
  * take (any head_dim % 32 == 0 up to 256, contiguous cache, no split). */
 wst_status_t launch_simple(const RowsLaunch &L);
