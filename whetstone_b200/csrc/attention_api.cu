@@ -84,6 +84,7 @@ wst_status_t decode_common(const char *who, const void *q, const void *k_cache,
   }
   L.n_seq = 1;
   L.n_tok = 1;
+  L.newest_row_only = true;
   L.n_q = n_q;
   L.n_kv = n_kv;
   L.hd = head_dim;

@@ -42,15 +42,21 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 /* Optional phase timestamps for tuning (compiled in only with -DWST_TRACE). */
 #ifdef WST_TRACE
-__device__ unsigned long long g_trace[4096 * 8];
-__device__ __forceinline__ void trace_stamp(int slot) {
+/* [bank][block][slot]; the bank is chosen on the host per launch, so that
+ * consecutive launches can be told apart (banks 0-3: rows kernel, 4-7: merge) */
+__device__ unsigned long long g_trace[8 * 512 * 8];
+int g_trace_bank = 0;
+__device__ __forceinline__ void trace_stamp_bank(int slot, int bank) {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   const unsigned int b = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (b < 4096) g_trace[b * 8 + slot] = t;
+  if (b < 512) g_trace[(bank * 512 + b) * 8 + slot] = t;
 }
+#define trace_stamp(slot) trace_stamp_bank(slot, a.trace_bank)
 #define WST_STAMP(slot) do { if (threadIdx.x == 0) trace_stamp(slot); } while (0)
+#define WST_TRACE_FIELD int trace_bank;
 #else
+#define WST_TRACE_FIELD
 #define WST_STAMP(slot) do { } while (0)
 #endif
 
@@ -70,6 +76,8 @@ struct RowsArgs {
   void *out;
   int partial_out;
   int n_splits, n_rowblk, tpb, rows_cap;
+  int early_spec; /* request the first tile before the grid dependency is resolved */
+  WST_TRACE_FIELD
 };
 
 template <int HD, int MT, int RG>
@@ -84,9 +92,11 @@ struct Cfg {
   static constexpr int STAGE_BYTES = 2 * NH * HALF_BYTES;
   static constexpr int NSTAGE = HD == 128 ? 4 : 6;
   static constexpr int Q_BYTES = NH * ROWS * 128;
-  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + Q_BYTES + 2 * NSTAGE * 8 + 64 + 1024;
+  /* ring | one spare stage (the re-read of the newest tile) | q tile | barriers */
+  static constexpr int SMEM_BYTES =
+      (NSTAGE + 1) * STAGE_BYTES + Q_BYTES + (2 * NSTAGE + 1) * 8 + 64 + 1024;
   /* the warp-combine dump [RG][4][16*MT][HD+4] floats reuses the ring and the q tile */
-  static_assert(RG * 4 * 16 * MT * (HD + 4) * 4 <= NSTAGE * STAGE_BYTES + Q_BYTES,
+  static_assert(RG * 4 * 16 * MT * (HD + 4) * 4 <= (NSTAGE + 1) * STAGE_BYTES + Q_BYTES,
                 "combine buffer must fit");
 };
 
@@ -126,30 +136,26 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t *qsm = smem + NSTAGE * STAGE_BYTES;
+  uint8_t *qsm = smem + (NSTAGE + 1) * STAGE_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(qsm + C::Q_BYTES);
   const uint32_t stages_u32 = smem_u32(smem);
+  const uint32_t spare_u32 = stages_u32 + NSTAGE * STAGE_BYTES;
   const uint32_t q_u32 = smem_u32(qsm);
   const uint32_t full_u32 = smem_u32(bars);
   const uint32_t empty_u32 = smem_u32(bars + NSTAGE);
+  const uint32_t spare_full_u32 = smem_u32(bars + 2 * NSTAGE);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) {
       mbar_init(full_u32 + 8 * i, 1);
       mbar_init(empty_u32 + 8 * i, C::CWARPS);
     }
+    mbar_init(spare_full_u32, 1);
     mbar_init_fence();
     tma_prefetch_desc(&kmap);
     tma_prefetch_desc(&vmap);
   }
   __syncthreads();
-
-  /* Everything above touches no global memory, so under programmatic dependent
-   * launch it overlaps the tail of the previous kernel in the stream.  From here
-   * on we read what that kernel may have written (cursor, q, cache rows). */
-  WST_STAMP(0);
-  grid_dependency_wait();
-  WST_STAMP(1);
 
   /* Slice `split` owns tiles split, split + n_splits, split + 2 n_splits, ...:
    * the first tiles of a slice do not depend on the sequence length, so for a
@@ -157,12 +163,8 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
    * cursor has even been read (tiles past the live rows are loaded and ignored;
    * they lie inside the cache allocation or read as zeros). */
   const int ns = a.n_splits;
-  auto issue = [&](int i) {
-    const int stage = i % NSTAGE;
-    const uint32_t full = full_u32 + 8 * stage;
+  auto issue_to = [&](int tile, uint32_t full, uint32_t kdst) {
     mbar_arrive_expect_tx(full, STAGE_BYTES);
-    const int tile = split + i * ns;
-    const uint32_t kdst = stages_u32 + stage * STAGE_BYTES;
     const uint32_t vdst = kdst + NH * HALF_BYTES;
     if constexpr (!PAGED) {
       const int plane = s * a.n_kv + kvh;
@@ -188,14 +190,38 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       }
     }
   };
+  auto issue = [&](int i) {
+    const int stage = i % NSTAGE;
+    issue_to(split + i * ns, full_u32 + 8 * stage, stages_u32 + stage * STAGE_BYTES);
+  };
   int spec = 0; /* tiles issued ahead of knowing the sequence length */
-  if (!PAGED && a.cu_tokens == nullptr) {
+  if (!PAGED && a.cu_tokens == nullptr)
     while (spec < NSTAGE && static_cast<long long>(split + spec * ns) * BN < a.max_seq) ++spec;
-    if (warp == C::CWARPS && lane < spec) issue(lane); /* one lane per stage, all at once */
+
+  /* Decode (one new token): the launch just before this one in the stream --
+   * still running under programmatic dependent launch -- can only be writing the
+   * newest cache row; every row in a tile below that one was written by launches
+   * that finished long ago.  So the slice's first tile is requested right here, before
+   * the dependency is resolved, and its latency hides behind the tail of the
+   * previous kernel.  If that tile is the one holding the newest row it is read
+   * again after the wait, into the spare stage. */
+  const bool early = !PAGED && a.early_spec != 0;
+  /* One tile per block is enough to hide the latency; measured on the 32k-context
+   * decode shape, requesting the whole ring here crowds out the last loads of the
+   * kernel still running and costs more than it hides. */
+  const int n_early = early ? min(spec, 1) : 0;
+  if (warp == C::CWARPS && lane < n_early) issue(lane);
+
+  /* Nothing else above touches global memory, so under programmatic dependent
+   * launch it overlaps the tail of the previous kernel in the stream.  From here
+   * on we read what that kernel may have written (cursor, q, newest cache rows). */
+  WST_STAMP(0);
+  grid_dependency_wait();
+  WST_STAMP(1);
+  if (warp == C::CWARPS && lane >= n_early && lane < spec) issue(lane); /* one lane per stage */
 #ifdef WST_TRACE
-    if (warp == C::CWARPS && lane == 0) trace_stamp(6);
+  if (warp == C::CWARPS && lane == 0) trace_stamp(6);
 #endif
-  }
 
   int tok_begin = s * a.tok_seq_stride, n_tok = a.n_tok;
   if (a.cu_tokens) {
@@ -257,9 +283,16 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int n_tiles = (kv_end + BN - 1) / BN;
   const int my_tiles = split < n_tiles ? (n_tiles - split + ns - 1) / ns : 0;
 
+  /* the slice's tile that holds the newest rows, if it was requested before the
+   * dependency was resolved: read again, consumed from the spare stage */
+  int reread = -1;
+  if (my_tiles > 0 && my_tiles - 1 < n_early && split + (my_tiles - 1) * ns == n_tiles - 1)
+    reread = my_tiles - 1;
+
   /* ------------------------------------------------------------ producer */
   if (warp == C::CWARPS) {
     if (lane != 0) return;
+    if (reread >= 0) issue_to(n_tiles - 1, spare_full_u32, spare_u32);
     for (int i = spec; i < my_tiles; ++i) {
       const int stage = i % NSTAGE, round = i / NSTAGE;
       if (i >= NSTAGE &&
@@ -317,7 +350,11 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     if (!mbar_wait(full_u32 + 8 * stage, round & 1, a.err_word, 0x102u)) break;
     if (i == 0) WST_STAMP(2);
     const int tile = split + i * ns;
-    const uint32_t kb = stages_u32 + stage * STAGE_BYTES;
+    uint32_t kb = stages_u32 + stage * STAGE_BYTES;
+    if (i == reread) {
+      if (!mbar_wait(spare_full_u32, 0, a.err_word, 0x104u)) break;
+      kb = spare_u32;
+    }
     const uint32_t vb = kb + NH * HALF_BYTES;
 
     /* S = Q K^T for this warp's 16 positions */
@@ -542,6 +579,7 @@ struct MergeArgs {
   const float *scratch;
   void *out;
   const int32_t *cu_tokens;
+  WST_TRACE_FIELD
   int n_tok, tok_seq_stride, n_q, n_kv, gqa;
   int n_splits, n_rowblk, tpb, rows_cap;
   int partial_out;
@@ -557,8 +595,10 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
   __shared__ float4 s_acc[GROUPS][LPR];
   __shared__ float s_m[GROUPS], s_l[GROUPS];
 
+  WST_STAMP(0);
   grid_launch_dependents();
   grid_dependency_wait();
+  WST_STAMP(1);
 
   const int row = blockIdx.x, unit = blockIdx.y;
   const int rb = unit % a.n_rowblk;
@@ -649,6 +689,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
                     col,
                 tot.x * inv, tot.y * inv, tot.z * inv, tot.w * inv);
   }
+  WST_STAMP(2);
 }
 
 /* ------------------------------------------------- portable fallback kernel */
@@ -828,6 +869,9 @@ extern "C" __attribute__((visibility("default"))) int wst_b200_trace_read(unsign
                                                                          int n) {
   return static_cast<int>(cudaMemcpyFromSymbol(dst, g_trace, sizeof(unsigned long long) * n));
 }
+extern "C" __attribute__((visibility("default"))) void wst_b200_trace_bank(int bank) {
+  g_trace_bank = bank & 3;
+}
 #endif
 
 bool rows_kernel_supports(int n_q, int n_kv, int hd, const void *k, const void *v) {
@@ -901,6 +945,10 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   a.n_rowblk = n_rowblk;
   a.tpb = tpb;
   a.rows_cap = rows_cap;
+#ifdef WST_TRACE
+  a.trace_bank = g_trace_bank;
+#endif
+  a.early_spec = (L.newest_row_only && !L.paged && !L.cu_tokens && L.n_tok == 1 && L.n_seq == 1) ? 1 : 0;
   a.err_word = device_error_word();
   if (!a.err_word) return WST_ERR_CUDA;
   CUtensorMap kmap, vmap;
@@ -966,6 +1014,9 @@ wst_status_t launch_split_merge(const SplitMerge &S) {
   m.tpb = S.tpb;
   m.rows_cap = S.rows_cap;
   m.partial_out = S.partial_out ? 1 : 0;
+#ifdef WST_TRACE
+  m.trace_bank = 4 + g_trace_bank;
+#endif
   const dim3 mgrid(static_cast<unsigned>(S.rows_cap), static_cast<unsigned>(S.n_units));
   cudaError_t e = S.hd == 128 ? launch_pdl(attn_merge_kernel<128>, mgrid, dim3(128), 0, m)
                               : launch_pdl(attn_merge_kernel<64>, mgrid, dim3(128), 0, m);

@@ -36,6 +36,10 @@ struct RowsLaunch {
   int tok_seq_stride = 0; /* no cu_tokens: sequence s owns tokens [s*stride, s*stride + n_tok) */
   int n_q = 0, n_kv = 0, hd = 0;
   float scale = 1.f;
+  /* Decode contract: of the rows this launch reads, the launch right before it in
+   * the stream can have written only the newest one (row pos0); the kernel may
+   * then request the older tiles before that launch has finished. */
+  bool newest_row_only = false;
   /* split scratch, floats: n_units * n_splits * rows_valid_max * (hd+2) */
   float *scratch = nullptr;
   long long scratch_floats = 0;

@@ -43,6 +43,7 @@ struct RopeArgs {
   int n_seq, max_pages, page_size, n_pool_pages;
   int n_per_seq; /* contiguous batch: tokens per sequence (0 = single sequence) */
   float eps;
+  int trigger_early; /* set by the launcher: single-token append under programmatic launch */
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -155,6 +156,11 @@ __device__ __forceinline__ TokenPlace place_token(const RopeArgs &a, int tok) {
 template <int E, bool PAGED>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 rope_append_kernel(const RopeArgs a) {
+  /* Under programmatic dependent launch: a single-token append lets the next
+   * kernel in the stream (the decode attention, which re-reads the one row
+   * written here after its own wait) start its prologue right away. */
+  if (a.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int HD = 64 * E;
   constexpr int HALF = HD / 2;
   const int lane = threadIdx.x & 31;
@@ -294,16 +300,32 @@ wst_status_t launch_rope(const RopeArgs &a, const char *name) {
   const bool vec_ok = aligned16(a.qkv) && aligned16(a.k_cache) && aligned16(a.v_cache) &&
                       aligned16(a.cos_tab) && aligned16(a.sin_tab) &&
                       (!a.q_gain || aligned16(a.q_gain)) && (!a.k_gain || aligned16(a.k_gain));
+  /* A single-token append (decode) is launched with programmatic stream
+   * serialization and lets its dependents start early; larger appends are
+   * ordinary launches, complete before anything after them starts. */
+  RopeArgs args = a;
+  args.trigger_early = 0;
+  if (!PAGED && a.n_tokens == 1 && vec_ok) args.trigger_early = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = args.trigger_early ? 1 : 0;
+  cudaError_t e;
   if (vec_ok && a.hd == 64) {
-    rope_append_kernel<1, PAGED><<<grid, block, 0, st>>>(a);
+    e = cudaLaunchKernelEx(&cfg, rope_append_kernel<1, PAGED>, args);
   } else if (vec_ok && a.hd == 128) {
-    rope_append_kernel<2, PAGED><<<grid, block, 0, st>>>(a);
+    e = cudaLaunchKernelEx(&cfg, rope_append_kernel<2, PAGED>, args);
   } else if (vec_ok && a.hd == 256) {
-    rope_append_kernel<4, PAGED><<<grid, block, 0, st>>>(a);
+    e = cudaLaunchKernelEx(&cfg, rope_append_kernel<4, PAGED>, args);
   } else {
-    rope_append_any_kernel<PAGED><<<grid, block, 0, st>>>(a);
+    e = cudaLaunchKernelEx(&cfg, rope_append_any_kernel<PAGED>, args);
   }
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(WST_ERR_CUDA, "%s (launch): %s (%s)", name,
                                     cudaGetErrorString(e), cudaGetErrorName(e));
   return WST_OK;
