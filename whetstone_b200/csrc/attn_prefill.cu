@@ -57,8 +57,12 @@ struct PCfg {
   static constexpr int OFF_V = OFF_K + NSTAGE * KV_BYTES;
   static constexpr int OFF_BAR = OFF_V + NSTAGE * KV_BYTES;
   static constexpr int NBAR = 4 * NSTAGE + 2 + 2 + 1 + 1 + 1;
-  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
-  static constexpr int THREADS = 192;
+  /* after the barriers and the tensor-memory slot: three [2][128] float areas through
+   * which the two threads of a query row exchange their partial maxima and sums */
+  static constexpr int OFF_XCH = OFF_BAR + 256;
+  static constexpr int SMEM_BYTES = OFF_XCH + 3 * 2 * 128 * 4 + 1024;
+  static constexpr int THREADS = 320; /* 8 softmax warps, the MMA warp, the TMA warp */
+  static_assert(NBAR * 8 + 16 <= 256, "barrier area");
   /* tensor-memory columns */
   static constexpr int COL_S = 0;      /* two S buffers of BN fp32 columns */
   static constexpr int COL_O = 2 * BN; /* the output accumulator, HD fp32 columns */
@@ -87,15 +91,14 @@ struct PrefillArgs {
 };
 
 /* Shared-memory matrix descriptor for tcgen05.mma: 128-byte swizzle, tile base
- * 1024-byte aligned, 8-row groups 1024 bytes apart. */
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((1024u >> 4) & 0x3FFFu) << 32;
-  d |= 1ull << 46; /* descriptor version for sm_100 */
-  d |= 2ull << 61; /* SWIZZLE_128B */
-  return d;
+ * 1024-byte aligned, 8-row groups 1024 bytes apart.  It is built in halves: the
+ * high word is fixed by the layout (group stride, version 1, 128-byte swizzle); the
+ * low word holds the address and the leading-dimension offset, both in 16-byte
+ * units, so moving the start by `bytes` adds bytes / 16 to it (shared-memory
+ * addresses stay below 2^18). */
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
 }
 
 /* Instruction descriptor, kind::f16: fp16 A and B, fp32 D, M x N tile. */
@@ -116,6 +119,15 @@ __device__ __forceinline__ void grid_dependency_wait() {
 __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+
+#ifdef WST_PHASE
+__device__ long long g_phase[32];
+#define PH(i) do { if (lane == 0 && wq == 0 && half == 0) { const long long now_ = clock64(); ph[i] += now_ - ph_t; ph_t = now_; } } while (0)
+#define PM(i) do { if (lane == 0) { const long long now_ = clock64(); pm[i] += now_ - pm_t; pm_t = now_; } } while (0)
+#else
+#define PH(i) do { } while (0)
+#define PM(i) do { } while (0)
+#endif
 
 template <int HD, bool PAGED>
 __global__ void __launch_bounds__(PCfg<HD>::THREADS, 1)
@@ -155,16 +167,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(S_FULL + i), 1);
-      mbar_init(bar(S_FREE + i), 128);
+      mbar_init(bar(S_FREE + i), 256);
     }
-    mbar_init(bar(P_READY), 128);
+    mbar_init(bar(P_READY), 256);
     mbar_init(bar(PV_DONE), 1);
-    mbar_init(bar(Q_READY), 128);
+    mbar_init(bar(Q_READY), 256);
     mbar_init_fence();
     tma_prefetch_desc(&kmap);
     tma_prefetch_desc(&vmap);
   }
-  if (warp == 4) {
+  constexpr int MMA_WARP = 8, TMA_WARP = 9;
+  if (warp == MMA_WARP) {
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -194,7 +207,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   const int n_tiles = split < all_tiles ? (all_tiles - split + ns - 1) / ns : 0;
   auto tile_of = [split, ns](int j) { return split + j * ns; };
 
-  if (warp == 5) {
+  if (warp == TMA_WARP) {
     /* ------------------------------------------------------ TMA producer */
     if (lane == 0) {
       for (int j = 0; j < n_tiles; ++j) {
@@ -246,17 +259,57 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == MMA_WARP) {
     /* -------------------------------------------------------- MMA issuer */
     constexpr uint32_t idesc_qk = umma_idesc(128, BN, 0);
     constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
     bool ok = mbar_wait(bar(Q_READY), 0, a.err_word, 0x210u);
     tc_fence_after_sync();
 
-    auto issue_pv = [&](int i) -> bool {
+    /* One k-step (16 along the contraction) of S(j) = Q K(j)^T and of
+     * O += P V(i); each is a 128 x 128 x 16 MMA, 64 clocks of the tensor pipe. */
+    const uint32_t k_lo0 = umma_desc_lo(sbase + C::OFF_K, 16);
+    const uint32_t v_lo0 = umma_desc_lo(sbase + C::OFF_V, HALF_BYTES);
+    auto s_step = [&](int j, int ks) {
+      const uint32_t off = (j % NSTAGE) * KV_BYTES + (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+      umma_ts_f16_lohi(tmem + C::COL_S + (j & 1) * BN, tmem + C::COL_Q + ks * 8, k_lo0 + (off >> 4),
+                       kDescHi, idesc_qk, ks > 0);
+    };
+    auto pv_step = [&](int i, int kk) {
+      const uint32_t off = (i % NSTAGE) * KV_BYTES + kk * 2048;
+      umma_ts_f16_lohi(tmem + C::COL_O, tmem + C::COL_P + kk * 8, v_lo0 + (off >> 4), kDescHi,
+                       idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+    };
+
+    /* the first two score tiles */
+    for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
+      if (!mbar_wait(bar(K_FULL + j), 0, a.err_word, 0x214u)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) s_step(j, ks);
+        umma_commit(bar(S_FULL + j));
+        umma_commit(bar(K_EMPTY + j));
+      }
+      __syncwarp();
+    }
+
+    /* step i: O += P(i) V(i) as soon as P(i) arrives, then S(i+2) = Q K(i+2)^T into
+     * the score buffer that the softmax of tile i handed back before it sent P(i).
+     * The softmax of tile i+1 runs meanwhile on the other score buffer. */
+#ifdef WST_PHASE
+    long long pm[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long pm_t = clock64();
+#endif
+    for (int i = 0; ok && i < n_tiles; ++i) {
       const int st = i % NSTAGE;
-      if (!mbar_wait(bar(P_READY), i & 1, a.err_word, 0x211u)) return false;
-      if (!mbar_wait(bar(V_FULL + st), (i / NSTAGE) & 1, a.err_word, 0x212u)) return false;
+      const int j = i + 2;
+      const bool has_s = j < n_tiles;
+      /* the operands in shared memory arrive long before P: look at their
+       * barriers first, so that only P(i) is waited for on the critical path */
+      if (!mbar_wait(bar(V_FULL + st), (i / NSTAGE) & 1, a.err_word, 0x212u)) { ok = false; break; }
+      if (has_s &&
+          !mbar_wait(bar(K_FULL + j % NSTAGE), (j / NSTAGE) & 1, a.err_word, 0x214u)) { ok = false; break; }
       const uint32_t vb = sbase + C::OFF_V + st * KV_BYTES;
       /* Cache rows past the live data can hold any bit pattern and 0 * NaN is
        * NaN: clear them in the last tile before the tensor core reads V. */
@@ -272,66 +325,74 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
         fence_async_smem();
         __syncwarp();
       }
+      PM(0);
+      if (!mbar_wait(bar(P_READY), i & 1, a.err_word, 0x211u)) { ok = false; break; }
       tc_fence_after_sync();
+      PM(1);
       if (lane == 0) {
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t bd = umma_desc(vb + kk * 2048, HALF_BYTES);
-          umma_ts_f16(tmem + C::COL_O, tmem + C::COL_P + kk * 8, bd, idesc_pv,
-                      (i > 0 || kk > 0) ? 1u : 0u);
-        }
-        umma_commit(bar(V_EMPTY + st));
+        for (int k = 0; k < BN / 16; ++k) pv_step(i, k);
         umma_commit(bar(PV_DONE));
+        umma_commit(bar(V_EMPTY + st));
       }
       __syncwarp();
-      return true;
+      PM(2);
+      if (has_s) {
+        if (!mbar_wait(bar(S_FREE + (j & 1)), ((j >> 1) - 1) & 1, a.err_word, 0x215u)) { ok = false; break; }
+        tc_fence_after_sync();
+        PM(3);
+        if (lane == 0) {
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k) s_step(j, k);
+          umma_commit(bar(S_FULL + (j & 1)));
+          umma_commit(bar(K_EMPTY + j % NSTAGE));
+        }
+        __syncwarp();
+        PM(4);
+      }
+    }
+#ifdef WST_PHASE
+    if (lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+      for (int i = 0; i < 8; ++i) g_phase[16 + i] = pm[i];
+#endif
+  } else {
+    /* ---- softmax + output: two threads per query row, 64 score columns each.
+     * One warp per scheduler cannot keep the special-function unit busy (the
+     * exponentials and the fp16 packing share it and need about 1000 clocks per
+     * 128 x 128 tile; loads, maxima and waits came on top, one after the other);
+     * with two warps per scheduler one warp's exponentials fill the other's gaps. */
+    constexpr int HB = BN / 2;  /* score columns per thread */
+    constexpr int OC = HD / 2;  /* output columns per thread */
+    const int wq = warp & 3, half = warp >> 2;
+    const int r = wq * 32 + lane; /* query row == TMEM lane */
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    float *xch = reinterpret_cast<float *>(smem + C::OFF_XCH);
+    /* the two warps that share 32 rows meet here; every thread of both executes
+     * every pair_sync of the kernel, whatever else went wrong */
+    auto pair_sync = [wq]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + wq) : "memory"); };
+    /* a barrier wait whose verdict is the same in every lane of the warp */
+    auto wait_all = [&](int which, uint32_t parity, unsigned code) {
+      return __all_sync(0xffffffffu, mbar_wait(bar(which), parity, a.err_word, code)) != 0;
     };
 
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const int st = j % NSTAGE;
-      if (!mbar_wait(bar(K_FULL + st), (j / NSTAGE) & 1, a.err_word, 0x214u)) { ok = false; break; }
-      if (j >= 2 && !mbar_wait(bar(S_FREE + (j & 1)), ((j >> 1) - 1) & 1, a.err_word, 0x215u)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      if (lane == 0) {
-        const uint32_t kb = sbase + C::OFF_K + st * KV_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_ts_f16(tmem + C::COL_S + (j & 1) * BN, tmem + C::COL_Q + ks * 8,
-                      umma_desc(kb + off, 16), idesc_qk, ks > 0);
-        }
-        umma_commit(bar(K_EMPTY + st));
-        umma_commit(bar(S_FULL + (j & 1)));
-      }
-      __syncwarp();
-      if (j >= 1 && !issue_pv(j - 1)) { ok = false; break; }
-    }
-    if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
-  } else {
-    /* ------------------------------------- softmax + output, one row each */
-    const int r = threadIdx.x; /* query row == TMEM lane */
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-
-    /* q row -> fp16 * scale * log2(e), two per 32-bit column of this row's TMEM lane */
+    /* q half-row -> fp16 * scale * log2(e), two per 32-bit column of this row's TMEM lane */
     {
       const bool valid = r < rows_valid;
       const float *src = a.q + static_cast<long long>(tok_base + r / a.gqa) * a.q_tok_stride +
-                         static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD;
+                         static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD + half * OC;
+      constexpr int QC = OC / 2; /* 32-bit columns this thread writes */
+      uint32_t packed[QC];
 #pragma unroll
-      for (int c0 = 0; c0 < HD / 2; c0 += 32) {
-        uint32_t packed[32];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (valid) f = __ldg(reinterpret_cast<const float4 *>(src + 2 * (c0 + e)));
-          packed[e] = pack_half2(f.x * a.qscale, f.y * a.qscale);
-          packed[e + 1] = pack_half2(f.z * a.qscale, f.w * a.qscale);
-        }
-        tmem_st_32x32(tmem + lane_base + C::COL_Q + c0, packed);
+      for (int e = 0; e < QC; e += 2) {
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid) f = __ldg(reinterpret_cast<const float4 *>(src + 2 * e));
+        packed[e] = pack_half2(f.x * a.qscale, f.y * a.qscale);
+        packed[e + 1] = pack_half2(f.z * a.qscale, f.w * a.qscale);
       }
+      if constexpr (QC == 32)
+        tmem_st_32x32(tmem + lane_base + C::COL_Q + half * QC, packed);
+      else
+        tmem_st_32x16(tmem + lane_base + C::COL_Q + half * QC, packed);
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(bar(Q_READY));
@@ -341,52 +402,73 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     /* A warp with no valid query row (a short last tile, or a handful of tokens
      * against a long prefix) only keeps the barrier protocol going: its rows of
      * S, P and O hold garbage that no other row depends on and nobody reads. */
-    const bool live = warp * 32 < rows_valid;
+#ifdef WST_ALL_DEAD
+    const bool live = false;
+#else
+    const bool live = wq * 32 < rows_valid;
+#endif
     float m_ref = -INFINITY; /* exponent offset in use for this row (log2 units) */
-    float l_run = 0.f;
-    bool ok = true;
+    float l_run = 0.f;       /* this thread's share of the row sum */
+    bool ok = true;          /* warp-uniform */
+#ifdef WST_PHASE
+    long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long ph_t = clock64();
+#endif
 
     for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, a.err_word, 0x220u)) { ok = false; break; }
+      if (ok) ok = wait_all(S_FULL + (j & 1), (j >> 1) & 1, 0x220u);
+      PH(0);
       if (!live) {
-        mbar_arrive(bar(S_FREE + (j & 1)));
-        /* not before the previous tile's P has been consumed: an early arrival
-         * would be counted into the phase the live warps have not finished */
-        if (j >= 1 && !mbar_wait(bar(PV_DONE), (j - 1) & 1, a.err_word, 0x224u)) { ok = false; break; }
-        mbar_arrive(bar(P_READY));
+        if (ok) {
+          mbar_arrive(bar(S_FREE + (j & 1)));
+          /* not before the previous tile's P has been consumed: an early arrival
+           * would be counted into the phase the live warps have not finished */
+          if (j >= 1) ok = wait_all(PV_DONE, (j - 1) & 1, 0x224u);
+          if (ok) mbar_arrive(bar(P_READY));
+        }
         continue;
       }
-      tc_fence_after_sync();
-      const uint32_t s_addr = tmem + lane_base + C::COL_S + (j & 1) * BN;
 
-      /* the whole score row into registers, then hand the buffer back at once */
-      uint32_t sv[BN];
+      /* this thread's 64 scores into registers, then hand the buffer back at once */
+      uint32_t sv[HB];
+      float mxh = -INFINITY;
+      if (ok) {
+        tc_fence_after_sync();
+        const uint32_t s_addr = tmem + lane_base + C::COL_S + (j & 1) * BN + half * HB;
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32)
-        tmem_ld_32x32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(bar(S_FREE + (j & 1)));
+        for (int c0 = 0; c0 < HB; c0 += 32)
+          tmem_ld_32x32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(bar(S_FREE + (j & 1)));
 
-      if (tile_of(j) * BN + BN > lim_min) { /* causal edge / end of sequence */
-        const int lim_local = lim - tile_of(j) * BN;
+        if (tile_of(j) * BN + BN > lim_min) { /* causal edge / end of sequence */
+          const int lim_local = lim - tile_of(j) * BN - half * HB;
 #pragma unroll
-        for (int c = 0; c < BN; ++c)
-          if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
+          for (int c = 0; c < HB; ++c)
+            if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < HB; c += 8)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
+        mxh = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
-      /* four independent chains: one warp per scheduler has nothing else to
-       * hide the latency of a 64-deep dependent max (or add) chain behind */
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < BN; c += 8)
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      /* the row maximum needs the other half's */
+      float *slot = xch + (j & 1) * 256;
+      slot[half * 128 + r] = mxh;
+      PH(1);
+      pair_sync();
+      const float mx = fmaxf(mxh, slot[(half ^ 1) * 128 + r]);
+      if (!ok) continue;
+      PH(2);
 
       /* Lazy rescale: keep the old offset unless some row of this warp outgrew
        * it by more than 2^8 (p then stays <= 256, exact enough in fp16 and far
-       * from its range); the vote keeps the protocol warp-uniform. */
+       * from its range); the vote keeps the protocol warp-uniform, and both warps
+       * of a pair see the same rows and the same maxima. */
       const bool grow = j == 0 || mx > m_ref + 8.f;
       const bool warp_grow = __any_sync(0xffffffffu, grow);
       const float m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
@@ -394,7 +476,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
 
       float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < BN; c += 8)
+      for (int c = 0; c < HB; c += 8)
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const float p = ex2(__uint_as_float(sv[c + k]) - m_use);
@@ -402,31 +484,33 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
           sv[c + k] = __float_as_uint(p);
         }
       const float psum = ((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7]));
-
-      /* PV of the previous tile must be finished: it reads P and writes O */
-      if (j >= 1 && !mbar_wait(bar(PV_DONE), (j - 1) & 1, a.err_word, 0x222u)) { ok = false; break; }
-
 #pragma unroll
-      for (int c = 0; c < BN / 2; ++c)
+      for (int c = 0; c < HB / 2; ++c)
         sv[c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
-#pragma unroll
-      for (int c0 = 0; c0 < BN / 2; c0 += 32)
-        tmem_st_32x32(tmem + lane_base + C::COL_P + c0,
-                      *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
 
-      if (warp_grow && j > 0) { /* move this warp's rows of O to the new offsets */
+#ifdef WST_PHASE
+      if (psum == 123.456f) ph[7] += 1;
+#endif
+      PH(3);
+      /* PV of the previous tile must be finished: it reads P and writes O */
+      if (j >= 1) ok = wait_all(PV_DONE, (j - 1) & 1, 0x222u);
+      if (!ok) continue;
+      PH(4);
+      tmem_st_32x32(tmem + lane_base + C::COL_P + half * (HB / 2),
+                    *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+
+      if (warp_grow && j > 0) { /* move this thread's half of the O rows to the new offsets */
         tc_fence_after_sync();
         const float factor = ex2(m_ref - m_use); /* 1 for rows that did not move */
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
+        for (int c0 = 0; c0 < OC; c0 += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(tmem + lane_base + C::COL_O + c0, v);
+          tmem_ld_32x32(tmem + lane_base + C::COL_O + half * OC + c0, v);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
-          tmem_st_32x32(tmem + lane_base + C::COL_O + c0, v);
+          tmem_st_32x32(tmem + lane_base + C::COL_O + half * OC + c0, v);
         }
-        tmem_st_wait();
         l_run *= factor;
       }
       m_ref = m_new;
@@ -435,48 +519,57 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(bar(P_READY));
+      PH(5);
     }
     grid_launch_dependents();
+#ifdef WST_PHASE
+    if (lane == 0 && wq == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+      for (int i = 0; i < 8; ++i) g_phase[i] = ph[i];
+      g_phase[8] = n_tiles;
+    }
+#endif
 
-    if (ok && n_tiles > 0)
-      ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, a.err_word, 0x223u);
-    if (ok && ns > 1) {
+    if (ok && n_tiles > 0) ok = wait_all(PV_DONE, (n_tiles - 1) & 1, 0x223u);
+    if (live) {
+      /* the row sum is the two threads' shares together */
+      float *slot = xch + 512;
+      slot[half * 128 + r] = l_run;
+      pair_sync();
+      l_run += slot[(half ^ 1) * 128 + r];
+    }
+    if (ok && live && ns > 1) {
       /* one slice of a split KV range: this row's (acc, m, l) for the merge kernel,
        * acc[HD] | m | l | pad pad, log2 units (attn_rows.cu reads the same rows) */
       tc_fence_after_sync();
-      if (live) {
-        const long long unit = static_cast<long long>(seq) * a.n_kv + kvh;
-        float *dst = a.scratch + ((unit * ns + split) * a.rows_cap + r) * (HD + 4);
+      const long long unit = static_cast<long long>(seq) * a.n_kv + kvh;
+      float *dst = a.scratch + ((unit * ns + split) * a.rows_cap + r) * (HD + 4) + half * OC;
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t v[32];
-          if (n_tiles > 0) { /* warp-uniform: the load is a warp-wide instruction */
-            tmem_ld_32x32(tmem + lane_base + C::COL_O + c0, v);
-            tmem_ld_wait();
-          } else {
+      for (int c0 = 0; c0 < OC; c0 += 32) {
+        uint32_t v[32];
+        if (n_tiles > 0) { /* warp-uniform: the load is a warp-wide instruction */
+          tmem_ld_32x32(tmem + lane_base + C::COL_O + half * OC + c0, v);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = 0u;
-          }
-          if (r < rows_valid) {
-#pragma unroll
-            for (int e = 0; e < 32; e += 4)
-              *reinterpret_cast<uint4 *>(dst + c0 + e) =
-                  make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-          }
+          for (int e = 0; e < 32; ++e) v[e] = 0u;
         }
-        if (r < rows_valid)
-          *reinterpret_cast<float2 *>(dst + HD) =
-              make_float2(n_tiles > 0 ? m_ref : -INFINITY, l_run);
+        if (r < rows_valid) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            *reinterpret_cast<uint4 *>(dst + c0 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+        }
       }
+      if (half == 0 && r < rows_valid)
+        *reinterpret_cast<float2 *>(dst + HD) = make_float2(n_tiles > 0 ? m_ref : -INFINITY, l_run);
     } else if (ok && live) {
       tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __half *dst = a.out + (static_cast<long long>(tok_base + r / a.gqa) * a.n_q +
-                             (kvh * a.gqa + r % a.gqa)) * HD;
+                             (kvh * a.gqa + r % a.gqa)) * HD + half * OC;
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
+      for (int c0 = 0; c0 < OC; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + C::COL_O + c0, v);
+        tmem_ld_32x32(tmem + lane_base + C::COL_O + half * OC + c0, v);
         tmem_ld_wait();
         if (r < rows_valid) {
 #pragma unroll
@@ -496,7 +589,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   /* common exit: every role gets here, then the allocating warp frees TMEM */
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, C::TMEM_COLS);
   }
@@ -528,14 +621,18 @@ struct P2Cfg {
   static constexpr int HALF_BYTES = BN * 128;
   static constexpr int Q_BYTES = NH * HALF_BYTES;   /* one query tile */
   static constexpr int KV_BYTES = NH * HALF_BYTES;
-  static constexpr int NSTAGE = 2;
+  /* K and V tiles go through ONE ring in the order they are consumed, K(0) V(0)
+   * K(1) V(1) ...: next to the two query tiles shared memory has room for five
+   * 32 KB slots (head_dim 128), and five slots in one ring keep two and a half
+   * KV tiles in flight where separate K and V rings could hold two each at most;
+   * a tile takes some 2500 clocks to arrive from L2. */
+  static constexpr int NSLOT = HD == 128 ? 5 : 8;
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + 2 * Q_BYTES;
-  static constexpr int OFF_V = OFF_K + NSTAGE * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_V + NSTAGE * KV_BYTES;
-  static constexpr int NBAR = 4 * NSTAGE + 2 + 2 + 2 + 1;
+  static constexpr int OFF_RING = OFF_Q + 2 * Q_BYTES;
+  static constexpr int OFF_BAR = OFF_RING + NSLOT * KV_BYTES;
+  static constexpr int NBAR = 2 * NSLOT + 2 + 2 + 2 + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
-  static constexpr int THREADS = 320; /* 2 x 4 softmax warps, MMA warp, TMA warp */
+  static constexpr int THREADS = 320; /* 2 x 4 softmax warps, MMA warp, TMA warp: 204 registers each */
   static constexpr int COL_S = 0;     /* S_i at COL_S + i*128, P_i over its first 64 columns */
   static constexpr int COL_O = 256;   /* O_i at COL_O + i*128 */
   static constexpr int TMEM_COLS = 512;
@@ -546,7 +643,7 @@ __global__ void __launch_bounds__(P2Cfg<HD>::THREADS, 1)
 attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
                          const __grid_constant__ CUtensorMap vmap, const PrefillArgs a) {
   using C = P2Cfg<HD>;
-  constexpr int BN = C::BN, NH = C::NH, NSTAGE = C::NSTAGE;
+  constexpr int BN = C::BN, NH = C::NH, NSLOT = C::NSLOT;
   constexpr int HALF_BYTES = C::HALF_BYTES, KV_BYTES = C::KV_BYTES;
 
   extern __shared__ uint8_t smem_raw[];
@@ -555,8 +652,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + C::OFF_BAR;
   auto bar = [bar0](int i) { return bar0 + 8u * i; };
-  constexpr int K_FULL = 0, V_FULL = NSTAGE, K_EMPTY = 2 * NSTAGE, V_EMPTY = 3 * NSTAGE;
-  constexpr int S_FULL = 4 * NSTAGE, P_READY = S_FULL + 2, O_DONE = P_READY + 2;
+  /* ring item 2j is K(j), item 2j+1 is V(j); item i lives in slot i % NSLOT */
+  constexpr int FULL = 0, EMPTY = NSLOT;
+  constexpr int S_FULL = 2 * NSLOT, P_READY = S_FULL + 2, O_DONE = P_READY + 2;
   constexpr int Q_READY = O_DONE + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + C::OFF_BAR + C::NBAR * 8);
 
@@ -567,11 +665,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
   const int seq = blockIdx.z;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NSTAGE; ++i) {
-      mbar_init(bar(K_FULL + i), 1);
-      mbar_init(bar(V_FULL + i), 1);
-      mbar_init(bar(K_EMPTY + i), 1);
-      mbar_init(bar(V_EMPTY + i), 1);
+    for (int i = 0; i < NSLOT; ++i) {
+      mbar_init(bar(FULL + i), 1);
+      mbar_init(bar(EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(S_FULL + i), 1);
@@ -614,22 +710,15 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
   if (warp == 9) {
     /* ------------------------------------------------------ TMA producer */
     if (lane == 0) {
-      for (int j = 0; j < T; ++j) {
-        const int st = j % NSTAGE, round = j / NSTAGE;
-        if (j >= NSTAGE && !mbar_wait(bar(K_EMPTY + st), (round - 1) & 1, a.err_word, 0x301u))
+      for (int i = 0; i < 2 * T; ++i) {
+        const int slot = i % NSLOT, round = i / NSLOT, j = i >> 1;
+        if (i >= NSLOT && !mbar_wait(bar(EMPTY + slot), (round - 1) & 1, a.err_word, 0x301u))
           break;
-        mbar_arrive_expect_tx(bar(K_FULL + st), KV_BYTES);
+        mbar_arrive_expect_tx(bar(FULL + slot), KV_BYTES);
 #pragma unroll
         for (int h = 0; h < NH; ++h)
-          tma_load_3d(sbase + C::OFF_K + st * KV_BYTES + h * HALF_BYTES, &kmap, bar(K_FULL + st),
-                      h * 64, j * BN, plane);
-        if (j >= NSTAGE && !mbar_wait(bar(V_EMPTY + st), (round - 1) & 1, a.err_word, 0x302u))
-          break;
-        mbar_arrive_expect_tx(bar(V_FULL + st), KV_BYTES);
-#pragma unroll
-        for (int h = 0; h < NH; ++h)
-          tma_load_3d(sbase + C::OFF_V + st * KV_BYTES + h * HALF_BYTES, &vmap, bar(V_FULL + st),
-                      h * 64, j * BN, plane);
+          tma_load_3d(sbase + C::OFF_RING + slot * KV_BYTES + h * HALF_BYTES, (i & 1) ? &vmap : &kmap,
+                      bar(FULL + slot), h * 64, j * BN, plane);
       }
     }
   } else if (warp == 8) {
@@ -640,25 +729,23 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     tc_fence_after_sync();
 
     auto issue_s = [&](int t, int j) { /* S_t = Q_t K(j)^T */
-      const int st = j % NSTAGE;
       if (lane == 0) {
-        const uint32_t qb = sbase + C::OFF_Q + t * C::Q_BYTES;
-        const uint32_t kb = sbase + C::OFF_K + st * KV_BYTES;
+        const uint32_t q_lo = umma_desc_lo(sbase + C::OFF_Q + t * C::Q_BYTES, 16);
+        const uint32_t k_lo = umma_desc_lo(sbase + C::OFF_RING + ((2 * j) % NSLOT) * KV_BYTES, 16);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_ss_f16(tmem + C::COL_S + t * 128, umma_desc(qb + off, 16), umma_desc(kb + off, 16),
-                      idesc_qk, ks > 0);
+          const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
+          umma_ss_f16_lohi(tmem + C::COL_S + t * 128, q_lo + off, k_lo + off, kDescHi, idesc_qk,
+                           ks > 0);
         }
         umma_commit(bar(S_FULL + t));
       }
       __syncwarp();
     };
     auto issue_pv = [&](int t, int j) -> bool { /* O_t += P_t V(j) */
-      const int st = j % NSTAGE;
-      if (!mbar_wait(bar(P_READY + t), j & 1, a.err_word, 0x311u)) return false;
-      if (!mbar_wait(bar(V_FULL + st), (j / NSTAGE) & 1, a.err_word, 0x312u)) return false;
-      const uint32_t vb = sbase + C::OFF_V + st * KV_BYTES;
+      const int item = 2 * j + 1;
+      if (!mbar_wait(bar(FULL + item % NSLOT), (item / NSLOT) & 1, a.err_word, 0x312u)) return false;
+      const uint32_t vb = sbase + C::OFF_RING + (item % NSLOT) * KV_BYTES;
       /* rows past the live data may hold anything and 0 * NaN is NaN: clear them
        * once, before the first PV that reads this tile */
       const bool first_use = t == 0 || j >= n_tiles[0];
@@ -674,36 +761,53 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
         fence_async_smem();
         __syncwarp();
       }
+      if (!mbar_wait(bar(P_READY + t), j & 1, a.err_word, 0x311u)) return false;
       tc_fence_after_sync();
       if (lane == 0) {
+        const uint32_t v_lo = umma_desc_lo(vb, HALF_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          umma_ts_f16(tmem + C::COL_O + t * 128, tmem + C::COL_S + t * 128 + kk * 8,
-                      umma_desc(vb + kk * 2048, HALF_BYTES), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_f16_lohi(tmem + C::COL_O + t * 128, tmem + C::COL_S + t * 128 + kk * 8,
+                           v_lo + ((kk * 2048) >> 4), kDescHi, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         if (j == n_tiles[t] - 1) umma_commit(bar(O_DONE + t));
       }
       __syncwarp();
       return true;
     };
 
+#ifdef WST_PHASE
+    long long pm[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long pm_t = clock64();
+#endif
     for (int j = 0; ok && j <= T; ++j) {
       if (j < T) {
-        if (!mbar_wait(bar(K_FULL + j % NSTAGE), (j / NSTAGE) & 1, a.err_word, 0x314u)) break;
+        if (!mbar_wait(bar(FULL + (2 * j) % NSLOT), ((2 * j) / NSLOT) & 1, a.err_word, 0x314u)) break;
         tc_fence_after_sync();
       }
+      PM(0);
       if (j < n_tiles[0]) issue_s(0, j);
+      PM(1);
       if (j >= 1 && j - 1 < n_tiles[1]) {
         if (!issue_pv(1, j - 1)) break;
-        if (lane == 0) umma_commit(bar(V_EMPTY + (j - 1) % NSTAGE)); /* last reader of V(j-1) */
+        if (lane == 0) umma_commit(bar(EMPTY + (2 * j - 1) % NSLOT)); /* last reader of V(j-1) */
         __syncwarp();
       }
+      PM(2);
       if (j < n_tiles[1]) {
         issue_s(1, j);
-        if (lane == 0) umma_commit(bar(K_EMPTY + j % NSTAGE)); /* last reader of K(j) */
+        if (lane == 0) umma_commit(bar(EMPTY + (2 * j) % NSLOT)); /* last reader of K(j) */
         __syncwarp();
       }
+      PM(3);
       if (j < n_tiles[0] && !issue_pv(0, j)) break;
+      PM(4);
     }
+#ifdef WST_PHASE
+    if (lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+      for (int i = 0; i < 8; ++i) g_phase[16 + i] = pm[i];
+      g_phase[8] = T;
+    }
+#endif
   } else {
     /* --------------------------- softmax + output: warpgroup t owns tile t */
     const int t = warp >> 2;
@@ -741,38 +845,67 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     const int lim_min = min(pos0 + tok0[t] + 1, a.max_seq);
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
+#ifdef WST_PHASE
+    long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long ph_t = clock64();
+    const int wq = warp, half = 0;
+#endif
 
     for (int j = 0; j < n_tiles[t]; ++j) {
       if (!mbar_wait(bar(S_FULL + t), j & 1, a.err_word, 0x320u)) { ok = false; break; }
+      PH(0);
       tc_fence_after_sync();
       const bool masked = j * BN + BN > lim_min;
       const int lim_local = lim - j * BN;
 
-      /* pass 1: row maximum, 64 columns at a time (the whole row would not fit in
-       * the registers 320 threads leave each other) */
+      /* the whole score row into registers: one read of tensor memory, and P can
+       * then go over the first 64 columns of S at once */
+      uint32_t sv[BN];
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32)
+        tmem_ld_32x32(s_col + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+      tmem_ld_wait();
+      if (masked) {
+#pragma unroll
+        for (int c = 0; c < BN; ++c)
+          if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t sv[64];
-        tmem_ld_32x32(s_col + h * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-        tmem_ld_32x32(s_col + h * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-        tmem_ld_wait();
-        if (masked) {
+      for (int c = 0; c < BN; c += 8)
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (h * 64 + c >= lim_local) sv[c] = 0xff800000u;
-        }
-#pragma unroll
-        for (int c = 0; c < 64; c += 8)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
-      }
+        for (int k = 0; k < 4; ++k)
+          mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+#ifdef WST_PHASE
+      if (mx == 123.456f) ph[7] += 1;
+#endif
+      PH(1);
       const bool grow = j == 0 || mx > m_ref + 8.f; /* lazy rescale, see the one-tile kernel */
       const bool warp_grow = __any_sync(0xffffffffu, grow);
       const float m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
+
+      float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < BN; c += 8)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float p = ex2(__uint_as_float(sv[c + k]) - m_use);
+          ps8[k] += p;
+          sv[c + k] = __float_as_uint(p);
+        }
+      const float psum = ((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7]));
+#pragma unroll
+      for (int c = 0; c < BN / 2; ++c)
+        sv[c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
+#ifdef WST_PHASE
+      if (psum == 123.456f) ph[7] += 1;
+#endif
+      PH(3);
+#pragma unroll
+      for (int c0 = 0; c0 < BN / 2; c0 += 32)
+        tmem_st_32x32(s_col + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
 
       /* S_t(j) is complete, and it was issued after PV_t(j-1): O_t is quiescent */
       if (warp_grow && j > 0) {
@@ -789,38 +922,17 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
         l_run *= factor;
       }
       m_ref = m_new;
-
-      /* pass 2: p = 2^(s - m), row sum, fp16 pairs; both halves are read before P
-       * is stored over the first 64 columns of S */
-      uint32_t pk[64];
-      float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t sv[64];
-        tmem_ld_32x32(s_col + h * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-        tmem_ld_32x32(s_col + h * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 64; c += 8)
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            float p = ex2(__uint_as_float(sv[c + k]) - m_use);
-            if (masked && h * 64 + c + k >= lim_local) p = 0.f;
-            ps8[k] += p;
-            sv[c + k] = __float_as_uint(p);
-          }
-#pragma unroll
-        for (int c = 0; c < 32; ++c)
-          pk[h * 32 + c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
-      }
-      l_run += ((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7]));
-      tmem_st_32x32(s_col, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
-      tmem_st_32x32(s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+      l_run += psum;
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(bar(P_READY + t));
+      PH(5);
     }
     grid_launch_dependents();
+#ifdef WST_PHASE
+    if (lane == 0 && warp == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+      for (int i = 0; i < 8; ++i) g_phase[i] = ph[i];
+#endif
 
     if (ok && n_tiles[t] > 0) ok = mbar_wait(bar(O_DONE + t), 0, a.err_word, 0x323u);
     if (ok && rows_valid > 0) {
@@ -911,6 +1023,14 @@ bool prefill_kernel_supports(int n_q, int n_kv, int hd, int n) {
   return static_cast<long long>(n) * gqa >= 64;
 }
 
+#ifdef WST_PHASE
+}  // namespace wst
+extern "C" __attribute__((visibility("default"))) int wst_b200_phase_read(long long *dst) {
+  return static_cast<int>(cudaMemcpyFromSymbol(dst, wst::g_phase, sizeof(long long) * 32));
+}
+namespace wst {
+#endif
+
 bool prefill_split_supports(int n_q, int n_kv, int hd, int n_tok_max) {
   if (hd != 64 && hd != 128) return false;
   if (n_kv <= 0 || n_q % n_kv != 0) return false;
@@ -980,13 +1100,14 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   st = cached_kv_tensor_map(&vmap, key);
   if (st != WST_OK) return st;
 
-  /* One tile per CTA by default.  The two-tile schedule measures the same per
-   * tile (1.18 us against 1.15 us on the 8192-token, 32-head shape): both are
-   * bound by the softmax's exponentials, 16 per clock and SM, and the second
-   * warpgroup shares that unit.  It is kept selectable because it halves the
-   * K/V traffic from L2 and is the schedule that pays once part of the
-   * exponentials moves to the FMA pipes. */
-  const bool pair = P.force_pair > 0 && splits == 1 && !P.page_table && !P.cu_tokens;
+  /* Two query tiles per CTA whenever there are two: the tiles' softmax warpgroups
+   * and MMAs overlap (835 against 729 TFLOP/s on the 4 x 8192-token, 32-head
+   * shape) and every K/V tile fetched from L2 serves 256 query rows.  The one-tile
+   * kernel takes what is left: launches too small to fill the GPU with pairs, paged
+   * caches, ragged batches and the sliced form. */
+  const bool enough = units * a.n_qtiles >= 2ll * facts.sm_count;
+  const bool pair = P.force_pair >= 0 && (P.force_pair > 0 || (a.n_qtiles >= 2 && enough)) &&
+                    splits == 1 && !P.page_table && !P.cu_tokens;
   const unsigned gx = splits > 1 ? splits : (pair ? (a.n_qtiles + 1) / 2 : a.n_qtiles);
   const dim3 grid(gx, static_cast<unsigned>(P.n_kv), static_cast<unsigned>(P.n_seq));
   if (pair)

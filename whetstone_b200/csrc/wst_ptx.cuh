@@ -145,6 +145,22 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+/* 2^x on the FMA and integer pipes instead of the special-function unit (which
+ * delivers 16 results per clock and SM and is what bounds a softmax over
+ * 128-wide tiles).  round-to-nearest split x = n + f, f in [-0.5, 0.5]; a cubic
+ * for 2^f (minimax in relative error, 7.5e-5 -- below half an fp16 ulp of the
+ * probability it becomes); n is added into the exponent field.  x is clamped at
+ * -125, so -inf (a masked score) gives 2^-125, which rounds to 0 in fp16. */
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f; /* 1.5 * 2^23: round(x) lands in the low mantissa bits */
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(0.0551716685f, f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 /* --------------------------------------------------------------- tcgen05 */
 
 /* Allocates `cols` (power of two, 32..512) tensor-memory columns; one full warp
@@ -191,6 +207,33 @@ __device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, ui
       : "memory");
 }
 
+/* The same two with the shared-memory descriptor given as its two 32-bit halves:
+ * the high half is a constant of the layout, the low half is a base plus a small
+ * offset per k-step, so the issuing thread spends one add per MMA on it. */
+__device__ __forceinline__ void umma_ss_f16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                 uint32_t desc_hi, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_f16_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                                 uint32_t desc_hi, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 /* Arrives on `bar` once every tcgen05.mma issued so far by this thread is done. */
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -223,6 +266,15 @@ __device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)
                "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
                "r"(r[7])
                : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+      "r"(r[15])
+      : "memory");
 }
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
