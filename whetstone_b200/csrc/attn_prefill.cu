@@ -120,14 +120,6 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-#ifdef WST_PHASE
-__device__ long long g_phase[32];
-#define PH(i) do { if (lane == 0 && wq == 0 && half == 0) { const long long now_ = clock64(); ph[i] += now_ - ph_t; ph_t = now_; } } while (0)
-#define PM(i) do { if (lane == 0) { const long long now_ = clock64(); pm[i] += now_ - pm_t; pm_t = now_; } } while (0)
-#else
-#define PH(i) do { } while (0)
-#define PM(i) do { } while (0)
-#endif
 
 template <int HD, bool PAGED>
 __global__ void __launch_bounds__(PCfg<HD>::THREADS, 1)
@@ -297,10 +289,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     /* step i: O += P(i) V(i) as soon as P(i) arrives, then S(i+2) = Q K(i+2)^T into
      * the score buffer that the softmax of tile i handed back before it sent P(i).
      * The softmax of tile i+1 runs meanwhile on the other score buffer. */
-#ifdef WST_PHASE
-    long long pm[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long pm_t = clock64();
-#endif
     for (int i = 0; ok && i < n_tiles; ++i) {
       const int st = i % NSTAGE;
       const int j = i + 2;
@@ -325,10 +313,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
         fence_async_smem();
         __syncwarp();
       }
-      PM(0);
       if (!mbar_wait(bar(P_READY), i & 1, a.err_word, 0x211u)) { ok = false; break; }
       tc_fence_after_sync();
-      PM(1);
       if (lane == 0) {
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) pv_step(i, k);
@@ -336,11 +322,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
         umma_commit(bar(V_EMPTY + st));
       }
       __syncwarp();
-      PM(2);
       if (has_s) {
         if (!mbar_wait(bar(S_FREE + (j & 1)), ((j >> 1) - 1) & 1, a.err_word, 0x215u)) { ok = false; break; }
         tc_fence_after_sync();
-        PM(3);
         if (lane == 0) {
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) s_step(j, k);
@@ -348,13 +332,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
           umma_commit(bar(K_EMPTY + j % NSTAGE));
         }
         __syncwarp();
-        PM(4);
       }
     }
-#ifdef WST_PHASE
-    if (lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-      for (int i = 0; i < 8; ++i) g_phase[16 + i] = pm[i];
-#endif
   } else {
     /* ---- softmax + output: two threads per query row, 64 score columns each.
      * One warp per scheduler cannot keep the special-function unit busy (the
@@ -402,22 +381,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     /* A warp with no valid query row (a short last tile, or a handful of tokens
      * against a long prefix) only keeps the barrier protocol going: its rows of
      * S, P and O hold garbage that no other row depends on and nobody reads. */
-#ifdef WST_ALL_DEAD
-    const bool live = false;
-#else
     const bool live = wq * 32 < rows_valid;
-#endif
     float m_ref = -INFINITY; /* exponent offset in use for this row (log2 units) */
     float l_run = 0.f;       /* this thread's share of the row sum */
     bool ok = true;          /* warp-uniform */
-#ifdef WST_PHASE
-    long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long ph_t = clock64();
-#endif
 
     for (int j = 0; j < n_tiles; ++j) {
       if (ok) ok = wait_all(S_FULL + (j & 1), (j >> 1) & 1, 0x220u);
-      PH(0);
       if (!live) {
         if (ok) {
           mbar_arrive(bar(S_FREE + (j & 1)));
@@ -459,11 +429,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       /* the row maximum needs the other half's */
       float *slot = xch + (j & 1) * 256;
       slot[half * 128 + r] = mxh;
-      PH(1);
       pair_sync();
       const float mx = fmaxf(mxh, slot[(half ^ 1) * 128 + r]);
       if (!ok) continue;
-      PH(2);
 
       /* Lazy rescale: keep the old offset unless some row of this warp outgrew
        * it by more than 2^8 (p then stays <= 256, exact enough in fp16 and far
@@ -488,14 +456,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       for (int c = 0; c < HB / 2; ++c)
         sv[c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
 
-#ifdef WST_PHASE
-      if (psum == 123.456f) ph[7] += 1;
-#endif
-      PH(3);
       /* PV of the previous tile must be finished: it reads P and writes O */
       if (j >= 1) ok = wait_all(PV_DONE, (j - 1) & 1, 0x222u);
       if (!ok) continue;
-      PH(4);
       tmem_st_32x32(tmem + lane_base + C::COL_P + half * (HB / 2),
                     *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
 
@@ -519,15 +482,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(bar(P_READY));
-      PH(5);
     }
     grid_launch_dependents();
-#ifdef WST_PHASE
-    if (lane == 0 && wq == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-      for (int i = 0; i < 8; ++i) g_phase[i] = ph[i];
-      g_phase[8] = n_tiles;
-    }
-#endif
 
     if (ok && n_tiles > 0) ok = wait_all(PV_DONE, (n_tiles - 1) & 1, 0x223u);
     if (live) {
@@ -775,39 +731,24 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
       return true;
     };
 
-#ifdef WST_PHASE
-    long long pm[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long pm_t = clock64();
-#endif
     for (int j = 0; ok && j <= T; ++j) {
       if (j < T) {
         if (!mbar_wait(bar(FULL + (2 * j) % NSLOT), ((2 * j) / NSLOT) & 1, a.err_word, 0x314u)) break;
         tc_fence_after_sync();
       }
-      PM(0);
       if (j < n_tiles[0]) issue_s(0, j);
-      PM(1);
       if (j >= 1 && j - 1 < n_tiles[1]) {
         if (!issue_pv(1, j - 1)) break;
         if (lane == 0) umma_commit(bar(EMPTY + (2 * j - 1) % NSLOT)); /* last reader of V(j-1) */
         __syncwarp();
       }
-      PM(2);
       if (j < n_tiles[1]) {
         issue_s(1, j);
         if (lane == 0) umma_commit(bar(EMPTY + (2 * j) % NSLOT)); /* last reader of K(j) */
         __syncwarp();
       }
-      PM(3);
       if (j < n_tiles[0] && !issue_pv(0, j)) break;
-      PM(4);
     }
-#ifdef WST_PHASE
-    if (lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-      for (int i = 0; i < 8; ++i) g_phase[16 + i] = pm[i];
-      g_phase[8] = T;
-    }
-#endif
   } else {
     /* --------------------------- softmax + output: warpgroup t owns tile t */
     const int t = warp >> 2;
@@ -845,15 +786,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     const int lim_min = min(pos0 + tok0[t] + 1, a.max_seq);
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
-#ifdef WST_PHASE
-    long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long ph_t = clock64();
-    const int wq = warp, half = 0;
-#endif
 
     for (int j = 0; j < n_tiles[t]; ++j) {
       if (!mbar_wait(bar(S_FULL + t), j & 1, a.err_word, 0x320u)) { ok = false; break; }
-      PH(0);
       tc_fence_after_sync();
       const bool masked = j * BN + BN > lim_min;
       const int lim_local = lim - j * BN;
@@ -877,10 +812,6 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
         for (int k = 0; k < 4; ++k)
           mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-#ifdef WST_PHASE
-      if (mx == 123.456f) ph[7] += 1;
-#endif
-      PH(1);
       const bool grow = j == 0 || mx > m_ref + 8.f; /* lazy rescale, see the one-tile kernel */
       const bool warp_grow = __any_sync(0xffffffffu, grow);
       const float m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
@@ -899,10 +830,6 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
       for (int c = 0; c < BN / 2; ++c)
         sv[c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
-#ifdef WST_PHASE
-      if (psum == 123.456f) ph[7] += 1;
-#endif
-      PH(3);
 #pragma unroll
       for (int c0 = 0; c0 < BN / 2; c0 += 32)
         tmem_st_32x32(s_col + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
@@ -926,13 +853,8 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(bar(P_READY + t));
-      PH(5);
     }
     grid_launch_dependents();
-#ifdef WST_PHASE
-    if (lane == 0 && warp == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-      for (int i = 0; i < 8; ++i) g_phase[i] = ph[i];
-#endif
 
     if (ok && n_tiles[t] > 0) ok = mbar_wait(bar(O_DONE + t), 0, a.err_word, 0x323u);
     if (ok && rows_valid > 0) {
@@ -1023,13 +945,6 @@ bool prefill_kernel_supports(int n_q, int n_kv, int hd, int n) {
   return static_cast<long long>(n) * gqa >= 64;
 }
 
-#ifdef WST_PHASE
-}  // namespace wst
-extern "C" __attribute__((visibility("default"))) int wst_b200_phase_read(long long *dst) {
-  return static_cast<int>(cudaMemcpyFromSymbol(dst, wst::g_phase, sizeof(long long) * 32));
-}
-namespace wst {
-#endif
 
 bool prefill_split_supports(int n_q, int n_kv, int hd, int n_tok_max) {
   if (hd != 64 && hd != 128) return false;
