@@ -441,6 +441,84 @@ def bench_also(torch, args):
     return out
 
 
+def bench_reference_cuda(torch):
+    """The engine's own CUDA kernels (built unmodified for sm_100a into oracle/_ref/
+    by oracle/Makefile) timed on the same GPU and the same buffer shapes: a reported
+    baseline beside the library's numbers, never part of the measured path.  They
+    launch on their own per-thread stream, so they are timed by the host clock over a
+    batch of calls with a device synchronize on both sides."""
+    import ctypes
+    from whetstone_b200 import decode, workloads as wl
+    from whetstone_b200._ffi import SIGNATURES
+
+    path = ROOT / "oracle" / "_ref" / "libwhetstone_ref.so"
+    if not path.exists():
+        return {"unavailable": "oracle/_ref/libwhetstone_ref.so not built"}
+    ref = ctypes.CDLL(str(path))
+    for name in ("wst_attn_decode", "wst_attn_partial_floats", "wst_attn_chunk",
+                 "wst_device_synchronize"):
+        fn = getattr(ref, name)
+        fn.restype, fn.argtypes = SIGNATURES[name]
+
+    def ptr(t):
+        return ctypes.c_void_p(t.data_ptr())
+
+    def timed(call, reps):
+        for _ in range(3):
+            call()
+        ref.wst_device_synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            call()
+        ref.wst_device_synchronize()
+        return (time.perf_counter() - t0) / reps
+
+    out = {"how": "host clock over a batch of calls, device synchronize on both sides"}
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    for key, s, ctx, reps in (("c1_decode_us", wl.QWEN25_05B, 513, 200),
+                              ("c3_decode_us", wl.QWEN25_7B, wl.C3["context"], 50)):
+        cache = decode.KvCache(s.n_kv, s.n_q, s.head_dim, ctx)
+        # distinct caches per call, so that the 126 MB L2 does not serve the re-reads
+        caches = [cache] + [decode.KvCache(s.n_kv, s.n_q, s.head_dim, ctx) for _ in range(3)]
+        for c in caches:
+            c.k.copy_(torch.randn(c.k.shape, generator=gen, device="cuda", dtype=torch.float16))
+            c.v.copy_(torch.randn(c.v.shape, generator=gen, device="cuda", dtype=torch.float16))
+        q = torch.randn(s.qkv_width, generator=gen, device="cuda")
+        o = torch.zeros(s.n_q * s.head_dim, dtype=torch.float16, device="cuda")
+        scratch = torch.zeros(max(ref.wst_attn_partial_floats(s.n_q, s.head_dim, ctx), 1),
+                              dtype=torch.float32, device="cuda")
+        cur = decode.DeviceCursor(ctx - 1)
+        torch.cuda.synchronize()
+        state = {"i": 0}
+
+        def call():
+            c = caches[state["i"] % len(caches)]
+            state["i"] += 1
+            ref.wst_attn_decode(ptr(q), ptr(c.k), ptr(c.v), ptr(scratch), ptr(o), s.n_q, s.n_kv,
+                                s.head_dim, ptr(cur.buf), ctx, s.scale)
+        out[key] = timed(call, reps) * 1e6
+        if key == "c3_decode_us":
+            out["c3_decode_gbs"] = wl.decode_bytes(s.n_q, s.n_kv, s.head_dim, ctx) / out[key] / 1e3
+        del caches, cache
+
+    # prefill: the last 512-token chunk of one c4 sequence (the whole config would
+    # take the scalar kernel seconds per layer)
+    s = wl.QWEN3_8B
+    n, prompt = wl.C4["chunk"], wl.C4["prompt"]
+    cache = decode.KvCache(s.n_kv, s.n_q, s.head_dim, prompt)
+    cache.k.copy_(torch.randn(cache.k.shape, generator=gen, device="cuda", dtype=torch.float16))
+    cache.v.copy_(torch.randn(cache.v.shape, generator=gen, device="cuda", dtype=torch.float16))
+    qkv = torch.randn(n, s.qkv_width, generator=gen, device="cuda")
+    o = torch.zeros(n * s.n_q * s.head_dim, dtype=torch.float16, device="cuda")
+    pos0 = prompt - n
+    torch.cuda.synchronize()
+    sec = timed(lambda: ref.wst_attn_chunk(ptr(qkv), ptr(cache.k), ptr(cache.v), ptr(o), s.n_q,
+                                           s.n_kv, s.head_dim, pos0, n, prompt, s.scale), 3)
+    out["c4_last_chunk_one_sequence_ms"] = sec * 1e3
+    out["c4_last_chunk_tflops"] = wl.prefill_flops(s.n_q, s.head_dim, pos0, n) / sec / 1e12
+    return out
+
+
 def run_ours(args):
     import torch
 
@@ -457,6 +535,9 @@ def run_ours(args):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
 
+    if args.only == "refcuda":
+        print(json.dumps({"only": "refcuda", "result": bench_reference_cuda(torch)}))
+        return
     if args.only not in (None, "c3"):
         # a single secondary workload, for profiling: prints its own small JSON line
         print(json.dumps({"only": args.only, "result": bench_also(torch, args)}))
@@ -464,8 +545,10 @@ def run_ours(args):
     res = bench_c3(torch, args, rank, world, dist)
     also = None
     cpu = None
+    refcuda = None
     if world == 1 and not args.no_also and args.only is None:
         also = bench_also(torch, args)
+        refcuda = bench_reference_cuda(torch)
     if world == 1 and rank == 0 and not args.no_cpu:
         gbs, layers, spent = cpu_decode_sample()
         cpu = {"value": gbs, "unit": UNIT, "cores": len(os.sched_getaffinity(0)), "kind": "port",
@@ -490,6 +573,8 @@ def run_ours(args):
             line["cpu_baseline"] = cpu
         if also:
             line["also"] = also
+        if refcuda:
+            line["reference_cuda_kernels"] = refcuda
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
@@ -504,7 +589,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip configs c1, c2, c4, c5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5"],
+    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "refcuda"],
                     help="run one workload only (c3 = the headline line without 'also')")
     ap.add_argument("--c4-layers", type=int, default=1)
     ap.add_argument("--c5-layers", type=int, default=4)
