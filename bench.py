@@ -40,7 +40,7 @@ UNIT = "GB/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel on
 # the c3 shape, from the ncu capture summarised in profiles/ (None until captured).
-NCU_DECODE_TRAFFIC_BYTES = None
+NCU_DECODE_TRAFFIC_BYTES = 67_760_000
 
 
 def peaks():
@@ -216,7 +216,7 @@ def bench_c3(torch, args, rank, world, dist):
         outs.append(torch.zeros(s.n_q * s.head_dim, dtype=torch.float16, device="cuda"))
     cursor = decode.DeviceCursor(per - 1)   # the new token is the shard's last row
     length = torch.tensor([per], dtype=torch.int32, device="cuda")
-    launches_per_step = layers
+    launches_per_step = 2 * layers          # slices kernel + merge kernel per layer
 
     if world == 1:
         def step():
@@ -227,7 +227,7 @@ def bench_c3(torch, args, rank, world, dist):
                 for _ in range(layers)]
         gathered = [torch.zeros((world, s.n_q, s.head_dim + 2), dtype=torch.float32,
                                 device="cuda") for _ in range(layers)]
-        launches_per_step = 2 * layers
+        launches_per_step = 3 * layers      # + the cross-rank merge; NCCL's kernels not counted
 
         def step():
             for i in range(layers):
