@@ -227,13 +227,38 @@ def bench_c3(torch, args, rank, world, dist):
                 for _ in range(layers)]
         gathered = [torch.zeros((world, s.n_q, s.head_dim + 2), dtype=torch.float32,
                                 device="cuda") for _ in range(layers)]
-        launches_per_step = 3 * layers      # + the cross-rank merge; NCCL's kernels not counted
+        launches_per_step = 3 * layers      # slices, slice merge, cross-rank exchange + merge
+        from whetstone_b200 import sharded
+        xch = sharded.PeerExchange(s.n_q, s.head_dim)
 
-        def step():
+        def step():         # the triples cross NVLink inside wst_attn_exchange_merge
+            for i in range(layers):
+                decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
+                xch.merge(mine[i], outs[i])
+
+        def step_nccl():    # the same with an NCCL all-gather and the local merge kernel
             for i in range(layers):
                 decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
                 dist.all_gather_into_tensor(gathered[i].view(-1, s.head_dim + 2), mine[i])
                 decode.attn_merge_partials(gathered[i], outs[i], s.n_q, s.head_dim)
+
+    exchange_note = None
+    if world > 1:
+        # both merges must agree before either is timed
+        step_nccl()
+        torch.cuda.synchronize()
+        want = [o.clone() for o in outs]
+        for o in outs:
+            o.zero_()
+        step()
+        torch.cuda.synchronize()
+        bad = torch.tensor([float(decode.device_error() != 0 or any(
+            (a.float() - b.float()).abs().max().item() > 2e-3 for a, b in zip(outs, want)))],
+            device="cuda")
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if bad.item() != 0:
+            exchange_note = "peer-memory exchange disagreed with the NCCL merge: NCCL variant timed"
+            step, step_nccl = step_nccl, step
 
     with ClockSampler(torch.cuda.current_device()) as clk:
         sec = timed_graph(torch, step, args.steps, args.warmup, dist if world > 1 else None)
@@ -261,8 +286,7 @@ def bench_c3(torch, args, rank, world, dist):
                 if rank == world - 1:   # the shard that owns the newest position appends
                     decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cursor)
                 decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
-                dist.all_gather_into_tensor(gathered[i].view(-1, s.head_dim + 2), mine[i])
-                decode.attn_merge_partials(gathered[i], outs[i], s.n_q, s.head_dim)
+                xch.merge(mine[i], outs[i])
                 host_out[i].copy_(outs[i], non_blocking=True)
     sec_e2e = timed_graph(torch, step_e2e, args.steps, args.warmup, dist if world > 1 else None)
     e2e = {"value": bytes_layer * layers / sec_e2e / 1e9, "unit": UNIT,
@@ -270,17 +294,26 @@ def bench_c3(torch, args, rank, world, dist):
            "d2h_bytes_per_step": layers * s.n_q * s.head_dim * 2,
            "ms_per_step": sec_e2e * 1e3}
 
+    extra = {}
+    if world > 1:
+        sec_nccl = timed_graph(torch, step_nccl, args.steps, args.warmup, dist)
+        extra["nccl_allgather_variant_us_per_layer"] = sec_nccl / layers * 1e6
+        if exchange_note:
+            extra["exchange_note"] = exchange_note
+        xch.close()
+
     pk = peaks()
     kernel_us = sec / layers * 1e6
     achieved = bytes_layer / world / (sec / layers) / 1e9      # per GPU, per launch
     roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                "frac": achieved / pk["hbm"], "traffic": NCU_DECODE_TRAFFIC_BYTES,
+                "frac": achieved / pk["hbm"],
+                "traffic": NCU_DECODE_TRAFFIC_BYTES if world == 1 else None,
                 "peak_source": pk["source"], "kernel": "attn_rows_kernel<128,1,1>",
                 "algorithmic_bytes_per_launch": bytes_layer // world,
                 "us_per_launch": kernel_us}
     return dict(value=value, sec=sec, clocks=clocks, e2e=e2e, roofline=roofline,
                 launches=launches_per_step * args.steps,
-                extra={"us_per_layer": kernel_us, "tokens_per_s": 1.0 / sec})
+                extra=dict(extra, us_per_layer=kernel_us, tokens_per_s=1.0 / sec))
 
 
 def bench_also(torch, args):
@@ -441,6 +474,95 @@ def bench_also(torch, args):
     return out
 
 
+def bench_sharded_units(torch, args, rank, world, dist):
+    """c4 and c5 on `world` GPUs: the (sequence, KV head) units are dealt to the ranks
+    and every rank runs the same entry points on its own units -- no collective on
+    the data path.  Time = max over ranks, throughput = the whole job's work / time.
+    KV heads are dealt first (each rank takes n_kv/world heads and their query heads of
+    every sequence); at 8 GPUs c5 has more ranks than KV heads, so the sequences,
+    longest first, are dealt alternately to the two ranks that share a head."""
+    import dataclasses
+    from whetstone_b200 import chunk, decode, paged, workloads as wl
+
+    pk = peaks()
+    gen = torch.Generator(device="cuda").manual_seed(70 + rank)
+
+    def randn16(shape):
+        return torch.randn(shape, generator=gen, device="cuda", dtype=torch.float16)
+
+    out = {}
+    # ---- c4
+    s4 = wl.QWEN3_8B
+    heads4 = max(1, s4.n_kv // world)              # KV heads on this rank
+    seq_groups4 = max(1, world // s4.n_kv)         # > 1 only beyond 8 GPUs
+    loc4 = dataclasses.replace(s4, n_q=heads4 * s4.gqa, n_kv=heads4)
+    n4, prompt4 = wl.C4["chunk"], wl.C4["prompt"]
+    nseq = wl.C4["n_seq"] // seq_groups4
+    table4 = decode.RopeTable(prompt4, loc4.head_dim, loc4.theta)
+    cache = chunk.KvCacheBatch(nseq, loc4.n_kv, loc4.head_dim, prompt4)
+    cache.k.copy_(randn16(cache.k.shape))
+    cache.v.copy_(randn16(cache.v.shape))
+    pool = [randn16((nseq, n4, loc4.qkv_width)).float() for _ in range(4)]
+    out4 = torch.zeros(nseq * n4 * loc4.n_q * loc4.head_dim, dtype=torch.float16, device="cuda")
+    chunks = prompt4 // n4
+    starts = [torch.full((nseq,), c * n4, dtype=torch.int32, device="cuda") for c in range(chunks)]
+    flops4 = wl.C4["n_seq"] * sum(wl.prefill_flops(s4.n_q, s4.head_dim, c * n4, n4)
+                                 for c in range(chunks))      # whole job, all ranks
+
+    def c4_attn():
+        for c in range(chunks):
+            chunk.attn_batch(pool[c % len(pool)], cache, out4, loc4.n_q, starts[c], n4)
+    sec = timed_graph(torch, c4_attn, 5, 3, dist)
+    tf = flops4 / sec / 1e12
+    out["c4_prefill_qwen3_8b"] = {
+        "tflops": tf, "ms_per_layer": sec * 1e3, "frac_of_aggregate_tensor_peak":
+        tf / (pk["tf_burst"] * world), "units_per_rank": nseq * heads4,
+        "partition": f"{heads4} of {s4.n_kv} KV heads x {nseq} sequences per rank, no collective"}
+    del cache, pool
+
+    # ---- c5
+    s5 = wl.QWEN25_7B
+    lengths = wl.c5_lengths()
+    drafts = wl.C5["drafts"]
+    heads5 = max(1, s5.n_kv // world)
+    groups5 = max(1, world // s5.n_kv)
+    order = np.argsort(-lengths, kind="stable")
+    mine = np.sort(order[(rank // s5.n_kv) % groups5::groups5]) if groups5 > 1 else np.arange(len(lengths))
+    my_len = lengths[mine]
+    loc5 = dataclasses.replace(s5, n_q=heads5 * s5.gqa, n_kv=heads5)
+    table_np, n_pages = wl.c5_page_table(my_len, drafts)
+    nseq5 = len(my_len)
+    total = nseq5 * drafts
+    max_len = int(my_len.max()) + drafts
+    pc = paged.PagedKvCache(n_pages, loc5.n_kv, loc5.head_dim, nseq5, table_np.shape[1])
+    pc.k.copy_(randn16(pc.k.shape))
+    pc.v.copy_(randn16(pc.v.shape))
+    pc.page_table.copy_(torch.from_numpy(table_np).cuda())
+    qkv5 = randn16((total, loc5.qkv_width)).float()
+    out5 = torch.zeros(total * loc5.n_q * loc5.head_dim, dtype=torch.float16, device="cuda")
+    pos0 = torch.from_numpy(my_len).cuda()
+    cu = torch.arange(nseq5 + 1, dtype=torch.int32, device="cuda") * drafts
+    scratch = torch.zeros(paged.verify_scratch_floats(nseq5, drafts, loc5.n_q, loc5.n_kv,
+                                                      loc5.head_dim, max_len),
+                          dtype=torch.float32, device="cuda")
+    rtab = decode.RopeTable(max_len, loc5.head_dim, loc5.theta)
+
+    def c5_step():
+        paged.rope_cache(qkv5, pc, rtab, loc5.n_q, pos0, cu, total)
+        paged.attn_verify(qkv5, pc, out5, scratch, loc5.n_q, pos0, cu, total, drafts, max_len)
+    sec = timed_graph(torch, c5_step, 20, 3, dist)
+    all_tok = len(lengths) * drafts
+    kv_bytes = int(2 * s5.n_kv * s5.head_dim * 2 * int((lengths.astype(np.int64) + drafts).sum()))
+    bytes5 = kv_bytes + all_tok * s5.n_q * s5.head_dim * (4 + 2)     # whole job, all ranks
+    gbs = bytes5 / sec / 1e9
+    out["c5_verify_7b_paged"] = {
+        "us_per_layer": sec * 1e6, "hbm_gbs": gbs,
+        "frac_of_aggregate_hbm_peak": gbs / (pk["hbm"] * world),
+        "tokens_verified_per_s": all_tok / (sec * s5.layers), "units_per_rank": nseq5 * heads5,
+        "partition": f"{heads5} of {s5.n_kv} KV heads x {nseq5} sequences per rank, no collective"}
+    return out
+
+
 def bench_reference_cuda(torch):
     """The engine's own CUDA kernels (built unmodified for sm_100a into oracle/_ref/
     by oracle/Makefile) timed on the same GPU and the same buffer shapes: a reported
@@ -549,6 +671,8 @@ def run_ours(args):
     if world == 1 and not args.no_also and args.only is None:
         also = bench_also(torch, args)
         refcuda = bench_reference_cuda(torch)
+    if world > 1 and not args.no_also and args.only is None:
+        also = bench_sharded_units(torch, args, rank, world, dist)
     if world == 1 and rank == 0 and not args.no_cpu:
         gbs, layers, spent = cpu_decode_sample()
         cpu = {"value": gbs, "unit": UNIT, "cores": len(os.sched_getaffinity(0)), "kind": "port",
@@ -562,7 +686,8 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": C3_NAME,
                        "parallelism": "single GPU" if world == 1 else
-                       f"KV sequence sharded over {world} GPUs, NCCL all-gather of (m,l,acc) + merge",
+                       f"KV sequence sharded over {world} GPUs; (m,l,acc) exchanged through peer memory "
+                       "inside the merge kernel (the NCCL all-gather variant is timed beside it)",
                        "l2": "inputs larger than L2: 1.88 GB of KV cache is streamed per step",
                        "launch": "one CUDA graph per step"},
             "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["launches"],

@@ -80,6 +80,36 @@ WST_API wst_status_t wst_attn_decode_partial(const void *q, const void *k_cache,
 WST_API wst_status_t wst_attn_merge_partials(const void *parts, void *out, int32_t n_parts,
                                      int32_t n_q, int32_t head_dim);
 
+/* The same merge with the exchange inside the kernel, for the GPUs of one box:
+ * every rank stores its triples into all ranks' mailboxes over NVLink -- plain peer
+ * stores of 8-byte {value, tag} packets, valid when the tag is the call's -- and
+ * merges the packets that arrive in its own mailbox, polling each for at most about
+ * a second.  No NCCL call, no fence and no host step between
+ * wst_attn_decode_partial and the fp16 result.
+ *   my_triples  [n_q][head_dim + 2] float, this rank's wst_attn_decode_partial output
+ *   out         [n_q][head_dim] half (every rank gets the full result)
+ *   mailboxes   DEVICE array of `world` pointers; entry g = rank g's mailbox,
+ *               8-byte packets [2][world][n_q][head_dim + 2], zeroed once before the
+ *               first call, mapped into this process (wst_b200_ipc_import)
+ *   state       this rank's uint32[n_q] call counters, zeroed once before the first call
+ * Every rank must make the same sequence of calls.  A wait that runs out sets the
+ * device error word (wst_b200_device_error) and leaves that head's `out` unwritten. */
+WST_API wst_status_t wst_attn_exchange_merge(const void *my_triples, void *out,
+                                             const void *mailboxes, void *state, int32_t rank,
+                                             int32_t world, int32_t n_q, int32_t head_dim);
+
+/* One device buffer shared by the processes of a box (one process per GPU).  The
+ * owner exports a 64-byte handle of a buffer from wst_malloc; another process
+ * imports it with its own device current and gets an address its kernels can use
+ * (peer access between the two GPUs is enabled by the import); close before exit. */
+WST_API wst_status_t wst_b200_ipc_export(const void *dev_ptr, void *handle64_out_host);
+WST_API wst_status_t wst_b200_ipc_import(const void *handle64_host, void **out_dev_ptr);
+WST_API wst_status_t wst_b200_ipc_close(void *dev_ptr);
+
+/* cudaDeviceEnablePeerAccess from the current device to peer_device ("already
+ * enabled" is not an error); fails if the two cannot be peers. */
+WST_API wst_status_t wst_b200_enable_peer_access(int32_t peer_device);
+
 /* --------------------------------------------- decode without a scratch buffer */
 
 /* wst_attn_decode for callers that cannot provide (or allocate) the split

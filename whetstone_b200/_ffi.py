@@ -106,6 +106,11 @@ SIGNATURES: dict[str, tuple] = {
     "wst_rope_table_host": (I, [P, P, I, I, c_double, I, c_double, c_double, c_double, I]),
     "wst_attn_decode_partial": (I, [P, P, P, P, P, I, I, I, P, I, F]),
     "wst_attn_merge_partials": (I, [P, P, I, I, I]),
+    "wst_attn_exchange_merge": (I, [P, P, P, P, I, I, I, I]),
+    "wst_b200_enable_peer_access": (I, [I]),
+    "wst_b200_ipc_export": (I, [P, P]),
+    "wst_b200_ipc_import": (I, [P, ctypes.POINTER(ctypes.c_void_p)]),
+    "wst_b200_ipc_close": (I, [P]),
     "wst_attn_decode_noscratch": (I, [P, P, P, P, I, I, I, P, I, F]),
     "wst_rope_cache_chunk_batch": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, P, F]),
     "wst_attn_chunk_batch": (I, [P, P, P, P, P, I, I, I, I, I, I, F]),

@@ -7,6 +7,7 @@
 
 #include "attn_prefill.cuh"
 #include "attn_rows.cuh"
+#include "wst_ptx.cuh"
 
 namespace wst {
 namespace {
@@ -151,6 +152,103 @@ __global__ void merge_partials_kernel(const float *__restrict__ parts, __half *_
   }
 }
 
+/* ---------------------------------------------------------------------------
+ * Cross-GPU merge through peer memory (the KV sequence of one long context is
+ * sharded over the GPUs of a box; each rank has its heads' (m, l, acc) triples).
+ * One block per query head; no block waits for another block of its own grid.
+ *
+ * Every float travels as an 8-byte packet {value, tag} written with ONE store, so a
+ * packet is valid exactly when its tag is this call's tag: no fence, no separate
+ * flag, no ordering between packets.  The block stores its head's triple into every
+ * rank's mailbox (plain stores to peer memory over NVLink), then reads the same
+ * head's packets of all ranks from its OWN mailbox, polling -- bounded -- each packet
+ * it needs until the tag is there, and merges.  The tag is a per-head call counter
+ * kept in device memory (graph replays advance it).  Mailboxes exist twice, used by
+ * tag parity: a rank can publish call t+2 only after it has received everybody's
+ * t+1, which they sent after reading t.  Every rank runs its own launch on its own
+ * GPU; nothing here waits for another launch on the same GPU. */
+struct ExchangeArgs {
+  const float *mine;        /* [n_q][hd+2] */
+  __half *out;              /* [n_q][hd] */
+  uint2 *const *mailboxes;  /* [world] -> packets [2][world][n_q][hd+2] on rank g */
+  unsigned int *state;      /* this rank: per-head call counters [n_q] */
+  unsigned int *err_word;
+  int rank, world, n_q, hd;
+};
+
+__device__ __forceinline__ uint2 ld_packet(const uint2 *p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_packet(uint2 *p, float value, unsigned int tag) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(value)),
+               "r"(tag)
+               : "memory");
+}
+/* value of a packet once its tag has arrived; false after about a second */
+__device__ __forceinline__ bool wait_packet(const uint2 *p, unsigned int tag, float *value) {
+  uint2 v = ld_packet(p);
+  if (v.y != tag) {
+    const long long t0 = clock64();
+    do {
+      if (clock64() - t0 > ptx::kWaitCycleLimit) return false;
+      v = ld_packet(p);
+    } while (v.y != tag);
+  }
+  *value = __uint_as_float(v.x);
+  return true;
+}
+
+__global__ void __launch_bounds__(128) exchange_merge_kernel(const ExchangeArgs a) {
+  /* the next kernel in the stream may start its prologue; this one needs the
+   * triples its predecessor wrote */
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int head = blockIdx.x, tid = threadIdx.x;
+  const int stride = a.hd + 2;
+  const unsigned int tag = a.state[head] + 1u;
+  const int par = static_cast<int>(tag & 1u);
+
+  /* 1. publish */
+  const float *src = a.mine + static_cast<long long>(head) * stride;
+  const long long slot = (static_cast<long long>(par) * a.world + a.rank) * a.n_q + head;
+  for (int i = tid; i < stride; i += blockDim.x) {
+    const float v = src[i];
+    for (int g = 0; g < a.world; ++g) st_packet(a.mailboxes[g] + slot * stride + i, v, tag);
+  }
+
+  /* 2. merge this head's triples of all ranks as they arrive in this GPU's mailbox */
+  const uint2 *box = a.mailboxes[a.rank] +
+                     (static_cast<long long>(par) * a.world * a.n_q + head) * stride;
+  const long long rank_stride = static_cast<long long>(a.n_q) * stride;
+  bool ok = true;
+  float big = -INFINITY;
+  for (int g = 0; ok && g < a.world; ++g) {
+    float m;
+    ok = wait_packet(box + g * rank_stride, tag, &m);
+    big = fmaxf(big, m);
+  }
+  for (int d = tid; ok && d < a.hd; d += blockDim.x) {
+    float num = 0.f, den = 0.f;
+    for (int g = 0; g < a.world; ++g) {
+      const uint2 *t = box + g * rank_stride;
+      float m, l, acc;
+      ok = wait_packet(t, tag, &m) && wait_packet(t + 1, tag, &l) && wait_packet(t + 2 + d, tag, &acc);
+      if (!ok) break;
+      if (m == -INFINITY) continue; /* an empty shard contributes nothing */
+      const float f = expf(m - big);
+      num = fmaf(acc, f, num);
+      den = fmaf(l, f, den);
+    }
+    if (ok)
+      a.out[static_cast<long long>(head) * a.hd + d] = __float2half_rn(den > 0.f ? num / den : 0.f);
+  }
+  if (!ok) atomicCAS(a.err_word, 0u, 0x401u);
+  __syncthreads(); /* every thread has read the counter and is done with the call */
+  if (tid == 0) a.state[head] = tag;
+}
+
 }  // namespace
 }  // namespace wst
 
@@ -223,6 +321,59 @@ extern "C" wst_status_t wst_attn_merge_partials(const void *parts, void *out, in
   merge_partials_kernel<<<n_q, threads, 0, current_stream()>>>(
       static_cast<const float *>(parts), static_cast<__half *>(out), n_parts, n_q, head_dim);
   WST_LAUNCHED("wst_attn_merge_partials");
+  return WST_OK;
+}
+
+extern "C" wst_status_t wst_attn_exchange_merge(const void *my_triples, void *out,
+                                                const void *mailboxes, void *state,
+                                                int32_t rank, int32_t world, int32_t n_q,
+                                                int32_t head_dim) {
+  WST_CHECK_ARG(my_triples && out && mailboxes && state, "wst_attn_exchange_merge: null pointer");
+  WST_CHECK_ARG(world >= 1 && world <= 32 && rank >= 0 && rank < world,
+                "wst_attn_exchange_merge: rank / world out of range");
+  WST_CHECK_ARG(n_q > 0 && head_dim > 0, "wst_attn_exchange_merge: non-positive shape");
+  ExchangeArgs a{};
+  a.mine = static_cast<const float *>(my_triples);
+  a.out = static_cast<__half *>(out);
+  a.mailboxes = static_cast<uint2 *const *>(mailboxes);
+  a.state = static_cast<unsigned int *>(state);
+  a.err_word = device_error_word();
+  if (!a.err_word) return WST_ERR_CUDA;
+  a.rank = rank;
+  a.world = world;
+  a.n_q = n_q;
+  a.hd = head_dim;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(n_q));
+  cfg.blockDim = dim3(128);
+  cfg.stream = current_stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, exchange_merge_kernel, a);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(WST_ERR_CUDA, "wst_attn_exchange_merge (launch): %s (%s)", cudaGetErrorString(e),
+                cudaGetErrorName(e));
+  return WST_OK;
+}
+
+extern "C" wst_status_t wst_b200_enable_peer_access(int32_t peer_device) {
+  int dev = 0;
+  WST_CUDA(cudaGetDevice(&dev));
+  if (peer_device == dev) return WST_OK;
+  int can = 0;
+  WST_CUDA(cudaDeviceCanAccessPeer(&can, dev, peer_device));
+  if (!can)
+    return fail(WST_ERR_CUDA, "device %d cannot access device %d as a peer", dev, peer_device);
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    return WST_OK;
+  }
+  if (e != cudaSuccess) return cuda_fail("cudaDeviceEnablePeerAccess", e);
   return WST_OK;
 }
 

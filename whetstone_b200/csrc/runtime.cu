@@ -6,6 +6,8 @@
 #include <cmath>
 #include <mutex>
 
+#include <cstring>
+
 #include "wst_common.cuh"
 
 namespace wst {
@@ -153,6 +155,36 @@ extern "C" wst_status_t wst_memset(void *dst, int32_t value, size_t bytes) {
   if (bytes == 0) return WST_OK;
   WST_CHECK_ARG(dst, "wst_memset: null dst");
   WST_CUDA(cudaMemset(dst, value, bytes));
+  return WST_OK;
+}
+
+/* Sharing one device allocation with the other processes of the box (one process
+ * per GPU): the owner exports a 64-byte handle of a buffer it got from wst_malloc,
+ * another process imports it WITH ITS OWN DEVICE CURRENT, so that the mapping
+ * belongs to the context whose kernels will use it (peer access is switched on as
+ * part of the import). */
+extern "C" wst_status_t wst_b200_ipc_export(const void *dev_ptr, void *handle_out_host) {
+  WST_CHECK_ARG(dev_ptr && handle_out_host, "wst_b200_ipc_export: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  WST_CUDA(cudaIpcGetMemHandle(&h, const_cast<void *>(dev_ptr)));
+  memcpy(handle_out_host, &h, sizeof(h));
+  return WST_OK;
+}
+
+extern "C" wst_status_t wst_b200_ipc_import(const void *handle_host, void **out_dev_ptr) {
+  WST_CHECK_ARG(handle_host && out_dev_ptr, "wst_b200_ipc_import: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle_host, sizeof(h));
+  void *p = nullptr;
+  WST_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *out_dev_ptr = p;
+  return WST_OK;
+}
+
+extern "C" wst_status_t wst_b200_ipc_close(void *dev_ptr) {
+  if (!dev_ptr) return WST_OK;
+  WST_CUDA(cudaIpcCloseMemHandle(dev_ptr));
   return WST_OK;
 }
 

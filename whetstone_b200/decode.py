@@ -204,6 +204,27 @@ def attn_merge_partials(parts: torch.Tensor, out: torch.Tensor, n_q: int, head_d
                                       head_dim))
 
 
+def attn_exchange_merge(mine: torch.Tensor, out: torch.Tensor, mailboxes: torch.Tensor,
+                        state: torch.Tensor, rank: int, world: int, n_q: int,
+                        head_dim: int) -> None:
+    """This rank's [n_q][head_dim+2] triples -> [n_q][head_dim] fp16 merged over all
+    ranks, exchanged through peer memory inside the kernel.  `mailboxes` is an int64
+    device array of the ranks' mailbox addresses (see sharded.PeerExchange)."""
+    _require_cuda(mine, "attn_exchange_merge: triples", torch.float32)
+    _require_cuda(out, "attn_exchange_merge: out", torch.float16)
+    _require_cuda(mailboxes, "attn_exchange_merge: mailboxes", torch.int64)
+    _require_cuda(state, "attn_exchange_merge: state", torch.int32)
+    if mine.numel() != n_q * (head_dim + 2) or out.numel() != n_q * head_dim:
+        raise ShapeError(5, "attn_exchange_merge: triples must be [n_q][head_dim+2] and out "
+                            "[n_q][head_dim]")
+    if mailboxes.numel() != world or state.numel() < n_q:
+        raise ShapeError(5, "attn_exchange_merge: one mailbox address per rank, one counter "
+                            "per head")
+    use_torch_stream()
+    check(lib.wst_attn_exchange_merge(_ptr(mine), _ptr(out), _ptr(mailboxes), _ptr(state), rank,
+                                      world, n_q, head_dim))
+
+
 def device_error() -> int:
     """Read and clear the device watchdog word (0 = no kernel gave up a wait)."""
     use_torch_stream()

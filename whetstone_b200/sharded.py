@@ -82,6 +82,72 @@ def gather_partials(mine: torch.Tensor, group=None) -> torch.Tensor:
     return out
 
 
+class PeerExchange:
+    """Mailboxes and flags of wst_attn_exchange_merge for the ranks of one box.
+
+    Every rank allocates a mailbox of its own (wst_malloc: 8-byte packets
+    [2][world][n_q][head_dim+2]), zeroes it, publishes its CUDA IPC handle to the
+    other ranks through the process group (once), imports theirs with its own device
+    current, and keeps a small device array with the addresses in rank order -- what
+    the kernel takes.  One instance serves any number of layers: calls are told apart
+    by the per-head call counters in `state`, and all ranks make the same sequence of
+    calls.
+    """
+
+    def __init__(self, n_q: int, head_dim: int, group=None):
+        import ctypes
+        from ._ffi import check, lib
+
+        self._lib, self._check = lib, check
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.n_q, self.head_dim = n_q, head_dim
+        dev = torch.device("cuda", torch.cuda.current_device())
+        total = 2 * self.world * n_q * (head_dim + 2) * 8
+        base = ctypes.c_void_p()
+        check(lib.wst_malloc(ctypes.byref(base), total))
+        self._base = base.value
+        check(lib.wst_memset(ctypes.c_void_p(self._base), 0, total))
+        check(lib.wst_device_synchronize())
+        handle = ctypes.create_string_buffer(64)
+        check(lib.wst_b200_ipc_export(ctypes.c_void_p(self._base), handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (dev.index, handle.raw), group=group)
+        self._imported = []
+        bases = []
+        for g, (peer_dev, raw) in enumerate(handles):
+            if g == self.rank:
+                bases.append(self._base)
+                continue
+            check(lib.wst_b200_enable_peer_access(peer_dev))
+            p = ctypes.c_void_p()
+            check(lib.wst_b200_ipc_import(ctypes.create_string_buffer(raw, 64), ctypes.byref(p)))
+            self._imported.append(p.value)
+            bases.append(p.value)
+        self.mailboxes_dev = torch.tensor(bases, dtype=torch.int64, device=dev)
+        self.state = torch.zeros(n_q, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # nobody launches before everybody has mapped everything
+
+    def merge(self, mine: torch.Tensor, out: torch.Tensor) -> None:
+        from . import decode
+        decode.attn_exchange_merge(mine, out, self.mailboxes_dev, self.state, self.rank,
+                                   self.world, self.n_q, self.head_dim)
+
+    def close(self, group=None) -> None:
+        """Unmaps the other ranks' buffers and frees this rank's (collective: every
+        rank calls it, after its last merge has finished)."""
+        import ctypes
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        for p in self._imported:
+            self._check(self._lib.wst_b200_ipc_close(ctypes.c_void_p(p)))
+        self._imported = []
+        dist.barrier(group=group)
+        if self._base:
+            self._check(self._lib.wst_free(ctypes.c_void_p(self._base)))
+            self._base = 0
+
+
 @dataclass
 class ShardedDecodeLayer:
     """One layer of long-context decode on this rank's slice of the KV sequence."""
@@ -89,6 +155,7 @@ class ShardedDecodeLayer:
     cache: "object"          # whetstone_b200.decode.KvCache holding rows [lo, hi)
     length: torch.Tensor     # device int32[1]: valid rows of the slice
     n_q: int
+    exchange: "PeerExchange | None" = None   # None: NCCL all-gather + local merge
 
     def __post_init__(self):
         hd = self.cache.head_dim
@@ -102,9 +169,12 @@ class ShardedDecodeLayer:
         (identical on every rank)."""
         from . import decode  # the CUDA path; importing it here keeps this module CPU-importable
         decode.attn_decode_partial(q, self.cache, self.mine, self.n_q, self.length)
+        if self.exchange is not None:
+            self.exchange.merge(self.mine, out)
+            return
         dist.all_gather_into_tensor(self.gathered.view(-1, self.mine.shape[1]), self.mine)
         decode.attn_merge_partials(self.gathered, out, self.n_q, self.cache.head_dim)
 
 
 __all__ = ["partition_units", "sequence_shard", "kv_head_units", "gather_partials",
-           "ShardedDecodeLayer"]
+           "PeerExchange", "ShardedDecodeLayer"]
