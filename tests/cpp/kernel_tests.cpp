@@ -324,6 +324,47 @@ static void attention_chunk_resumes_mid_cache() {
   }
 }
 
+/* Not in the engine's tests (it has no batched form): three sequences appended and
+ * attended in one launch each must equal the same sequences run one by one. */
+static void batched_chunk_matches_one_sequence_at_a_time() {
+  const size_t n_seq = 3, n_q = 8, n_kv = 2, hd = 128, max_seq = 96, n = 40;
+  const size_t stride = (n_q + 2 * n_kv) * hd;
+  const int32_t starts[n_seq] = {0, 17, 50};
+  RopeTable rope(max_seq, hd, 1e6);
+  const auto prefix = noise(stride * 50, 505);
+  const auto all = noise(stride * n * n_seq, 606);
+  chunk::KvCacheBatch batch(n_seq, n_kv, hd, max_seq);
+  std::vector<std::vector<float>> want(n_seq);
+  std::vector<uint16_t> k_host(n_seq * n_kv * max_seq * hd), v_host(k_host.size());
+  for (size_t s = 0; s < n_seq; ++s) {
+    KvCache one(n_kv, n_q, hd, max_seq);
+    if (starts[s] > 0) {
+      auto pre = DeviceBuffer<float>::from_slice(std::vector<float>(prefix.begin(), prefix.begin() + starts[s] * stride));
+      chunk::rope_cache(pre, one, rope, n_q, 0, starts[s]);
+    }
+    /* the batch's cache starts from the same prefix rows */
+    auto k1 = one.k.to_vec(), v1 = one.v.to_vec();
+    std::copy(k1.begin(), k1.end(), k_host.begin() + s * k1.size());
+    std::copy(v1.begin(), v1.end(), v_host.begin() + s * v1.size());
+    auto q1 = DeviceBuffer<float>::from_slice(std::vector<float>(all.begin() + s * n * stride, all.begin() + (s + 1) * n * stride));
+    chunk::rope_cache(q1, one, rope, n_q, starts[s], n);
+    auto o1 = DeviceBuffer<uint16_t>::zeros(n * n_q * hd);
+    chunk::attn(q1, one, o1, n_q, starts[s], n);
+    want[s] = from_f16(o1.to_vec());
+  }
+  batch.k.copy_from_host(k_host);
+  batch.v.copy_from_host(v_host);
+  auto pos = DeviceBuffer<int32_t>::from_slice(std::vector<int32_t>(starts, starts + n_seq));
+  auto qkv = DeviceBuffer<float>::from_slice(all);
+  chunk::rope_cache_batch(qkv, batch, rope, n_q, pos, n);
+  auto out = DeviceBuffer<uint16_t>::zeros(n_seq * n * n_q * hd);
+  chunk::attn_batch(qkv, batch, out, n_q, pos, n);
+  const auto got = from_f16(out.to_vec());
+  for (size_t s = 0; s < n_seq; ++s)
+    for (size_t i = 0; i < n * n_q * hd; ++i)
+      close(got[s * n * n_q * hd + i], want[s][i], 4e-3f, "batched attention element");
+}
+
 static void shape_errors_are_typed_and_launch_nothing() {
   KvCache cache(2, 14, 64, 32);
   RopeTable table(32, 64, 1e6);
@@ -384,6 +425,7 @@ int main() {
       {"attention_over_two_positions_matches_an_explicit_softmax", attention_over_two_positions_matches_an_explicit_softmax},
       {"rope_and_attention_chunk_match_sequential_decode", rope_and_attention_chunk_match_sequential_decode},
       {"attention_chunk_resumes_mid_cache", attention_chunk_resumes_mid_cache},
+      {"batched_chunk_matches_one_sequence_at_a_time", batched_chunk_matches_one_sequence_at_a_time},
       {"shape_errors_are_typed_and_launch_nothing", shape_errors_are_typed_and_launch_nothing},
       {"decode_step_replays_as_a_graph", decode_step_replays_as_a_graph},
   };

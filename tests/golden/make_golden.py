@@ -2,7 +2,9 @@
 
 Run in a container that has the reference checkout mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
+
+(default: the directory ``reference`` beside this repository).
 
 It imports ``rope``, ``softmax`` and ``rms_norm`` from the reference's
 ``bench/reference_numpy.py`` (the file cannot travel with this repository, so
@@ -48,7 +50,7 @@ def reference_prefill(ref, q, k, v, n_q, n_kv, hd, theta):
 
 
 def main() -> None:
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(__file__).resolve().parents[3] / "reference"
     ref = load_reference(root)
     out: dict[str, np.ndarray] = {}
     rng = np.random.default_rng(20250)

@@ -305,7 +305,119 @@ inline void attn(const DeviceBuffer<float> &qkv, const KvCache &cache, DeviceBuf
                        1.0f / std::sqrt(static_cast<float>(hd))));
 }
 
+/* Several sequences per launch: caches [n_seq][n_kv][max_seq][head_dim], qkv
+ * [n_seq][n][stride], out [n_seq][n][n_q*head_dim], one chunk start per sequence in
+ * device memory (no counterpart in the engine, which runs one sequence). */
+struct KvCacheBatch {
+  DeviceBuffer<uint16_t> k, v;
+  size_t n_seq, n_kv, head_dim, max_seq;
+  KvCacheBatch(size_t n_seq_, size_t n_kv_, size_t head_dim_, size_t max_seq_)
+      : n_seq(n_seq_), n_kv(n_kv_), head_dim(head_dim_), max_seq(max_seq_) {
+    k = DeviceBuffer<uint16_t>::zeros(n_seq * n_kv * max_seq * head_dim);
+    v = DeviceBuffer<uint16_t>::zeros(n_seq * n_kv * max_seq * head_dim);
+  }
+};
+
+inline void rope_cache_batch(DeviceBuffer<float> &qkv, KvCacheBatch &cache, const RopeTable &table,
+                             size_t n_q, const DeviceBuffer<int32_t> &seq_pos0, size_t n,
+                             const QkNorm *qk_norm = nullptr) {
+  using detail::S;
+  const size_t hd = cache.head_dim, stride = (n_q + 2 * cache.n_kv) * hd;
+  if (qkv.len() < cache.n_seq * n * stride)
+    throw Error::shape("rope_cache_chunk_batch: qkv[" + S(qkv.len()) + "] needs " +
+                       S(cache.n_seq) + " * " + S(n) + " * " + S(stride));
+  if (seq_pos0.len() != cache.n_seq)
+    throw Error::shape("rope_cache_chunk_batch: one chunk start per sequence");
+  if (table.half_dim != hd / 2 || table.max_seq < cache.max_seq)
+    throw Error::shape("rope_cache_chunk_batch: rotary table does not match the cache geometry");
+  const auto np = detail::norm_ptrs(qk_norm);
+  check(wst_rope_cache_chunk_batch(qkv.as_mut_ptr(), cache.k.as_mut_ptr(), cache.v.as_mut_ptr(),
+                                   table.cos.as_ptr(), table.sin.as_ptr(), seq_pos0.as_ptr(),
+                                   static_cast<int32_t>(cache.n_seq), static_cast<int32_t>(n_q),
+                                   static_cast<int32_t>(cache.n_kv), static_cast<int32_t>(hd),
+                                   static_cast<int32_t>(n), static_cast<int32_t>(cache.max_seq),
+                                   np.q, np.k, np.eps));
+}
+
+inline void attn_batch(const DeviceBuffer<float> &qkv, const KvCacheBatch &cache,
+                       DeviceBuffer<uint16_t> &out, size_t n_q,
+                       const DeviceBuffer<int32_t> &seq_pos0, size_t n) {
+  using detail::S;
+  const size_t hd = cache.head_dim, stride = (n_q + 2 * cache.n_kv) * hd;
+  if (qkv.len() < cache.n_seq * n * stride)
+    throw Error::shape("attn_chunk_batch: qkv[" + S(qkv.len()) + "] needs " + S(cache.n_seq) +
+                       " * " + S(n) + " * " + S(stride));
+  if (out.len() < cache.n_seq * n * n_q * hd) throw Error::shape("attn_chunk_batch: out too small");
+  if (seq_pos0.len() != cache.n_seq)
+    throw Error::shape("attn_chunk_batch: one chunk start per sequence");
+  check(wst_attn_chunk_batch(qkv.as_ptr(), cache.k.as_ptr(), cache.v.as_ptr(), out.as_mut_ptr(),
+                             seq_pos0.as_ptr(), static_cast<int32_t>(cache.n_seq),
+                             static_cast<int32_t>(n_q), static_cast<int32_t>(cache.n_kv),
+                             static_cast<int32_t>(hd), static_cast<int32_t>(n),
+                             static_cast<int32_t>(cache.max_seq),
+                             1.0f / std::sqrt(static_cast<float>(hd))));
+}
+
 }  // namespace chunk
+
+/* --------------------------------------- one long sequence over several GPUs */
+
+/* This rank's mailbox for wst_attn_exchange_merge and the other ranks' mapped into
+ * this process.  The 64-byte handles travel between the processes by whatever
+ * channel the host has (`handle()` out, `import_peer()` in, rank order). */
+class PeerMailbox {
+ public:
+  PeerMailbox(int rank, int world, size_t n_q, size_t head_dim)
+      : rank_(rank), world_(world), n_q_(n_q), head_dim_(head_dim), addr_(world, nullptr) {
+    const size_t bytes = 2 * static_cast<size_t>(world) * n_q * (head_dim + 2) * 8;
+    check(wst_malloc(&own_, bytes));
+    check(wst_memset(own_, 0, bytes));
+    check(wst_device_synchronize());
+    addr_[rank] = own_;
+    state_ = DeviceBuffer<uint32_t>::zeros(n_q);
+  }
+  PeerMailbox(const PeerMailbox &) = delete;
+  PeerMailbox &operator=(const PeerMailbox &) = delete;
+  ~PeerMailbox() {
+    for (int g = 0; g < world_; ++g)
+      if (g != rank_ && addr_[g]) wst_b200_ipc_close(addr_[g]);
+    if (own_) wst_free(own_);
+  }
+  std::vector<uint8_t> handle() const {
+    std::vector<uint8_t> h(64);
+    check(wst_b200_ipc_export(own_, h.data()));
+    return h;
+  }
+  void import_peer(int g, const std::vector<uint8_t> &handle64) {
+    if (g == rank_ || g < 0 || g >= world_ || handle64.size() != 64)
+      throw Error::shape("PeerMailbox::import_peer: bad rank or handle");
+    check(wst_b200_ipc_import(handle64.data(), &addr_[g]));
+  }
+  /* after every peer has been imported */
+  void seal() {
+    std::vector<uint64_t> a(world_);
+    for (int g = 0; g < world_; ++g) {
+      if (!addr_[g]) throw Error::shape("PeerMailbox::seal: a rank is missing");
+      a[g] = reinterpret_cast<uint64_t>(addr_[g]);
+    }
+    table_ = DeviceBuffer<uint64_t>::from_slice(a);
+  }
+  void merge(const DeviceBuffer<float> &my_triples, DeviceBuffer<uint16_t> &out) {
+    if (my_triples.len() != n_q_ * (head_dim_ + 2) || out.len() != n_q_ * head_dim_)
+      throw Error::shape("PeerMailbox::merge: triples [n_q][head_dim+2], out [n_q][head_dim]");
+    check(wst_attn_exchange_merge(my_triples.as_ptr(), out.as_mut_ptr(), table_.as_ptr(),
+                                  state_.as_mut_ptr(), rank_, world_, static_cast<int32_t>(n_q_),
+                                  static_cast<int32_t>(head_dim_)));
+  }
+
+ private:
+  int rank_, world_;
+  size_t n_q_, head_dim_;
+  void *own_ = nullptr;
+  std::vector<void *> addr_;
+  DeviceBuffer<uint64_t> table_;
+  DeviceBuffer<uint32_t> state_;
+};
 
 /* ------------------------------------------------------------ paged batch */
 
