@@ -94,7 +94,7 @@ struct Cfg {
   static constexpr int Q_BYTES = NH * ROWS * 128;
   /* ring | one spare stage (the re-read of the newest tile) | q tile | barriers */
   static constexpr int SMEM_BYTES =
-      (NSTAGE + 1) * STAGE_BYTES + Q_BYTES + (2 * NSTAGE + 1) * 8 + 64 + 1024;
+      (NSTAGE + 1) * STAGE_BYTES + Q_BYTES + (2 * NSTAGE + 2) * 8 + 64 + 1024;
   /* the warp-combine dump [RG][4][16*MT][HD+4] floats reuses the ring and the q tile */
   static_assert(RG * 4 * 16 * MT * (HD + 4) * 4 <= (NSTAGE + 1) * STAGE_BYTES + Q_BYTES,
                 "combine buffer must fit");
@@ -144,6 +144,7 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const uint32_t full_u32 = smem_u32(bars);
   const uint32_t empty_u32 = smem_u32(bars + NSTAGE);
   const uint32_t spare_full_u32 = smem_u32(bars + 2 * NSTAGE);
+  const uint32_t go_u32 = smem_u32(bars + 2 * NSTAGE + 1); /* "dependency resolved", see below */
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) {
@@ -151,6 +152,7 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       mbar_init(empty_u32 + 8 * i, C::CWARPS);
     }
     mbar_init(spare_full_u32, 1);
+    st_shared_volatile(go_u32, 0u);
     mbar_init_fence();
     tma_prefetch_desc(&kmap);
     tma_prefetch_desc(&vmap);
@@ -201,24 +203,43 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   /* Decode (one new token): the launch just before this one in the stream --
    * still running under programmatic dependent launch -- can only be writing the
    * newest cache row; every row in a tile below that one was written by launches
-   * that finished long ago.  So the slice's first tile is requested right here, before
-   * the dependency is resolved, and its latency hides behind the tail of the
-   * previous kernel.  If that tile is the one holding the newest row it is read
-   * again after the wait, into the spare stage. */
+   * that finished long ago.  So the slice's first tile is requested right here,
+   * before the dependency is resolved, and its latency hides behind the tail of
+   * the previous kernel.  The rest of the ring follows a little later (slow start):
+   * when the first tile has landed -- the kernel ahead has then had that long to
+   * get its own last loads out; requesting the whole ring at once was measured to
+   * crowd those out and to cost as much as it hides -- or as soon as a consumer
+   * thread reports the dependency resolved, whichever comes first.  A tile that
+   * holds the newest row and was requested early is read again after the wait,
+   * into the spare stage. */
   const bool early = !PAGED && a.early_spec != 0;
-  /* One tile per block is enough to hide the latency; measured on the 32k-context
-   * decode shape, requesting the whole ring here crowds out the last loads of the
-   * kernel still running and costs more than it hides. */
-  const int n_early = early ? min(spec, 1) : 0;
-  if (warp == C::CWARPS && lane < n_early) issue(lane);
-
-  /* Nothing else above touches global memory, so under programmatic dependent
-   * launch it overlaps the tail of the previous kernel in the stream.  From here
-   * on we read what that kernel may have written (cursor, q, newest cache rows). */
+  const int n_early = early ? spec : 0;
   WST_STAMP(0);
-  grid_dependency_wait();
+  if (early) {
+    if (warp == C::CWARPS) {
+      if (lane == 0 && spec > 0) {
+        issue(0);
+        if (spec > 1) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(full_u32, 0) && ld_shared_volatile(go_u32) == 0u)
+            if (clock64() - t0 > kWaitCycleLimit) break; /* only a hint: go on */
+          for (int i = 1; i < spec; ++i) issue(i);
+        }
+      }
+      __syncwarp();
+      grid_dependency_wait();
+    } else {
+      grid_dependency_wait();
+      if (threadIdx.x == 0) st_shared_volatile(go_u32, 1u);
+    }
+  } else {
+    /* Nothing above touches global memory, so under programmatic dependent launch
+     * it overlaps the tail of the previous kernel in the stream.  From here on we
+     * read what that kernel may have written (cursor, q, cache rows). */
+    grid_dependency_wait();
+    if (warp == C::CWARPS && lane < spec) issue(lane); /* one lane per stage */
+  }
   WST_STAMP(1);
-  if (warp == C::CWARPS && lane >= n_early && lane < spec) issue(lane); /* one lane per stage */
 #ifdef WST_TRACE
   if (warp == C::CWARPS && lane == 0) trace_stamp(6);
 #endif

@@ -67,6 +67,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
   return true;
 }
 
+__device__ __forceinline__ uint32_t ld_shared_volatile(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_shared_volatile(uint32_t addr, uint32_t v) {
+  asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
 /* ------------------------------------------------------------------ TMA */
 
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
