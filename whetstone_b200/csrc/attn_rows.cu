@@ -205,11 +205,11 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
    * newest cache row; every row in a tile below that one was written by launches
    * that finished long ago.  So the slice's first tile is requested right here,
    * before the dependency is resolved, and its latency hides behind the tail of
-   * the previous kernel.  The rest of the ring follows a little later (slow start):
-   * when the first tile has landed -- the kernel ahead has then had that long to
-   * get its own last loads out; requesting the whole ring at once was measured to
-   * crowd those out and to cost as much as it hides -- or as soon as a consumer
-   * thread reports the dependency resolved, whichever comes first.  A tile that
+   * the previous kernel.  The rest of the ring follows one tile at a time (slow
+   * start): tile i+1 is requested when tile i has landed -- the kernel ahead keeps
+   * getting its own last loads out in between; requesting the whole ring at once
+   * was measured to crowd those out and to cost as much as it hides -- or as soon
+   * as a consumer thread reports the dependency resolved, whichever comes first.  A tile that
    * holds the newest row and was requested early is read again after the wait,
    * into the spare stage. */
   const bool early = !PAGED && a.early_spec != 0;
@@ -219,11 +219,11 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     if (warp == C::CWARPS) {
       if (lane == 0 && spec > 0) {
         issue(0);
-        if (spec > 1) {
+        for (int i = 1; i < spec; ++i) {
           const long long t0 = clock64();
-          while (!mbar_try_wait(full_u32, 0) && ld_shared_volatile(go_u32) == 0u)
+          while (!mbar_try_wait(full_u32 + 8 * (i - 1), 0) && ld_shared_volatile(go_u32) == 0u)
             if (clock64() - t0 > kWaitCycleLimit) break; /* only a hint: go on */
-          for (int i = 1; i < spec; ++i) issue(i);
+          issue(i);
         }
       }
       __syncwarp();
