@@ -432,6 +432,7 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
       if (splits > (len + 127) / 128) splits = (len + 127) / 128;
       if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
       P.n_splits = splits;
+      P.max_len = len;
     }
     return launch_prefill(P);
   }
@@ -585,12 +586,16 @@ extern "C" wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_poo
     P.scratch = static_cast<float *>(scratch);
     P.scratch_floats =
         wst_attn_verify_scratch_floats(n_seq, max_tokens_per_seq, n_q, n_kv, head_dim, max_len);
+    /* slices of about 2048 positions (contiguous runs of 16 tiles): sequences get as
+     * many working CTAs as their length asks for; more, shorter slices only when the
+     * batch is too small to fill the GPU otherwise */
     int splits = facts.sm_count / (n_seq * n_kv);
     const int by_len = (max_len + 2047) / 2048;
     if (splits < by_len) splits = by_len;
     const int tiles = (max_len + 127) / 128;
     if (splits > tiles) splits = tiles;
     if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
+    P.max_len = max_len;
     P.n_splits = splits < 1 ? 1 : splits;
     return launch_prefill(P);
   }

@@ -82,6 +82,7 @@ struct PrefillArgs {
   const int32_t *page_table; /* paged cache: [n_seq][max_pages] */
   int max_pages, n_pool_pages;
   int n_splits, rows_cap;
+  int tiles_per_slice; /* sliced mode: KV tiles per slice (0 otherwise) */
   int n_q, n_kv, gqa;
   int pos0, n, max_seq;
   int tpt;      /* tokens per 128-row tile = 128 / gqa */
@@ -195,9 +196,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   const int kv_end = ntok > 0 ? min(pos0 + tok0 + ntok, a.max_seq) : 0; /* live rows seen */
   const int lim_min = min(pos0 + tok0 + 1, a.max_seq);
   const int all_tiles = (kv_end + BN - 1) / BN;
-  /* this CTA's tiles: split, split + ns, split + 2 ns, ... */
-  const int n_tiles = split < all_tiles ? (all_tiles - split + ns - 1) / ns : 0;
-  auto tile_of = [split, ns](int j) { return split + j * ns; };
+  /* this CTA's tiles: all of them, or (sliced) the slice's contiguous run of
+   * a.tiles_per_slice tiles -- slices past the end of a short sequence get none and
+   * only publish an empty partial, so that the CTAs that do work are equally long
+   * whatever the sequence lengths are */
+  const int first_tile = split * a.tiles_per_slice;
+  const int slice_cap = split == ns - 1 ? all_tiles : a.tiles_per_slice; /* the last takes the rest */
+  const int n_tiles = ns > 1 ? max(min(all_tiles - first_tile, slice_cap), 0) : all_tiles;
+  auto tile_of = [first_tile](int j) { return first_tile + j; };
 
   if (warp == TMA_WARP) {
     /* ------------------------------------------------------ TMA producer */
@@ -356,7 +362,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
 
     /* q half-row -> fp16 * scale * log2(e), two per 32-bit column of this row's TMEM lane */
     {
-      const bool valid = r < rows_valid;
+      const bool valid = r < rows_valid && n_tiles > 0; /* a slice without tiles needs no q */
       const float *src = a.q + static_cast<long long>(tok_base + r / a.gqa) * a.q_tok_stride +
                          static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD + half * OC;
       constexpr int QC = OC / 2; /* 32-bit columns this thread writes */
@@ -991,6 +997,8 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   if (!P.scratch || !aligned16(P.scratch)) splits = 1;
   while (splits > 1 && units * splits * a.rows_cap * (P.hd + 4) > P.scratch_floats) --splits;
   a.n_splits = splits;
+  const int max_tiles = (P.max_len > 0 ? P.max_len : P.max_seq) / 128 + 1;
+  a.tiles_per_slice = splits > 1 ? (max_tiles + splits - 1) / splits : 0;
 
   CUtensorMap kmap, vmap;
   KvMapKey key{};

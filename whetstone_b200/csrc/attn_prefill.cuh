@@ -29,6 +29,7 @@ struct PrefillLaunch {
   /* few query rows against a long prefix: cut the KV range into n_splits slices
    * (needs n * gqa <= 128 and scratch of n_seq*n_kv*n_splits*n*gqa*(hd+4) floats) */
   int n_splits = 0;
+  int max_len = 0; /* sliced mode: upper bound on any sequence's visible length (0: max_seq) */
   float *scratch = nullptr;
   long long scratch_floats = 0;
   float scale = 1.f;
