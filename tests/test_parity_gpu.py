@@ -243,6 +243,38 @@ def test_chunk_matches_oracle(chunk_kernel_choice, n_q, n_kv, hd, pos0, n):
                           f"chunk {n_q}/{n_kv}/{hd} pos0 {pos0} n {n}")
 
 
+@pytest.mark.parametrize("ramp", [0.0, 0.02, 0.3, -0.3])
+def test_chunk_with_scores_that_drift_along_the_sequence(chunk_kernel_choice, ramp):
+    """Scores that grow (or fall) steadily along the cache: the running exponent
+    offset has to move many times (ramp 0.3: by some 50 units of log2 per 128-position
+    tile), which is where a lazily or optimistically kept offset is put to the test."""
+    if chunk_kernel_choice == 1:
+        pytest.skip("one path per case is enough for the portable kernel")
+    n_q, n_kv, hd, pos0, n = 8, 2, 128, 256, 384
+    rng = np.random.default_rng(int(1000 * abs(ramp)) + 5)
+    top = pos0 + n
+    direction = rng.standard_normal(hd)
+    direction /= np.linalg.norm(direction)
+    # k(pos) = noise + ramp * pos * direction, q = noise + 4 * direction: the score
+    # of a late position exceeds an early one's by about ramp * 4 * distance / sqrt(hd)
+    k = (0.3 * rng.standard_normal((n_kv, top, hd)) +
+         ramp * np.arange(top)[None, :, None] * direction[None, None, :] * np.sqrt(hd)).astype(np.float16)
+    v = workloads.f16_values(rng, (n_kv, top, hd), np.float16)
+    cache = decode.KvCache(n_kv, n_q, hd, top + 13)
+    fill_bits(cache.k, NAN16)
+    fill_bits(cache.v, NAN16)
+    cache.k[:, :top] = dev(k)
+    cache.v[:, :top] = dev(v)
+    qkv = np.zeros((n, (n_q + 2 * n_kv) * hd), np.float32)
+    q = (0.3 * rng.standard_normal((n, n_q, hd)) + 4.0 * direction).astype(np.float16).astype(np.float32)
+    qkv[:, : n_q * hd] = q.reshape(n, -1)
+    out = torch.zeros(n * n_q * hd, dtype=torch.float16, device="cuda")
+    chunk.attn(dev(qkv), cache, out, n_q, pos0, n)
+    want = orc.chunk_attention(q.astype(np.float64), k, v, pos0, 1.0 / np.sqrt(hd))
+    assert_close_per_head(host(out).astype(np.float64).reshape(n, n_q, hd), want,
+                          f"drifting scores, ramp {ramp}")
+
+
 def _cache_view(batch, s_idx):
     """One sequence of a KvCacheBatch as a single-sequence KvCache (no copy)."""
     view = decode.KvCache.__new__(decode.KvCache)

@@ -799,40 +799,59 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
       const bool masked = j * BN + BN > lim_min;
       const int lim_local = lim - j * BN;
 
-      /* the whole score row into registers: one read of tensor memory, and P can
-       * then go over the first 64 columns of S at once */
+      /* The whole score row into registers: one read of tensor memory, and P can
+       * then go over the first 64 columns of S at once.
+       * After the first tile the row maximum is not computed: the exponentials are
+       * taken against the offset in use, and only if some row of the warp comes out
+       * with a sum of 2^15 or more (so that a probability might leave fp16's range;
+       * infinities and NaNs land here too) is the tile done again the exact way --
+       * maximum, new offset, O rescaled -- from the scores still in tensor memory.
+       * 64 three-input maxima and their dependency chain per tile, a seventh of the
+       * softmax, are saved; offsets move as rarely as with the 2^8 rule. */
       uint32_t sv[BN];
+      bool exact = j == 0;
+      bool warp_grow;
+      float m_new, m_use, psum;
+      for (;;) {
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32)
-        tmem_ld_32x32(s_col + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
-      tmem_ld_wait();
-      if (masked) {
+        for (int c0 = 0; c0 < BN; c0 += 32)
+          tmem_ld_32x32(s_col + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+        tmem_ld_wait();
+        if (masked) {
 #pragma unroll
-        for (int c = 0; c < BN; ++c)
-          if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < BN; c += 8)
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const bool grow = j == 0 || mx > m_ref + 8.f; /* lazy rescale, see the one-tile kernel */
-      const bool warp_grow = __any_sync(0xffffffffu, grow);
-      const float m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-
-      float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < BN; c += 8)
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float p = ex2(__uint_as_float(sv[c + k]) - m_use);
-          ps8[k] += p;
-          sv[c + k] = __float_as_uint(p);
+          for (int c = 0; c < BN; ++c)
+            if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
         }
-      const float psum = ((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7]));
+        if (exact) {
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int c = 0; c < BN; c += 8)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          const bool grow = j == 0 || mx > m_ref + 8.f; /* rows that are fine keep their offset */
+          warp_grow = __any_sync(0xffffffffu, grow);
+          m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
+        } else {
+          warp_grow = false;
+          m_new = m_ref;
+        }
+        m_use = m_new == -INFINITY ? 0.f : m_new;
+
+        float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < BN; c += 8)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float p = ex2(__uint_as_float(sv[c + k]) - m_use);
+            ps8[k] += p;
+            sv[c + k] = __float_as_uint(p);
+          }
+        psum = ((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7]));
+        if (exact || !__any_sync(0xffffffffu, !(psum < 32768.f))) break;
+        exact = true;
+      }
 #pragma unroll
       for (int c = 0; c < BN / 2; ++c)
         sv[c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
