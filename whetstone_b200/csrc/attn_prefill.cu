@@ -706,11 +706,13 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     };
     auto issue_pv = [&](int t, int j) -> bool { /* O_t += P_t V(j) */
       const int item = 2 * j + 1;
-      if (!mbar_wait(bar(FULL + item % NSLOT), (item / NSLOT) & 1, a.err_word, 0x312u)) return false;
-      const uint32_t vb = sbase + C::OFF_RING + (item % NSLOT) * KV_BYTES;
-      /* rows past the live data may hold anything and 0 * NaN is NaN: clear them
-       * once, before the first PV that reads this tile */
+      /* the first PV that reads this tile waits for it (the second finds it there) ... */
       const bool first_use = t == 0 || j >= n_tiles[0];
+      if (first_use &&
+          !mbar_wait(bar(FULL + item % NSLOT), (item / NSLOT) & 1, a.err_word, 0x312u)) return false;
+      const uint32_t vb = sbase + C::OFF_RING + (item % NSLOT) * KV_BYTES;
+      /* ... and clears its rows past the live data, which may hold anything, and
+       * 0 * NaN is NaN */
       if (first_use && j * BN + BN > kv_end[1]) {
         const int first = kv_end[1] - j * BN;
         for (int idx = first * (NH * 8) + lane; idx < BN * NH * 8; idx += 32) {
