@@ -121,6 +121,40 @@ def test_decode_matches_oracle(kernel_choice, n_q, n_kv, hd, seq):
                           f"decode {n_q}/{n_kv}/{hd} seq {seq}")
 
 
+@pytest.mark.parametrize("prefix", [3, 200, 1500])
+def test_decode_right_after_a_chunk_append(prefix):
+    """A multi-row append, a one-row append and the decode attention back to back on
+    one stream, repeated without a synchronize in between: the decode kernel asks for
+    its first tiles before its grid dependency is resolved, and must still see every
+    row the launches ahead of it wrote (and re-read the tile with the newest row)."""
+    n_q, n_kv, hd, theta = 28, 4, 128, 1e6
+    rng = np.random.default_rng(prefix)
+    steps = 6
+    max_seq = prefix + steps + 9
+    width = (n_q + 2 * n_kv) * hd
+    table = decode.RopeTable(max_seq, hd, theta)
+    cache = decode.KvCache(n_kv, n_q, hd, max_seq)
+    fill_bits(cache.k, NAN16)
+    fill_bits(cache.v, NAN16)
+    pre = workloads.f16_values(rng, (prefix, width))
+    rows = workloads.f16_values(rng, (steps, width))
+    outs = torch.zeros(steps, n_q * hd, dtype=torch.float16, device="cuda")
+    pre_d, rows_d = dev(pre), dev(rows)
+    cur = decode.DeviceCursor(prefix)
+    chunk.rope_cache(pre_d, cache, table, n_q, 0, prefix)
+    for j in range(steps):
+        decode.rope_cache(rows_d[j], cache, table, n_q, cur)
+        decode.attn_decode(rows_d[j], cache, outs[j], n_q, cur)
+        cur.advance(max_seq)
+    torch.cuda.synchronize()
+    _, k_pre, v_pre = orc.rope_append(pre, np.arange(prefix), n_q, n_kv, hd, theta)
+    qr, k_new, v_new = orc.rope_append(rows, prefix + np.arange(steps), n_q, n_kv, hd, theta)
+    k_all, v_all = np.concatenate([k_pre, k_new]), np.concatenate([v_pre, v_new])
+    want = orc.attention_blocked(qr, k_all, v_all, prefix + 1 + np.arange(steps))
+    assert_close_per_head(host(outs).astype(np.float64).reshape(steps, n_q, hd), want,
+                          f"decode after chunk append, prefix {prefix}")
+
+
 @pytest.mark.parametrize("hd", [32, 96, 160, 192, 224, 256])
 def test_decode_other_head_widths(hd):
     rng = np.random.default_rng(hd)
