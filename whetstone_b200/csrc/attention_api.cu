@@ -45,6 +45,18 @@ float *chunk_workspace() {
   return ws[dev];
 }
 
+/* Slices of the KV range for a chunk launch of `tiles` (unit, query tile) pairs
+ * against at most `len` positions: none when the tiles fill the GPU by themselves or
+ * the prefix is short; else enough to fill it, in runs of at least two KV tiles. */
+int chunk_slices(int sm_count, long long tiles, int len) {
+  if (tiles <= 0 || tiles * 2 > sm_count || len <= 512) return 1;
+  long long s = sm_count / tiles;
+  const long long kv_tiles = (len + 127) / 128;
+  if (s > kv_tiles / 2) s = kv_tiles / 2;
+  if (s > kRowsMaxSplits) s = kRowsMaxSplits;
+  return s < 2 ? 1 : static_cast<int>(s);
+}
+
 int max_splits_for(int max_seq) {
   int t = (max_seq + kRowsTile - 1) / kRowsTile;
   if (t > kRowsMaxSplits) t = kRowsMaxSplits;
@@ -399,16 +411,16 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
    * them (or the prefix is short enough that it does not matter); a few tokens
    * against a long prefix go to the split-KV kernel instead. */
   bool use_prefill = tc_ok && choice != 2 && prefill_kernel_supports(n_q, n_kv, head_dim, n);
-  bool sliced = false;
+  int splits = 1;
   if (use_prefill && choice != 3 && choice != 4) {
+    DeviceFacts facts;
+    if (!device_facts(&facts)) return WST_ERR_CUDA;
     const int gqa = n_q / n_kv;
-    const long long tiles = (static_cast<long long>(n) * gqa + 127) / 128 * n_kv;
-    if (!(tiles >= 32 || static_cast<long long>(pos0) + n <= 2048)) {
-      /* more than one mma.sync row tile but at most one tcgen05 tile per KV head:
-       * the same kernel, one CTA per slice of the prefix */
-      sliced = n * gqa > 16 && prefill_split_supports(n_q, n_kv, head_dim, n);
-      use_prefill = sliced;
-    }
+    splits = chunk_slices(facts.sm_count, (static_cast<long long>(n) * gqa + 127) / 128 * n_kv,
+                          pos0 + n);
+    /* at most one mma.sync row tile per KV head against a long prefix: the decode
+     * kernel's row-block form streams that better than a 128-row tcgen05 tile */
+    if (splits > 1 && n * gqa <= 16) use_prefill = false;
   }
   if (use_prefill) {
     PrefillLaunch P;
@@ -421,18 +433,11 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
     P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
     P.pos0 = pos0; P.n = n; P.max_seq = max_seq; P.scale = scale;
     P.force_pair = choice == 4 ? 1 : (choice == 3 ? -1 : 0);
-    if (sliced) {
-      DeviceFacts facts;
-      if (!device_facts(&facts)) return WST_ERR_CUDA;
+    if (splits > 1) {
       P.scratch = chunk_workspace();
       P.scratch_floats = P.scratch ? kChunkWorkspaceFloats : 0;
-      const int len = pos0 + n;
-      int splits = facts.sm_count / n_kv;
-      if (splits < (len + 2047) / 2048) splits = (len + 2047) / 2048;
-      if (splits > (len + 127) / 128) splits = (len + 127) / 128;
-      if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
       P.n_splits = splits;
-      P.max_len = len;
+      P.max_len = pos0 + n;
     }
     return launch_prefill(P);
   }

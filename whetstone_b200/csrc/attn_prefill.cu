@@ -146,8 +146,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   /* blockIdx.x is the query tile (longest prefixes first) or, when the KV range
    * is cut into slices (few query rows against a long prefix), the slice */
   const int ns = a.n_splits;
-  const int split = ns > 1 ? static_cast<int>(blockIdx.x) : 0;
-  const int qtile = ns > 1 ? 0 : a.n_qtiles - 1 - static_cast<int>(blockIdx.x);
+  const int split = ns > 1 ? static_cast<int>(blockIdx.x) % ns : 0;
+  const int qtile = a.n_qtiles - 1 - static_cast<int>(blockIdx.x) / (ns > 1 ? ns : 1);
   const int kvh = blockIdx.y;
   const int seq = blockIdx.z;
 
@@ -503,7 +503,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       /* one slice of a split KV range: this row's (acc, m, l) for the merge kernel,
        * acc[HD] | m | l | pad pad, log2 units (attn_rows.cu reads the same rows) */
       tc_fence_after_sync();
-      const long long unit = static_cast<long long>(seq) * a.n_kv + kvh;
+      const long long unit = (static_cast<long long>(seq) * a.n_kv + kvh) * a.n_qtiles + qtile;
       float *dst = a.scratch + ((unit * ns + split) * a.rows_cap + r) * (HD + 4) + half * OC;
 #pragma unroll
       for (int c0 = 0; c0 < OC; c0 += 32) {
@@ -1010,13 +1010,14 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   a.err_word = device_error_word();
   if (!a.err_word) return WST_ERR_CUDA;
 
-  /* slices of the KV range: only for a single query tile per unit */
+  /* slices of the KV range: every (unit, query tile) writes one partial per slice */
   int splits = P.n_splits > 0 ? P.n_splits : 1;
-  if (a.n_qtiles != 1) splits = 1;
-  a.rows_cap = P.n * a.gqa;
+  a.rows_cap = (P.n < a.tpt ? P.n : a.tpt) * a.gqa;
   const long long units = static_cast<long long>(P.n_seq) * P.n_kv;
   if (!P.scratch || !aligned16(P.scratch)) splits = 1;
-  while (splits > 1 && units * splits * a.rows_cap * (P.hd + 4) > P.scratch_floats) --splits;
+  while (splits > 1 &&
+         units * a.n_qtiles * splits * a.rows_cap * (P.hd + 4) > P.scratch_floats)
+    --splits;
   a.n_splits = splits;
   const int max_tiles = (P.max_len > 0 ? P.max_len : P.max_seq) / 128 + 1;
   a.tiles_per_slice = splits > 1 ? (max_tiles + splits - 1) / splits : 0;
@@ -1052,7 +1053,7 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   const bool enough = units * a.n_qtiles >= 2ll * facts.sm_count;
   const bool pair = P.force_pair >= 0 && (P.force_pair > 0 || (a.n_qtiles >= 2 && enough)) &&
                     splits == 1 && !P.page_table && !P.cu_tokens;
-  const unsigned gx = splits > 1 ? splits : (pair ? (a.n_qtiles + 1) / 2 : a.n_qtiles);
+  const unsigned gx = splits > 1 ? a.n_qtiles * splits : (pair ? (a.n_qtiles + 1) / 2 : a.n_qtiles);
   const dim3 grid(gx, static_cast<unsigned>(P.n_kv), static_cast<unsigned>(P.n_seq));
   if (pair)
     st = P.hd == 128
@@ -1078,10 +1079,10 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   m.n_kv = P.n_kv;
   m.hd = P.hd;
   m.n_splits = splits;
-  m.n_rowblk = 1;
-  m.tpb = P.n;
+  m.n_rowblk = a.n_qtiles;
+  m.tpb = a.tpt;
   m.rows_cap = a.rows_cap;
-  m.n_units = static_cast<int>(units);
+  m.n_units = static_cast<int>(units * a.n_qtiles);
   m.name = P.name;
   return launch_split_merge(m);
 }
