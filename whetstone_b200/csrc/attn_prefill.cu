@@ -1,32 +1,33 @@
-/* Kernel set 3: causal chunked-prefill attention on the 5th-generation tensor
- * cores.
+/* Kernel sets 3 and 4: causal chunked-prefill attention, and the ragged paged
+ * verify step, on the 5th-generation tensor cores.
  *
- * One CTA owns 128 query rows of one KV head -- rows are (token, head-in-group)
- * pairs, token-major, so a tile covers 128/gqa consecutive tokens and all the
- * query heads that share the KV head -- and walks the visible prefix in tiles of
- * 128 cache positions.  Per tile:
+ * Query rows are (token, head-in-group) pairs, token-major, 128 per tile -- a tile
+ * covers 128/gqa consecutive tokens and all the query heads that share a KV head --
+ * and a tile walks its visible prefix in tiles of 128 cache positions.  Per step:
  *
- *   S  = Q K^T   tcgen05.mma (M128 x N128 x K16 steps): Q is the A operand and
- *                lives in TENSOR MEMORY for the whole kernel (written once with
- *                tcgen05.st), K tiles are the B operand in 128-byte-swizzled
- *                shared memory, the fp32 accumulator is in tensor memory
- *   softmax      128 threads, one query row each (a TMEM lane is a row, so row
- *                max and row sum need no shuffles); fp32, exp2 with scale*log2(e)
- *                folded into q; P goes back into tensor memory as fp16 pairs
- *                (tcgen05.st) and is the A operand of the next MMA, so neither Q
- *                nor P ever crosses shared memory: per tile only K and V do
- *                (TMA in, tensor core out), which is what shared-memory
- *                bandwidth can sustain at the MMA rate
+ *   S  = Q K^T   tcgen05.mma (M128 x N128 x K16 steps), K tiles as the B operand in
+ *                128-byte-swizzled shared memory (TMA), fp32 accumulator in tensor
+ *                memory
+ *   softmax      one TMEM lane is one query row, so row maximum and row sum need no
+ *                shuffles; fp32, exp2 with scale*log2(e) folded into q; P goes back
+ *                into tensor memory as fp16 pairs (tcgen05.st) and is the A operand
+ *                of the next MMA: P never crosses shared memory
  *   O += P V     tcgen05.mma (M128 x N(head_dim) x K16 steps) accumulating in
- *                tensor memory across tiles.  The exponent offset of a row is only
- *                moved when its maximum grows by more than 2^8 ("lazy rescale");
- *                then the row's owner multiplies its O lane in place
- *                (tcgen05.ld / tcgen05.st) before the next PV is issued.
+ *                tensor memory across tiles.  The exponent offset of a row moves
+ *                only when it has to ("lazy rescale"); then the row's owner
+ *                multiplies its O lane in place (tcgen05.ld / tcgen05.st).
  *
- * Warp roles: warps 0-3 softmax/epilogue, warp 4 issues the MMAs (one elected
- * lane), warp 5 feeds K and V tiles with TMA.  S is double-buffered in tensor
- * memory, so QK^T of tile j+1 runs on the tensor cores while the CUDA cores do
- * the softmax of tile j.  Every wait is bounded.
+ * Two kernels:
+ *   attn_prefill_kernel<HD, PAGED>   one tile per CTA.  Q too is a tensor-memory
+ *       operand; S double-buffered; two softmax threads per row (8 warps), one MMA
+ *       warp, one TMA warp.  Paged caches, ragged batches, and the sliced form
+ *       (grid.x = query tiles x slices of the KV range, partial rows for the slice
+ *       merge kernel of attn_rows.cu) for launches that cannot fill the GPU.
+ *   attn_prefill_pair_kernel<HD>     two tiles of one KV head per CTA, each with a
+ *       softmax warpgroup of its own (one thread per row): one tile's softmax runs
+ *       under the other tile's MMAs and every K/V tile serves 256 rows.  The
+ *       default for launches of at least two waves of tiles.
+ * Every wait is bounded.
  *
  * Semantics: cuda/chunk_ops.cu:187-264 of the engine (query j sees cache rows
  * [0, pos0 + j]; fp32 softmax state; fp16 output).
