@@ -67,7 +67,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE, text=True)
+                 "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -267,27 +267,29 @@ def bench_c3(torch, args, rank, world, dist):
     bytes_layer = wl.decode_bytes(s.n_q, s.n_kv, s.head_dim, ctx)   # whole job, all ranks
     value = bytes_layer * layers / sec / 1e9
 
-    # end to end: each layer's qkv comes from pinned host memory, the new token is
-    # appended (RoPE), attended, and the result goes back to the host
-    host_in = [q.cpu().pin_memory() for q in qkvs]
-    host_out = [torch.zeros(s.n_q * s.head_dim, dtype=torch.float16).pin_memory()
-                for _ in range(layers)]
+    # end to end: the step's inputs (every layer's qkv row) come from pinned host memory
+    # in one copy, each layer appends its token (RoPE) and attends, and the step's
+    # results (every layer's attention output) go back to the host in one copy
+    host_in = torch.stack([q.cpu() for q in qkvs]).pin_memory()
+    dev_in = torch.empty_like(host_in, device="cuda")
+    dev_out = torch.zeros(layers, s.n_q * s.head_dim, dtype=torch.float16, device="cuda")
+    host_out = torch.zeros(layers, s.n_q * s.head_dim, dtype=torch.float16).pin_memory()
     if world == 1:
         def step_e2e():
+            dev_in.copy_(host_in, non_blocking=True)
             for i in range(layers):
-                qkvs[i].copy_(host_in[i], non_blocking=True)
-                decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cursor)
-                decode.attn_decode(qkvs[i], caches[i], outs[i], s.n_q, cursor)
-                host_out[i].copy_(outs[i], non_blocking=True)
+                decode.rope_cache(dev_in[i], caches[i], table, s.n_q, cursor)
+                decode.attn_decode(dev_in[i], caches[i], dev_out[i], s.n_q, cursor)
+            host_out.copy_(dev_out, non_blocking=True)
     else:
         def step_e2e():
+            dev_in.copy_(host_in, non_blocking=True)
             for i in range(layers):
-                qkvs[i].copy_(host_in[i], non_blocking=True)
                 if rank == world - 1:   # the shard that owns the newest position appends
-                    decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cursor)
-                decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
-                xch.merge(mine[i], outs[i])
-                host_out[i].copy_(outs[i], non_blocking=True)
+                    decode.rope_cache(dev_in[i], caches[i], table, s.n_q, cursor)
+                decode.attn_decode_partial(dev_in[i], caches[i], mine[i], s.n_q, length)
+                xch.merge(mine[i], dev_out[i])
+            host_out.copy_(dev_out, non_blocking=True)
     sec_e2e = timed_graph(torch, step_e2e, args.steps, args.warmup, dist if world > 1 else None)
     e2e = {"value": bytes_layer * layers / sec_e2e / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": layers * s.qkv_width * 4,
