@@ -1049,10 +1049,14 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   /* Two query tiles per CTA whenever there are two: the tiles' softmax warpgroups
    * and MMAs overlap (835 against 729 TFLOP/s on the 4 x 8192-token, 32-head
    * shape) and every K/V tile fetched from L2 serves 256 query rows.  The one-tile
-   * kernel takes what is left: launches too small to fill the GPU with pairs, paged
-   * caches, ragged batches and the sliced form. */
-  const bool enough = units * a.n_qtiles >= 2ll * facts.sm_count;
-  const bool pair = P.force_pair >= 0 && (P.force_pair > 0 || (a.n_qtiles >= 2 && enough)) &&
+   * kernel takes what is left: launches that finish sooner with one tile per CTA
+   * (few tiles), paged caches, ragged batches and the sliced form. */
+  /* waves x measured clocks per KV tile: about 2250 for a CTA with one query tile,
+   * 3700 for one with two */
+  const long long tiles = units * a.n_qtiles, pairs = units * ((a.n_qtiles + 1) / 2);
+  const long long sm = facts.sm_count;
+  const bool pays = (pairs + sm - 1) / sm * 3700 < (tiles + sm - 1) / sm * 2250;
+  const bool pair = P.force_pair >= 0 && (P.force_pair > 0 || (a.n_qtiles >= 2 && pays)) &&
                     splits == 1 && !P.page_table && !P.cu_tokens;
   const unsigned gx = splits > 1 ? a.n_qtiles * splits : (pair ? (a.n_qtiles + 1) / 2 : a.n_qtiles);
   const dim3 grid(gx, static_cast<unsigned>(P.n_kv), static_cast<unsigned>(P.n_seq));
