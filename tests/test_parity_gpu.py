@@ -477,3 +477,35 @@ def test_paged_verify_ragged_token_counts(verify_kernel_choice):
         v_all = np.concatenate([v_ctx[s].astype(np.float64).transpose(1, 0, 2), vv])
         want = orc.attention_blocked(qr, k_all, v_all, L + 1 + np.arange(c))
         assert_close_per_head(got[cu_np[s]:cu_np[s + 1]], want, f"ragged seq {s}")
+
+
+# ------------------------------------------- bounded waits report, never hang
+
+def test_exchange_wait_runs_out_and_reports():
+    """wst_attn_exchange_merge with a second "rank" that never publishes: every
+    block's poll gives up after its bound (about a second), the device error word
+    says so, nothing is written to `out`, and the context stays usable.  Both
+    mailboxes are plain local buffers: no second kernel, no second GPU."""
+    n_q, hd, world = 4, 64, 2
+    packets = 2 * world * n_q * (hd + 2)
+    own = torch.zeros(packets * 2, dtype=torch.int32, device="cuda")
+    silent_peer = torch.zeros(packets * 2, dtype=torch.int32, device="cuda")
+    boxes = torch.tensor([own.data_ptr(), silent_peer.data_ptr()], dtype=torch.int64, device="cuda")
+    state = torch.zeros(n_q, dtype=torch.int32, device="cuda")
+    mine = torch.ones(n_q, hd + 2, dtype=torch.float32, device="cuda")
+    out = torch.full((n_q * hd,), 7.0, dtype=torch.float16, device="cuda")
+    assert decode.device_error() == 0
+    decode.attn_exchange_merge(mine, out, boxes, state, 0, world, n_q, hd)
+    torch.cuda.synchronize()
+    assert decode.device_error() == 0x401
+    assert torch.all(out == 7.0)                      # no head was merged
+    assert torch.all(state == 1)                      # the call is closed all the same
+    assert decode.device_error() == 0                 # reading the word cleared it
+    # with world = 1 the same buffers work at once
+    out1 = torch.zeros(n_q * hd, dtype=torch.float16, device="cuda")
+    boxes1 = torch.tensor([own.data_ptr()], dtype=torch.int64, device="cuda")
+    mine[:, 0] = 0.0   # m = 0, l = 1, acc = 1  ->  out = 1
+    decode.attn_exchange_merge(mine, out1, boxes1, state, 0, 1, n_q, hd)
+    torch.cuda.synchronize()
+    assert decode.device_error() == 0
+    assert torch.allclose(out1.float(), torch.ones_like(out1.float()))
