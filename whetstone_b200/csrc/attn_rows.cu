@@ -212,6 +212,12 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
    * as a consumer thread reports the dependency resolved, whichever comes first.  A tile that
    * holds the newest row and was requested early is read again after the wait,
    * into the spare stage. */
+  /* Let the kernels behind this one in the stream be scheduled as early as there is
+   * room for them (the slice merge is resident at once and waits for this grid; the
+   * next launch's blocks start the moment this one's leave their SM, a launch latency
+   * sooner than if they were released after the stream); what they may read is
+   * ordered by their own griddepcontrol.wait, not by this. */
+  grid_launch_dependents();
   const bool early = !PAGED && a.early_spec != 0;
   const int n_early = early ? spec : 0;
   WST_STAMP(0);
@@ -499,9 +505,6 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   for (int i = my_tiles; i < spec; ++i)
     if (!mbar_wait(full_u32 + 8 * (i % NSTAGE), (i / NSTAGE) & 1, a.err_word, 0x103u)) break;
 
-  /* The cache has been streamed: let the next kernel in the stream start its
-   * prologue while this one combines its warps. */
-  grid_launch_dependents();
   WST_STAMP(3);
 
   /* row sums live spread over the four lanes of a quad */
