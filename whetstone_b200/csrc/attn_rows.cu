@@ -222,6 +222,15 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int n_early = early ? spec : 0;
   WST_STAMP(0);
   if (early) {
+    /* the group's q rows and the cursor towards L2 while the dependency is open: a
+     * prefetch has no architectural effect, whatever the launch ahead still writes */
+    if (warp == 0) {
+      const char *qrow = reinterpret_cast<const char *>(a.q + static_cast<long long>(kvh) * a.gqa * HD);
+      const int lines = (a.gqa * HD * 4 + 127) / 128;
+      for (int l = lane; l < lines; l += 32)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(qrow + l * 128));
+      if (lane == 0 && a.pos0_dev) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.pos0_dev));
+    }
     if (warp == C::CWARPS) {
       if (lane == 0 && spec > 0) {
         issue(0);
