@@ -262,7 +262,26 @@ def bench_c3(torch, args, rank, world, dist):
 
     with ClockSampler(torch.cuda.current_device()) as clk:
         sec = timed_graph(torch, step, args.steps, args.warmup, dist if world > 1 else None)
+        sampled_after = False
+        if world == 1 and len(clk.rows) < 3:
+            # a timed region shorter than the sampler's start-up: keep the same load
+            # running (untimed) until it has seen the clocks
+            sampled_after = True
+            t_end = time.perf_counter() + 1.0
+            while len(clk.rows) < 3 and time.perf_counter() < t_end:
+                for _ in range(20):
+                    step()
+                torch.cuda.synchronize()
+        elif world > 1 and sec * args.steps < 0.15:
+            # every rank runs the same number of extra (untimed) steps: `sec` is the
+            # all-reduced maximum, so the count agrees across ranks
+            sampled_after = True
+            for _ in range(int(0.25 / sec) + 1):
+                step()
+            torch.cuda.synchronize()
     clocks = clk.summary()
+    if sampled_after and clk.rows:
+        clocks["sampled"] = "same load, right after the timed region (region shorter than the sampler's start-up)"
 
     bytes_layer = wl.decode_bytes(s.n_q, s.n_kv, s.head_dim, ctx)   # whole job, all ranks
     value = bytes_layer * layers / sec / 1e9
