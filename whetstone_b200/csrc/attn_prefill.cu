@@ -152,6 +152,30 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
   const int kvh = blockIdx.y;
   const int seq = blockIdx.z;
 
+  if (ns > 1 && split > 0) {
+    /* A slice past the end of a short sequence has no tiles: publish the empty
+     * partial the merge kernel expects and leave before barriers and tensor memory are
+     * set up (about half of the CTAs of a ragged batch are of this kind). */
+    grid_dependency_wait();
+    const int e_pos0 = a.pos0_dev ? max(a.pos0_dev[seq], 0) : a.pos0;
+    int e_ntok = a.n;
+    if (a.cu_tokens) e_ntok = a.cu_tokens[seq + 1] - a.cu_tokens[seq];
+    const int e_tok0 = qtile * a.tpt;
+    e_ntok = max(min(a.tpt, e_ntok - e_tok0), 0);
+    const int e_kv_end = e_ntok > 0 ? min(e_pos0 + e_tok0 + e_ntok, a.max_seq) : 0;
+    const int e_tiles = (e_kv_end + BN - 1) / BN;
+    if (e_tiles - split * a.tiles_per_slice <= 0) {
+      constexpr int V4 = (HD + 4) / 4; /* float4 per scratch row: acc[HD] | m l pad pad */
+      const long long unit = (static_cast<long long>(seq) * a.n_kv + kvh) * a.n_qtiles + qtile;
+      float4 *dst = reinterpret_cast<float4 *>(a.scratch + (unit * ns + split) * a.rows_cap * (HD + 4));
+      const int n4 = e_ntok * a.gqa * V4;
+      for (int idx = threadIdx.x; idx < n4; idx += blockDim.x)
+        dst[idx] = idx % V4 == V4 - 1 ? make_float4(-INFINITY, 0.f, 0.f, 0.f)
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+      return;
+    }
+  }
+
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) {
       mbar_init(bar(K_FULL + i), 1);
