@@ -107,7 +107,21 @@ WST_API wst_status_t wst_rope_cache(void *qkv, void *k_cache, void *v_cache, con
  *   partials   scratch of wst_attn_partial_floats() floats
  *   out        [n_q][head_dim] half
  *   scale      multiplies the scores (callers pass 1/sqrt(head_dim))
- * Requires n_q % n_kv == 0, head_dim % 32 == 0, head_dim <= 256. */
+ * Requires n_q % n_kv == 0, head_dim % 32 == 0, head_dim <= 256.
+ *
+ * Stream-order precondition (this library only; the engine's kernel has none): the
+ * kernel is launched with programmatic stream serialization and asks for cache rows
+ * below *pos before the launches ahead of it in the stream have finished.  So,
+ * between the last ordinary kernel launch (one without that attribute: every
+ * launch of the engine today) that wrote rows [0, *pos) of this layer's k_cache /
+ * v_cache and this call, the stream may hold only launches that write no such row:
+ * this library's wst_rope_cache (it writes row *pos alone, and the kernel re-reads
+ * that row after its dependency has resolved), wst_attn_decode of other layers,
+ * GEMVs and the like.  The engine's call order (qkv GEMV, wst_rope_cache,
+ * wst_attn_decode: crates/whetstone-core/src/engine.rs:526-536) satisfies it.  A
+ * host that rewrites older rows right before a decode (restoring a cache from a
+ * snapshot, say) either synchronises first or switches the early requests off
+ * with wst_b200_set_decode_overlap(0). */
 WST_API wst_status_t wst_attn_decode(const void *q, const void *k_cache, const void *v_cache,
                              void *partials, void *out, int32_t n_q, int32_t n_kv,
                              int32_t head_dim, const void *pos, int32_t max_seq,
@@ -133,7 +147,12 @@ WST_API wst_status_t wst_rope_cache_chunk(void *qkv, void *k_cache, void *v_cach
  * both chunked prefill and speculative verification.
  * whetstone.h:360-362, cuda/chunk_ops.cu:187-291.
  *   qkv   as above (q of token j, head h at j*stride + h*head_dim)
- *   out   [n][n_q * head_dim] half */
+ *   out   [n][n_q * head_dim] half
+ * A few tokens against a long prefix are cut into slices of the KV range; their
+ * partial rows go to a 16 MiB workspace the library keeps per host thread and
+ * device, allocated by the thread's first such call (an ordinary call, not one under
+ * capture) or by wst_b200_reserve_chunk_workspace (whetstone_b200.h).  Without one
+ * the call still runs, unsplit, returns WST_OK and says so in wst_last_error(). */
 WST_API wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache, const void *v_cache,
                             void *out, int32_t n_q, int32_t n_kv, int32_t head_dim,
                             int32_t pos0, int32_t n, int32_t max_seq, float scale);

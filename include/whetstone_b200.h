@@ -43,6 +43,26 @@ WST_API wst_status_t wst_b200_device_error(uint32_t *out_code);
  * A debugging aid for A/B checks; process-wide. */
 WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
 
+/* Measurement knobs of the decode kernel, process-wide; value -1 or 0 restores the
+ * default.  Results do not depend on them beyond fp32 summation order.
+ *   key 1  slices of the KV sequence per KV head (default: SMs / KV heads)
+ *   key 2  cache tiles requested at once before the launch ahead has finished
+ *   key 3  1 = the slice that finishes last merges the slices inside the kernel,
+ *          0 = a second kernel merges them
+ *   key 4  stages of the shared-memory ring in use */
+WST_API wst_status_t wst_b200_set_tuning(int32_t key, int32_t value);
+
+/* 0: wst_attn_decode waits for everything ahead of it in the stream before it asks
+ * for any cache row (no stream-order precondition, see whetstone.h); 1 (default):
+ * it asks for the rows below the cursor early.  Process-wide. */
+WST_API wst_status_t wst_b200_set_decode_overlap(int32_t on);
+
+/* Allocates the calling thread's 16 MiB split workspace of wst_attn_chunk /
+ * wst_attn_chunk_batch on the current device now (once; later calls return at
+ * once), so that no chunk call ever has to: call it at start-up, outside any
+ * capture.  WST_ERR_OOM with the reason if it cannot be had. */
+WST_API wst_status_t wst_b200_reserve_chunk_workspace(void);
+
 /* --------------------------------------------------------- RoPE table */
 
 /* cos/sin tables [max_seq][head_dim/2] float, angles evaluated in double on the
@@ -98,6 +118,27 @@ WST_API wst_status_t wst_attn_exchange_merge(const void *my_triples, void *out,
                                              const void *mailboxes, void *state, int32_t rank,
                                              int32_t world, int32_t n_q, int32_t head_dim);
 
+/* wst_attn_decode_partial and the exchange in ONE kernel, for the GPUs of one box:
+ * the slice of this rank's shard that finishes last merges the shard's slices,
+ * stores each head's (m, l, acc) triple into the other ranks' mailboxes (plain peer
+ * stores over NVLink, 8-byte {value, tag} packets), waits -- each packet for at most
+ * about a second -- for theirs in its own mailbox, and writes the fp16 result.  One
+ * launch per layer and rank, no NCCL call, no host step.
+ *   len         device int32: valid rows of THIS rank's shard (as wst_attn_decode_partial)
+ *   partials    scratch of wst_attn_partial_floats() floats
+ *   out         [n_q][head_dim] half (every rank gets the full result)
+ *   mailboxes, state, rank, world   as for wst_attn_exchange_merge; the two entry
+ *               points may share them as long as every rank makes the same sequence
+ *               of calls
+ * Needs head_dim 64 or 128 and at most 32 query heads per KV head
+ * (WST_ERR_SHAPE otherwise: use wst_attn_decode_partial + wst_attn_exchange_merge). */
+WST_API wst_status_t wst_attn_decode_sharded(const void *q, const void *k_cache,
+                                             const void *v_cache, void *partials, void *out,
+                                             int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                             const void *len, int32_t max_seq, float scale,
+                                             const void *mailboxes, void *state, int32_t rank,
+                                             int32_t world);
+
 /* One device buffer shared by the processes of a box (one process per GPU).  The
  * owner exports a 64-byte handle of a buffer from wst_malloc; another process
  * imports it with its own device current and gets an address its kernels can use
@@ -120,7 +161,13 @@ WST_API wst_status_t wst_b200_enable_peer_access(int32_t peer_device);
  * to an array built into the library (2 MiB of device memory per GPU, held from
  * load to exit).
  *
- *   - Nothing is allocated or freed, on any call.
+ *   - No call allocates or frees device memory.  The array itself is part of the
+ *     library's device image: the CUDA driver sets that image up (and with it the
+ *     2 MiB) when the library's kernels are first used on a device.  A host that
+ *     hands all device memory to its own pool should therefore make one call of
+ *     this entry point (or any attention call of this library) per device BEFORE
+ *     the pool takes the memory, or load the library with
+ *     CUDA_MODULE_LOADING=EAGER.
  *   - Limit: n_q * min(64, ceil(max_seq / 64)) * (head_dim + 4) floats must not
  *     exceed 524288 (e.g. 28 heads of 128 at any context: 236544).  Larger shapes
  *     are refused with WST_ERR_INVALID_ARG; use wst_attn_decode for them.

@@ -162,6 +162,53 @@ def test_c4_batched_prefill_with_qk_norm():
                               f"c4 seq {seq} token {c * n + j} vs single-token path")
 
 
+def test_c4_through_the_batched_entry_points_at_full_size():
+    """Layer 0 the way the benchmark runs it: one batched cache [4][8][8192][128], every
+    chunk step ONE wst_rope_cache_chunk_batch (QK-norm gains of the config) and ONE
+    wst_attn_chunk_batch over the four sequences, chunk starts in device memory.
+    Chunks 0, 1 and 15 of sequences 0 and 2 against the oracle (chunk 15 on a spread of
+    its 512 rows: the oracle needs seconds per 100 rows at 8192 keys); V bits exact and K
+    within one fp16 ulp over the whole batched cache of those sequences."""
+    s, cfg = wl.QWEN3_8B, wl.C4
+    n, prompt, eps, n_seq = cfg["chunk"], cfg["prompt"], cfg["eps"], cfg["n_seq"]
+    chunks = prompt // n
+    gq, gk = wl.c4_gains(0)
+    norm = decode.QkNorm(dev(gq), dev(gk), eps)
+    table = decode.RopeTable(prompt, s.head_dim, s.theta)
+    batch = chunk.KvCacheBatch(n_seq, s.n_kv, s.head_dim, prompt)
+    fill_bits(batch.k, NAN16)
+    fill_bits(batch.v, NAN16)
+    checked = (0, 2)
+    k_all = {q: np.zeros((prompt, s.n_kv, s.head_dim)) for q in checked}
+    v_all = {q: np.zeros((prompt, s.n_kv, s.head_dim)) for q in checked}
+    out = torch.zeros(n_seq * n * s.n_q * s.head_dim, dtype=torch.float16, device="cuda")
+    spread = np.unique(np.concatenate([np.arange(0, 40), np.arange(250, 262), np.arange(n - 36, n)]))
+    for c in range(chunks):
+        qkv = np.stack([wl.c4_chunk(0, q, c) for q in range(n_seq)])
+        qd = dev(qkv)
+        starts = torch.full((n_seq,), c * n, dtype=torch.int32, device="cuda")
+        chunk.rope_cache_batch(qd, batch, table, s.n_q, starts, n, norm)
+        rotated = {}
+        for q in checked:
+            rotated[q], k_all[q][c * n:(c + 1) * n], v_all[q][c * n:(c + 1) * n] = orc.rope_append(
+                qkv[q], c * n + np.arange(n), s.n_q, s.n_kv, s.head_dim, s.theta, gq, gk, eps)
+        if c not in (0, 1, chunks - 1):
+            continue
+        chunk.attn_batch(qd, batch, out, s.n_q, starts, n)
+        got = host(out).astype(np.float64).reshape(n_seq, n, s.n_q, s.head_dim)
+        rows = np.arange(n) if c < 2 else spread
+        for q in checked:
+            want = orc.attention_blocked(rotated[q][rows], k_all[q][:(c + 1) * n],
+                                         v_all[q][:(c + 1) * n], c * n + 1 + rows, s.scale)
+            assert_close_per_head(got[q][rows], want, f"c4 batched, sequence {q}, chunk {c}")
+    for q in checked:
+        assert np.array_equal(bits16(batch.v[q]),
+                              v_all[q].transpose(1, 0, 2).astype(np.float16).view(np.uint16))
+        assert_k_cache_matches(bits16(batch.k[q]), k_all[q].transpose(1, 0, 2),
+                               f"c4 batched K cache, sequence {q}")
+    assert decode.device_error() == 0
+
+
 def test_c5_paged_verify_16_sequences():
     s, cfg = wl.QWEN25_7B, wl.C5
     drafts = cfg["drafts"]

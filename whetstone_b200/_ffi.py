@@ -107,6 +107,10 @@ SIGNATURES: dict[str, tuple] = {
     "wst_attn_decode_partial": (I, [P, P, P, P, P, I, I, I, P, I, F]),
     "wst_attn_merge_partials": (I, [P, P, I, I, I]),
     "wst_attn_exchange_merge": (I, [P, P, P, P, I, I, I, I]),
+    "wst_attn_decode_sharded": (I, [P, P, P, P, P, I, I, I, P, I, F, P, P, I, I]),
+    "wst_b200_set_tuning": (I, [I, I]),
+    "wst_b200_set_decode_overlap": (I, [I]),
+    "wst_b200_reserve_chunk_workspace": (I, []),
     "wst_b200_enable_peer_access": (I, [I]),
     "wst_b200_ipc_export": (I, [P, P]),
     "wst_b200_ipc_import": (I, [P, ctypes.POINTER(ctypes.c_void_p)]),

@@ -18,31 +18,47 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 /* wst_attn_chunk has no scratch argument (the engine's chunk kernel never
  * splits the sequence), but a handful of draft tokens against a long prefix
- * must be split to fill the GPU.  The slices' triples go to a per-device
- * workspace of fixed size, allocated by the first chunk call on that device --
- * which, as for every lazily initialised part of this ABI, has to be an
- * ordinary (not graph-captured) call.  Calls that overlap on the GPU from
- * different streams would share it; the engine is single-stream. */
+ * must be split to fill the GPU.  The slices' partial rows go to a workspace of
+ * fixed size (16 MiB) that the library keeps per host thread and device (the engine
+ * drives a GPU from one thread, on that thread's stream); one thread that switches
+ * streams with wst_b200_set_stream shares its workspace between them and must not let
+ * two such chunk calls overlap on the GPU.  It is allocated by
+ * wst_b200_reserve_chunk_workspace, or by the thread's first chunk call that wants
+ * it -- which, as for every lazily initialised part of this ABI, has to be an
+ * ordinary (not graph-captured) call.  When there is none and none can be had
+ * (capture in progress, out of memory), the call still runs, unsplit, and says so in
+ * the thread's error text.  Never freed: it lives as long as the process. */
 constexpr long long kChunkWorkspaceFloats = 4ll << 20; /* 16 MiB */
 
-float *chunk_workspace() {
-  static float *ws[64] = {};
-  static std::mutex mu;
+/* Returns nullptr (and the reason) when no workspace exists and none can be made. */
+float *chunk_workspace(const char **why) {
+  static thread_local float *ws[64] = {};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!ws[dev]) {
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    cudaStreamIsCapturing(current_stream(), &cap);
-    if (cap != cudaStreamCaptureStatusNone) return nullptr;
-    void *p = nullptr;
-    if (cudaMalloc(&p, kChunkWorkspaceFloats * sizeof(float)) != cudaSuccess) {
-      cudaGetLastError();
-      return nullptr;
-    }
-    ws[dev] = static_cast<float *>(p);
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *why = "cudaGetDevice failed";
+    return nullptr;
   }
+  if (ws[dev]) return ws[dev];
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(current_stream(), &cap);
+  if (cap != cudaStreamCaptureStatusNone) {
+    *why = "the stream is being captured and this thread has no workspace yet";
+    return nullptr;
+  }
+  void *p = nullptr;
+  if (cudaMalloc(&p, kChunkWorkspaceFloats * sizeof(float)) != cudaSuccess) {
+    cudaGetLastError();
+    *why = "cudaMalloc of the 16 MiB workspace failed";
+    return nullptr;
+  }
+  ws[dev] = static_cast<float *>(p);
   return ws[dev];
+}
+
+/* Records, without failing the call, that a launch ran unsplit for want of a workspace. */
+void note_unsplit(const char *who, const char *why) {
+  fail(WST_OK, "%s: ran without splitting the KV range (%s); call "
+               "wst_b200_reserve_chunk_workspace once outside any capture", who, why);
 }
 
 /* Slices of the KV range for a chunk launch of `tiles` (unit, query tile) pairs
@@ -80,7 +96,9 @@ wst_status_t check_decode_shape(const char *who, int32_t n_q, int32_t n_kv, int3
 wst_status_t decode_common(const char *who, const void *q, const void *k_cache,
                            const void *v_cache, void *partials, void *out, int32_t n_q,
                            int32_t n_kv, int32_t head_dim, const void *pos, int32_t max_seq,
-                           float scale, bool partial_out) {
+                           float scale, bool len_is_count, bool partial_out,
+                           const void *mailboxes = nullptr, void *xstate = nullptr, int rank = 0,
+                           int world = 1) {
   RowsLaunch L;
   L.name = who;
   L.q = static_cast<const float *>(q);
@@ -89,7 +107,7 @@ wst_status_t decode_common(const char *who, const void *q, const void *k_cache,
   L.v = static_cast<const __half *>(v_cache);
   L.max_seq = max_seq;
   L.pos0_dev = static_cast<const int32_t *>(pos);
-  if (partial_out) {
+  if (len_is_count) {
     L.pos0_bias = -1; /* `len` counts rows: the last visible one is len-1 */
     L.clamp_pos0_nonneg = false;
   } else {
@@ -107,9 +125,15 @@ wst_status_t decode_common(const char *who, const void *q, const void *k_cache,
   L.max_len = max_seq;
   L.out = out;
   L.partial_out = partial_out;
+  L.mailboxes = mailboxes;
+  L.xstate = xstate;
+  L.rank = rank;
+  L.world = world;
   if (g_kernel_choice.load() != 1 && rows_kernel_supports(n_q, n_kv, head_dim, k_cache, v_cache) &&
       aligned16(q))
     return launch_rows(L);
+  if (world > 1)
+    return fail(WST_ERR_SHAPE, "%s: needs head_dim 64 or 128 and 16-byte aligned buffers", who);
   return launch_simple(L);
 }
 
@@ -169,7 +193,7 @@ __global__ void merge_partials_kernel(const float *__restrict__ parts, __half *_
  * sharded over the GPUs of a box; each rank has its heads' (m, l, acc) triples).
  * One block per query head; no block waits for another block of its own grid.
  *
- * Every float travels as an 8-byte packet {value, tag} written with ONE store, so a
+ * Every float travels as an 8-byte packet {value, tag} written with ONE 64-bit store, so a
  * packet is valid exactly when its tag is this call's tag: no fence, no separate
  * flag, no ordering between packets.  The block stores its head's triple into every
  * rank's mailbox (plain stores to peer memory over NVLink), then reads the same
@@ -188,27 +212,26 @@ struct ExchangeArgs {
   int rank, world, n_q, hd;
 };
 
-__device__ __forceinline__ uint2 ld_packet(const uint2 *p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ void st_packet(uint2 *p, float value, unsigned int tag) {
-  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(value)),
-               "r"(tag)
-               : "memory");
+  const unsigned long long pk = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(value);
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(pk) : "memory");
 }
 /* value of a packet once its tag has arrived; false after about a second */
 __device__ __forceinline__ bool wait_packet(const uint2 *p, unsigned int tag, float *value) {
-  uint2 v = ld_packet(p);
-  if (v.y != tag) {
+  auto load = [p]() {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+  };
+  unsigned long long v = load();
+  if (static_cast<unsigned int>(v >> 32) != tag) {
     const long long t0 = clock64();
     do {
       if (clock64() - t0 > ptx::kWaitCycleLimit) return false;
-      v = ld_packet(p);
-    } while (v.y != tag);
+      v = load();
+    } while (static_cast<unsigned int>(v >> 32) != tag);
   }
-  *value = __uint_as_float(v.x);
+  *value = __uint_as_float(static_cast<unsigned int>(v));
   return true;
 }
 
@@ -272,6 +295,30 @@ extern "C" wst_status_t wst_b200_set_kernel_choice(int32_t choice) {
   return WST_OK;
 }
 
+extern "C" wst_status_t wst_b200_set_tuning(int32_t key, int32_t value) {
+  RowsTuning &t = rows_tuning();
+  switch (key) {
+    case 1: t.decode_splits = value; break;
+    case 2: t.early_depth = value; break;
+    case 3: t.fused_merge = value; break;
+    case 4: t.ring_stages = value; break;
+    default: return fail(WST_ERR_INVALID_ARG, "wst_b200_set_tuning: unknown key %d", key);
+  }
+  return WST_OK;
+}
+
+extern "C" wst_status_t wst_b200_set_decode_overlap(int32_t on) {
+  set_decode_overlap(on != 0);
+  return WST_OK;
+}
+
+extern "C" wst_status_t wst_b200_reserve_chunk_workspace(void) {
+  const char *why = "";
+  if (!chunk_workspace(&why))
+    return fail(WST_ERR_OOM, "wst_b200_reserve_chunk_workspace: %s", why);
+  return WST_OK;
+}
+
 extern "C" int32_t wst_attn_partial_floats(int32_t n_q, int32_t head_dim, int32_t max_seq) {
   if (n_q <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
   const long long f = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 4);
@@ -287,7 +334,7 @@ extern "C" wst_status_t wst_attn_decode(const void *q, const void *k_cache, cons
   wst_status_t st = check_decode_shape("wst_attn_decode", n_q, n_kv, head_dim, max_seq);
   if (st != WST_OK) return st;
   return decode_common("wst_attn_decode", q, k_cache, v_cache, partials, out, n_q, n_kv,
-                       head_dim, pos, max_seq, scale, false);
+                       head_dim, pos, max_seq, scale, false, false);
 }
 
 extern "C" wst_status_t wst_attn_decode_noscratch(const void *q, const void *k_cache,
@@ -308,7 +355,7 @@ extern "C" wst_status_t wst_attn_decode_noscratch(const void *q, const void *k_c
   st = builtin_scratch(&scratch);
   if (st != WST_OK) return st;
   return decode_common("wst_attn_decode_noscratch", q, k_cache, v_cache, scratch, out, n_q,
-                       n_kv, head_dim, pos, max_seq, scale, false);
+                       n_kv, head_dim, pos, max_seq, scale, false, false);
 }
 
 extern "C" wst_status_t wst_attn_decode_partial(const void *q, const void *k_cache,
@@ -321,7 +368,25 @@ extern "C" wst_status_t wst_attn_decode_partial(const void *q, const void *k_cac
   wst_status_t st = check_decode_shape("wst_attn_decode_partial", n_q, n_kv, head_dim, max_seq);
   if (st != WST_OK) return st;
   return decode_common("wst_attn_decode_partial", q, k_cache, v_cache, partials, out_partial,
-                       n_q, n_kv, head_dim, len, max_seq, scale, true);
+                       n_q, n_kv, head_dim, len, max_seq, scale, true, true);
+}
+
+extern "C" wst_status_t wst_attn_decode_sharded(const void *q, const void *k_cache,
+                                                const void *v_cache, void *partials, void *out,
+                                                int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                                const void *len, int32_t max_seq, float scale,
+                                                const void *mailboxes, void *state,
+                                                int32_t rank, int32_t world) {
+  WST_CHECK_ARG(q && k_cache && v_cache && out && len && partials && mailboxes && state,
+                "wst_attn_decode_sharded: null pointer");
+  WST_CHECK_ARG(world >= 1 && world <= 32 && rank >= 0 && rank < world,
+                "wst_attn_decode_sharded: rank / world out of range");
+  wst_status_t st = check_decode_shape("wst_attn_decode_sharded", n_q, n_kv, head_dim, max_seq);
+  if (st != WST_OK) return st;
+  /* the kernel counts rows like wst_attn_decode_partial: `len`, not a cursor */
+  return decode_common("wst_attn_decode_sharded", q, k_cache, v_cache, partials, out, n_q, n_kv,
+                       head_dim, len, max_seq, scale, /*len_is_count=*/true,
+                       /*partial_out=*/false, mailboxes, state, rank, world);
 }
 
 extern "C" wst_status_t wst_attn_merge_partials(const void *parts, void *out, int32_t n_parts,
@@ -434,10 +499,12 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
     P.pos0 = pos0; P.n = n; P.max_seq = max_seq; P.scale = scale;
     P.force_pair = choice == 4 ? 1 : (choice == 3 ? -1 : 0);
     if (splits > 1) {
-      P.scratch = chunk_workspace();
+      const char *why = "";
+      P.scratch = chunk_workspace(&why);
       P.scratch_floats = P.scratch ? kChunkWorkspaceFloats : 0;
       P.n_splits = splits;
       P.max_len = pos0 + n;
+      if (!P.scratch) note_unsplit("wst_attn_chunk", why);
     }
     return launch_prefill(P);
   }
@@ -459,8 +526,12 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
   L.max_len = pos0 + n;
   L.out = out;
   if (!tc_ok) return launch_simple(L);
-  L.scratch = chunk_workspace();
-  L.scratch_floats = L.scratch ? kChunkWorkspaceFloats : 0;
+  {
+    const char *why = "";
+    L.scratch = chunk_workspace(&why);
+    L.scratch_floats = L.scratch ? kChunkWorkspaceFloats : 0;
+    if (!L.scratch && pos0 + n > 2 * kRowsTile) note_unsplit("wst_attn_chunk", why);
+  }
   return launch_rows(L);
 }
 
@@ -500,6 +571,24 @@ extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cach
     P.n_q = n_q; P.n_kv = n_kv; P.hd = head_dim;
     P.n = n; P.max_seq = max_seq; P.scale = scale;
     P.force_pair = choice == 4 ? 1 : (choice == 3 ? -1 : 0);
+    if (choice != 3 && choice != 4) {
+      /* too few (unit, query tile) pairs to fill the GPU: cut every tile's visible
+       * prefix into equal slices (the chunk starts are device data, so the cut is made
+       * in the kernel, per tile) */
+      DeviceFacts facts;
+      if (!device_facts(&facts)) return WST_ERR_CUDA;
+      const int gqa = n_q / n_kv;
+      const int splits = chunk_slices(
+          facts.sm_count, (static_cast<long long>(n) * gqa + 127) / 128 * n_kv * n_seq, max_seq);
+      if (splits > 1) {
+        const char *why = "";
+        P.scratch = chunk_workspace(&why);
+        P.scratch_floats = P.scratch ? kChunkWorkspaceFloats : 0;
+        P.n_splits = splits;
+        P.even_slices = true;
+        if (!P.scratch) note_unsplit("wst_attn_chunk_batch", why);
+      }
+    }
     return launch_prefill(P);
   }
   /* few tokens per sequence: the split-KV kernel, one grid over all sequences.
@@ -522,8 +611,12 @@ extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cach
   L.scale = scale;
   L.max_len = max_seq;
   L.out = out;
-  L.scratch = chunk_workspace();
-  L.scratch_floats = L.scratch ? kChunkWorkspaceFloats : 0;
+  {
+    const char *why = "";
+    L.scratch = chunk_workspace(&why);
+    L.scratch_floats = L.scratch ? kChunkWorkspaceFloats : 0;
+    if (!L.scratch && max_seq > 2 * kRowsTile) note_unsplit("wst_attn_chunk_batch", why);
+  }
   return launch_rows(L);
 }
 

@@ -83,7 +83,8 @@ struct PrefillArgs {
   const int32_t *page_table; /* paged cache: [n_seq][max_pages] */
   int max_pages, n_pool_pages;
   int n_splits, rows_cap;
-  int tiles_per_slice; /* sliced mode: KV tiles per slice (0 otherwise) */
+  int tiles_per_slice; /* sliced mode: KV tiles per slice; 0 = each query tile cuts its own
+                        * prefix into n_splits equal runs */
   int n_q, n_kv, gqa;
   int pos0, n, max_seq;
   int tpt;      /* tokens per 128-row tile = 128 / gqa */
@@ -164,7 +165,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     e_ntok = max(min(a.tpt, e_ntok - e_tok0), 0);
     const int e_kv_end = e_ntok > 0 ? min(e_pos0 + e_tok0 + e_ntok, a.max_seq) : 0;
     const int e_tiles = (e_kv_end + BN - 1) / BN;
-    if (e_tiles - split * a.tiles_per_slice <= 0) {
+    const int e_tps = a.tiles_per_slice > 0 ? a.tiles_per_slice : (e_tiles + ns - 1) / ns;
+    if (e_tiles - split * e_tps <= 0) {
       constexpr int V4 = (HD + 4) / 4; /* float4 per scratch row: acc[HD] | m l pad pad */
       const long long unit = (static_cast<long long>(seq) * a.n_kv + kvh) * a.n_qtiles + qtile;
       float4 *dst = reinterpret_cast<float4 *>(a.scratch + (unit * ns + split) * a.rows_cap * (HD + 4));
@@ -225,8 +227,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
    * a.tiles_per_slice tiles -- slices past the end of a short sequence get none and
    * only publish an empty partial, so that the CTAs that do work are equally long
    * whatever the sequence lengths are */
-  const int first_tile = split * a.tiles_per_slice;
-  const int slice_cap = split == ns - 1 ? all_tiles : a.tiles_per_slice; /* the last takes the rest */
+  const int tps = a.tiles_per_slice > 0 ? a.tiles_per_slice : (all_tiles + ns - 1) / (ns > 1 ? ns : 1);
+  const int first_tile = split * tps;
+  const int slice_cap = split == ns - 1 ? all_tiles : tps; /* the last takes the rest */
   const int n_tiles = ns > 1 ? max(min(all_tiles - first_tile, slice_cap), 0) : all_tiles;
   auto tile_of = [first_tile](int j) { return first_tile + j; };
 
@@ -1045,7 +1048,7 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
     --splits;
   a.n_splits = splits;
   const int max_tiles = (P.max_len > 0 ? P.max_len : P.max_seq) / 128 + 1;
-  a.tiles_per_slice = splits > 1 ? (max_tiles + splits - 1) / splits : 0;
+  a.tiles_per_slice = splits > 1 && !P.even_slices ? (max_tiles + splits - 1) / splits : 0;
 
   CUtensorMap kmap, vmap;
   KvMapKey key{};

@@ -30,6 +30,10 @@ struct PrefillLaunch {
    * (needs n * gqa <= 128 and scratch of n_seq*n_kv*n_splits*n*gqa*(hd+4) floats) */
   int n_splits = 0;
   int max_len = 0; /* sliced mode: upper bound on any sequence's visible length (0: max_seq) */
+  /* sliced mode: false = slices are runs of ceil(max_len tiles / n_splits) tiles (equal
+   * work per CTA whatever the sequence lengths); true = every query tile cuts its own
+   * visible prefix into n_splits equal runs (lengths unknown to the host) */
+  bool even_slices = false;
   float *scratch = nullptr;
   long long scratch_floats = 0;
   float scale = 1.f;

@@ -27,6 +27,10 @@
  * (chunk: query j sees rows [0, pos0+j]) of the engine.
  */
 
+#include <atomic>
+#include <mutex>
+#include <unordered_map>
+
 #include "attn_rows.cuh"
 #include "tensor_map.cuh"
 #include "wst_ptx.cuh"
@@ -40,29 +44,10 @@ using namespace ptx;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
-/* Optional phase timestamps for tuning (compiled in only with -DWST_TRACE). */
-#ifdef WST_TRACE
-/* [bank][block][slot]; the bank is chosen on the host per launch, so that
- * consecutive launches can be told apart (banks 0-3: rows kernel, 4-7: merge) */
-__device__ unsigned long long g_trace[8 * 512 * 8];
-int g_trace_bank = 0;
-__device__ __forceinline__ void trace_stamp_bank(int slot, int bank) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  const unsigned int b = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (b < 512) g_trace[(bank * 512 + b) * 8 + slot] = t;
-}
-#define trace_stamp(slot) trace_stamp_bank(slot, a.trace_bank)
-#define WST_STAMP(slot) do { if (threadIdx.x == 0) trace_stamp(slot); } while (0)
-#define WST_TRACE_FIELD int trace_bank;
-#else
-#define WST_TRACE_FIELD
-#define WST_STAMP(slot) do { } while (0)
-#endif
-
 struct RowsArgs {
   const float *q;
   long long q_tok_stride;
+  const __half *k, *v; /* the cache itself, next to the tensor maps: the newest row is patched by plain loads */
   const int32_t *page_table;
   int max_pages, n_pool_pages;
   const int32_t *pos0_dev;
@@ -76,8 +61,17 @@ struct RowsArgs {
   void *out;
   int partial_out;
   int n_splits, n_rowblk, tpb, rows_cap;
-  int early_spec; /* request the first tile before the grid dependency is resolved */
-  WST_TRACE_FIELD
+  int nstage;      /* ring stages in use, 2 .. Cfg::NSTAGE */
+  int early_depth; /* 0: nothing is requested before the grid dependency resolves; else the
+                    * number of tiles requested at once ahead of it (the rest of the ring
+                    * follows one tile at a time) */
+  /* fused slice merge: per-unit arrival counters (zero between launches), or null when
+   * the separate merge kernel follows */
+  unsigned int *tickets;
+  /* cross-GPU exchange inside the fused merge (world > 1), see exchange_and_finish */
+  uint2 *const *mailboxes;
+  unsigned int *xstate;
+  int rank, world;
 };
 
 template <int HD, int MT, int RG>
@@ -90,14 +84,14 @@ struct Cfg {
   static constexpr int THREADS = CTHREADS + 32;
   static constexpr int HALF_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = 2 * NH * HALF_BYTES;
-  static constexpr int NSTAGE = HD == 128 ? 4 : 6;
+  static constexpr int RING_BYTES = kRowsRingBytes;
+  static constexpr int NSTAGE = RING_BYTES / STAGE_BYTES; /* 6 (head_dim 128) or 12 (64) */
   static constexpr int Q_BYTES = NH * ROWS * 128;
-  /* ring | one spare stage (the re-read of the newest tile) | q tile | barriers */
-  static constexpr int SMEM_BYTES =
-      (NSTAGE + 1) * STAGE_BYTES + Q_BYTES + (2 * NSTAGE + 2) * 8 + 64 + 1024;
-  /* the warp-combine dump [RG][4][16*MT][HD+4] floats reuses the ring and the q tile */
-  static_assert(RG * 4 * 16 * MT * (HD + 4) * 4 <= (NSTAGE + 1) * STAGE_BYTES + Q_BYTES,
-                "combine buffer must fit");
+  /* ring | q tile | barriers (full, empty per stage; merge) and the flag word */
+  static constexpr int SMEM_BYTES = RING_BYTES + Q_BYTES + (2 * NSTAGE + 2) * 8 + 64 + 1024;
+  /* the warp-combine dump [RG][4][16*MT][HD+4] floats reuses the ring */
+  static_assert(RG * 4 * 16 * MT * (HD + 4) * 4 <= RING_BYTES, "combine buffer must fit");
+  static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA");
 };
 
 __device__ __forceinline__ void grid_dependency_wait() {
@@ -119,12 +113,44 @@ __device__ __forceinline__ void consumer_bar(int threads) {
   asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
+/* ---- packets of the cross-GPU exchange: {value, tag} in ONE 64-bit access, so a
+ * packet is valid exactly when its tag is the call's tag */
+__device__ __forceinline__ unsigned long long make_packet(float value, unsigned int tag) {
+  return (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(value);
+}
+__device__ __forceinline__ void st_packet(uint2 *p, float value, unsigned int tag) {
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(make_packet(value, tag)) : "memory");
+}
+__device__ __forceinline__ void st_packet2(uint2 *p, float v0, float v1, unsigned int tag) {
+  asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(make_packet(v0, tag)),
+               "l"(make_packet(v1, tag))
+               : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_packet(const uint2 *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+/* value of a packet once its tag has arrived; false after about a second */
+__device__ __forceinline__ bool wait_packet(const uint2 *p, unsigned int tag, float *value) {
+  unsigned long long v = ld_packet(p);
+  if (static_cast<unsigned int>(v >> 32) != tag) {
+    const long long t0 = clock64();
+    do {
+      if (clock64() - t0 > kWaitCycleLimit) return false;
+      v = ld_packet(p);
+    } while (static_cast<unsigned int>(v >> 32) != tag);
+  }
+  *value = __uint_as_float(static_cast<unsigned int>(v));
+  return true;
+}
+
 template <int HD, int MT, int RG, bool PAGED>
 __global__ void __launch_bounds__(Cfg<HD, MT, RG>::THREADS, 1)
 attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap, const RowsArgs a) {
   using C = Cfg<HD, MT, RG>;
-  constexpr int BN = C::BN, NH = C::NH, ROWS = C::ROWS, NSTAGE = C::NSTAGE;
+  constexpr int BN = C::BN, NH = C::NH, ROWS = C::ROWS;
   constexpr int HALF_BYTES = C::HALF_BYTES, STAGE_BYTES = C::STAGE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,26 +158,26 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int kvh = blockIdx.y / a.n_rowblk;
   const int rb = blockIdx.y % a.n_rowblk;
   const int s = blockIdx.z;
+  const int nst = a.nstage;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t *qsm = smem + (NSTAGE + 1) * STAGE_BYTES;
+  uint8_t *qsm = smem + C::RING_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(qsm + C::Q_BYTES);
   const uint32_t stages_u32 = smem_u32(smem);
-  const uint32_t spare_u32 = stages_u32 + NSTAGE * STAGE_BYTES;
   const uint32_t q_u32 = smem_u32(qsm);
   const uint32_t full_u32 = smem_u32(bars);
-  const uint32_t empty_u32 = smem_u32(bars + NSTAGE);
-  const uint32_t spare_full_u32 = smem_u32(bars + 2 * NSTAGE);
-  const uint32_t go_u32 = smem_u32(bars + 2 * NSTAGE + 1); /* "dependency resolved", see below */
+  const uint32_t empty_u32 = smem_u32(bars + C::NSTAGE);
+  const uint32_t merge_u32 = smem_u32(bars + 2 * C::NSTAGE);
+  const uint32_t go_u32 = smem_u32(bars + 2 * C::NSTAGE + 1); /* "dependency resolved", see below */
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NSTAGE; ++i) {
+    for (int i = 0; i < nst; ++i) {
       mbar_init(full_u32 + 8 * i, 1);
       mbar_init(empty_u32 + 8 * i, C::CWARPS);
     }
-    mbar_init(spare_full_u32, 1);
+    mbar_init(merge_u32, 1);
     st_shared_volatile(go_u32, 0u);
     mbar_init_fence();
     tma_prefetch_desc(&kmap);
@@ -193,34 +219,31 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     }
   };
   auto issue = [&](int i) {
-    const int stage = i % NSTAGE;
+    const int stage = i % nst;
     issue_to(split + i * ns, full_u32 + 8 * stage, stages_u32 + stage * STAGE_BYTES);
   };
   int spec = 0; /* tiles issued ahead of knowing the sequence length */
   if (!PAGED && a.cu_tokens == nullptr)
-    while (spec < NSTAGE && static_cast<long long>(split + spec * ns) * BN < a.max_seq) ++spec;
+    while (spec < nst && static_cast<long long>(split + spec * ns) * BN < a.max_seq) ++spec;
 
   /* Decode (one new token): the launch just before this one in the stream --
    * still running under programmatic dependent launch -- can only be writing the
    * newest cache row; every row in a tile below that one was written by launches
-   * that finished long ago.  So the slice's first tile is requested right here,
-   * before the dependency is resolved, and its latency hides behind the tail of
-   * the previous kernel.  The rest of the ring follows one tile at a time (slow
-   * start): tile i+1 is requested when tile i has landed -- the kernel ahead keeps
-   * getting its own last loads out in between; requesting the whole ring at once
-   * was measured to crowd those out and to cost as much as it hides -- or as soon
-   * as a consumer thread reports the dependency resolved, whichever comes first.  A tile that
-   * holds the newest row and was requested early is read again after the wait,
-   * into the spare stage. */
+   * that finished long ago.  So the slice's first tiles are requested right here,
+   * before the dependency is resolved, and their latency hides behind the tail of
+   * the previous kernel: `early_depth` of them at once, the rest of the ring one at
+   * a time (tile i+1 when tile i has landed, or as soon as a consumer thread
+   * reports the dependency resolved, whichever comes first), so that the kernel
+   * ahead keeps getting its own last loads out in between.  The newest row of a
+   * tile requested this early is read again after the wait, with plain loads, and
+   * stored over the copy in shared memory. */
   /* Let the kernels behind this one in the stream be scheduled as early as there is
-   * room for them (the slice merge is resident at once and waits for this grid; the
-   * next launch's blocks start the moment this one's leave their SM, a launch latency
-   * sooner than if they were released after the stream); what they may read is
-   * ordered by their own griddepcontrol.wait, not by this. */
+   * room for them (the next launch's blocks start the moment this one's leave their
+   * SM, a launch latency sooner than if they were released after the stream); what
+   * they may read is ordered by their own griddepcontrol.wait, not by this. */
   grid_launch_dependents();
-  const bool early = !PAGED && a.early_spec != 0;
+  const bool early = !PAGED && a.early_depth > 0;
   const int n_early = early ? spec : 0;
-  WST_STAMP(0);
   if (early) {
     /* the group's q rows and the cursor towards L2 while the dependency is open: a
      * prefetch has no architectural effect, whatever the launch ahead still writes */
@@ -233,8 +256,9 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     }
     if (warp == C::CWARPS) {
       if (lane == 0 && spec > 0) {
-        issue(0);
-        for (int i = 1; i < spec; ++i) {
+        const int burst = a.early_depth < spec ? a.early_depth : spec;
+        for (int i = 0; i < burst; ++i) issue(i);
+        for (int i = burst; i < spec; ++i) {
           const long long t0 = clock64();
           while (!mbar_try_wait(full_u32 + 8 * (i - 1), 0) && ld_shared_volatile(go_u32) == 0u)
             if (clock64() - t0 > kWaitCycleLimit) break; /* only a hint: go on */
@@ -254,10 +278,6 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     grid_dependency_wait();
     if (warp == C::CWARPS && lane < spec) issue(lane); /* one lane per stage */
   }
-  WST_STAMP(1);
-#ifdef WST_TRACE
-  if (warp == C::CWARPS && lane == 0) trace_stamp(6);
-#endif
 
   int tok_begin = s * a.tok_seq_stride, n_tok = a.n_tok;
   if (a.cu_tokens) {
@@ -319,20 +339,18 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int n_tiles = (kv_end + BN - 1) / BN;
   const int my_tiles = split < n_tiles ? (n_tiles - split + ns - 1) / ns : 0;
 
-  /* the slice's tile that holds the newest rows, if it was requested before the
-   * dependency was resolved: read again, consumed from the spare stage */
-  int reread = -1;
+  /* the slice's tile that holds the newest row, if it was requested before the
+   * dependency was resolved: that one row is patched from global memory */
+  int patch = -1;
   if (my_tiles > 0 && my_tiles - 1 < n_early && split + (my_tiles - 1) * ns == n_tiles - 1)
-    reread = my_tiles - 1;
+    patch = my_tiles - 1;
 
   /* ------------------------------------------------------------ producer */
   if (warp == C::CWARPS) {
     if (lane != 0) return;
-    if (reread >= 0) issue_to(n_tiles - 1, spare_full_u32, spare_u32);
     for (int i = spec; i < my_tiles; ++i) {
-      const int stage = i % NSTAGE, round = i / NSTAGE;
-      if (i >= NSTAGE &&
-          !mbar_wait(empty_u32 + 8 * stage, (round - 1) & 1, a.err_word, 0x101u))
+      const int stage = i % nst, round = i / nst;
+      if (i >= nst && !mbar_wait(empty_u32 + 8 * stage, (round - 1) & 1, a.err_word, 0x101u))
         break;
       issue(i);
     }
@@ -344,8 +362,21 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int w = warp & 3;   /* positions [16w, 16w+16) of every tile */
   const int ctid = threadIdx.x;
 
+  /* the newest row's 16-byte chunks (K then V), one per lane, asked for now and
+   * stored over the early copy when that tile is consumed (only the warp that owns
+   * the row's positions; early requests are made for one row group only) */
+  const int prow_new = (kv_end - 1) & (BN - 1);
+  const bool patcher = patch >= 0 && w == (prow_new >> 4) && lane < 2 * NH * 8;
+  uint4 patch_val = make_uint4(0u, 0u, 0u, 0u);
+  if (patcher) {
+    const int ch = lane % (NH * 8);
+    const __half *src = (lane < NH * 8 ? a.k : a.v) +
+                        (static_cast<long long>(s * a.n_kv + kvh) * a.max_seq + (kv_end - 1)) * HD +
+                        ch * 8;
+    patch_val = __ldcg(reinterpret_cast<const uint4 *>(src));
+  }
+
   consumer_bar(C::CTHREADS);
-  WST_STAMP(7);
 
   int lim[MT][2];
 #pragma unroll
@@ -381,17 +412,23 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       for (int c = 0; c < 4; ++c) o[mt][nt][c] = 0.f;
   }
 
+  int stage = 0;
+  uint32_t phase = 0;
   for (int i = 0; i < my_tiles; ++i) {
-    const int stage = i % NSTAGE, round = i / NSTAGE;
-    if (!mbar_wait(full_u32 + 8 * stage, round & 1, a.err_word, 0x102u)) break;
-    if (i == 0) WST_STAMP(2);
+    if (!mbar_wait(full_u32 + 8 * stage, phase, a.err_word, 0x102u)) break;
     const int tile = split + i * ns;
-    uint32_t kb = stages_u32 + stage * STAGE_BYTES;
-    if (i == reread) {
-      if (!mbar_wait(spare_full_u32, 0, a.err_word, 0x104u)) break;
-      kb = spare_u32;
-    }
+    const uint32_t kb = stages_u32 + stage * STAGE_BYTES;
     const uint32_t vb = kb + NH * HALF_BYTES;
+    if (i == patch) {
+      if (patcher) {
+        const int ch = lane % (NH * 8);
+        const uint32_t dst = (lane < NH * 8 ? kb : vb) + (ch >> 3) * HALF_BYTES + swz128(prow_new, ch & 7);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(patch_val.x),
+                     "r"(patch_val.y), "r"(patch_val.z), "r"(patch_val.w)
+                     : "memory");
+      }
+      __syncwarp();
+    }
 
     /* S = Q K^T for this warp's 16 positions */
     float sacc[MT][2][4];
@@ -507,14 +544,16 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
 
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_u32 + 8 * stage);
+    if (++stage == nst) {
+      stage = 0;
+      phase ^= 1u;
+    }
   }
 
   /* Tiles that were streamed ahead but lie past this slice's share: wait for
    * them to land, nothing may still be in flight when the ring is reused. */
   for (int i = my_tiles; i < spec; ++i)
-    if (!mbar_wait(full_u32 + 8 * (i % NSTAGE), (i / NSTAGE) & 1, a.err_word, 0x103u)) break;
-
-  WST_STAMP(3);
+    if (!mbar_wait(full_u32 + 8 * (i % nst), (i / nst) & 1, a.err_word, 0x103u)) break;
 
   /* row sums live spread over the four lanes of a quad */
 #pragma unroll
@@ -549,10 +588,10 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       }
     }
   consumer_bar(C::CTHREADS);
-  WST_STAMP(4);
 
   const int unit = (s * a.n_kv + kvh) * a.n_rowblk + rb;
-  const bool single = ns == 1;
+  const bool fused = a.tickets != nullptr; /* the last slice to arrive finishes the unit */
+  const bool direct = ns == 1 && !fused;
   for (int idx = ctid; idx < rows_valid * (HD / 4); idx += C::CTHREADS) {
     const int r = idx / (HD / 4), c4 = idx % (HD / 4);
     const float *cell = dump + (static_cast<size_t>(r / RPG) * 4 * RPG + r % RPG) * DR;
@@ -576,13 +615,13 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       den = fmaf(wgt, cell[static_cast<size_t>(k) * RPG * DR + HD + 1], den);
     }
     const int head = kvh * a.gqa + r % a.gqa;
-    if (single && !a.partial_out) {
+    if (direct && !a.partial_out) {
       const int tok = tok_begin + tok0 + r / a.gqa;
       const float inv = den > 0.f ? 1.f / den : 0.f;
       store_half4(static_cast<__half *>(a.out) +
                       (static_cast<long long>(tok) * a.n_q + head) * HD + 4 * c4,
                   acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-    } else if (single) { /* the caller's (m, l, acc) triple, natural-log m */
+    } else if (direct) { /* the caller's (m, l, acc) triple, natural-log m */
       float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (HD + 2);
       if (c4 == 0) {
         dst[0] = M * kLn2;
@@ -590,14 +629,173 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[0] = make_float2(acc.x, acc.y);
       reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[1] = make_float2(acc.z, acc.w);
-    } else { /* this slice's row for the merge kernel */
+    } else { /* this slice's row, for the fused merge below or the merge kernel */
       float *dst = a.scratch +
                    ((static_cast<long long>(unit) * ns + split) * a.rows_cap + r) * DR;
       *reinterpret_cast<float4 *>(dst + 4 * c4) = acc;
       if (c4 == 0) *reinterpret_cast<float2 *>(dst + HD) = make_float2(M, den);
     }
   }
-  WST_STAMP(5);
+  if (!fused) return;
+
+  /* ---- fused slice merge.  Every slice of a unit takes a ticket after its rows
+   * are out (stores, fence, block barrier, one atomic); the slice that draws the
+   * last one brings all the unit's rows back with one bulk copy into the idle
+   * ring -- one memory round trip -- and finishes the unit.  Nothing spins; the
+   * counter is left at zero for the next launch. */
+  __threadfence();
+  consumer_bar(C::CTHREADS);
+  if (ctid == 0) {
+    const unsigned int prev = ns > 1 ? atomicAdd(a.tickets + unit, 1u) : 0u;
+    const bool last = prev == static_cast<unsigned int>(ns - 1);
+    if (last) {
+      if (ns > 1) a.tickets[unit] = 0u;
+      __threadfence();
+    }
+    st_shared_volatile(go_u32, last ? 2u : 3u);
+  }
+  consumer_bar(C::CTHREADS);
+  if (ld_shared_volatile(go_u32) != 2u) return;
+
+  const int slice_floats = a.rows_cap * DR;
+  const uint32_t unit_bytes = static_cast<uint32_t>(ns * slice_floats * 4);
+  float *mbuf = reinterpret_cast<float *>(smem);                /* [ns][rows_cap][DR] */
+  float *wbuf = mbuf + static_cast<size_t>(ns) * slice_floats;  /* [rows][kRowsMaxSplits] weights */
+  float *rowm = wbuf + ROWS * kRowsMaxSplits;                    /* [rows] maximum, denominator */
+  float *rowl = rowm + ROWS;
+  if (ctid == 0) {
+    /* other blocks' stores (generic proxy) before this block's bulk copy (async proxy) */
+    asm volatile("fence.proxy.async;" ::: "memory");
+    mbar_arrive_expect_tx(merge_u32, unit_bytes);
+    const char *src = reinterpret_cast<const char *>(
+        a.scratch + static_cast<long long>(unit) * ns * slice_floats);
+    constexpr uint32_t kPiece = 32768;
+    for (uint32_t off = 0; off < unit_bytes; off += kPiece)
+      bulk_load(stages_u32 + off, src + off, min(kPiece, unit_bytes - off), merge_u32);
+  }
+  const bool landed = mbar_wait(merge_u32, 0, a.err_word, 0x105u);
+
+  /* one warp per row: maximum over the slices, weights, denominator */
+  for (int r = warp; r < rows_valid; r += C::CWARPS) {
+    float M = -INFINITY;
+    for (int sp = lane; sp < ns; sp += 32)
+      M = fmaxf(M, mbuf[static_cast<size_t>(sp) * slice_floats + r * DR + HD]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float m_use = M == -INFINITY ? 0.f : M;
+    float den = 0.f;
+    for (int sp = lane; sp < ns; sp += 32) {
+      const float *row = mbuf + static_cast<size_t>(sp) * slice_floats + r * DR;
+      const float wgt = ex2(row[HD] - m_use);
+      wbuf[r * kRowsMaxSplits + sp] = wgt;
+      den = fmaf(wgt, row[HD + 1], den);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
+    if (lane == 0) {
+      rowm[r] = M;
+      rowl[r] = den;
+    }
+  }
+  consumer_bar(C::CTHREADS);
+
+  const bool exchange = a.world > 1;
+  bool ok = landed;
+  for (int idx = ctid; idx < rows_valid * (HD / 4); idx += C::CTHREADS) {
+    const int r = idx / (HD / 4), c4 = idx % (HD / 4);
+    const float *col = mbuf + r * DR + 4 * c4;
+    const float *wr = wbuf + r * kRowsMaxSplits;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int sp = 0; sp < ns; ++sp) {
+      const float wgt = wr[sp];
+      const float4 v = *reinterpret_cast<const float4 *>(col + static_cast<size_t>(sp) * slice_floats);
+      acc.x = fmaf(wgt, v.x, acc.x);
+      acc.y = fmaf(wgt, v.y, acc.y);
+      acc.z = fmaf(wgt, v.z, acc.z);
+      acc.w = fmaf(wgt, v.w, acc.w);
+    }
+    float big = rowm[r];
+    float den = rowl[r];
+    const int head = kvh * a.gqa + r % a.gqa;
+    const int tok = tok_begin + tok0 + r / a.gqa;
+
+    if (exchange) {
+      /* The KV sequence is sharded over the GPUs of the box: this rank's triple of the
+       * head goes into every other rank's mailbox (plain peer stores over NVLink), the
+       * others' are awaited in this GPU's own mailbox -- each packet for at most about
+       * a second -- and folded in.  The tag is a per-head call counter in device memory
+       * (graph replays advance it); mailboxes exist twice, used by tag parity: a rank
+       * can publish call t+2 only after it has received everybody's t+1, which they
+       * sent after reading t. */
+      const float m_nat = big * kLn2;
+      const unsigned int tag = a.xstate[head] + 1u;
+      const int par = static_cast<int>(tag & 1u);
+      const int stride = HD + 2;
+      const long long my_slot = (static_cast<long long>(par) * a.world + a.rank) * a.n_q + head;
+      for (int g = 0; g < a.world; ++g) {
+        if (g == a.rank) continue;
+        uint2 *dst = a.mailboxes[g] + my_slot * stride;
+        if (c4 == 0) {
+          st_packet(dst, m_nat, tag);
+          st_packet(dst + 1, den, tag);
+        }
+        st_packet2(dst + 2 + 4 * c4, acc.x, acc.y, tag);
+        st_packet2(dst + 4 + 4 * c4, acc.z, acc.w, tag);
+      }
+      const uint2 *box = a.mailboxes[a.rank] + (static_cast<long long>(par) * a.world * a.n_q + head) * stride;
+      const long long rank_stride = static_cast<long long>(a.n_q) * stride;
+      float top = m_nat;
+      for (int g = 0; ok && g < a.world; ++g) {
+        if (g == a.rank) continue;
+        float m_g;
+        ok = wait_packet(box + g * rank_stride, tag, &m_g);
+        top = fmaxf(top, m_g);
+      }
+      float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+      float dsum = 0.f;
+      for (int g = 0; ok && g < a.world; ++g) {
+        float m_g = m_nat, l_g = den;
+        float4 a_g = acc;
+        if (g != a.rank) {
+          const uint2 *t = box + g * rank_stride;
+          ok = wait_packet(t, tag, &m_g) && wait_packet(t + 1, tag, &l_g) &&
+               wait_packet(t + 2 + 4 * c4, tag, &a_g.x) && wait_packet(t + 3 + 4 * c4, tag, &a_g.y) &&
+               wait_packet(t + 4 + 4 * c4, tag, &a_g.z) && wait_packet(t + 5 + 4 * c4, tag, &a_g.w);
+          if (!ok) break;
+        }
+        if (m_g == -INFINITY) continue; /* an empty shard contributes nothing */
+        const float f = expf(m_g - top);
+        tot.x = fmaf(a_g.x, f, tot.x);
+        tot.y = fmaf(a_g.y, f, tot.y);
+        tot.z = fmaf(a_g.z, f, tot.z);
+        tot.w = fmaf(a_g.w, f, tot.w);
+        dsum = fmaf(l_g, f, dsum);
+      }
+      acc = tot;
+      den = dsum;
+    }
+    if (!ok) continue;
+    if (a.partial_out && !exchange) {
+      float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (HD + 2);
+      if (c4 == 0) {
+        dst[0] = big * kLn2;
+        dst[1] = den;
+      }
+      reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[0] = make_float2(acc.x, acc.y);
+      reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[1] = make_float2(acc.z, acc.w);
+    } else {
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      store_half4(static_cast<__half *>(a.out) + (static_cast<long long>(tok) * a.n_q + head) * HD +
+                      4 * c4,
+                  acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    }
+  }
+  if (exchange) {
+    if (!ok) atomicCAS(a.err_word, 0u, 0x401u);
+    consumer_bar(C::CTHREADS); /* every thread has read its head's counter */
+    if (ctid < rows_valid && ctid < a.gqa) a.xstate[kvh * a.gqa + ctid] += 1u;
+  }
 }
 
 /* ---------------------------------------------------------- slice merge */
@@ -612,7 +810,6 @@ struct MergeArgs {
   const float *scratch;
   void *out;
   const int32_t *cu_tokens;
-  WST_TRACE_FIELD
   int n_tok, tok_seq_stride, n_q, n_kv, gqa;
   int n_splits, n_rowblk, tpb, rows_cap;
   int partial_out;
@@ -628,10 +825,8 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
   __shared__ float4 s_acc[GROUPS][LPR];
   __shared__ float s_m[GROUPS], s_l[GROUPS];
 
-  WST_STAMP(0);
   grid_launch_dependents();
   grid_dependency_wait();
-  WST_STAMP(1);
 
   const int row = blockIdx.x, unit = blockIdx.y;
   const int rb = unit % a.n_rowblk;
@@ -722,7 +917,6 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
                     col,
                 tot.x * inv, tot.y * inv, tot.z * inv, tot.w * inv);
   }
-  WST_STAMP(2);
 }
 
 /* ------------------------------------------------- portable fallback kernel */
@@ -897,16 +1091,6 @@ int rows_for(int gqa, int n_tok) {
 
 }  // namespace
 
-#ifdef WST_TRACE
-extern "C" __attribute__((visibility("default"))) int wst_b200_trace_read(unsigned long long *dst,
-                                                                         int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_trace, sizeof(unsigned long long) * n));
-}
-extern "C" __attribute__((visibility("default"))) void wst_b200_trace_bank(int bank) {
-  g_trace_bank = bank & 3;
-}
-#endif
-
 bool rows_kernel_supports(int n_q, int n_kv, int hd, const void *k, const void *v) {
   if (hd != 64 && hd != 128) return false;
   if (n_kv <= 0 || n_q % n_kv != 0 || n_q / n_kv > 64) return false;
@@ -931,11 +1115,72 @@ long long rows_scratch_floats(int n_units_times_rows, int splits, int hd) {
   return static_cast<long long>(n_units_times_rows) * splits * (hd + 4);
 }
 
+/* Arrival counters of the fused slice merge.  They live in the library's device
+ * image (zero when the module loads) and every launch leaves its counters at zero
+ * again.  Launches that may overlap on the GPU must not share counters; two such
+ * launches necessarily have different scratch buffers, so a slot of counters is
+ * bound to each scratch address the first time it is seen (per device).  When the
+ * slots run out the launch falls back to the separate merge kernel. */
+constexpr int kTicketUnits = 64;
+constexpr int kTicketSlots = 1024;
+static __device__ unsigned int g_tickets[kTicketSlots * kTicketUnits];
+
+unsigned int *ticket_slot(const void *scratch) {
+  struct PerDevice {
+    unsigned int *base = nullptr;
+    std::unordered_map<const void *, int> slots;
+  };
+  static PerDevice devs[64];
+  static std::mutex mu;
+  static thread_local const void *last_key = nullptr;
+  static thread_local int last_dev = -1;
+  static thread_local unsigned int *last_ptr = nullptr;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (last_key == scratch && last_dev == dev) return last_ptr;
+  std::lock_guard<std::mutex> lock(mu);
+  PerDevice &d = devs[dev];
+  if (!d.base) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_tickets) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    d.base = static_cast<unsigned int *>(p);
+  }
+  auto it = d.slots.find(scratch);
+  int slot;
+  if (it != d.slots.end()) {
+    slot = it->second;
+  } else {
+    if (static_cast<int>(d.slots.size()) >= kTicketSlots) return nullptr;
+    slot = static_cast<int>(d.slots.size());
+    d.slots.emplace(scratch, slot);
+  }
+  last_key = scratch;
+  last_dev = dev;
+  last_ptr = d.base + static_cast<size_t>(slot) * kTicketUnits;
+  return last_ptr;
+}
+
+RowsTuning &rows_tuning() {
+  static RowsTuning t;
+  return t;
+}
+
+static std::atomic<int> g_decode_overlap{1};
+bool decode_overlap_allowed() { return g_decode_overlap.load() != 0; }
+void set_decode_overlap(bool on) { g_decode_overlap.store(on ? 1 : 0); }
+
+/* tiles a decode launch requests at once ahead of its grid dependency */
+constexpr int kDefaultEarlyDepth = 1;
+
 wst_status_t launch_rows(const RowsLaunch &L) {
   DeviceFacts facts;
   if (!device_facts(&facts)) return WST_ERR_CUDA;
   if (facts.cc_major < 10)
     return fail(WST_ERR_UNSUPPORTED_ARCH, "%s: this library is built for sm_100a only", L.name);
+  const RowsTuning &tune = rows_tuning();
 
   const int gqa = L.n_q / L.n_kv;
   const int rows = rows_for(gqa, L.n_tok);
@@ -944,8 +1189,14 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   const int n_rowblk = (L.n_tok + tpb - 1) / tpb;
   const int n_units = L.n_seq * L.n_kv * n_rowblk;
   const int rows_cap = tpb * gqa;
+  const bool decode_shape = !L.paged && !L.cu_tokens && L.n_tok == 1 && L.n_seq == 1;
 
   int splits = L.want_splits > 0 ? L.want_splits : rows_pick_splits(n_units, L.max_len, facts.sm_count);
+  if (decode_shape && L.want_splits <= 0 && tune.decode_splits > 0) {
+    splits = tune.decode_splits;
+    const int tiles = (L.max_len + kRowsTile - 1) / kRowsTile;
+    if (splits > tiles) splits = tiles;
+  }
   if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
   /* the slices must fit the caller's scratch */
   if (!aligned16(L.scratch)) splits = 1; /* the merge reads scratch rows as float4 */
@@ -953,9 +1204,27 @@ wst_status_t launch_rows(const RowsLaunch &L) {
          (!L.scratch || rows_scratch_floats(n_units * rows_cap, splits, L.hd) > L.scratch_floats))
     --splits;
 
+  /* Fused merge: the unit's partial rows (plus the weights) must fit the idle ring,
+   * and the launch needs a slot of arrival counters. */
+  const bool exchange = L.world > 1;
+  const long long unit_bytes = static_cast<long long>(splits) * rows_cap * (L.hd + 4) * 4;
+  bool fused = (splits > 1 || exchange) && L.scratch && aligned16(L.scratch) &&
+               rows_scratch_floats(n_units * rows_cap, splits, L.hd) <= L.scratch_floats &&
+               n_units <= kTicketUnits &&
+               unit_bytes + static_cast<long long>(rows) * (kRowsMaxSplits + 2) * 4 <= kRowsRingBytes &&
+               (exchange || tune.fused_merge != 0);
+  unsigned int *tickets = fused ? ticket_slot(L.scratch) : nullptr;
+  if (!tickets) fused = false;
+  if (exchange && !(fused && decode_shape && L.mailboxes && L.xstate))
+    return fail(WST_ERR_SHAPE,
+                "%s: the in-kernel exchange takes one token of one contiguous sequence with a "
+                "split scratch (head_dim 64 or 128)", L.name);
+
   RowsArgs a{};
   a.q = L.q;
   a.q_tok_stride = L.q_tok_stride;
+  a.k = L.k;
+  a.v = L.v;
   a.page_table = L.page_table;
   a.max_pages = L.max_pages;
   a.n_pool_pages = L.n_pool_pages;
@@ -978,10 +1247,21 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   a.n_rowblk = n_rowblk;
   a.tpb = tpb;
   a.rows_cap = rows_cap;
-#ifdef WST_TRACE
-  a.trace_bank = g_trace_bank;
-#endif
-  a.early_spec = (L.newest_row_only && !L.paged && !L.cu_tokens && L.n_tok == 1 && L.n_seq == 1) ? 1 : 0;
+  a.tickets = tickets;
+  a.mailboxes = static_cast<uint2 *const *>(L.mailboxes);
+  a.xstate = static_cast<unsigned int *>(L.xstate);
+  a.rank = L.rank;
+  a.world = exchange ? L.world : 1;
+  const int max_stages = kRowsRingBytes / (L.hd == 128 ? 32768 : 16384);
+  a.nstage = max_stages;
+  if (tune.ring_stages >= 2 && tune.ring_stages < max_stages) a.nstage = tune.ring_stages;
+  /* requests ahead of the grid dependency: decode only (the launch ahead writes at
+   * most the newest row), one row group (the patch of that row is a warp's job) */
+  a.early_depth = 0;
+  if (L.newest_row_only && decode_shape && rows <= 32 && decode_overlap_allowed()) {
+    a.early_depth = tune.early_depth >= 0 ? tune.early_depth : kDefaultEarlyDepth;
+    if (a.early_depth > a.nstage) a.early_depth = a.nstage;
+  }
   a.err_word = device_error_word();
   if (!a.err_word) return WST_ERR_CUDA;
   CUtensorMap kmap, vmap;
@@ -1011,7 +1291,7 @@ wst_status_t launch_rows(const RowsLaunch &L) {
     st = L.paged ? launch_shape<64, true>(L, a, kmap, vmap, grid, rows)
                  : launch_shape<64, false>(L, a, kmap, vmap, grid, rows);
   }
-  if (st != WST_OK || splits == 1) return st;
+  if (st != WST_OK || splits == 1 || fused) return st;
 
   SplitMerge m;
   m.scratch = L.scratch;
@@ -1047,9 +1327,6 @@ wst_status_t launch_split_merge(const SplitMerge &S) {
   m.tpb = S.tpb;
   m.rows_cap = S.rows_cap;
   m.partial_out = S.partial_out ? 1 : 0;
-#ifdef WST_TRACE
-  m.trace_bank = 4 + g_trace_bank;
-#endif
   const dim3 mgrid(static_cast<unsigned>(S.rows_cap), static_cast<unsigned>(S.n_units));
   cudaError_t e = S.hd == 128 ? launch_pdl(attn_merge_kernel<128>, mgrid, dim3(128), 0, m)
                               : launch_pdl(attn_merge_kernel<64>, mgrid, dim3(128), 0, m);

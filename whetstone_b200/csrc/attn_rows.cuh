@@ -10,6 +10,21 @@ namespace wst {
 
 constexpr int kRowsTile = 64;       /* cache positions per pipeline stage */
 constexpr int kRowsMaxSplits = 64;  /* upper bound on sequence slices */
+constexpr int kRowsRingBytes = 196608; /* shared memory of the K/V ring: 6 stages at head_dim 128 */
+
+/* Measurement knobs of the row-block kernel (wst_b200_set_tuning); -1 / 0 = automatic. */
+struct RowsTuning {
+  int decode_splits = 0;  /* slices of a decode launch (0: one per SM and KV head) */
+  int early_depth = -1;   /* tiles requested at once ahead of the grid dependency */
+  int fused_merge = -1;   /* 1: the last slice to arrive merges; 0: separate merge kernel */
+  int ring_stages = 0;    /* ring depth in use (0: all the shared memory holds) */
+};
+RowsTuning &rows_tuning();
+
+/* Whether a decode launch may request cache tiles before the launch ahead of it in
+ * the stream has finished (wst_b200_set_decode_overlap; on by default). */
+bool decode_overlap_allowed();
+void set_decode_overlap(bool on);
 
 struct RowsLaunch {
   /* queries: q of (token t, head h) at q + t*q_tok_stride + h*hd, fp32 */
@@ -48,6 +63,12 @@ struct RowsLaunch {
   /* output: fp16 [token][n_q*hd], or (partial mode) fp32 [n_q][hd+2] triples */
   void *out = nullptr;
   bool partial_out = false;
+  /* KV sequence sharded over `world` GPUs: the per-head triples are exchanged through
+   * the ranks' mailboxes inside the kernel and `out` is the merged fp16 result
+   * (needs the fused merge: one token, one sequence, scratch given) */
+  const void *mailboxes = nullptr; /* device array of `world` mailbox addresses */
+  void *xstate = nullptr;          /* this rank's per-head call counters */
+  int rank = 0, world = 1;
   const char *name = "attention";
 };
 

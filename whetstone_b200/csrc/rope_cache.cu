@@ -16,6 +16,7 @@
  * narrowed to fp16 into cache row `pos`; positions clamped, never trusted.
  */
 
+#include "attn_rows.cuh"
 #include "wst_common.cuh"
 
 namespace wst {
@@ -233,6 +234,9 @@ rope_append_kernel(const RopeArgs a) {
 template <bool PAGED>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 rope_append_any_kernel(const RopeArgs a) {
+  /* may be launched with programmatic stream serialization like the fast path */
+  if (a.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int hd = a.hd, half = hd >> 1;
   const int lane = threadIdx.x & 31;
   const int heads = a.n_q + a.n_kv;
@@ -305,7 +309,7 @@ wst_status_t launch_rope(const RopeArgs &a, const char *name) {
    * ordinary launches, complete before anything after them starts. */
   RopeArgs args = a;
   args.trigger_early = 0;
-  if (!PAGED && a.n_tokens == 1 && vec_ok) args.trigger_early = 1;
+  if (!PAGED && a.n_tokens == 1 && vec_ok && decode_overlap_allowed()) args.trigger_early = 1;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = block;

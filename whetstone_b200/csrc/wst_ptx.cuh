@@ -104,6 +104,16 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 
+/* Untiled bulk copy global -> this CTA's shared memory, completion counted in bytes
+ * on `bar`.  Both addresses 16-byte aligned, `bytes` a multiple of 16. */
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
 /* Orders generic-proxy writes to shared memory before async-proxy reads of it
  * (tcgen05.mma / TMA store reading what threads just stored). */
 __device__ __forceinline__ void fence_async_smem() {

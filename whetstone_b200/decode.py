@@ -225,6 +225,36 @@ def attn_exchange_merge(mine: torch.Tensor, out: torch.Tensor, mailboxes: torch.
                                       world, n_q, head_dim))
 
 
+def attn_decode_sharded(qkv: torch.Tensor, cache: KvCache, out: torch.Tensor, n_q: int,
+                        length: torch.Tensor, mailboxes: torch.Tensor, state: torch.Tensor,
+                        rank: int, world: int, scale: float | None = None) -> None:
+    """attn_decode_partial and the cross-GPU exchange in one kernel: rows [0, *length) of
+    this rank's shard -> out [n_q*head_dim] fp16 merged over all ranks."""
+    hd = cache.head_dim
+    _require_cuda(qkv, "attn_decode_sharded: qkv", torch.float32)
+    _require_cuda(out, "attn_decode_sharded: out", torch.float16)
+    _require_cuda(length, "attn_decode_sharded: length", torch.int32)
+    _require_cuda(mailboxes, "attn_decode_sharded: mailboxes", torch.int64)
+    _require_cuda(state, "attn_decode_sharded: state", torch.int32)
+    if qkv.numel() < n_q * hd or out.numel() != n_q * hd:
+        raise ShapeError(5, "attn_decode_sharded: qkv must hold n_q*head_dim queries and out "
+                            "exactly n_q*head_dim")
+    if mailboxes.numel() != world or state.numel() < n_q:
+        raise ShapeError(5, "attn_decode_sharded: one mailbox address per rank, one counter "
+                            "per head")
+    use_torch_stream()
+    check(lib.wst_attn_decode_sharded(
+        _ptr(qkv), _ptr(cache.k), _ptr(cache.v), _ptr(cache.partials), _ptr(out), n_q,
+        cache.n_kv, hd, _ptr(length), cache.max_seq,
+        float(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(mailboxes),
+        _ptr(state), rank, world))
+
+
+def set_tuning(key: int, value: int) -> None:
+    """Measurement knobs of the decode kernel (wst_b200_set_tuning)."""
+    check(lib.wst_b200_set_tuning(key, value))
+
+
 def device_error() -> int:
     """Read and clear the device watchdog word (0 = no kernel gave up a wait)."""
     use_torch_stream()
@@ -235,6 +265,7 @@ def device_error() -> int:
 
 __all__ = [
     "RopeScaling", "RopeTable", "KvCache", "DeviceCursor", "QkNorm", "rope_cache",
-    "attn_decode", "attn_decode_partial", "attn_merge_partials", "use_torch_stream",
+    "attn_decode", "attn_decode_partial", "attn_merge_partials", "attn_decode_sharded",
+    "set_tuning", "use_torch_stream",
     "device_error", "_ffi",
 ]

@@ -133,6 +133,13 @@ class PeerExchange:
         decode.attn_exchange_merge(mine, out, self.mailboxes_dev, self.state, self.rank,
                                    self.world, self.n_q, self.head_dim)
 
+    def decode(self, q: torch.Tensor, cache, out: torch.Tensor, length: torch.Tensor) -> None:
+        """Attention over this rank's shard and the exchange in one kernel
+        (wst_attn_decode_sharded)."""
+        from . import decode
+        decode.attn_decode_sharded(q, cache, out, self.n_q, length, self.mailboxes_dev,
+                                   self.state, self.rank, self.world)
+
     def close(self, group=None) -> None:
         """Unmaps the other ranks' buffers and frees this rank's (collective: every
         rank calls it, after its last merge has finished)."""
@@ -156,6 +163,7 @@ class ShardedDecodeLayer:
     length: torch.Tensor     # device int32[1]: valid rows of the slice
     n_q: int
     exchange: "PeerExchange | None" = None   # None: NCCL all-gather + local merge
+    fused: bool = False                      # with an exchange: one kernel per layer
 
     def __post_init__(self):
         hd = self.cache.head_dim
@@ -168,6 +176,9 @@ class ShardedDecodeLayer:
         """q [>= n_q*head_dim] fp32 (replicated on every rank) -> out [n_q*head_dim] fp16
         (identical on every rank)."""
         from . import decode  # the CUDA path; importing it here keeps this module CPU-importable
+        if self.exchange is not None and self.fused:
+            self.exchange.decode(q, self.cache, out, self.length)
+            return
         decode.attn_decode_partial(q, self.cache, self.mine, self.n_q, self.length)
         if self.exchange is not None:
             self.exchange.merge(self.mine, out)
