@@ -12,9 +12,15 @@ the C ABI (H2D of each layer's qkv, RoPE/append, attention, D2H of the output).
 The other four configs are reported under "also" (prefill in TFLOP/s).
 
 With N > 1 (one process per GPU, torchrun) the KV sequence of c3 is sharded over
-the ranks: each rank runs the partial-softmax kernel on its shard, the
-(m, l, acc) triples are all-gathered with NCCL and merged.  Total work is fixed,
-so scaling is "strong".
+the ranks: each rank attends over its shard and the per-head (m, l, acc) triples
+cross NVLink inside the same kernel (wst_attn_decode_sharded); the two-kernel
+exchange and the NCCL all-gather + local merge are timed beside it.  Before any
+timing, layer 0's shards are gathered on rank 0 and every variant is checked
+against the numpy oracle there.  Total work is fixed, so scaling is "strong".
+
+Every timed region is the driver's `--steps` block repeated until at least 0.25 s
+of device time have passed; the line carries the mean, p10/p50/p90 over the
+repeats and the contention flag the engine's own benchmark prints (p90 > 1.5 p50).
 """
 
 from __future__ import annotations
@@ -159,9 +165,26 @@ C3_NAME = ("c3: Qwen2.5-7B-shaped decode attention, batch 1, context 32768, 28 l
 # this library
 # --------------------------------------------------------------------------
 
-def timed_graph(torch, fn, steps, warmup, dist=None):
-    """Captures fn() into a CUDA graph (after eager warm-up), replays it `steps`
-    times between CUDA events on the launching stream.  Returns seconds/step."""
+MIN_REGION_S = 0.25
+
+
+class Timing(float):
+    """Seconds per step (the float itself) plus how it was measured."""
+
+    stats: dict
+
+    def __new__(cls, sec, stats):
+        obj = super().__new__(cls, sec)
+        obj.stats = stats
+        return obj
+
+
+def timed_graph(torch, fn, steps, warmup, dist=None, min_region_s=MIN_REGION_S):
+    """Captures fn() into a CUDA graph (after eager warm-up) and replays it in blocks
+    of `steps` between CUDA events on the launching stream, block after block with no
+    gap, until at least `min_region_s` of device time have passed; a barrier and a
+    synchronize bracket the whole region.  Returns seconds per step (mean over the
+    region, max over ranks) with the per-block statistics attached."""
     for _ in range(2):
         fn()
     torch.cuda.synchronize()
@@ -177,61 +200,128 @@ def timed_graph(torch, fn, steps, warmup, dist=None):
     for _ in range(max(warmup, 3)):
         run()
     torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
+
+    def region(blocks):
+        if dist is not None:
+            dist.barrier()
         torch.cuda.synchronize()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(steps):
-        run()
-    t1.record()
-    torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    sec = t0.elapsed_time(t1) / 1e3 / steps
-    if dist is not None:
-        t = torch.tensor([sec], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec = float(t.item())
-    return sec
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
+        marks[0].record()
+        for b in range(blocks):
+            for _ in range(steps):
+                run()
+            marks[b + 1].record()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        per = torch.tensor([marks[b].elapsed_time(marks[b + 1]) / 1e3 for b in range(blocks)],
+                           dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(per, op=dist.ReduceOp.MAX)
+        return per.cpu().numpy()
+
+    first = region(1)                      # one block: how long is it?
+    blocks = int(min(max(math.ceil(min_region_s / max(float(first[0]), 1e-9)), 1), 2000))
+    per = region(blocks)                   # every rank computes the same count from the max
+    total = float(per.sum())
+    sec = total / (blocks * steps)
+    p10, p50, p90 = (float(np.percentile(per, q)) / steps for q in (10, 50, 90))
+    return Timing(sec, {"timed_region_s": total, "repeats": blocks, "steps_per_repeat": steps,
+                        "ms_per_step_p10": p10 * 1e3, "ms_per_step_p50": p50 * 1e3,
+                        "ms_per_step_p90": p90 * 1e3, "contended": bool(p90 > 1.5 * p50)})
 
 
-def bench_c3(torch, args, rank, world, dist):
+def require_clean(torch, decode, dist, what):
+    """After a timed region: no kernel may have given up a bounded wait (a kernel that
+    leaves its loop early would make the region look faster)."""
+    bad = torch.tensor([float(decode.device_error() != 0)], device="cuda")
+    if dist is not None:
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+    if bad.item() != 0:
+        raise SystemExit(f"bench: a kernel gave up a bounded wait during '{what}'; no number is reported")
+
+
+def oracle_check_layer0(torch, dist, rank, world, cache, q_dev, ctx, s, variants, outs0):
+    """Gathers layer 0's KV shards on rank 0, runs the numpy oracle there once and
+    requires every variant's fp16 result (already computed, one tensor per variant in
+    `outs0`) within the parity bar.  Outside every timed region.  Returns the worst
+    (max abs, min cosine) per variant; exits non-zero on failure."""
+    k_parts = [torch.empty_like(cache.k) for _ in range(world)] if rank == 0 else None
+    v_parts = [torch.empty_like(cache.v) for _ in range(world)] if rank == 0 else None
+    if world > 1:
+        dist.gather(cache.k, k_parts, dst=0)
+        dist.gather(cache.v, v_parts, dst=0)
+    else:
+        k_parts, v_parts = [cache.k], [cache.v]
+    verdict = {}
+    ok = torch.ones(1, device="cuda")
+    if rank == 0:
+        from oracle import attention_oracle as orc   # checker only, never timed
+        k = torch.cat(k_parts, dim=1).cpu().numpy()
+        v = torch.cat(v_parts, dim=1).cpu().numpy()
+        q = q_dev[: s.n_q * s.head_dim].cpu().numpy().astype(np.float64).reshape(s.n_q, s.head_dim)
+        want = orc.decode_attention(q, k, v, ctx, s.scale)
+        for name, out in zip(variants, outs0):
+            got = out.cpu().numpy().astype(np.float64).reshape(s.n_q, s.head_dim)
+            mx, cs = orc.error_stats(got, want)
+            verdict[name] = {"max_abs": mx, "min_cos": cs}
+            if not (mx <= 2e-3 and cs >= 0.9999):
+                ok.zero_()
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() == 0:
+        raise SystemExit(f"bench: parity against the oracle failed before timing: {verdict}")
+    return verdict
+
+
+def bench_c3(torch, args, rank, world, dist, ctx=None, layers=None, headline=True):
     from whetstone_b200 import decode, workloads as wl
 
     s = wl.QWEN25_7B
-    ctx = wl.C3["context"]
-    layers = s.layers
+    ctx = ctx or wl.C3["context"]
+    layers = layers or s.layers
     per = ctx // world                      # rows of the KV sequence on this rank
     gen = torch.Generator(device="cuda").manual_seed(wl.C3["seed"] + rank)
-    table = decode.RopeTable(ctx, s.head_dim, s.theta)
+    gen_q = torch.Generator(device="cuda").manual_seed(wl.C3["seed"] + 77)   # q is replicated
+    table = decode.RopeTable(per, s.head_dim, s.theta) if headline else None
     caches, qkvs, outs = [], [], []
     for _ in range(layers):
         c = decode.KvCache(s.n_kv, s.n_q, s.head_dim, per)
         c.k.copy_(torch.randn(c.k.shape, generator=gen, device="cuda", dtype=torch.float16))
         c.v.copy_(torch.randn(c.v.shape, generator=gen, device="cuda", dtype=torch.float16))
         caches.append(c)
-        qkvs.append(torch.randn(s.qkv_width, generator=gen, device="cuda",
+        qkvs.append(torch.randn(s.qkv_width, generator=gen_q, device="cuda",
                                 dtype=torch.float16).float())
         outs.append(torch.zeros(s.n_q * s.head_dim, dtype=torch.float16, device="cuda"))
     cursor = decode.DeviceCursor(per - 1)   # the new token is the shard's last row
     length = torch.tensor([per], dtype=torch.int32, device="cuda")
-    launches_per_step = 2 * layers          # slices kernel + merge kernel per layer
+    grp = dist if world > 1 else None
+    extra = {}
 
     if world == 1:
+        launches_per_step = layers          # one kernel per layer (the slices merge inside it)
+
         def step():
             for i in range(layers):
                 decode.attn_decode(qkvs[i], caches[i], outs[i], s.n_q, cursor)
+        step()
+        torch.cuda.synchronize()
+        parity = oracle_check_layer0(torch, dist, rank, world, caches[0], qkvs[0], ctx, s,
+                                     ["decode"], [outs[0]])
     else:
         mine = [torch.zeros((s.n_q, s.head_dim + 2), dtype=torch.float32, device="cuda")
                 for _ in range(layers)]
         gathered = [torch.zeros((world, s.n_q, s.head_dim + 2), dtype=torch.float32,
                                 device="cuda") for _ in range(layers)]
-        launches_per_step = 3 * layers      # slices, slice merge, cross-rank exchange + merge
+        launches_per_step = layers          # attention + exchange + merge in one kernel
         from whetstone_b200 import sharded
         xch = sharded.PeerExchange(s.n_q, s.head_dim)
 
-        def step():         # the triples cross NVLink inside wst_attn_exchange_merge
+        def step():         # one kernel per layer: the triples cross NVLink inside it
+            for i in range(layers):
+                xch.decode(qkvs[i], caches[i], outs[i], length)
+
+        def step_two_kernels():   # partial attention, then the exchange + merge kernel
             for i in range(layers):
                 decode.attn_decode_partial(qkvs[i], caches[i], mine[i], s.n_q, length)
                 xch.merge(mine[i], outs[i])
@@ -242,49 +332,51 @@ def bench_c3(torch, args, rank, world, dist):
                 dist.all_gather_into_tensor(gathered[i].view(-1, s.head_dim + 2), mine[i])
                 decode.attn_merge_partials(gathered[i], outs[i], s.n_q, s.head_dim)
 
-    exchange_note = None
-    if world > 1:
-        # both merges must agree before either is timed
-        step_nccl()
-        torch.cuda.synchronize()
-        want = [o.clone() for o in outs]
-        for o in outs:
-            o.zero_()
+        # every variant against the oracle on layer 0, before anything is timed
+        got0 = []
+        for fn in (step, step_two_kernels, step_nccl):
+            for o in outs:
+                o.zero_()
+            fn()
+            torch.cuda.synchronize()
+            got0.append(outs[0].clone())
+        require_clean(torch, decode, grp, "parity check")
+        parity = oracle_check_layer0(torch, dist, rank, world, caches[0], qkvs[0], ctx, s,
+                                     ["one_kernel", "two_kernels", "nccl_allgather"], got0)
         step()
         torch.cuda.synchronize()
-        bad = torch.tensor([float(decode.device_error() != 0 or any(
-            (a.float() - b.float()).abs().max().item() > 2e-3 for a, b in zip(outs, want)))],
-            device="cuda")
-        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+    want = [o.clone() for o in outs]
+
+    def same_as_before(what):
+        bad = torch.tensor([float(any((a.float() - b.float()).abs().max().item() > 2e-3
+                                      for a, b in zip(outs, want)))], device="cuda")
+        if grp is not None:
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         if bad.item() != 0:
-            exchange_note = "peer-memory exchange disagreed with the NCCL merge: NCCL variant timed"
-            step, step_nccl = step_nccl, step
+            raise SystemExit(f"bench: outputs after '{what}' differ from the checked ones")
 
     with ClockSampler(torch.cuda.current_device()) as clk:
-        sec = timed_graph(torch, step, args.steps, args.warmup, dist if world > 1 else None)
-        sampled_after = False
-        if world == 1 and len(clk.rows) < 3:
-            # a timed region shorter than the sampler's start-up: keep the same load
-            # running (untimed) until it has seen the clocks
-            sampled_after = True
-            t_end = time.perf_counter() + 1.0
-            while len(clk.rows) < 3 and time.perf_counter() < t_end:
-                for _ in range(20):
-                    step()
-                torch.cuda.synchronize()
-        elif world > 1 and sec * args.steps < 0.15:
-            # every rank runs the same number of extra (untimed) steps: `sec` is the
-            # all-reduced maximum, so the count agrees across ranks
-            sampled_after = True
-            for _ in range(int(0.25 / sec) + 1):
-                step()
-            torch.cuda.synchronize()
+        sec = timed_graph(torch, step, args.steps, args.warmup, grp)
     clocks = clk.summary()
-    if sampled_after and clk.rows:
-        clocks["sampled"] = "same load, right after the timed region (region shorter than the sampler's start-up)"
+    require_clean(torch, decode, grp, "c3")
+    same_as_before("c3")
 
     bytes_layer = wl.decode_bytes(s.n_q, s.n_kv, s.head_dim, ctx)   # whole job, all ranks
     value = bytes_layer * layers / sec / 1e9
+    kernel_us = sec / layers * 1e6
+    pk = peaks()
+    achieved = bytes_layer / world / (sec / layers) / 1e9      # per GPU, per launch
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": achieved / pk["hbm"],
+                "traffic": NCU_DECODE_TRAFFIC_BYTES if world == 1 and ctx == wl.C3["context"] else None,
+                "peak_source": pk["source"], "kernel": "attn_rows_kernel<128,1,1,0>",
+                "algorithmic_bytes_per_launch": bytes_layer // world,
+                "us_per_launch": kernel_us}
+    if not headline:
+        if world > 1:
+            xch.close()
+        return dict(us_per_layer=kernel_us, hbm_gbs=value, frac_of_aggregate_hbm_peak=value / (pk["hbm"] * world),
+                    context=ctx, layers_timed=layers, **sec.stats)
 
     # end to end: the step's inputs (every layer's qkv row) come from pinned host memory
     # in one copy, each layer appends its token (RoPE) and attends, and the step's
@@ -306,35 +398,27 @@ def bench_c3(torch, args, rank, world, dist):
             for i in range(layers):
                 if rank == world - 1:   # the shard that owns the newest position appends
                     decode.rope_cache(dev_in[i], caches[i], table, s.n_q, cursor)
-                decode.attn_decode_partial(dev_in[i], caches[i], mine[i], s.n_q, length)
-                xch.merge(mine[i], dev_out[i])
+                xch.decode(dev_in[i], caches[i], dev_out[i], length)
             host_out.copy_(dev_out, non_blocking=True)
-    sec_e2e = timed_graph(torch, step_e2e, args.steps, args.warmup, dist if world > 1 else None)
+    sec_e2e = timed_graph(torch, step_e2e, args.steps, args.warmup, grp)
+    require_clean(torch, decode, grp, "c3 end to end")
     e2e = {"value": bytes_layer * layers / sec_e2e / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": layers * s.qkv_width * 4,
            "d2h_bytes_per_step": layers * s.n_q * s.head_dim * 2,
-           "ms_per_step": sec_e2e * 1e3}
+           "ms_per_step": sec_e2e * 1e3, **sec_e2e.stats}
 
-    extra = {}
     if world > 1:
+        sec_two = timed_graph(torch, step_two_kernels, args.steps, args.warmup, dist)
+        extra["two_kernel_variant_us_per_layer"] = sec_two / layers * 1e6
         sec_nccl = timed_graph(torch, step_nccl, args.steps, args.warmup, dist)
         extra["nccl_allgather_variant_us_per_layer"] = sec_nccl / layers * 1e6
-        if exchange_note:
-            extra["exchange_note"] = exchange_note
+        require_clean(torch, decode, grp, "c3 variants")
         xch.close()
 
-    pk = peaks()
-    kernel_us = sec / layers * 1e6
-    achieved = bytes_layer / world / (sec / layers) / 1e9      # per GPU, per launch
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                "frac": achieved / pk["hbm"],
-                "traffic": NCU_DECODE_TRAFFIC_BYTES if world == 1 else None,
-                "peak_source": pk["source"], "kernel": "attn_rows_kernel<128,1,1>",
-                "algorithmic_bytes_per_launch": bytes_layer // world,
-                "us_per_launch": kernel_us}
     return dict(value=value, sec=sec, clocks=clocks, e2e=e2e, roofline=roofline,
-                launches=launches_per_step * args.steps,
-                extra=dict(extra, us_per_layer=kernel_us, tokens_per_s=1.0 / sec))
+                launches=launches_per_step * args.steps * sec.stats["repeats"],
+                extra=dict(extra, us_per_layer=kernel_us, tokens_per_s=1.0 / sec,
+                           parity_checked=parity, **sec.stats))
 
 
 def bench_also(torch, args):
@@ -370,8 +454,10 @@ def bench_also(torch, args):
                 decode.rope_cache(qkvs[i], caches[i], table, s.n_q, cur)
                 decode.attn_decode(qkvs[i], caches[i], outs[i], s.n_q, cur)
         sec = timed_graph(torch, c1_step, args.steps, args.warmup)
+        require_clean(torch, decode, None, "c1")
         out["c1_decode_0.5b"] = {"us_per_layer": sec / s.layers * 1e6,
-                                 "note": "append + attention, 513 rows, latency-bound"}
+                                 "note": "append + attention, 513 rows, latency-bound",
+                                 **sec.stats}
 
     # ---- c2: 0.5B chunked prefill, 2048 tokens = 8 chunks of 256, 24 layers
     if want("c2"):
@@ -397,10 +483,13 @@ def bench_also(torch, args):
                                outs[i][c * n * s.n_q * s.head_dim:], s.n_q, c * n, n)
         c2_rope()
         sec = timed_graph(torch, c2_attn, min(args.steps, 50), args.warmup)
+        require_clean(torch, decode, None, "c2")
         tf = flops_layer * s.layers / sec / 1e12
         out["c2_prefill_0.5b"] = {"tflops": tf, "ms_per_layer": sec / s.layers * 1e3,
                                   "frac_of_tensor_peak": tf / pk["tf_burst"],
-                                  "flops_per_layer": flops_layer}
+                                  "flops_per_layer": flops_layer,
+                                  "us_per_chunk_step": sec / s.layers / (prompt // n) * 1e6,
+                                  **sec.stats}
         del caches, qkv_src, qkv_buf, outs
 
     # ---- c4: Qwen3-8B prefill, 4 x 8192 tokens in 512-token chunks, QK-norm; a
@@ -428,6 +517,11 @@ def bench_also(torch, args):
             for c in range(chunks):
                 buf = pool[c % len(pool)].clone()
                 chunk.rope_cache_batch(buf, caches[l], table4, s4.n_q, starts[c], n4, norm)
+        # the attention is timed on rotated, normed q rows: what the append leaves in the
+        # projection buffer (k and v parts of a row are inputs only and stay as they were)
+        for c in range(len(pool)):
+            chunk.rope_cache_batch(pool[c], caches[0], table4, s4.n_q, starts[c], n4, norm)
+        rope_src = [p.clone() for p in pool]
         rope_bytes = n4 * s4.qkv_width * 4 + n4 * s4.n_q * s4.head_dim * 4 + \
             2 * n4 * s4.n_kv * s4.head_dim * 2
 
@@ -439,19 +533,22 @@ def bench_also(torch, args):
         def c4_rope():
             for l in range(lay4):
                 for c in range(chunks):
-                    chunk.rope_cache_batch(pool[c % len(pool)], caches[l], table4, s4.n_q,
+                    chunk.rope_cache_batch(rope_src[c % len(pool)], caches[l], table4, s4.n_q,
                                            starts[c], n4, norm)
         sec = timed_graph(torch, c4_attn, max(1, min(args.steps, 20) // 4), 3)
+        require_clean(torch, decode, None, "c4")
         tf = flops4 * lay4 / sec / 1e12
         sec_r = timed_graph(torch, c4_rope, max(1, min(args.steps, 20) // 4), 3)
         rope_gbs = rope_bytes * lay4 * nseq * chunks / sec_r / 1e9
         out["c4_prefill_qwen3_8b"] = {
             "tflops": tf, "ms_per_layer": sec / lay4 * 1e3,
             "frac_of_tensor_peak": tf / pk["tf_burst"],
+            "frac_of_sustained_tensor_peak": tf / pk["tf_sustained"],
             "flops_per_layer": flops4, "layers_timed": lay4, "layers_in_model": s4.layers,
-            "launch": "one batched launch per chunk step (4 sequences)",
-            "rope_append_gbs": rope_gbs, "rope_append_frac_of_hbm": rope_gbs / pk["hbm"]}
-        del caches, pool
+            "launch": "one batched launch per chunk step (4 sequences), q rows rotated and normed",
+            "rope_append_gbs": rope_gbs, "rope_append_frac_of_hbm": rope_gbs / pk["hbm"],
+            **sec.stats}
+        del caches, pool, rope_src
 
     # ---- c5: speculative verify, 16 sequences x 5 drafts, paged cache, 28 layers
     if want("c5"):
@@ -485,13 +582,15 @@ def bench_also(torch, args):
                 paged.attn_verify(qkv5[l], pcs[l], out5, scratch, s5.n_q, pos0, cu, total, drafts,
                                   max_len)
         sec = timed_graph(torch, c5_step, min(args.steps, 50), args.warmup)
+        require_clean(torch, decode, None, "c5")
         kv_bytes = int(2 * s5.n_kv * s5.head_dim * 2 * int((lengths.astype(np.int64) + drafts).sum()))
         bytes5 = kv_bytes + total * s5.n_q * s5.head_dim * (4 + 2) + table_np.size * 4
         gbs = bytes5 * lay5 / sec / 1e9
         out["c5_verify_7b_paged"] = {"us_per_layer": sec / lay5 * 1e6, "hbm_gbs": gbs,
                                      "frac_of_hbm_peak": gbs / pk["hbm"], "bytes_per_layer": bytes5,
                                      "layers_timed": lay5, "layers_in_model": s5.layers,
-                                     "tokens_verified_per_s": total / (sec / lay5 * s5.layers)}
+                                     "tokens_verified_per_s": total / (sec / lay5 * s5.layers),
+                                     **sec.stats}
     return out
 
 
@@ -534,11 +633,13 @@ def bench_sharded_units(torch, args, rank, world, dist):
         for c in range(chunks):
             chunk.attn_batch(pool[c % len(pool)], cache, out4, loc4.n_q, starts[c], n4)
     sec = timed_graph(torch, c4_attn, 5, 3, dist)
+    require_clean(torch, decode, dist, "c4 sharded")
     tf = flops4 / sec / 1e12
     out["c4_prefill_qwen3_8b"] = {
         "tflops": tf, "ms_per_layer": sec * 1e3, "frac_of_aggregate_tensor_peak":
         tf / (pk["tf_burst"] * world), "units_per_rank": nseq * heads4,
-        "partition": f"{heads4} of {s4.n_kv} KV heads x {nseq} sequences per rank, no collective"}
+        "partition": f"{heads4} of {s4.n_kv} KV heads x {nseq} sequences per rank, no collective",
+        **sec.stats}
     del cache, pool
 
     # ---- c5
@@ -572,6 +673,7 @@ def bench_sharded_units(torch, args, rank, world, dist):
         paged.rope_cache(qkv5, pc, rtab, loc5.n_q, pos0, cu, total)
         paged.attn_verify(qkv5, pc, out5, scratch, loc5.n_q, pos0, cu, total, drafts, max_len)
     sec = timed_graph(torch, c5_step, 20, 3, dist)
+    require_clean(torch, decode, dist, "c5 sharded")
     all_tok = len(lengths) * drafts
     kv_bytes = int(2 * s5.n_kv * s5.head_dim * 2 * int((lengths.astype(np.int64) + drafts).sum()))
     bytes5 = kv_bytes + all_tok * s5.n_q * s5.head_dim * (4 + 2)     # whole job, all ranks
@@ -580,7 +682,8 @@ def bench_sharded_units(torch, args, rank, world, dist):
         "us_per_layer": sec * 1e6, "hbm_gbs": gbs,
         "frac_of_aggregate_hbm_peak": gbs / (pk["hbm"] * world),
         "tokens_verified_per_s": all_tok / (sec * s5.layers), "units_per_rank": nseq5 * heads5,
-        "partition": f"{heads5} of {s5.n_kv} KV heads x {nseq5} sequences per rank, no collective"}
+        "partition": f"{heads5} of {s5.n_kv} KV heads x {nseq5} sequences per rank, no collective",
+        **sec.stats}
     return out
 
 
@@ -694,6 +797,11 @@ def run_ours(args):
         refcuda = bench_reference_cuda(torch)
     if world > 1 and not args.no_also and args.only is None:
         also = bench_sharded_units(torch, args, rank, world, dist)
+    if also is not None and not args.no_long:
+        # the same sequence split where it pays: 8 x 32768 rows of context (a stated
+        # subset of layers; every layer does identical work)
+        also["c3_context_262144"] = bench_c3(torch, args, rank, world, dist, ctx=262144,
+                                             layers=args.long_layers, headline=False)
     if world == 1 and rank == 0 and not args.no_cpu:
         gbs, layers, spent = cpu_decode_sample()
         cpu = {"value": gbs, "unit": UNIT, "cores": len(os.sched_getaffinity(0)), "kind": "port",
@@ -708,9 +816,11 @@ def run_ours(args):
             "config": {"workload": C3_NAME,
                        "parallelism": "single GPU" if world == 1 else
                        f"KV sequence sharded over {world} GPUs; (m,l,acc) exchanged through peer memory "
-                       "inside the merge kernel (the NCCL all-gather variant is timed beside it)",
+                       "inside the attention kernel (the two-kernel and NCCL all-gather variants are "
+                       "timed beside it)",
                        "l2": "inputs larger than L2: 1.88 GB of KV cache is streamed per step",
-                       "launch": "one CUDA graph per step"},
+                       "launch": "one CUDA graph per step, the --steps block repeated until "
+                                 ">= 0.25 s of device time"},
             "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["launches"],
             "roofline": res["roofline"],
         }
@@ -737,7 +847,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "refcuda"],
                     help="run one workload only (c3 = the headline line without 'also')")
-    ap.add_argument("--c4-layers", type=int, default=1)
+    ap.add_argument("--no-long", action="store_true", help="skip the 262144-row decode leg")
+    ap.add_argument("--long-layers", type=int, default=8)
+    ap.add_argument("--c4-layers", type=int, default=4)
     ap.add_argument("--c5-layers", type=int, default=4)
     args = ap.parse_args()
     if args.impl == "reference":

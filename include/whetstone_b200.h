@@ -47,9 +47,8 @@ WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
  * default.  Results do not depend on them beyond fp32 summation order.
  *   key 1  slices of the KV sequence per KV head (default: SMs / KV heads)
  *   key 2  cache tiles requested at once before the launch ahead has finished
- *   key 3  1 = the slice that finishes last merges the slices inside the kernel,
- *          0 = a second kernel merges them
- *   key 4  stages of the shared-memory ring in use */
+ *   key 4  stages of the shared-memory ring in use (head_dim 128: 2..6; at 3 or
+ *          fewer, two blocks of consecutive launches share an SM) */
 WST_API wst_status_t wst_b200_set_tuning(int32_t key, int32_t value);
 
 /* 0: wst_attn_decode waits for everything ahead of it in the stream before it asks
@@ -118,12 +117,14 @@ WST_API wst_status_t wst_attn_exchange_merge(const void *my_triples, void *out,
                                              const void *mailboxes, void *state, int32_t rank,
                                              int32_t world, int32_t n_q, int32_t head_dim);
 
-/* wst_attn_decode_partial and the exchange in ONE kernel, for the GPUs of one box:
- * the slice of this rank's shard that finishes last merges the shard's slices,
- * stores each head's (m, l, acc) triple into the other ranks' mailboxes (plain peer
- * stores over NVLink, 8-byte {value, tag} packets), waits -- each packet for at most
- * about a second -- for theirs in its own mailbox, and writes the fp16 result.  One
- * launch per layer and rank, no NCCL call, no host step.
+/* wst_attn_decode_partial and the exchange as ONE call, for the GPUs of one box: the
+ * kernel that merges the slices of this rank's shard (one block per query head, the
+ * head's triple in registers) stores that triple into the other ranks' mailboxes
+ * (plain peer stores over NVLink, 8-byte {value, tag} packets), waits -- each packet
+ * for at most about a second -- for theirs in its own mailbox, and writes the fp16
+ * result.  Two launches per layer and rank (slices, merge + exchange) where
+ * wst_attn_decode_partial + wst_attn_exchange_merge take three and a round trip
+ * through memory more; no NCCL call, no host step.
  *   len         device int32: valid rows of THIS rank's shard (as wst_attn_decode_partial)
  *   partials    scratch of wst_attn_partial_floats() floats
  *   out         [n_q][head_dim] half (every rank gets the full result)

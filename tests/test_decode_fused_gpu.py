@@ -1,6 +1,6 @@
-"""The decode kernel's variants (the slice merge inside the kernel or as a second
-kernel, how many tiles are asked for ahead of the grid dependency, ring depth, slice
-count) and the sharded form whose cross-GPU exchange runs inside the same kernel,
+"""The decode kernel's variants (how many tiles are asked for ahead of the grid
+dependency, ring depth -- at half the ring two blocks share an SM -- and slice count)
+and the sharded form whose cross-GPU exchange runs inside the slice-merge kernel,
 through the C ABI against the numpy oracle.  Semantics: cuda/attention.cu:57-193 of
 the engine; the knobs change summation order only."""
 
@@ -14,13 +14,13 @@ from whetstone_b200 import chunk, decode, workloads
 
 pytestmark = pytest.mark.gpu
 
-SPLITS, EARLY, FUSED, STAGES = 1, 2, 3, 4
+SPLITS, EARLY, STAGES = 1, 2, 4
 
 
 @pytest.fixture(autouse=True)
 def default_tuning_and_no_watchdog_trips():
     yield
-    for key, val in ((SPLITS, 0), (EARLY, -1), (FUSED, -1), (STAGES, 0)):
+    for key, val in ((SPLITS, 0), (EARLY, -1), (STAGES, 0)):
         decode.set_tuning(key, val)
     assert decode.device_error() == 0, "a kernel gave up waiting on a barrier"
 
@@ -29,23 +29,22 @@ def rand16(rng, shape):
     return workloads.f16_values(rng, shape, np.float16)
 
 
-VARIANTS = [  # (fused, early, stages, splits)
-    (1, 1, 0, 0), (0, 1, 0, 0), (1, 0, 0, 0), (1, 6, 6, 0), (0, 6, 0, 0), (1, 2, 2, 0),
-    (1, 3, 4, 36), (1, 6, 0, 5), (0, 2, 3, 64), (1, 12, 0, 2),
+VARIANTS = [  # (early, stages, splits)
+    (1, 0, 0), (0, 0, 0), (6, 6, 0), (2, 2, 0), (3, 3, 0), (3, 4, 36), (6, 0, 5), (2, 3, 64),
+    (12, 12, 2),
 ]
 
 
-@pytest.mark.parametrize("fused,early,stages,splits", VARIANTS)
+@pytest.mark.parametrize("early,stages,splits", VARIANTS)
 @pytest.mark.parametrize("n_q,n_kv,hd,seq", [(28, 4, 128, 1), (28, 4, 128, 65), (28, 4, 128, 700),
                                              (28, 4, 128, 9000), (14, 2, 64, 513),
                                              (14, 2, 64, 4099), (64, 2, 64, 2000),
                                              (16, 1, 128, 3100)])
-def test_decode_variants_match_oracle(fused, early, stages, splits, n_q, n_kv, hd, seq):
-    decode.set_tuning(FUSED, fused)
+def test_decode_variants_match_oracle(early, stages, splits, n_q, n_kv, hd, seq):
     decode.set_tuning(EARLY, early)
     decode.set_tuning(STAGES, stages)
     decode.set_tuning(SPLITS, splits)
-    rng = np.random.default_rng(seq * 7 + n_q + fused)
+    rng = np.random.default_rng(seq * 7 + n_q + early)
     max_seq = seq + 91
     cache = decode.KvCache(n_kv, n_q, hd, max_seq)
     fill_bits(cache.k, NAN16)
@@ -55,24 +54,24 @@ def test_decode_variants_match_oracle(fused, early, stages, splits, n_q, n_kv, h
     cache.k[:, :seq] = dev(k)
     cache.v[:, :seq] = dev(v)
     want = None
-    # three calls in a row on one scratch: the arrival counters must be back at zero
+    # three calls in a row on one scratch
     for rep in range(3):
         q = workloads.f16_values(rng, (n_q, hd))
         out = torch.zeros(n_q * hd, dtype=torch.float16, device="cuda")
         decode.attn_decode(dev(q), cache, out, n_q, decode.DeviceCursor(seq - 1))
         want = orc.decode_attention(q, k, v, seq)
         assert_close_per_head(host(out).astype(np.float64).reshape(n_q, hd), want,
-                              f"decode variant {(fused, early, stages, splits)} seq {seq} call {rep}")
+                              f"decode variant {(early, stages, splits)} seq {seq} call {rep}")
 
 
-@pytest.mark.parametrize("fused,early", [(1, 6), (1, 1), (0, 6), (1, 0)])
+@pytest.mark.parametrize("early,stages", [(6, 6), (2, 0), (3, 3), (0, 0)])
 @pytest.mark.parametrize("prefix", [3, 200, 1500, 5000])
-def test_append_then_decode_back_to_back(fused, early, prefix):
+def test_append_then_decode_back_to_back(early, stages, prefix):
     """One-row appends and decode attention back to back with no synchronize: the
     decode kernel asks for tiles before the append ahead of it has finished and must
     still see the row it wrote (the newest row is patched after the dependency)."""
-    decode.set_tuning(FUSED, fused)
     decode.set_tuning(EARLY, early)
+    decode.set_tuning(STAGES, stages)
     n_q, n_kv, hd, theta = 28, 4, 128, 1e6
     rng = np.random.default_rng(prefix + early)
     steps = 70   # crosses a 64-row tile boundary
@@ -98,12 +97,11 @@ def test_append_then_decode_back_to_back(fused, early, prefix):
     k_all, v_all = np.concatenate([k_pre, k_new]), np.concatenate([v_pre, v_new])
     want = orc.attention_blocked(qr, k_all, v_all, prefix + 1 + np.arange(steps))
     assert_close_per_head(host(outs).astype(np.float64).reshape(steps, n_q, hd), want,
-                          f"append + decode, prefix {prefix}, fused {fused}, early {early}")
+                          f"append + decode, prefix {prefix}, early {early}, stages {stages}")
 
 
-def test_partial_output_of_the_fused_merge():
-    """wst_attn_decode_partial through the in-kernel merge: the (m, l, acc) triple."""
-    decode.set_tuning(FUSED, 1)
+def test_partial_output_is_the_reference_triple():
+    """wst_attn_decode_partial: the (m, l, acc) triple of cuda/attention.cu:50-55."""
     rng = np.random.default_rng(8)
     n_q, n_kv, hd, seq = 28, 4, 128, 2500
     k, v = rand16(rng, (n_kv, seq, hd)), rand16(rng, (n_kv, seq, hd))
@@ -116,7 +114,7 @@ def test_partial_output_of_the_fused_merge():
                                torch.tensor([seq], dtype=torch.int32, device="cuda"))
     p = host(part).astype(np.float64)
     got = p[:, 2:] / p[:, 1:2]
-    assert_close_per_head(got, orc.decode_attention(q, k, v, seq), "fused partial", max_abs=1e-3)
+    assert_close_per_head(got, orc.decode_attention(q, k, v, seq), "partial triple", max_abs=1e-3)
     # m is the row maximum of the scaled scores, in natural-log units
     kk = k.astype(np.float64)
     for head in (0, 13, 27):
@@ -138,7 +136,8 @@ def test_sharded_decode_merges_a_peers_triples():
     """Two shards of one sequence, one GPU, no second kernel: the peer's triples are
     computed with wst_attn_decode_partial and laid into this rank's mailbox the way
     the peer's kernel would store them; wst_attn_decode_sharded then attends over
-    shard 0, publishes, finds the peer's packets, merges and writes the fp16 result.
+    shard 0 and its merge kernel publishes, finds the peer's packets, merges and writes
+    the fp16 result.
     Two calls: both mailbox halves and the call counter."""
     rng = np.random.default_rng(17)
     n_q, n_kv, hd, world = 28, 4, 128, 2
@@ -190,7 +189,7 @@ def test_sharded_decode_merges_a_peers_triples():
 def test_sharded_decode_wait_runs_out_and_reports():
     """A peer that never publishes: the polls give up after their bound (about a
     second), the device error word says so, `out` stays as it was, the counters still
-    advance and the context stays usable.  Local buffers only, one kernel."""
+    advance and the context stays usable.  Local buffers only, one rank's launches."""
     rng = np.random.default_rng(4)
     n_q, n_kv, hd, world, seq = 14, 2, 64, 2, 900
     stride = hd + 2

@@ -300,7 +300,6 @@ extern "C" wst_status_t wst_b200_set_tuning(int32_t key, int32_t value) {
   switch (key) {
     case 1: t.decode_splits = value; break;
     case 2: t.early_depth = value; break;
-    case 3: t.fused_merge = value; break;
     case 4: t.ring_stages = value; break;
     default: return fail(WST_ERR_INVALID_ARG, "wst_b200_set_tuning: unknown key %d", key);
   }

@@ -28,8 +28,6 @@
  */
 
 #include <atomic>
-#include <mutex>
-#include <unordered_map>
 
 #include "attn_rows.cuh"
 #include "tensor_map.cuh"
@@ -65,13 +63,8 @@ struct RowsArgs {
   int early_depth; /* 0: nothing is requested before the grid dependency resolves; else the
                     * number of tiles requested at once ahead of it (the rest of the ring
                     * follows one tile at a time) */
-  /* fused slice merge: per-unit arrival counters (zero between launches), or null when
-   * the separate merge kernel follows */
-  unsigned int *tickets;
-  /* cross-GPU exchange inside the fused merge (world > 1), see exchange_and_finish */
-  uint2 *const *mailboxes;
-  unsigned int *xstate;
-  int rank, world;
+  int via_scratch; /* a single slice still writes its row to scratch: the merge kernel
+                    * follows (it carries the cross-GPU exchange) */
 };
 
 template <int HD, int MT, int RG>
@@ -84,14 +77,19 @@ struct Cfg {
   static constexpr int THREADS = CTHREADS + 32;
   static constexpr int HALF_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = 2 * NH * HALF_BYTES;
-  static constexpr int RING_BYTES = kRowsRingBytes;
-  static constexpr int NSTAGE = RING_BYTES / STAGE_BYTES; /* 6 (head_dim 128) or 12 (64) */
+  static constexpr int NSTAGE = kRowsRingBytes / STAGE_BYTES; /* at most: 6 (head_dim 128) or 12 (64) */
   static constexpr int Q_BYTES = NH * ROWS * 128;
-  /* ring | q tile | barriers (full, empty per stage; merge) and the flag word */
-  static constexpr int SMEM_BYTES = RING_BYTES + Q_BYTES + (2 * NSTAGE + 2) * 8 + 64 + 1024;
   /* the warp-combine dump [RG][4][16*MT][HD+4] floats reuses the ring */
-  static_assert(RG * 4 * 16 * MT * (HD + 4) * 4 <= RING_BYTES, "combine buffer must fit");
-  static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA");
+  static constexpr int DUMP_BYTES = RG * 4 * 16 * MT * (HD + 4) * 4;
+  static constexpr int MIN_STAGES = (DUMP_BYTES + STAGE_BYTES - 1) / STAGE_BYTES < 2
+                                        ? 2
+                                        : (DUMP_BYTES + STAGE_BYTES - 1) / STAGE_BYTES;
+  /* ring of `stages` stages | q tile | barriers (full, empty per stage) and the flag word */
+  static constexpr int smem_bytes(int stages) {
+    return stages * STAGE_BYTES + Q_BYTES + (2 * NSTAGE + 2) * 8 + 64 + 1024;
+  }
+  static_assert(MIN_STAGES <= NSTAGE, "combine buffer must fit the ring");
+  static_assert(smem_bytes(NSTAGE) <= 232448, "shared memory of one CTA");
 };
 
 __device__ __forceinline__ void grid_dependency_wait() {
@@ -113,38 +111,6 @@ __device__ __forceinline__ void consumer_bar(int threads) {
   asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
-/* ---- packets of the cross-GPU exchange: {value, tag} in ONE 64-bit access, so a
- * packet is valid exactly when its tag is the call's tag */
-__device__ __forceinline__ unsigned long long make_packet(float value, unsigned int tag) {
-  return (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(value);
-}
-__device__ __forceinline__ void st_packet(uint2 *p, float value, unsigned int tag) {
-  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(make_packet(value, tag)) : "memory");
-}
-__device__ __forceinline__ void st_packet2(uint2 *p, float v0, float v1, unsigned int tag) {
-  asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(make_packet(v0, tag)),
-               "l"(make_packet(v1, tag))
-               : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_packet(const uint2 *p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-/* value of a packet once its tag has arrived; false after about a second */
-__device__ __forceinline__ bool wait_packet(const uint2 *p, unsigned int tag, float *value) {
-  unsigned long long v = ld_packet(p);
-  if (static_cast<unsigned int>(v >> 32) != tag) {
-    const long long t0 = clock64();
-    do {
-      if (clock64() - t0 > kWaitCycleLimit) return false;
-      v = ld_packet(p);
-    } while (static_cast<unsigned int>(v >> 32) != tag);
-  }
-  *value = __uint_as_float(static_cast<unsigned int>(v));
-  return true;
-}
-
 template <int HD, int MT, int RG, bool PAGED>
 __global__ void __launch_bounds__(Cfg<HD, MT, RG>::THREADS, 1)
 attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
@@ -163,21 +129,19 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t *qsm = smem + C::RING_BYTES;
+  uint8_t *qsm = smem + nst * STAGE_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(qsm + C::Q_BYTES);
   const uint32_t stages_u32 = smem_u32(smem);
   const uint32_t q_u32 = smem_u32(qsm);
   const uint32_t full_u32 = smem_u32(bars);
   const uint32_t empty_u32 = smem_u32(bars + C::NSTAGE);
-  const uint32_t merge_u32 = smem_u32(bars + 2 * C::NSTAGE);
-  const uint32_t go_u32 = smem_u32(bars + 2 * C::NSTAGE + 1); /* "dependency resolved", see below */
+  const uint32_t go_u32 = smem_u32(bars + 2 * C::NSTAGE); /* "dependency resolved", see below */
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < nst; ++i) {
       mbar_init(full_u32 + 8 * i, 1);
       mbar_init(empty_u32 + 8 * i, C::CWARPS);
     }
-    mbar_init(merge_u32, 1);
     st_shared_volatile(go_u32, 0u);
     mbar_init_fence();
     tma_prefetch_desc(&kmap);
@@ -590,8 +554,7 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   consumer_bar(C::CTHREADS);
 
   const int unit = (s * a.n_kv + kvh) * a.n_rowblk + rb;
-  const bool fused = a.tickets != nullptr; /* the last slice to arrive finishes the unit */
-  const bool direct = ns == 1 && !fused;
+  const bool direct = ns == 1 && !a.via_scratch;
   for (int idx = ctid; idx < rows_valid * (HD / 4); idx += C::CTHREADS) {
     const int r = idx / (HD / 4), c4 = idx % (HD / 4);
     const float *cell = dump + (static_cast<size_t>(r / RPG) * 4 * RPG + r % RPG) * DR;
@@ -629,172 +592,12 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[0] = make_float2(acc.x, acc.y);
       reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[1] = make_float2(acc.z, acc.w);
-    } else { /* this slice's row, for the fused merge below or the merge kernel */
+    } else { /* this slice's row for the merge kernel */
       float *dst = a.scratch +
                    ((static_cast<long long>(unit) * ns + split) * a.rows_cap + r) * DR;
       *reinterpret_cast<float4 *>(dst + 4 * c4) = acc;
       if (c4 == 0) *reinterpret_cast<float2 *>(dst + HD) = make_float2(M, den);
     }
-  }
-  if (!fused) return;
-
-  /* ---- fused slice merge.  Every slice of a unit takes a ticket after its rows
-   * are out (stores, fence, block barrier, one atomic); the slice that draws the
-   * last one brings all the unit's rows back with one bulk copy into the idle
-   * ring -- one memory round trip -- and finishes the unit.  Nothing spins; the
-   * counter is left at zero for the next launch. */
-  __threadfence();
-  consumer_bar(C::CTHREADS);
-  if (ctid == 0) {
-    const unsigned int prev = ns > 1 ? atomicAdd(a.tickets + unit, 1u) : 0u;
-    const bool last = prev == static_cast<unsigned int>(ns - 1);
-    if (last) {
-      if (ns > 1) a.tickets[unit] = 0u;
-      __threadfence();
-    }
-    st_shared_volatile(go_u32, last ? 2u : 3u);
-  }
-  consumer_bar(C::CTHREADS);
-  if (ld_shared_volatile(go_u32) != 2u) return;
-
-  const int slice_floats = a.rows_cap * DR;
-  const uint32_t unit_bytes = static_cast<uint32_t>(ns * slice_floats * 4);
-  float *mbuf = reinterpret_cast<float *>(smem);                /* [ns][rows_cap][DR] */
-  float *wbuf = mbuf + static_cast<size_t>(ns) * slice_floats;  /* [rows][kRowsMaxSplits] weights */
-  float *rowm = wbuf + ROWS * kRowsMaxSplits;                    /* [rows] maximum, denominator */
-  float *rowl = rowm + ROWS;
-  if (ctid == 0) {
-    /* other blocks' stores (generic proxy) before this block's bulk copy (async proxy) */
-    asm volatile("fence.proxy.async;" ::: "memory");
-    mbar_arrive_expect_tx(merge_u32, unit_bytes);
-    const char *src = reinterpret_cast<const char *>(
-        a.scratch + static_cast<long long>(unit) * ns * slice_floats);
-    constexpr uint32_t kPiece = 32768;
-    for (uint32_t off = 0; off < unit_bytes; off += kPiece)
-      bulk_load(stages_u32 + off, src + off, min(kPiece, unit_bytes - off), merge_u32);
-  }
-  const bool landed = mbar_wait(merge_u32, 0, a.err_word, 0x105u);
-
-  /* one warp per row: maximum over the slices, weights, denominator */
-  for (int r = warp; r < rows_valid; r += C::CWARPS) {
-    float M = -INFINITY;
-    for (int sp = lane; sp < ns; sp += 32)
-      M = fmaxf(M, mbuf[static_cast<size_t>(sp) * slice_floats + r * DR + HD]);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-    const float m_use = M == -INFINITY ? 0.f : M;
-    float den = 0.f;
-    for (int sp = lane; sp < ns; sp += 32) {
-      const float *row = mbuf + static_cast<size_t>(sp) * slice_floats + r * DR;
-      const float wgt = ex2(row[HD] - m_use);
-      wbuf[r * kRowsMaxSplits + sp] = wgt;
-      den = fmaf(wgt, row[HD + 1], den);
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
-    if (lane == 0) {
-      rowm[r] = M;
-      rowl[r] = den;
-    }
-  }
-  consumer_bar(C::CTHREADS);
-
-  const bool exchange = a.world > 1;
-  bool ok = landed;
-  for (int idx = ctid; idx < rows_valid * (HD / 4); idx += C::CTHREADS) {
-    const int r = idx / (HD / 4), c4 = idx % (HD / 4);
-    const float *col = mbuf + r * DR + 4 * c4;
-    const float *wr = wbuf + r * kRowsMaxSplits;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-    for (int sp = 0; sp < ns; ++sp) {
-      const float wgt = wr[sp];
-      const float4 v = *reinterpret_cast<const float4 *>(col + static_cast<size_t>(sp) * slice_floats);
-      acc.x = fmaf(wgt, v.x, acc.x);
-      acc.y = fmaf(wgt, v.y, acc.y);
-      acc.z = fmaf(wgt, v.z, acc.z);
-      acc.w = fmaf(wgt, v.w, acc.w);
-    }
-    float big = rowm[r];
-    float den = rowl[r];
-    const int head = kvh * a.gqa + r % a.gqa;
-    const int tok = tok_begin + tok0 + r / a.gqa;
-
-    if (exchange) {
-      /* The KV sequence is sharded over the GPUs of the box: this rank's triple of the
-       * head goes into every other rank's mailbox (plain peer stores over NVLink), the
-       * others' are awaited in this GPU's own mailbox -- each packet for at most about
-       * a second -- and folded in.  The tag is a per-head call counter in device memory
-       * (graph replays advance it); mailboxes exist twice, used by tag parity: a rank
-       * can publish call t+2 only after it has received everybody's t+1, which they
-       * sent after reading t. */
-      const float m_nat = big * kLn2;
-      const unsigned int tag = a.xstate[head] + 1u;
-      const int par = static_cast<int>(tag & 1u);
-      const int stride = HD + 2;
-      const long long my_slot = (static_cast<long long>(par) * a.world + a.rank) * a.n_q + head;
-      for (int g = 0; g < a.world; ++g) {
-        if (g == a.rank) continue;
-        uint2 *dst = a.mailboxes[g] + my_slot * stride;
-        if (c4 == 0) {
-          st_packet(dst, m_nat, tag);
-          st_packet(dst + 1, den, tag);
-        }
-        st_packet2(dst + 2 + 4 * c4, acc.x, acc.y, tag);
-        st_packet2(dst + 4 + 4 * c4, acc.z, acc.w, tag);
-      }
-      const uint2 *box = a.mailboxes[a.rank] + (static_cast<long long>(par) * a.world * a.n_q + head) * stride;
-      const long long rank_stride = static_cast<long long>(a.n_q) * stride;
-      float top = m_nat;
-      for (int g = 0; ok && g < a.world; ++g) {
-        if (g == a.rank) continue;
-        float m_g;
-        ok = wait_packet(box + g * rank_stride, tag, &m_g);
-        top = fmaxf(top, m_g);
-      }
-      float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
-      float dsum = 0.f;
-      for (int g = 0; ok && g < a.world; ++g) {
-        float m_g = m_nat, l_g = den;
-        float4 a_g = acc;
-        if (g != a.rank) {
-          const uint2 *t = box + g * rank_stride;
-          ok = wait_packet(t, tag, &m_g) && wait_packet(t + 1, tag, &l_g) &&
-               wait_packet(t + 2 + 4 * c4, tag, &a_g.x) && wait_packet(t + 3 + 4 * c4, tag, &a_g.y) &&
-               wait_packet(t + 4 + 4 * c4, tag, &a_g.z) && wait_packet(t + 5 + 4 * c4, tag, &a_g.w);
-          if (!ok) break;
-        }
-        if (m_g == -INFINITY) continue; /* an empty shard contributes nothing */
-        const float f = expf(m_g - top);
-        tot.x = fmaf(a_g.x, f, tot.x);
-        tot.y = fmaf(a_g.y, f, tot.y);
-        tot.z = fmaf(a_g.z, f, tot.z);
-        tot.w = fmaf(a_g.w, f, tot.w);
-        dsum = fmaf(l_g, f, dsum);
-      }
-      acc = tot;
-      den = dsum;
-    }
-    if (!ok) continue;
-    if (a.partial_out && !exchange) {
-      float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (HD + 2);
-      if (c4 == 0) {
-        dst[0] = big * kLn2;
-        dst[1] = den;
-      }
-      reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[0] = make_float2(acc.x, acc.y);
-      reinterpret_cast<float2 *>(dst + 2 + 4 * c4)[1] = make_float2(acc.z, acc.w);
-    } else {
-      const float inv = den > 0.f ? 1.f / den : 0.f;
-      store_half4(static_cast<__half *>(a.out) + (static_cast<long long>(tok) * a.n_q + head) * HD +
-                      4 * c4,
-                  acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-    }
-  }
-  if (exchange) {
-    if (!ok) atomicCAS(a.err_word, 0u, 0x401u);
-    consumer_bar(C::CTHREADS); /* every thread has read its head's counter */
-    if (ctid < rows_valid && ctid < a.gqa) a.xstate[kvh * a.gqa + ctid] += 1u;
   }
 }
 
@@ -813,7 +616,44 @@ struct MergeArgs {
   int n_tok, tok_seq_stride, n_q, n_kv, gqa;
   int n_splits, n_rowblk, tpb, rows_cap;
   int partial_out;
+  /* cross-GPU exchange (world > 1): one token, so a block is one query head */
+  uint2 *const *mailboxes; /* [world] -> packets [2][world][n_q][hd+2] on rank g */
+  unsigned int *xstate;    /* this rank: per-head call counters [n_q] */
+  unsigned int *err_word;
+  int rank, world;
 };
+
+/* ---- packets of the cross-GPU exchange: {value, tag} in ONE 64-bit access, so a
+ * packet is valid exactly when its tag is the call's tag */
+__device__ __forceinline__ unsigned long long make_packet(float value, unsigned int tag) {
+  return (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(value);
+}
+__device__ __forceinline__ void st_packet(uint2 *p, float value, unsigned int tag) {
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(make_packet(value, tag)) : "memory");
+}
+__device__ __forceinline__ void st_packet2(uint2 *p, float v0, float v1, unsigned int tag) {
+  asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(make_packet(v0, tag)),
+               "l"(make_packet(v1, tag))
+               : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_packet(const uint2 *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+/* value of a packet once its tag has arrived; false after about a second */
+__device__ __forceinline__ bool wait_packet(const uint2 *p, unsigned int tag, float *value) {
+  unsigned long long v = ld_packet(p);
+  if (static_cast<unsigned int>(v >> 32) != tag) {
+    const long long t0 = clock64();
+    do {
+      if (clock64() - t0 > kWaitCycleLimit) return false;
+      v = ld_packet(p);
+    } while (static_cast<unsigned int>(v >> 32) != tag);
+  }
+  *value = __uint_as_float(static_cast<unsigned int>(v));
+  return true;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
@@ -902,6 +742,77 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
   }
   const int head = kvh * a.gqa + row % a.gqa;
   const int col = 4 * threadIdx.x;
+
+  if (a.world > 1) {
+    /* The KV sequence is sharded over the GPUs of the box.  This rank's triple of the
+     * head goes into every other rank's mailbox (plain peer stores over NVLink), the
+     * others' are awaited in this GPU's own mailbox -- each packet for at most about a
+     * second -- and folded in.  Every float travels as an 8-byte {value, tag} packet
+     * written with one 64-bit store, so a packet is valid exactly when its tag is this
+     * call's: no fence, no flag, no ordering between packets.  The tag is a per-head
+     * call counter in device memory (graph replays advance it); mailboxes exist twice,
+     * used by tag parity: a rank can publish call t+2 only after it has received
+     * everybody's t+1, which they sent after reading t.  Every rank runs its own launch
+     * on its own GPU; nothing here waits for another launch on the same GPU. */
+    const float m_nat = big * kLn2;
+    const unsigned int tag = a.xstate[head] + 1u;
+    const int par = static_cast<int>(tag & 1u);
+    constexpr int stride = HD + 2;
+    const long long my_slot = (static_cast<long long>(par) * a.world + a.rank) * a.n_q + head;
+    for (int g = 0; g < a.world; ++g) {
+      if (g == a.rank) continue;
+      uint2 *dst = a.mailboxes[g] + my_slot * stride;
+      if (threadIdx.x == 0) {
+        st_packet(dst, m_nat, tag);
+        st_packet(dst + 1, dsum, tag);
+      }
+      st_packet2(dst + 2 + col, tot.x, tot.y, tag);
+      st_packet2(dst + 4 + col, tot.z, tot.w, tag);
+    }
+    const uint2 *box = a.mailboxes[a.rank] +
+                       (static_cast<long long>(par) * a.world * a.n_q + head) * stride;
+    const long long rank_stride = static_cast<long long>(a.n_q) * stride;
+    bool ok = true;
+    float top = m_nat;
+    for (int g = 0; ok && g < a.world; ++g) {
+      if (g == a.rank) continue;
+      float m_g;
+      ok = wait_packet(box + g * rank_stride, tag, &m_g);
+      top = fmaxf(top, m_g);
+    }
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    float lsum = 0.f;
+    for (int g = 0; ok && g < a.world; ++g) {
+      float m_g = m_nat, l_g = dsum;
+      float4 a_g = tot;
+      if (g != a.rank) {
+        const uint2 *t = box + g * rank_stride;
+        ok = wait_packet(t, tag, &m_g) && wait_packet(t + 1, tag, &l_g) &&
+             wait_packet(t + 2 + col, tag, &a_g.x) && wait_packet(t + 3 + col, tag, &a_g.y) &&
+             wait_packet(t + 4 + col, tag, &a_g.z) && wait_packet(t + 5 + col, tag, &a_g.w);
+        if (!ok) break;
+      }
+      if (m_g == -INFINITY) continue; /* an empty shard contributes nothing */
+      const float f = expf(m_g - top);
+      sum.x = fmaf(a_g.x, f, sum.x);
+      sum.y = fmaf(a_g.y, f, sum.y);
+      sum.z = fmaf(a_g.z, f, sum.z);
+      sum.w = fmaf(a_g.w, f, sum.w);
+      lsum = fmaf(l_g, f, lsum);
+    }
+    ok = __all_sync(__activemask(), ok);
+    if (ok) {
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+      store_half4(static_cast<__half *>(a.out) + static_cast<long long>(head) * HD + col,
+                  sum.x * inv, sum.y * inv, sum.z * inv, sum.w * inv);
+    } else if (threadIdx.x == 0) {
+      atomicCAS(a.err_word, 0u, 0x401u);
+    }
+    __syncwarp(); /* every lane has read the counter and is done with the call */
+    if (threadIdx.x == 0) a.xstate[head] = tag;
+    return;
+  }
+
   if (a.partial_out) {
     float *dst = static_cast<float *>(a.out) + static_cast<long long>(head) * (HD + 2);
     if (threadIdx.x == 0) {
@@ -1063,10 +974,17 @@ wst_status_t launch_cfg(const RowsLaunch &L, const RowsArgs &args, const CUtenso
   WST_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
     WST_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  C::SMEM_BYTES));
+                                  C::smem_bytes(C::NSTAGE)));
     configured_dev = dev;
   }
-  cudaError_t e = launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM_BYTES, kmap, vmap, args);
+  /* the ring depth in use sizes the block's shared memory: at half the ring two blocks
+   * (of consecutive launches) share an SM */
+  RowsArgs sized = args;
+  if (sized.nstage < C::MIN_STAGES) sized.nstage = C::MIN_STAGES;
+  if (sized.nstage > C::NSTAGE) sized.nstage = C::NSTAGE;
+  if (sized.early_depth > sized.nstage) sized.early_depth = sized.nstage;
+  cudaError_t e = launch_pdl(kern, grid, dim3(C::THREADS), C::smem_bytes(sized.nstage), kmap, vmap,
+                             sized);
   if (e != cudaSuccess)
     return fail(WST_ERR_CUDA, "%s (launch): %s (%s)", L.name, cudaGetErrorString(e),
                 cudaGetErrorName(e));
@@ -1115,54 +1033,6 @@ long long rows_scratch_floats(int n_units_times_rows, int splits, int hd) {
   return static_cast<long long>(n_units_times_rows) * splits * (hd + 4);
 }
 
-/* Arrival counters of the fused slice merge.  They live in the library's device
- * image (zero when the module loads) and every launch leaves its counters at zero
- * again.  Launches that may overlap on the GPU must not share counters; two such
- * launches necessarily have different scratch buffers, so a slot of counters is
- * bound to each scratch address the first time it is seen (per device).  When the
- * slots run out the launch falls back to the separate merge kernel. */
-constexpr int kTicketUnits = 64;
-constexpr int kTicketSlots = 1024;
-static __device__ unsigned int g_tickets[kTicketSlots * kTicketUnits];
-
-unsigned int *ticket_slot(const void *scratch) {
-  struct PerDevice {
-    unsigned int *base = nullptr;
-    std::unordered_map<const void *, int> slots;
-  };
-  static PerDevice devs[64];
-  static std::mutex mu;
-  static thread_local const void *last_key = nullptr;
-  static thread_local int last_dev = -1;
-  static thread_local unsigned int *last_ptr = nullptr;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (last_key == scratch && last_dev == dev) return last_ptr;
-  std::lock_guard<std::mutex> lock(mu);
-  PerDevice &d = devs[dev];
-  if (!d.base) {
-    void *p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_tickets) != cudaSuccess) {
-      cudaGetLastError();
-      return nullptr;
-    }
-    d.base = static_cast<unsigned int *>(p);
-  }
-  auto it = d.slots.find(scratch);
-  int slot;
-  if (it != d.slots.end()) {
-    slot = it->second;
-  } else {
-    if (static_cast<int>(d.slots.size()) >= kTicketSlots) return nullptr;
-    slot = static_cast<int>(d.slots.size());
-    d.slots.emplace(scratch, slot);
-  }
-  last_key = scratch;
-  last_dev = dev;
-  last_ptr = d.base + static_cast<size_t>(slot) * kTicketUnits;
-  return last_ptr;
-}
-
 RowsTuning &rows_tuning() {
   static RowsTuning t;
   return t;
@@ -1172,8 +1042,10 @@ static std::atomic<int> g_decode_overlap{1};
 bool decode_overlap_allowed() { return g_decode_overlap.load() != 0; }
 void set_decode_overlap(bool on) { g_decode_overlap.store(on ? 1 : 0); }
 
-/* tiles a decode launch requests at once ahead of its grid dependency */
-constexpr int kDefaultEarlyDepth = 1;
+/* tiles a decode launch requests at once ahead of its grid dependency, and the ring
+ * depth of a decode launch at head_dim 128 (twice as many half-size stages at 64) */
+constexpr int kDefaultEarlyDepth = 2;
+constexpr int kDecodeStages = 6;
 
 wst_status_t launch_rows(const RowsLaunch &L) {
   DeviceFacts facts;
@@ -1204,18 +1076,10 @@ wst_status_t launch_rows(const RowsLaunch &L) {
          (!L.scratch || rows_scratch_floats(n_units * rows_cap, splits, L.hd) > L.scratch_floats))
     --splits;
 
-  /* Fused merge: the unit's partial rows (plus the weights) must fit the idle ring,
-   * and the launch needs a slot of arrival counters. */
+  /* The cross-GPU exchange rides in the merge kernel (one block per query head). */
   const bool exchange = L.world > 1;
-  const long long unit_bytes = static_cast<long long>(splits) * rows_cap * (L.hd + 4) * 4;
-  bool fused = (splits > 1 || exchange) && L.scratch && aligned16(L.scratch) &&
-               rows_scratch_floats(n_units * rows_cap, splits, L.hd) <= L.scratch_floats &&
-               n_units <= kTicketUnits &&
-               unit_bytes + static_cast<long long>(rows) * (kRowsMaxSplits + 2) * 4 <= kRowsRingBytes &&
-               (exchange || tune.fused_merge != 0);
-  unsigned int *tickets = fused ? ticket_slot(L.scratch) : nullptr;
-  if (!tickets) fused = false;
-  if (exchange && !(fused && decode_shape && L.mailboxes && L.xstate))
+  if (exchange && !(decode_shape && L.mailboxes && L.xstate && L.scratch && aligned16(L.scratch) &&
+                    rows_scratch_floats(n_units * rows_cap, splits, L.hd) <= L.scratch_floats))
     return fail(WST_ERR_SHAPE,
                 "%s: the in-kernel exchange takes one token of one contiguous sequence with a "
                 "split scratch (head_dim 64 or 128)", L.name);
@@ -1247,14 +1111,11 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   a.n_rowblk = n_rowblk;
   a.tpb = tpb;
   a.rows_cap = rows_cap;
-  a.tickets = tickets;
-  a.mailboxes = static_cast<uint2 *const *>(L.mailboxes);
-  a.xstate = static_cast<unsigned int *>(L.xstate);
-  a.rank = L.rank;
-  a.world = exchange ? L.world : 1;
+  a.via_scratch = exchange ? 1 : 0;
   const int max_stages = kRowsRingBytes / (L.hd == 128 ? 32768 : 16384);
   a.nstage = max_stages;
-  if (tune.ring_stages >= 2 && tune.ring_stages < max_stages) a.nstage = tune.ring_stages;
+  if (decode_shape) a.nstage = L.hd == 128 ? kDecodeStages : 2 * kDecodeStages;
+  if (tune.ring_stages >= 2 && tune.ring_stages <= max_stages) a.nstage = tune.ring_stages;
   /* requests ahead of the grid dependency: decode only (the launch ahead writes at
    * most the newest row), one row group (the patch of that row is a warp's job) */
   a.early_depth = 0;
@@ -1291,7 +1152,7 @@ wst_status_t launch_rows(const RowsLaunch &L) {
     st = L.paged ? launch_shape<64, true>(L, a, kmap, vmap, grid, rows)
                  : launch_shape<64, false>(L, a, kmap, vmap, grid, rows);
   }
-  if (st != WST_OK || splits == 1 || fused) return st;
+  if (st != WST_OK || (splits == 1 && !exchange)) return st;
 
   SplitMerge m;
   m.scratch = L.scratch;
@@ -1308,6 +1169,10 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   m.rows_cap = rows_cap;
   m.n_units = n_units;
   m.partial_out = L.partial_out;
+  m.mailboxes = L.mailboxes;
+  m.xstate = L.xstate;
+  m.rank = L.rank;
+  m.world = exchange ? L.world : 1;
   m.name = L.name;
   return launch_split_merge(m);
 }
@@ -1327,6 +1192,12 @@ wst_status_t launch_split_merge(const SplitMerge &S) {
   m.tpb = S.tpb;
   m.rows_cap = S.rows_cap;
   m.partial_out = S.partial_out ? 1 : 0;
+  m.mailboxes = static_cast<uint2 *const *>(S.mailboxes);
+  m.xstate = static_cast<unsigned int *>(S.xstate);
+  m.rank = S.rank;
+  m.world = S.world;
+  m.err_word = device_error_word();
+  if (!m.err_word) return WST_ERR_CUDA;
   const dim3 mgrid(static_cast<unsigned>(S.rows_cap), static_cast<unsigned>(S.n_units));
   cudaError_t e = S.hd == 128 ? launch_pdl(attn_merge_kernel<128>, mgrid, dim3(128), 0, m)
                               : launch_pdl(attn_merge_kernel<64>, mgrid, dim3(128), 0, m);

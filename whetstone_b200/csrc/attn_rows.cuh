@@ -16,7 +16,6 @@ constexpr int kRowsRingBytes = 196608; /* shared memory of the K/V ring: 6 stage
 struct RowsTuning {
   int decode_splits = 0;  /* slices of a decode launch (0: one per SM and KV head) */
   int early_depth = -1;   /* tiles requested at once ahead of the grid dependency */
-  int fused_merge = -1;   /* 1: the last slice to arrive merges; 0: separate merge kernel */
   int ring_stages = 0;    /* ring depth in use (0: all the shared memory holds) */
 };
 RowsTuning &rows_tuning();
@@ -65,7 +64,7 @@ struct RowsLaunch {
   bool partial_out = false;
   /* KV sequence sharded over `world` GPUs: the per-head triples are exchanged through
    * the ranks' mailboxes inside the kernel and `out` is the merged fp16 result
-   * (needs the fused merge: one token, one sequence, scratch given) */
+   * (one token, one sequence, scratch given) */
   const void *mailboxes = nullptr; /* device array of `world` mailbox addresses */
   void *xstate = nullptr;          /* this rank's per-head call counters */
   int rank = 0, world = 1;
@@ -93,6 +92,10 @@ struct SplitMerge {
   int n_q = 0, n_kv = 0, hd = 0;
   int n_splits = 1, n_rowblk = 1, tpb = 1, rows_cap = 1, n_units = 1;
   bool partial_out = false;
+  /* cross-GPU exchange inside the merge (world > 1; one token, one sequence) */
+  const void *mailboxes = nullptr;
+  void *xstate = nullptr;
+  int rank = 0, world = 1;
   const char *name = "attention";
 };
 wst_status_t launch_split_merge(const SplitMerge &m);
