@@ -555,22 +555,26 @@ def bench_also(torch, args):
         s5 = wl.QWEN25_7B
         lengths = wl.c5_lengths()
         drafts = wl.C5["drafts"]
-        table_np, n_pages = wl.c5_page_table(lengths, drafts)
         nseq5 = len(lengths)
         total = nseq5 * drafts
         max_len = int(lengths.max()) + drafts
-        lay5 = args.c5_layers
+        # pages and launch arrays come from the host-side page manager (C++,
+        # whetstone_b200/host/paged_kv.hpp): sequences grown in interleaved turns, then one
+        # verify step of `drafts` rows per sequence, longest context first
+        n_pages = int(sum(-(-(int(n) + drafts) // 16) for n in lengths))
+        mgr = paged.PagedKvManager(n_pages, max_len)
+        ids = wl.c5_fill_manager(mgr, lengths)
+        step5 = mgr.build_step(mgr.schedule([(i, drafts) for i in ids], 10 ** 6, nseq5))
+        table_np = step5.page_table
         pcs = []
         for _ in range(lay5):
             pc = paged.PagedKvCache(n_pages, s5.n_kv, s5.head_dim, nseq5, table_np.shape[1])
             pc.k.copy_(randn16(pc.k.shape))
             pc.v.copy_(randn16(pc.v.shape))
-            pc.page_table.copy_(torch.from_numpy(table_np).cuda())
+            pos0, cu = step5.upload(pc)
             pcs.append(pc)
         qkv5 = [randn16((total, s5.qkv_width)).float() for _ in range(lay5)]
         out5 = torch.zeros(total * s5.n_q * s5.head_dim, dtype=torch.float16, device="cuda")
-        pos0 = torch.from_numpy(lengths).cuda()
-        cu = torch.arange(nseq5 + 1, dtype=torch.int32, device="cuda") * drafts
         scratch = torch.zeros(paged.verify_scratch_floats(nseq5, drafts, s5.n_q, s5.n_kv,
                                                           s5.head_dim, max_len),
                               dtype=torch.float32, device="cuda")

@@ -247,6 +247,64 @@ WST_API wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_pool, 
 WST_API int64_t wst_attn_verify_scratch_floats(int32_t n_seq, int32_t max_tokens_per_seq, int32_t n_q,
                                        int32_t n_kv, int32_t head_dim, int32_t max_len);
 
+/* ----------------------------- host side: paged KV-cache manager and scheduler */
+
+/* Bookkeeping for many sequences over one pool of 16-token pages: which pages a
+ * sequence owns, how many rows of them are committed context, and the host arrays
+ * (page_table, seq_pos0, cu_tokens) that wst_rope_cache_paged and
+ * wst_attn_verify_paged take.  It stands where the engine has one contiguous cache
+ * and one cursor (crates/whetstone-kernels/src/decode.rs:162-212,
+ * crates/whetstone-core/src/engine.rs:264-286, 865-880) and follows the engine's
+ * speculative loop (crates/whetstone-core/src/speculate.rs:185-256): reserve rows,
+ * launch append + attention, commit what was accepted, rewind over what was not --
+ * rejected rows are not erased, the next append writes over them.  The C++ classes
+ * are in whetstone_b200/host/paged_kv.hpp; these are their C bindings.  Host work
+ * only: no call here touches a GPU; a manager is used from one thread at a time.
+ *
+ *   wst_pkv_create      pool of n_pool_pages pages, no sequence longer than max_len
+ *   wst_pkv_open/close  a new empty sequence (ids are reused) / all its pages back
+ *   wst_pkv_query       length and page count of `seq` (seq < 0: skip) and the
+ *                       pool's free pages; any out pointer may be NULL
+ *   wst_pkv_reserve     room for n_tokens more rows; WST_ERR_OOM and no change if the
+ *                       pool is short, WST_ERR_SHAPE past max_len
+ *   wst_pkv_commit      n_tokens reserved rows now count as context
+ *   wst_pkv_rewind      context length back to pos (<= length); pages stay mapped
+ *   wst_pkv_trim        pages beyond length + keep_tokens go back to the pool
+ *   wst_pkv_schedule    from n_waiting (seq, n_tokens) requests picks this step's
+ *                       batch, longest context first, within max_tokens_per_step,
+ *                       max_sequences_per_step and the pool's free pages; writes the
+ *                       chosen requests' indices in launch order
+ *   wst_pkv_build_step  reserves every entry's rows (all or none: WST_ERR_OOM leaves
+ *                       the manager unchanged) and fills the HOST arrays
+ *                       page_table [n_seq][max_pages], seq_pos0 [n_seq],
+ *                       cu_tokens [n_seq + 1]; totals_out4 = total_tokens,
+ *                       max_tokens_per_seq, max_len, max_pages
+ *   wst_pkv_assign_units  deals the n_seq * n_kv (batch slot, KV head) units to
+ *                       `world` GPUs, heaviest first to the least loaded rank;
+ *                       rank_of_unit_out[slot * n_kv + kv_head] */
+WST_API wst_status_t wst_pkv_create(int32_t n_pool_pages, int32_t max_len, void **out_mgr);
+WST_API wst_status_t wst_pkv_destroy(void *mgr);
+WST_API wst_status_t wst_pkv_open(void *mgr, int32_t *out_seq);
+WST_API wst_status_t wst_pkv_close(void *mgr, int32_t seq);
+WST_API wst_status_t wst_pkv_query(void *mgr, int32_t seq, int32_t *out_length,
+                                   int32_t *out_pages, int32_t *out_free_pages);
+WST_API wst_status_t wst_pkv_reserve(void *mgr, int32_t seq, int32_t n_tokens);
+WST_API wst_status_t wst_pkv_commit(void *mgr, int32_t seq, int32_t n_tokens);
+WST_API wst_status_t wst_pkv_rewind(void *mgr, int32_t seq, int32_t pos);
+WST_API wst_status_t wst_pkv_trim(void *mgr, int32_t seq, int32_t keep_tokens,
+                                  int32_t *out_returned);
+WST_API wst_status_t wst_pkv_schedule(void *mgr, const int32_t *seqs, const int32_t *n_tokens,
+                                      int32_t n_waiting, int32_t max_tokens_per_step,
+                                      int32_t max_sequences_per_step, int32_t *chosen_out,
+                                      int32_t *n_chosen_out);
+WST_API wst_status_t wst_pkv_build_step(void *mgr, const int32_t *seqs, const int32_t *n_tokens,
+                                        int32_t n_seq, int32_t *page_table_host,
+                                        int32_t *seq_pos0_host, int32_t *cu_tokens_host,
+                                        int32_t *totals_out4);
+WST_API wst_status_t wst_pkv_assign_units(const int32_t *seq_pos0_host,
+                                          const int32_t *cu_tokens_host, int32_t n_seq,
+                                          int32_t n_kv, int32_t world, int32_t *rank_of_unit_out);
+
 #ifdef __cplusplus
 }
 #endif

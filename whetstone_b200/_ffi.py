@@ -121,6 +121,20 @@ SIGNATURES: dict[str, tuple] = {
     "wst_rope_cache_paged": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, F]),
     "wst_attn_verify_paged": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F]),
     "wst_attn_verify_scratch_floats": (c_int64, [I, I, I, I, I, I]),
+    # host-side paged KV-cache manager and scheduler (no GPU work)
+    "wst_pkv_create": (I, [I, I, ctypes.POINTER(c_void_p)]),
+    "wst_pkv_destroy": (I, [P]),
+    "wst_pkv_open": (I, [P, ctypes.POINTER(c_int32)]),
+    "wst_pkv_close": (I, [P, I]),
+    "wst_pkv_query": (I, [P, I, ctypes.POINTER(c_int32), ctypes.POINTER(c_int32),
+                          ctypes.POINTER(c_int32)]),
+    "wst_pkv_reserve": (I, [P, I, I]),
+    "wst_pkv_commit": (I, [P, I, I]),
+    "wst_pkv_rewind": (I, [P, I, I]),
+    "wst_pkv_trim": (I, [P, I, I, ctypes.POINTER(c_int32)]),
+    "wst_pkv_schedule": (I, [P, P, P, I, I, I, P, ctypes.POINTER(c_int32)]),
+    "wst_pkv_build_step": (I, [P, P, P, I, P, P, P, P]),
+    "wst_pkv_assign_units": (I, [P, P, I, I, I, P]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -1064,10 +1064,19 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   const bool decode_shape = !L.paged && !L.cu_tokens && L.n_tok == 1 && L.n_seq == 1;
 
   int splits = L.want_splits > 0 ? L.want_splits : rows_pick_splits(n_units, L.max_len, facts.sm_count);
-  if (decode_shape && L.want_splits <= 0 && tune.decode_splits > 0) {
-    splits = tune.decode_splits;
+  if (decode_shape && L.want_splits <= 0) {
+    /* Decode leaves an eighth of the SMs without a slice.  The slices are a static,
+     * equal partition, so one launch is as slow as its slowest SM; and the free SMs take
+     * the merge kernel's blocks and the first blocks of the NEXT launch, which fill
+     * their rings and wait, so consecutive launches overlap like a software pipeline.
+     * Measured at 28/4/128: 13.1 us per layer at context 32768 with 32 slices per KV
+     * head against 14.2 with 37 (all 148 SMs), 33.4 against 40.6 at context 100000. */
+    int cap = facts.sm_count * 7 / 8 / (n_units > 0 ? n_units : 1);
+    if (cap < 1) cap = 1;
+    if (tune.decode_splits > 0) cap = tune.decode_splits;
     const int tiles = (L.max_len + kRowsTile - 1) / kRowsTile;
-    if (splits > tiles) splits = tiles;
+    if (cap > tiles) cap = tiles;
+    if (splits > cap || tune.decode_splits > 0) splits = cap;
   }
   if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
   /* the slices must fit the caller's scratch */

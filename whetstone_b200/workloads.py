@@ -137,6 +137,25 @@ def c5_page_table(lengths: np.ndarray, drafts: int, page: int = 16, seed: int | 
     return table, total
 
 
+def c5_fill_manager(manager, lengths: np.ndarray, seed: int | None = None):
+    """Brings one sequence per entry of `lengths` up to its length in a page manager
+    (whetstone_b200.paged.PagedKvManager), growing the sequences in seeded random turns
+    of one to four pages so that their pages interleave in the pool (no sequence is
+    contiguous).  Returns the sequence ids in the order of `lengths`."""
+    rng = np.random.default_rng((C5["seed"] if seed is None else seed) + 2)
+    ids = [manager.open() for _ in lengths]
+    left = [int(n) for n in lengths]
+    while any(left):
+        i = int(rng.integers(0, len(left)))
+        if not left[i]:
+            continue
+        n = min(left[i], 16 * int(rng.integers(1, 5)))
+        manager.reserve(ids[i], n)
+        manager.commit(ids[i], n)
+        left[i] -= n
+    return ids
+
+
 def prefill_flops(n_q: int, head_dim: int, pos0: int, n: int) -> int:
     """Causal-exact FLOPs of one chunk: 4 * head_dim * n_q * sum_j (pos0 + j + 1)."""
     pairs = n * pos0 + n * (n + 1) // 2
