@@ -1,7 +1,8 @@
 """Worker of tests/test_multi_gpu.py: one process per GPU (torchrun).  Long-context
 decode with the KV sequence sharded over the ranks, merged (a) by an NCCL all-gather
-and the local merge kernel and (b) through peer memory inside
-wst_attn_exchange_merge; both are compared with the numpy oracle on every rank."""
+and the local merge kernel, (b) through peer memory inside wst_attn_exchange_merge and
+(c) through peer memory inside the slice-merge kernel of wst_attn_decode_sharded; all
+are compared with the numpy oracle on every rank."""
 
 import os
 import sys
@@ -30,13 +31,14 @@ def main():
     lo, hi = sharded.sequence_shard(ctx, world, rank)
     length = torch.tensor([hi - lo], dtype=torch.int32, device="cuda")
     xch = sharded.PeerExchange(n_q, hd)
-    lay_nccl, lay_p2p, qd = [], [], []
+    lay_nccl, lay_p2p, lay_one, qd = [], [], [], []
     for l in range(layers):
         cache = decode.KvCache(n_kv, n_q, hd, max(hi - lo, 1))
         cache.k.copy_(torch.from_numpy(ks[l][:, lo:hi].copy()).cuda())
         cache.v.copy_(torch.from_numpy(vs[l][:, lo:hi].copy()).cuda())
         lay_nccl.append(sharded.ShardedDecodeLayer(cache, length, n_q))
         lay_p2p.append(sharded.ShardedDecodeLayer(cache, length, n_q, exchange=xch))
+        lay_one.append(sharded.ShardedDecodeLayer(cache, length, n_q, exchange=xch, fused=True))
         qd.append(torch.from_numpy(qs[l]).cuda())
     want = []
     for l in range(layers):
@@ -63,13 +65,21 @@ def main():
         for l in range(layers):
             lay_p2p[l].attend(qd[l], outs[l])
         check(outs, "peer exchange")
+    # the exchange inside the slice-merge kernel, mixed with the two-kernel form on the
+    # same mailboxes (every rank makes the same sequence of calls)
+    for rnd in range(4):
+        for o in outs:
+            o.zero_()
+        for l in range(layers):
+            (lay_one if (rnd + l) % 3 else lay_p2p)[l].attend(qd[l], outs[l])
+        check(outs, "exchange in the merge kernel")
     # ... and as a CUDA graph replayed several times
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=side):
         for l in range(layers):
-            lay_p2p[l].attend(qd[l], outs[l])
+            (lay_one if l % 2 else lay_p2p)[l].attend(qd[l], outs[l])
     for _ in range(4):
         for o in outs:
             o.zero_()

@@ -148,7 +148,7 @@ class PagedKvManager:
         self.max_pages = (max_len + PAGE_SIZE - 1) // PAGE_SIZE
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:   # lib is gone at interpreter exit
             lib.wst_pkv_destroy(self._h)
             self._h = None
 
