@@ -558,6 +558,7 @@ def bench_also(torch, args):
         nseq5 = len(lengths)
         total = nseq5 * drafts
         max_len = int(lengths.max()) + drafts
+        lay5 = args.c5_layers
         # pages and launch arrays come from the host-side page manager (C++,
         # whetstone_b200/host/paged_kv.hpp): sequences grown in interleaved turns, then one
         # verify step of `drafts` rows per sequence, longest context first

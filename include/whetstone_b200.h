@@ -38,7 +38,9 @@ WST_API wst_status_t wst_b200_device_error(uint32_t *out_code);
  *   0 = automatic (default)
  *   1 = force the portable CUDA-core kernel
  *   2 = wst_attn_chunk: force the split-KV mma.sync kernel
- *   3 = wst_attn_chunk: force the tcgen05 prefill kernel (one query tile per CTA)
+ *   3 = wst_attn_chunk: force the tcgen05 prefill kernel (one query tile per CTA);
+ *       wst_attn_verify_paged: one CTA per slice of the KV range instead of one
+ *       persistent CTA per SM
  *   4 = wst_attn_chunk: force the tcgen05 prefill kernel with two query tiles per CTA
  * A debugging aid for A/B checks; process-wide. */
 WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
@@ -48,7 +50,8 @@ WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
  *   key 1  slices of the KV sequence per KV head (default: SMs / KV heads)
  *   key 2  cache tiles requested at once before the launch ahead has finished
  *   key 4  stages of the shared-memory ring in use (head_dim 128: 2..6; at 3 or
- *          fewer, two blocks of consecutive launches share an SM) */
+ *          fewer, two blocks of consecutive launches share an SM)
+ *   key 5  persistent CTAs of wst_attn_verify_paged (default: one per SM) */
 WST_API wst_status_t wst_b200_set_tuning(int32_t key, int32_t value);
 
 /* 0: wst_attn_decode waits for everything ahead of it in the stream before it asks

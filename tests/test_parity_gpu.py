@@ -401,10 +401,11 @@ def build_paged_case(rng, shape, lengths, drafts, theta=1e6, with_nan=True):
     return cache, table_np, k_ctx, v_ctx
 
 
-@pytest.fixture(params=[0, 2], ids=["auto", "rows"])
+@pytest.fixture(params=[0, 2, 3], ids=["auto", "rows", "slices"])
 def verify_kernel_choice(request):
-    """0: the tcgen05 kernel over slices of the KV range when every query row of a
-    (sequence, KV head) fits one 128-row tile; 2: the mma.sync row-block kernel."""
+    """0: when every query row of a (sequence, KV head) fits one 128-row tile, the
+    persistent tcgen05 kernel over equal spans of all units' KV tiles; 3: the same tile
+    pipeline with one CTA per slice of the KV range; 2: the mma.sync row-block kernel."""
     check(lib.wst_b200_set_kernel_choice(request.param))
     yield request.param
     check(lib.wst_b200_set_kernel_choice(0))

@@ -301,6 +301,7 @@ extern "C" wst_status_t wst_b200_set_tuning(int32_t key, int32_t value) {
     case 1: t.decode_splits = value; break;
     case 2: t.early_depth = value; break;
     case 4: t.ring_stages = value; break;
+    case 5: t.verify_ctas = value; break;
     default: return fail(WST_ERR_INVALID_ARG, "wst_b200_set_tuning: unknown key %d", key);
   }
   return WST_OK;
@@ -659,8 +660,7 @@ extern "C" wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_poo
                 "KV head and 16-byte aligned buffers");
   if (g_kernel_choice.load() != 2 &&
       prefill_split_supports(n_q, n_kv, head_dim, max_tokens_per_seq)) {
-    /* all query rows of a (sequence, KV head) unit fit one 128-row tcgen05 tile:
-     * one CTA per (slice of ~2048 positions, KV head, sequence) */
+    /* all query rows of a (sequence, KV head) unit fit one 128-row tcgen05 tile */
     DeviceFacts facts;
     if (!device_facts(&facts)) return WST_ERR_CUDA;
     PrefillLaunch P;
@@ -683,16 +683,21 @@ extern "C" wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_poo
     P.scratch = static_cast<float *>(scratch);
     P.scratch_floats =
         wst_attn_verify_scratch_floats(n_seq, max_tokens_per_seq, n_q, n_kv, head_dim, max_len);
-    /* slices of about 2048 positions (contiguous runs of 16 tiles): sequences get as
-     * many working CTAs as their length asks for; more, shorter slices only when the
-     * batch is too small to fill the GPU otherwise */
+    P.max_len = max_len;
+    if (g_kernel_choice.load() != 3) {
+      /* one persistent CTA per SM over equal spans of all units' KV tiles */
+      P.span_ctas = rows_tuning().verify_ctas;
+      return launch_verify_span(P);
+    }
+    /* kernel choice 3: one CTA per slice of about 2048 positions (contiguous runs of 16
+     * tiles), the older schedule: sequences get as many working CTAs as their length
+     * asks for; more, shorter slices only when the batch is too small to fill the GPU */
     int splits = facts.sm_count / (n_seq * n_kv);
     const int by_len = (max_len + 2047) / 2048;
     if (splits < by_len) splits = by_len;
     const int tiles = (max_len + 127) / 128;
     if (splits > tiles) splits = tiles;
     if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
-    P.max_len = max_len;
     P.n_splits = splits < 1 ? 1 : splits;
     return launch_prefill(P);
   }

@@ -57,11 +57,11 @@ struct PCfg {
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + NSTAGE * KV_BYTES;
   static constexpr int OFF_BAR = OFF_V + NSTAGE * KV_BYTES;
-  static constexpr int NBAR = 4 * NSTAGE + 2 + 2 + 1 + 1 + 1;
+  static constexpr int NBAR = 4 * NSTAGE + 2 + 2 + 1 + 1 + 1 + 1;
   /* after the barriers and the tensor-memory slot: three [2][128] float areas through
    * which the two threads of a query row exchange their partial maxima and sums */
   static constexpr int OFF_XCH = OFF_BAR + 256;
-  static constexpr int SMEM_BYTES = OFF_XCH + 3 * 2 * 128 * 4 + 1024;
+  static constexpr int SMEM_BYTES = OFF_XCH + 3 * 2 * 128 * 4 + 64 + 1024; /* + 64: a span's start */
   static constexpr int THREADS = 320; /* 8 softmax warps, the MMA warp, the TMA warp */
   static_assert(NBAR * 8 + 16 <= 256, "barrier area");
   /* tensor-memory columns */
@@ -946,10 +946,563 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
   }
 }
 
+/* ------------------------------------------------------------------------
+ * Ragged paged verify as ONE persistent wave: attn_verify_span_kernel.
+ *
+ * The (sequence, KV head) units of a ragged batch differ in length by an order of
+ * magnitude, and every unit has a single 128-row query tile (a few draft tokens x the
+ * heads of the GQA group).  With one CTA per (unit, slice) each CTA pays a prologue
+ * (length, page table, first K tile from DRAM, first two score tiles) and an epilogue
+ * that nothing else on its SM overlaps, and the last wave is ragged.  Here the KV
+ * tiles of ALL units are laid end to end (unit-major) and cut into gridDim.x equal
+ * spans; a CTA walks its span, which may cross unit boundaries -- each stretch inside
+ * one unit is a "piece" and produces one partial row set (a slice of that unit).  The
+ * TMA producer runs ahead across pieces, so the next piece's page ids and first tiles
+ * arrive while the current piece is still in its softmax and epilogue; the MMA and
+ * softmax warps carry their barrier phases on a tile counter that never restarts.
+ * Every CTA streams the same number of tiles (+-1), whatever the lengths are.
+ *
+ * Same tile pipeline as attn_prefill_kernel (Q and P in tensor memory, two score
+ * buffers, two softmax threads per row, lazy rescale); the slices of a unit are
+ * merged by attn_merge_kernel, which reads each unit's slice count from the tail of
+ * the scratch buffer.
+ * ---------------------------------------------------------------------- */
+struct SpanArgs {
+  const float *q;
+  long long q_tok_stride;
+  float *scratch;            /* [unit][max_slices][rows_cap][hd+4], then int32 counts[n_units] */
+  int *slice_counts;
+  const int32_t *pos0_dev;   /* [n_seq] */
+  const int32_t *cu_tokens;  /* [n_seq + 1] */
+  const int32_t *page_table; /* [n_seq][max_pages] */
+  int max_pages, n_pool_pages;
+  int n_seq, n_q, n_kv, gqa, max_seq;
+  int max_slices, rows_cap;
+  int min_span; /* tiles: no unit may be cut into more than max_slices pieces */
+  float qscale;
+  unsigned int *err_word;
+};
+
+/* One stretch of a CTA's span inside one unit. */
+struct SpanPiece {
+  int seq, kvh, first, n, slice, count; /* count > 0 only on the unit's first piece */
+  int pos0, tok_begin, ntok, kv_end;
+};
+
+/* Walks the pieces of a span; every role of the CTA runs its own copy. */
+struct SpanWalk {
+  int seq, kvh, tile; /* where the next piece starts */
+  long long g, hi;    /* global tile index of that point, end of the span */
+  long long before;   /* tiles of all units of earlier sequences */
+  int span, cta;
+  const SpanArgs *a;
+
+  __device__ __forceinline__ static int seq_tiles(const SpanArgs &a, int s, int *pos0, int *tok_begin,
+                                                  int *ntok, int *kv_end) {
+    const int b = a.cu_tokens[s];
+    const int n = a.cu_tokens[s + 1] - b;
+    const int p0 = max(a.pos0_dev[s], 0);
+    const int end = n > 0 ? min(p0 + n, a.max_seq) : 0;
+    *pos0 = p0;
+    *tok_begin = b;
+    *ntok = n;
+    *kv_end = end;
+    return (end + 127) / 128;
+  }
+
+  __device__ __forceinline__ bool next(SpanPiece *p) {
+    while (g < hi && seq < a->n_seq) {
+      const int t = seq_tiles(*a, seq, &p->pos0, &p->tok_begin, &p->ntok, &p->kv_end);
+      if (t == 0) { /* a sequence without tokens in this step */
+        ++seq;
+        continue;
+      }
+      const long long left = hi - g;
+      const int n = static_cast<int>(min(static_cast<long long>(t - tile), left));
+      const long long unit_start = before + static_cast<long long>(kvh) * t;
+      p->seq = seq;
+      p->kvh = kvh;
+      p->first = tile;
+      p->n = n;
+      p->slice = cta - static_cast<int>(unit_start / span);
+      p->count = tile == 0 ? static_cast<int>((unit_start + t - 1) / span - unit_start / span) + 1 : 0;
+      g += n;
+      tile += n;
+      if (tile == t) {
+        tile = 0;
+        if (++kvh == a->n_kv) {
+          kvh = 0;
+          before += static_cast<long long>(a->n_kv) * t;
+          ++seq;
+        }
+      }
+      return true;
+    }
+    return false;
+  }
+};
+
+template <int HD>
+__global__ void __launch_bounds__(PCfg<HD>::THREADS, 1)
+attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
+                        const __grid_constant__ CUtensorMap vmap,
+                        const __grid_constant__ SpanArgs a) {
+  using C = PCfg<HD>;
+  constexpr int BN = C::BN, NH = C::NH, NSTAGE = C::NSTAGE;
+  constexpr int HALF_BYTES = C::HALF_BYTES, KV_BYTES = C::KV_BYTES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  auto bar = [bar0](int i) { return bar0 + 8u * i; };
+  constexpr int K_FULL = 0, V_FULL = NSTAGE, K_EMPTY = 2 * NSTAGE, V_EMPTY = 3 * NSTAGE;
+  constexpr int S_FULL = 4 * NSTAGE, S_FREE = S_FULL + 2, P_READY = S_FREE + 2;
+  constexpr int PV_DONE = P_READY + 1, Q_READY = PV_DONE + 1, EPI_DONE = Q_READY + 1;
+  static_assert(EPI_DONE < C::NBAR, "barrier area");
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + C::OFF_BAR + C::NBAR * 8);
+  /* where this CTA's span starts, written by warp 0: seq, kvh, tile, span, g(lo,hi) lo hi, before */
+  long long *walk0 = reinterpret_cast<long long *>(smem + C::OFF_XCH + 3 * 2 * 128 * 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSTAGE; ++i) {
+      mbar_init(bar(K_FULL + i), 1);
+      mbar_init(bar(V_FULL + i), 1);
+      mbar_init(bar(K_EMPTY + i), 1);
+      mbar_init(bar(V_EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(S_FREE + i), 256);
+    }
+    mbar_init(bar(P_READY), 256);
+    mbar_init(bar(PV_DONE), 1);
+    mbar_init(bar(Q_READY), 256);
+    mbar_init(bar(EPI_DONE), 256);
+    mbar_init_fence();
+    tma_prefetch_desc(&kmap);
+    tma_prefetch_desc(&vmap);
+  }
+  constexpr int MMA_WARP = 8, TMA_WARP = 9;
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  grid_launch_dependents();
+  grid_dependency_wait();
+
+  /* ---- where does this CTA's span start?  warp 0: total tiles, span length, and the
+   * (sequence, KV head, tile) at global tile index cta * span */
+  if (warp == 0) {
+    int pos0, tb, nt, ke;
+    long long total = 0;
+    for (int s0 = 0; s0 < a.n_seq; s0 += 32) {
+      const int s = s0 + lane;
+      long long t = s < a.n_seq ? SpanWalk::seq_tiles(a, s, &pos0, &tb, &nt, &ke) : 0;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+      total += t;
+    }
+    total *= a.n_kv;
+    long long span = (total + gridDim.x - 1) / gridDim.x;
+    if (span < a.min_span) span = a.min_span;
+    const long long lo = static_cast<long long>(blockIdx.x) * span;
+    const long long hi = min(lo + span, total);
+    /* the sequence that holds global tile `lo` */
+    long long before = 0;
+    int seq = a.n_seq, kvh = 0, tile = 0;
+    if (lo < total) {
+      for (int s0 = 0; s0 < a.n_seq && seq == a.n_seq; s0 += 32) {
+        const int s = s0 + lane;
+        const long long mine = s < a.n_seq
+                                   ? static_cast<long long>(a.n_kv) * SpanWalk::seq_tiles(a, s, &pos0, &tb, &nt, &ke)
+                                   : 0;
+        long long incl = mine;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const long long up = __shfl_up_sync(0xffffffffu, incl, off);
+          if (lane >= off) incl += up;
+        }
+        const bool here = mine > 0 && before + incl - mine <= lo && lo < before + incl;
+        const unsigned vote = __ballot_sync(0xffffffffu, here);
+        if (vote) {
+          const int src = __ffs(vote) - 1;
+          const long long start = __shfl_sync(0xffffffffu, before + incl - mine, src);
+          const long long t = __shfl_sync(0xffffffffu, mine, src) / a.n_kv;
+          seq = s0 + src;
+          kvh = static_cast<int>((lo - start) / t);
+          tile = static_cast<int>((lo - start) % t);
+          before = start;
+        } else {
+          before += __shfl_sync(0xffffffffu, incl, 31);
+        }
+      }
+    }
+    if (lane == 0) {
+      walk0[0] = seq;
+      walk0[1] = kvh;
+      walk0[2] = tile;
+      walk0[3] = span;
+      walk0[4] = lo;
+      walk0[5] = hi;
+      walk0[6] = before;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  SpanWalk walk;
+  walk.seq = static_cast<int>(walk0[0]);
+  walk.kvh = static_cast<int>(walk0[1]);
+  walk.tile = static_cast<int>(walk0[2]);
+  walk.span = static_cast<int>(walk0[3]);
+  walk.g = walk0[4];
+  walk.hi = walk0[5];
+  walk.before = walk0[6];
+  walk.cta = static_cast<int>(blockIdx.x);
+  walk.a = &a;
+  const int n_total = walk.hi > walk.g ? static_cast<int>(walk.hi - walk.g) : 0; /* tiles of this CTA */
+
+  if (n_total == 0) {
+    /* nothing to do: fall through to the common exit */
+  } else if (warp == TMA_WARP) {
+    /* ------------------------------------------------------ TMA producer */
+    if (lane == 0) {
+      SpanPiece pc;
+      int G = 0;
+      bool ok = true;
+      while (ok && walk.next(&pc)) {
+        for (int j = 0; j < pc.n; ++j, ++G) {
+          const int st = G % NSTAGE, round = G / NSTAGE;
+          if (G >= NSTAGE && !mbar_wait(bar(K_EMPTY + st), (round - 1) & 1, a.err_word, 0x501u)) {
+            ok = false;
+            break;
+          }
+          const int jt = pc.first + j;
+          int pages[BN / 16];
+#pragma unroll
+          for (int pg = 0; pg < BN / 16; ++pg) {
+            const int slot = jt * (BN / 16) + pg;
+            int page = slot < a.max_pages
+                           ? a.page_table[static_cast<long long>(pc.seq) * a.max_pages + slot]
+                           : -1;
+            /* an unmapped slot reads as zeros: coordinate just past the pool */
+            pages[pg] = (page < 0 || page >= a.n_pool_pages) ? a.n_pool_pages : page;
+          }
+          mbar_arrive_expect_tx(bar(K_FULL + st), KV_BYTES);
+#pragma unroll
+          for (int pg = 0; pg < BN / 16; ++pg)
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+              tma_load_4d(sbase + C::OFF_K + st * KV_BYTES + h * HALF_BYTES + pg * 16 * 128, &kmap,
+                          bar(K_FULL + st), h * 64, 0, pc.kvh, pages[pg]);
+          if (G >= NSTAGE && !mbar_wait(bar(V_EMPTY + st), (round - 1) & 1, a.err_word, 0x502u)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(bar(V_FULL + st), KV_BYTES);
+#pragma unroll
+          for (int pg = 0; pg < BN / 16; ++pg)
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+              tma_load_4d(sbase + C::OFF_V + st * KV_BYTES + h * HALF_BYTES + pg * 16 * 128, &vmap,
+                          bar(V_FULL + st), h * 64, 0, pc.kvh, pages[pg]);
+        }
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    /* -------------------------------------------------------- MMA issuer.
+     * Program over the CTA's tiles g = 0 .. n_total-1, whatever piece they belong to:
+     *     S(0) S(1)   then for every g:   PV(g)  S(g+2)
+     * S of a piece's first tile waits for that piece's Q; PV of a piece's first tile
+     * starts a new accumulation and waits until the epilogue of the piece before has
+     * read O. */
+    constexpr uint32_t idesc_qk = umma_idesc(128, BN, 0);
+    constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
+    const uint32_t k_lo0 = umma_desc_lo(sbase + C::OFF_K, 16);
+    const uint32_t v_lo0 = umma_desc_lo(sbase + C::OFF_V, HALF_BYTES);
+    /* two walkers: one for the S stream (two tiles ahead), one for the PV stream */
+    SpanWalk ws = walk, wp = walk;
+    SpanPiece ps, pp;
+    int s_left = 0, s_piece = -1;  /* tiles left in the S stream's current piece */
+    int p_left = 0, p_piece = -1, p_pos = 0;
+    bool ok = true;
+
+    auto issue_s = [&](int g) -> bool {
+      bool first = false;
+      if (s_left == 0) {
+        if (!ws.next(&ps)) return false;
+        s_left = ps.n;
+        ++s_piece;
+        first = true;
+      }
+      --s_left;
+      if (first && !mbar_wait(bar(Q_READY), s_piece & 1, a.err_word, 0x510u)) return false;
+      if (!mbar_wait(bar(K_FULL + g % NSTAGE), (g / NSTAGE) & 1, a.err_word, 0x514u)) return false;
+      if (g >= 2 && !mbar_wait(bar(S_FREE + (g & 1)), ((g >> 1) - 1) & 1, a.err_word, 0x515u))
+        return false;
+      tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (g % NSTAGE) * KV_BYTES + (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_ts_f16_lohi(tmem + C::COL_S + (g & 1) * BN, tmem + C::COL_Q + ks * 8,
+                           k_lo0 + (off >> 4), kDescHi, idesc_qk, ks > 0);
+        }
+        umma_commit(bar(S_FULL + (g & 1)));
+        umma_commit(bar(K_EMPTY + g % NSTAGE));
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_pv = [&](int g) -> bool {
+      if (p_left == 0) {
+        if (!wp.next(&pp)) return false;
+        p_left = pp.n;
+        p_pos = 0;
+        ++p_piece;
+        /* the epilogue of the piece before must have read O */
+        if (p_piece > 0 && !mbar_wait(bar(EPI_DONE), (p_piece - 1) & 1, a.err_word, 0x516u))
+          return false;
+      }
+      const int st = g % NSTAGE;
+      if (!mbar_wait(bar(V_FULL + st), (g / NSTAGE) & 1, a.err_word, 0x512u)) return false;
+      const uint32_t vb = sbase + C::OFF_V + st * KV_BYTES;
+      const int jt = pp.first + p_pos;
+      /* Cache rows past the live data can hold any bit pattern and 0 * NaN is NaN:
+       * clear them in the sequence's last tile before the tensor core reads V. */
+      if (jt * BN + BN > pp.kv_end) {
+        const int first_dead = pp.kv_end - jt * BN;
+        for (int idx = first_dead * (NH * 8) + lane; idx < BN * NH * 8; idx += 32) {
+          const int row = idx / (NH * 8), rest = idx % (NH * 8);
+          asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(
+                           vb + (rest >> 3) * HALF_BYTES + row * 128 + (rest & 7) * 16),
+                       "r"(0u)
+                       : "memory");
+        }
+        fence_async_smem();
+        __syncwarp();
+      }
+      if (!mbar_wait(bar(P_READY), g & 1, a.err_word, 0x511u)) return false;
+      tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint32_t off = st * KV_BYTES + kk * 2048;
+          umma_ts_f16_lohi(tmem + C::COL_O, tmem + C::COL_P + kk * 8, v_lo0 + (off >> 4), kDescHi,
+                           idesc_pv, (p_pos > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(PV_DONE));
+        umma_commit(bar(V_EMPTY + st));
+      }
+      __syncwarp();
+      ++p_pos;
+      --p_left;
+      return true;
+    };
+
+    for (int g = 0; ok && g < 2 && g < n_total; ++g) ok = issue_s(g);
+    for (int g = 0; ok && g < n_total; ++g) {
+      ok = issue_pv(g);
+      if (ok && g + 2 < n_total) ok = issue_s(g + 2);
+    }
+  } else {
+    /* ---- softmax + partial output: two threads per query row, 64 score columns each */
+    constexpr int HB = BN / 2;
+    constexpr int OC = HD / 2;
+    const int wq = warp & 3, half = warp >> 2;
+    const int r = wq * 32 + lane; /* query row == TMEM lane */
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    float *xch = reinterpret_cast<float *>(smem + C::OFF_XCH);
+    auto pair_sync = [wq]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + wq) : "memory"); };
+    auto wait_all = [&](int which, uint32_t parity, unsigned code) {
+      return __all_sync(0xffffffffu, mbar_wait(bar(which), parity, a.err_word, code)) != 0;
+    };
+    /* q half-row of (piece, row r) -> fp16 * scale * log2(e) into this row's TMEM lane */
+    auto stage_q = [&](const SpanPiece &pc) {
+      const int rows_valid = pc.ntok * a.gqa;
+      const bool valid = r < rows_valid;
+      const float *src = a.q + static_cast<long long>(pc.tok_begin + r / a.gqa) * a.q_tok_stride +
+                         static_cast<long long>(pc.kvh * a.gqa + r % a.gqa) * HD + half * OC;
+      constexpr int QC = OC / 2;
+      uint32_t packed[QC];
+#pragma unroll
+      for (int e = 0; e < QC; e += 2) {
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid) f = __ldg(reinterpret_cast<const float4 *>(src + 2 * e));
+        packed[e] = pack_half2(f.x * a.qscale, f.y * a.qscale);
+        packed[e + 1] = pack_half2(f.z * a.qscale, f.w * a.qscale);
+      }
+      if constexpr (QC == 32)
+        tmem_st_32x32(tmem + lane_base + C::COL_Q + half * QC, packed);
+      else
+        tmem_st_32x16(tmem + lane_base + C::COL_Q + half * QC, packed);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(bar(Q_READY));
+    };
+
+    SpanWalk wk = walk;
+    SpanPiece pc, nxt;
+    bool have = wk.next(&pc);
+    if (have) stage_q(pc);
+    int G = 0, piece = 0;
+    bool ok = true; /* warp-uniform */
+    while (have) {
+      const int rows_valid = pc.ntok * a.gqa;
+      const int lim = r < rows_valid ? min(pc.pos0 + r / a.gqa + 1, a.max_seq) : pc.kv_end;
+      const int lim_min = min(pc.pos0 + 1, a.max_seq);
+      const bool live = wq * 32 < rows_valid;
+      float m_ref = -INFINITY, l_run = 0.f;
+
+      for (int j = 0; j < pc.n; ++j, ++G) {
+        const int jt = pc.first + j;
+        if (ok) ok = wait_all(S_FULL + (G & 1), (G >> 1) & 1, 0x520u);
+        if (!live) {
+          if (ok) {
+            mbar_arrive(bar(S_FREE + (G & 1)));
+            if (G >= 1) ok = wait_all(PV_DONE, (G - 1) & 1, 0x524u);
+            if (ok) mbar_arrive(bar(P_READY));
+          }
+          continue;
+        }
+        uint32_t sv[HB];
+        float mxh = -INFINITY;
+        if (ok) {
+          tc_fence_after_sync();
+          const uint32_t s_addr = tmem + lane_base + C::COL_S + (G & 1) * BN + half * HB;
+#pragma unroll
+          for (int c0 = 0; c0 < HB; c0 += 32)
+            tmem_ld_32x32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          mbar_arrive(bar(S_FREE + (G & 1)));
+          if (jt * BN + BN > lim_min) { /* causal edge / end of sequence */
+            const int lim_local = lim - jt * BN - half * HB;
+#pragma unroll
+            for (int c = 0; c < HB; ++c)
+              if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
+          }
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int c = 0; c < HB; c += 8)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
+          mxh = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        }
+        float *slot = xch + (G & 1) * 256;
+        slot[half * 128 + r] = mxh;
+        pair_sync();
+        const float mx = fmaxf(mxh, slot[(half ^ 1) * 128 + r]);
+        if (!ok) continue;
+
+        const bool grow = j == 0 || mx > m_ref + 8.f; /* lazy rescale, as in attn_prefill_kernel */
+        const bool warp_grow = __any_sync(0xffffffffu, grow);
+        const float m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+
+        float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < HB; c += 8)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float p = ex2(__uint_as_float(sv[c + k]) - m_use);
+            ps8[k] += p;
+            sv[c + k] = __float_as_uint(p);
+          }
+        const float psum = ((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7]));
+#pragma unroll
+        for (int c = 0; c < HB / 2; ++c)
+          sv[c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
+
+        /* PV of the tile before must be finished: it reads P and writes O */
+        if (G >= 1) ok = wait_all(PV_DONE, (G - 1) & 1, 0x522u);
+        if (!ok) continue;
+        tmem_st_32x32(tmem + lane_base + C::COL_P + half * (HB / 2),
+                      *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        if (warp_grow && j > 0) {
+          tc_fence_after_sync();
+          const float factor = ex2(m_ref - m_use);
+#pragma unroll
+          for (int c0 = 0; c0 < OC; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem + lane_base + C::COL_O + half * OC + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
+            tmem_st_32x32(tmem + lane_base + C::COL_O + half * OC + c0, v);
+          }
+          l_run *= factor;
+        }
+        m_ref = m_new;
+        l_run += psum;
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(bar(P_READY));
+      }
+
+      /* The last S of this piece has been read, so Q is free: stage the next piece's q
+       * BEFORE this piece's epilogue -- the MMA warp issues the next piece's first score
+       * tile ahead of this piece's last PV and would otherwise wait for Q while the
+       * epilogue waits for that PV. */
+      const bool more = wk.next(&nxt);
+      if (more) stage_q(nxt);
+
+      /* ---- epilogue: this piece's (acc, m, l) rows for the merge kernel */
+      if (ok) ok = wait_all(PV_DONE, (G - 1) & 1, 0x523u);
+      if (live) {
+        float *slot = xch + 512;
+        slot[half * 128 + r] = l_run;
+        pair_sync();
+        l_run += slot[(half ^ 1) * 128 + r];
+        pair_sync(); /* both halves have read before the next piece writes the slot */
+      }
+      const long long unit = static_cast<long long>(pc.seq) * a.n_kv + pc.kvh;
+      if (ok && live) {
+        tc_fence_after_sync();
+        float *dst = a.scratch + ((unit * a.max_slices + pc.slice) * a.rows_cap + r) * (HD + 4) + half * OC;
+#pragma unroll
+        for (int c0 = 0; c0 < OC; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + lane_base + C::COL_O + half * OC + c0, v);
+          tmem_ld_wait();
+          if (r < rows_valid) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              *reinterpret_cast<uint4 *>(dst + c0 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+          }
+        }
+        if (half == 0 && r < rows_valid)
+          *reinterpret_cast<float2 *>(dst + HD) = make_float2(m_ref, l_run);
+      }
+      if (pc.count > 0 && threadIdx.x == 0) a.slice_counts[unit] = pc.count;
+      tc_fence_before_sync();
+      mbar_arrive(bar(EPI_DONE)); /* O may be overwritten */
+      pc = nxt;
+      have = more;
+      ++piece;
+    }
+  }
+
+  /* common exit: every role gets here, then the allocating warp frees TMEM */
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <class Cfg, class Kern>
-wst_status_t launch_kernel(const PrefillLaunch &P, Kern kern, const PrefillArgs &args,
+template <class Cfg, class Kern, class Args>
+wst_status_t launch_kernel(const PrefillLaunch &P, Kern kern, const Args &args,
                            const CUtensorMap &kmap, const CUtensorMap &vmap, dim3 grid) {
   /* the opt-in to > 48 KB of dynamic shared memory is per function and device */
   static thread_local const void *configured_fn[8] = {};
@@ -1000,6 +1553,92 @@ bool prefill_kernel_supports(int n_q, int n_kv, int hd, int n) {
   return static_cast<long long>(n) * gqa >= 64;
 }
 
+
+wst_status_t launch_verify_span(const PrefillLaunch &P) {
+  DeviceFacts facts;
+  if (!device_facts(&facts)) return WST_ERR_CUDA;
+  if (facts.cc_major < 10)
+    return fail(WST_ERR_UNSUPPORTED_ARCH, "%s: this library is built for sm_100a only", P.name);
+  if (!aligned16(P.qkv) || !aligned16(P.k) || !aligned16(P.v) || !aligned16(P.out) ||
+      !aligned16(P.scratch))
+    return fail(WST_ERR_INVALID_ARG, "%s: buffers must be 16-byte aligned", P.name);
+  const int gqa = P.n_q / P.n_kv;
+  const int rows_cap = P.n * gqa;
+  const long long units = static_cast<long long>(P.n_seq) * P.n_kv;
+  const long long row_floats = static_cast<long long>(rows_cap) * (P.hd + 4);
+  /* slices a unit may be cut into: what the scratch holds (after it, one count per unit) */
+  long long cap = (P.scratch_floats - units) / (units * row_floats);
+  if (cap > kRowsMaxSplits) cap = kRowsMaxSplits;
+  if (cap < 2) return fail(WST_ERR_INVALID_ARG, "%s: scratch too small", P.name);
+  const int max_tiles = (P.max_len > 0 ? P.max_len : P.max_seq) / 128 + 1;
+
+  SpanArgs a{};
+  a.q = P.qkv;
+  a.q_tok_stride = P.q_tok_stride;
+  a.scratch = P.scratch;
+  a.slice_counts = reinterpret_cast<int *>(P.scratch + units * cap * row_floats);
+  a.pos0_dev = P.pos0_dev;
+  a.cu_tokens = P.cu_tokens;
+  a.page_table = P.page_table;
+  a.max_pages = P.max_pages;
+  a.n_pool_pages = P.n_pool_pages;
+  a.n_seq = P.n_seq;
+  a.n_q = P.n_q;
+  a.n_kv = P.n_kv;
+  a.gqa = gqa;
+  a.max_seq = P.max_seq;
+  a.max_slices = static_cast<int>(cap);
+  a.rows_cap = rows_cap;
+  a.min_span = (max_tiles + static_cast<int>(cap) - 2) / (static_cast<int>(cap) - 1);
+  if (a.min_span < 1) a.min_span = 1;
+  a.qscale = P.scale * kLog2e;
+  a.err_word = device_error_word();
+  if (!a.err_word) return WST_ERR_CUDA;
+
+  CUtensorMap kmap, vmap;
+  KvMapKey key{};
+  key.d0 = static_cast<uint64_t>(P.hd);
+  key.d1 = 16;
+  key.d2 = static_cast<uint64_t>(P.n_kv);
+  key.d3 = static_cast<uint64_t>(P.n_pool_pages);
+  key.b1 = 16;
+  key.rank = 4;
+  key.base = P.k;
+  wst_status_t st = cached_kv_tensor_map(&kmap, key);
+  if (st != WST_OK) return st;
+  key.base = P.v;
+  st = cached_kv_tensor_map(&vmap, key);
+  if (st != WST_OK) return st;
+
+  /* one persistent CTA per SM, never more CTAs than there can be tiles */
+  long long ctas = facts.sm_count;
+  const long long tiles_bound = units * max_tiles;
+  if (ctas > tiles_bound) ctas = tiles_bound;
+  if (P.span_ctas > 0 && P.span_ctas < ctas) ctas = P.span_ctas;
+  const dim3 grid(static_cast<unsigned>(ctas));
+  st = P.hd == 128
+           ? launch_kernel<PCfg<128>>(P, attn_verify_span_kernel<128>, a, kmap, vmap, grid)
+           : launch_kernel<PCfg<64>>(P, attn_verify_span_kernel<64>, a, kmap, vmap, grid);
+  if (st != WST_OK) return st;
+
+  SplitMerge m;
+  m.scratch = P.scratch;
+  m.out = P.out;
+  m.cu_tokens = P.cu_tokens;
+  m.n_tok = P.n;
+  m.tok_seq_stride = 0;
+  m.n_q = P.n_q;
+  m.n_kv = P.n_kv;
+  m.hd = P.hd;
+  m.n_splits = static_cast<int>(cap);
+  m.slice_counts = a.slice_counts;
+  m.n_rowblk = 1;
+  m.tpb = P.n;
+  m.rows_cap = rows_cap;
+  m.n_units = static_cast<int>(units);
+  m.name = P.name;
+  return launch_split_merge(m);
+}
 
 bool prefill_split_supports(int n_q, int n_kv, int hd, int n_tok_max) {
   if (hd != 64 && hd != 128) return false;

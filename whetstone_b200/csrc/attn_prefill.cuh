@@ -37,6 +37,7 @@ struct PrefillLaunch {
   float *scratch = nullptr;
   long long scratch_floats = 0;
   float scale = 1.f;
+  int span_ctas = 0;  /* launch_verify_span: CTAs to use (0: one per SM) */
   int force_pair = 0; /* 0 = automatic, 1 = two query tiles per CTA, -1 = one */
   const char *name = "attention";
 };
@@ -49,5 +50,11 @@ bool prefill_kernel_supports(int n_q, int n_kv, int hd, int n);
 bool prefill_split_supports(int n_q, int n_kv, int hd, int n_tok_max);
 
 wst_status_t launch_prefill(const PrefillLaunch &P);
+
+/* Ragged paged verify (every unit's query rows in one 128-row tile, prefill_split_supports):
+ * the KV tiles of all (sequence, KV head) units end to end, cut into one equal span per
+ * persistent CTA, + the slice-merge kernel.  Needs P.page_table, P.cu_tokens, P.pos0_dev,
+ * P.scratch and P.max_len. */
+wst_status_t launch_verify_span(const PrefillLaunch &P);
 
 }  // namespace wst

@@ -615,6 +615,7 @@ struct MergeArgs {
   const int32_t *cu_tokens;
   int n_tok, tok_seq_stride, n_q, n_kv, gqa;
   int n_splits, n_rowblk, tpb, rows_cap;
+  const int *slice_counts; /* per unit, or null: n_splits for all */
   int partial_out;
   /* cross-GPU exchange (world > 1): one token, so a block is one query head */
   uint2 *const *mailboxes; /* [world] -> packets [2][world][n_q][hd+2] on rank g */
@@ -636,23 +637,11 @@ __device__ __forceinline__ void st_packet2(uint2 *p, float v0, float v1, unsigne
                "l"(make_packet(v1, tag))
                : "memory");
 }
-__device__ __forceinline__ unsigned long long ld_packet(const uint2 *p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-/* value of a packet once its tag has arrived; false after about a second */
-__device__ __forceinline__ bool wait_packet(const uint2 *p, unsigned int tag, float *value) {
-  unsigned long long v = ld_packet(p);
-  if (static_cast<unsigned int>(v >> 32) != tag) {
-    const long long t0 = clock64();
-    do {
-      if (clock64() - t0 > kWaitCycleLimit) return false;
-      v = ld_packet(p);
-    } while (static_cast<unsigned int>(v >> 32) != tag);
-  }
-  *value = __uint_as_float(static_cast<unsigned int>(v));
-  return true;
+/* two adjacent packets (16-byte aligned) in one request; each half is still a single
+ * 64-bit access */
+__device__ __forceinline__ void ld_packet2(const uint2 *p, unsigned long long &a,
+                                           unsigned long long &b) {
+  asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 
 template <int HD>
@@ -684,8 +673,8 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = warp * SUB + lane / LPR, c4 = lane % LPR;
-  const int ns = a.n_splits;
-  const float *base = a.scratch + (static_cast<long long>(unit) * ns * a.rows_cap + row) * DR;
+  const int ns = a.slice_counts ? min(a.slice_counts[unit], a.n_splits) : a.n_splits;
+  const float *base = a.scratch + (static_cast<long long>(unit) * a.n_splits * a.rows_cap + row) * DR;
   const long long sp_stride = static_cast<long long>(a.rows_cap) * DR;
 
   float4 v[PER];
@@ -772,33 +761,60 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
     const uint2 *box = a.mailboxes[a.rank] +
                        (static_cast<long long>(par) * a.world * a.n_q + head) * stride;
     const long long rank_stride = static_cast<long long>(a.n_q) * stride;
-    bool ok = true;
-    float top = m_nat;
-    for (int g = 0; ok && g < a.world; ++g) {
-      if (g == a.rank) continue;
-      float m_g;
-      ok = wait_packet(box + g * rank_stride, tag, &m_g);
-      top = fmaxf(top, m_g);
+    /* Fold the peers' triples in as they arrive, in any order (running maximum, like
+     * the online softmax itself).  Per pass the packets of up to four pending peers are
+     * requested together -- three 16-byte loads each, all in flight at once -- so a pass
+     * costs one round trip to this GPU's L2, not one per packet. */
+    float top = m_nat == -INFINITY ? -INFINITY : m_nat;
+    float4 sum = tot;
+    float lsum = dsum;
+    if (m_nat == -INFINITY) {
+      sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      lsum = 0.f;
     }
-    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-    float lsum = 0.f;
-    for (int g = 0; ok && g < a.world; ++g) {
-      float m_g = m_nat, l_g = dsum;
-      float4 a_g = tot;
-      if (g != a.rank) {
-        const uint2 *t = box + g * rank_stride;
-        ok = wait_packet(t, tag, &m_g) && wait_packet(t + 1, tag, &l_g) &&
-             wait_packet(t + 2 + col, tag, &a_g.x) && wait_packet(t + 3 + col, tag, &a_g.y) &&
-             wait_packet(t + 4 + col, tag, &a_g.z) && wait_packet(t + 5 + col, tag, &a_g.w);
-        if (!ok) break;
+    unsigned int pending = (a.world >= 32 ? 0xffffffffu : ((1u << a.world) - 1u)) & ~(1u << a.rank);
+    bool ok = true;
+    const long long t0 = clock64();
+    while (pending != 0u) {
+      for (int base = 0; base < a.world; base += 4) {
+        unsigned long long pk[4][6];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int g = base + k;
+          if (g < a.world && ((pending >> g) & 1u)) {
+            const uint2 *t = box + g * rank_stride;
+            ld_packet2(t, pk[k][0], pk[k][1]);
+            ld_packet2(t + 2 + col, pk[k][2], pk[k][3]);
+            ld_packet2(t + 4 + col, pk[k][4], pk[k][5]);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int g = base + k;
+          if (g < a.world && ((pending >> g) & 1u)) {
+            bool here = true;
+#pragma unroll
+            for (int i = 0; i < 6; ++i) here = here && static_cast<unsigned int>(pk[k][i] >> 32) == tag;
+            if (!here) continue;
+            pending &= ~(1u << g);
+            const float m_g = __uint_as_float(static_cast<unsigned int>(pk[k][0]));
+            if (m_g == -INFINITY) continue; /* an empty shard contributes nothing */
+            const float top_new = fmaxf(top, m_g);
+            const float f_old = top == -INFINITY ? 0.f : expf(top - top_new);
+            const float f_new = expf(m_g - top_new);
+            sum.x = fmaf(__uint_as_float(static_cast<unsigned int>(pk[k][2])), f_new, sum.x * f_old);
+            sum.y = fmaf(__uint_as_float(static_cast<unsigned int>(pk[k][3])), f_new, sum.y * f_old);
+            sum.z = fmaf(__uint_as_float(static_cast<unsigned int>(pk[k][4])), f_new, sum.z * f_old);
+            sum.w = fmaf(__uint_as_float(static_cast<unsigned int>(pk[k][5])), f_new, sum.w * f_old);
+            lsum = fmaf(__uint_as_float(static_cast<unsigned int>(pk[k][1])), f_new, lsum * f_old);
+            top = top_new;
+          }
+        }
       }
-      if (m_g == -INFINITY) continue; /* an empty shard contributes nothing */
-      const float f = expf(m_g - top);
-      sum.x = fmaf(a_g.x, f, sum.x);
-      sum.y = fmaf(a_g.y, f, sum.y);
-      sum.z = fmaf(a_g.z, f, sum.z);
-      sum.w = fmaf(a_g.w, f, sum.w);
-      lsum = fmaf(l_g, f, lsum);
+      if (pending != 0u && clock64() - t0 > kWaitCycleLimit) {
+        ok = false;
+        break;
+      }
     }
     ok = __all_sync(__activemask(), ok);
     if (ok) {
@@ -1201,6 +1217,7 @@ wst_status_t launch_split_merge(const SplitMerge &S) {
   m.tpb = S.tpb;
   m.rows_cap = S.rows_cap;
   m.partial_out = S.partial_out ? 1 : 0;
+  m.slice_counts = S.slice_counts;
   m.mailboxes = static_cast<uint2 *const *>(S.mailboxes);
   m.xstate = static_cast<unsigned int *>(S.xstate);
   m.rank = S.rank;

@@ -17,6 +17,7 @@ struct RowsTuning {
   int decode_splits = 0;  /* slices of a decode launch (0: one per SM and KV head) */
   int early_depth = -1;   /* tiles requested at once ahead of the grid dependency */
   int ring_stages = 0;    /* ring depth in use (0: all the shared memory holds) */
+  int verify_ctas = 0;    /* persistent CTAs of the ragged verify kernel (0: one per SM) */
 };
 RowsTuning &rows_tuning();
 
@@ -91,6 +92,9 @@ struct SplitMerge {
   int n_tok = 1, tok_seq_stride = 0;
   int n_q = 0, n_kv = 0, hd = 0;
   int n_splits = 1, n_rowblk = 1, tpb = 1, rows_cap = 1, n_units = 1;
+  /* slices per unit in device memory (the scratch keeps n_splits slots per unit), or
+   * null: every unit has n_splits slices */
+  const int *slice_counts = nullptr;
   bool partial_out = false;
   /* cross-GPU exchange inside the merge (world > 1; one token, one sequence) */
   const void *mailboxes = nullptr;
