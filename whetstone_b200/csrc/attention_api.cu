@@ -684,7 +684,13 @@ extern "C" wst_status_t wst_attn_verify_paged(const void *qkv, const void *k_poo
     P.scratch_floats =
         wst_attn_verify_scratch_floats(n_seq, max_tokens_per_seq, n_q, n_kv, head_dim, max_len);
     P.max_len = max_len;
-    if (g_kernel_choice.load() != 3) {
+    /* the span kernel needs room for at least two slices per unit in the scratch
+     * (a tiny batch against a short prefix has less: the sliced schedule takes it) */
+    const long long units = static_cast<long long>(n_seq) * n_kv;
+    const long long slice_floats =
+        units * max_tokens_per_seq * (n_q / n_kv) * (static_cast<long long>(head_dim) + 4);
+    const bool span_fits = (P.scratch_floats - units) / slice_floats >= 2;
+    if (g_kernel_choice.load() != 3 && span_fits) {
       /* one persistent CTA per SM over equal spans of all units' KV tiles */
       P.span_ctas = rows_tuning().verify_ctas;
       return launch_verify_span(P);

@@ -1171,47 +1171,49 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
   if (n_total == 0) {
     /* nothing to do: fall through to the common exit */
   } else if (warp == TMA_WARP) {
-    /* ------------------------------------------------------ TMA producer */
-    if (lane == 0) {
+    /* ------------------------------------------------------ TMA producer.
+     * A 128-position tile of a paged cache is sixteen 2 KB boxes for K and sixteen for
+     * V (eight 16-token pages x two 128-byte halves at head_dim 128).  The whole warp
+     * issues them: lanes 0-15 own the K boxes, lanes 16-31 the V boxes, one box per
+     * lane, and the two half-warps run their rings independently (K is wanted a tile
+     * earlier than V).  Each lane fetches its page id one tile ahead, so no tile waits
+     * for a page-table load. */
+    {
+      constexpr int BOXES = (BN / 16) * NH; /* per operand */
+      const int which = lane >> 4, sub = lane & 15;
+      const bool active = sub < BOXES;
+      const int pg = sub / NH, h = sub % NH;
+      const unsigned halfmask = which ? 0xffff0000u : 0x0000ffffu;
+      const int FULL = which ? V_FULL : K_FULL, EMPTY = which ? V_EMPTY : K_EMPTY;
+      const CUtensorMap *map = which ? &vmap : &kmap;
+      const uint32_t dst0 = sbase + (which ? C::OFF_V : C::OFF_K) + h * HALF_BYTES + pg * 16 * 128;
+      auto page_of = [&](int seq, int jt) {
+        const int slot = jt * (BN / 16) + pg;
+        int page = (active && slot < a.max_pages)
+                       ? a.page_table[static_cast<long long>(seq) * a.max_pages + slot]
+                       : -1;
+        /* an unmapped slot reads as zeros: coordinate just past the pool */
+        return (page < 0 || page >= a.n_pool_pages) ? a.n_pool_pages : page;
+      };
       SpanPiece pc;
       int G = 0;
       bool ok = true;
       while (ok && walk.next(&pc)) {
+        int page_next = page_of(pc.seq, pc.first);
         for (int j = 0; j < pc.n; ++j, ++G) {
           const int st = G % NSTAGE, round = G / NSTAGE;
-          if (G >= NSTAGE && !mbar_wait(bar(K_EMPTY + st), (round - 1) & 1, a.err_word, 0x501u)) {
-            ok = false;
-            break;
+          const int page = page_next;
+          if (j + 1 < pc.n) page_next = page_of(pc.seq, pc.first + j + 1);
+          if (G >= NSTAGE) {
+            const bool got = mbar_wait(bar(EMPTY + st), (round - 1) & 1, a.err_word, 0x501u + which);
+            if (!__all_sync(halfmask, got)) {
+              ok = false;
+              break;
+            }
           }
-          const int jt = pc.first + j;
-          int pages[BN / 16];
-#pragma unroll
-          for (int pg = 0; pg < BN / 16; ++pg) {
-            const int slot = jt * (BN / 16) + pg;
-            int page = slot < a.max_pages
-                           ? a.page_table[static_cast<long long>(pc.seq) * a.max_pages + slot]
-                           : -1;
-            /* an unmapped slot reads as zeros: coordinate just past the pool */
-            pages[pg] = (page < 0 || page >= a.n_pool_pages) ? a.n_pool_pages : page;
-          }
-          mbar_arrive_expect_tx(bar(K_FULL + st), KV_BYTES);
-#pragma unroll
-          for (int pg = 0; pg < BN / 16; ++pg)
-#pragma unroll
-            for (int h = 0; h < NH; ++h)
-              tma_load_4d(sbase + C::OFF_K + st * KV_BYTES + h * HALF_BYTES + pg * 16 * 128, &kmap,
-                          bar(K_FULL + st), h * 64, 0, pc.kvh, pages[pg]);
-          if (G >= NSTAGE && !mbar_wait(bar(V_EMPTY + st), (round - 1) & 1, a.err_word, 0x502u)) {
-            ok = false;
-            break;
-          }
-          mbar_arrive_expect_tx(bar(V_FULL + st), KV_BYTES);
-#pragma unroll
-          for (int pg = 0; pg < BN / 16; ++pg)
-#pragma unroll
-            for (int h = 0; h < NH; ++h)
-              tma_load_4d(sbase + C::OFF_V + st * KV_BYTES + h * HALF_BYTES + pg * 16 * 128, &vmap,
-                          bar(V_FULL + st), h * 64, 0, pc.kvh, pages[pg]);
+          if (sub == 0) mbar_arrive_expect_tx(bar(FULL + st), KV_BYTES);
+          __syncwarp(halfmask);
+          if (active) tma_load_4d(dst0 + st * KV_BYTES, map, bar(FULL + st), h * 64, 0, pc.kvh, page);
         }
       }
     }
