@@ -233,7 +233,6 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       grid_dependency_wait();
     } else {
       grid_dependency_wait();
-      if (threadIdx.x == 0) st_shared_volatile(go_u32, 1u);
     }
   } else {
     /* Nothing above touches global memory, so under programmatic dependent launch
@@ -288,6 +287,11 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       packed.w = pack_half2(hi[it].z * a.qscale, hi[it].w * a.qscale);
       *reinterpret_cast<uint4 *>(qsm + (ch >> 3) * (ROWS * 128) + swz128(row, ch & 7)) = packed;
     }
+    /* the dependency is resolved and this thread's q rows are here: only now may the
+     * producer ask for the rest of the ring at once -- released any earlier, those
+     * requests (tens of KB per SM) queue ahead of the q loads and the first tile is
+     * consumed 0.8 us later */
+    if (threadIdx.x == 0) st_shared_volatile(go_u32, 1u);
   }
 
   int pos0 = a.pos0_dev ? pos_raw + a.pos0_bias : a.pos0_val;
@@ -655,6 +659,10 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
   __shared__ float s_m[GROUPS], s_l[GROUPS];
 
   grid_launch_dependents();
+  /* the ranks' mailbox addresses never change: fetched while the dependency is open */
+  uint2 *peer_box[8];
+#pragma unroll
+  for (int g = 0; g < 8; ++g) peer_box[g] = (a.world > 1 && g < a.world) ? a.mailboxes[g] : nullptr;
   grid_dependency_wait();
 
   const int row = blockIdx.x, unit = blockIdx.y;
@@ -673,6 +681,9 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = warp * SUB + lane / LPR, c4 = lane % LPR;
+  /* the head's call counter (exchange only), in flight together with the partial rows */
+  const int head_x = ((unit / a.n_rowblk) % a.n_kv) * a.gqa + row % a.gqa;
+  const unsigned int xcount = a.world > 1 ? __ldcg(a.xstate + head_x) : 0u;
   const int ns = a.slice_counts ? min(a.slice_counts[unit], a.n_splits) : a.n_splits;
   const float *base = a.scratch + (static_cast<long long>(unit) * a.n_splits * a.rows_cap + row) * DR;
   const long long sp_stride = static_cast<long long>(a.rows_cap) * DR;
@@ -744,22 +755,29 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
      * everybody's t+1, which they sent after reading t.  Every rank runs its own launch
      * on its own GPU; nothing here waits for another launch on the same GPU. */
     const float m_nat = big * kLn2;
-    const unsigned int tag = a.xstate[head] + 1u;
+    const unsigned int tag = xcount + 1u;
     const int par = static_cast<int>(tag & 1u);
     constexpr int stride = HD + 2;
     const long long my_slot = (static_cast<long long>(par) * a.world + a.rank) * a.n_q + head;
-    for (int g = 0; g < a.world; ++g) {
-      if (g == a.rank) continue;
-      uint2 *dst = a.mailboxes[g] + my_slot * stride;
+    auto publish = [&](uint2 *mailbox) {
+      uint2 *dst = mailbox + my_slot * stride;
       if (threadIdx.x == 0) {
         st_packet(dst, m_nat, tag);
         st_packet(dst + 1, dsum, tag);
       }
       st_packet2(dst + 2 + col, tot.x, tot.y, tag);
       st_packet2(dst + 4 + col, tot.z, tot.w, tag);
+    };
+    uint2 *own_box = nullptr;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) { /* the first eight ranks' addresses are in registers */
+      if (g == a.rank) own_box = peer_box[g];
+      if (g < a.world && g != a.rank) publish(peer_box[g]);
     }
-    const uint2 *box = a.mailboxes[a.rank] +
-                       (static_cast<long long>(par) * a.world * a.n_q + head) * stride;
+    for (int g = 8; g < a.world; ++g)
+      if (g != a.rank) publish(a.mailboxes[g]);
+    if (a.rank >= 8) own_box = a.mailboxes[a.rank];
+    const uint2 *box = own_box + (static_cast<long long>(par) * a.world * a.n_q + head) * stride;
     const long long rank_stride = static_cast<long long>(a.n_q) * stride;
     /* Fold the peers' triples in as they arrive, in any order (running maximum, like
      * the online softmax itself).  Per pass the packets of up to four pending peers are
