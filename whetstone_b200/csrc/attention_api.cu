@@ -302,7 +302,6 @@ extern "C" wst_status_t wst_b200_set_tuning(int32_t key, int32_t value) {
     case 2: t.early_depth = value; break;
     case 4: t.ring_stages = value; break;
     case 5: t.verify_ctas = value; break;
-    case 6: t.early_delay_ns = value; break;
     default: return fail(WST_ERR_INVALID_ARG, "wst_b200_set_tuning: unknown key %d", key);
   }
   return WST_OK;

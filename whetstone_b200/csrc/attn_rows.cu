@@ -63,7 +63,6 @@ struct RowsArgs {
   int early_depth; /* 0: nothing is requested before the grid dependency resolves; else the
                     * number of tiles requested at once ahead of it (the rest of the ring
                     * follows one tile at a time) */
-  int early_delay; /* SM clocks a block lets pass before its requests ahead of the dependency */
   int via_scratch; /* a single slice still writes its row to scratch: the merge kernel
                     * follows (it carries the cross-GPU exchange) */
 };
@@ -221,11 +220,6 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     }
     if (warp == C::CWARPS) {
       if (lane == 0 && spec > 0) {
-        if (a.early_delay > 0) { /* let the kernel ahead get its last, latency-bound loads out */
-          const long long t0 = clock64();
-          while (clock64() - t0 < a.early_delay && ld_shared_volatile(go_u32) == 0u) {
-          }
-        }
         const int burst = a.early_depth < spec ? a.early_depth : spec;
         for (int i = 0; i < burst; ++i) issue(i);
         for (int i = burst; i < spec; ++i) {
@@ -1172,7 +1166,6 @@ wst_status_t launch_rows(const RowsLaunch &L) {
     a.early_depth = tune.early_depth >= 0 ? tune.early_depth : kDefaultEarlyDepth;
     if (a.early_depth > a.nstage) a.early_depth = a.nstage;
   }
-  a.early_delay = tune.early_delay_ns > 0 ? tune.early_delay_ns * 2 : 0; /* ~2 clocks per ns */
   a.err_word = device_error_word();
   if (!a.err_word) return WST_ERR_CUDA;
   CUtensorMap kmap, vmap;

@@ -17,7 +17,6 @@ struct RowsTuning {
   int decode_splits = 0;  /* slices of a decode launch (0: one per SM and KV head) */
   int early_depth = -1;   /* tiles requested at once ahead of the grid dependency */
   int ring_stages = 0;    /* ring depth in use (0: all the shared memory holds) */
-  int early_delay_ns = 0; /* a decode block waits this long before its early requests */
   int verify_ctas = 0;    /* persistent CTAs of the ragged verify kernel (0: one per SM) */
 };
 RowsTuning &rows_tuning();
