@@ -1050,6 +1050,15 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
   using C = PCfg<HD>;
   constexpr int BN = C::BN, NH = C::NH, NSTAGE = C::NSTAGE;
   constexpr int HALF_BYTES = C::HALF_BYTES, KV_BYTES = C::KV_BYTES;
+  /* head_dim 128: a page's two 128-byte halves come in ONE 4 KB box (5-D tensor map;
+   * half as many requests per tile, and the TMA unit's rate is per request), which lays
+   * a tile down as [page][half][16 rows][128 B] instead of [half][128 rows][128 B].  An
+   * 8-row group of one half is then 4096 bytes from the same rows of the next page and
+   * 1024 from the other eight rows of its own page, so the score MMA runs as two N = 64
+   * halves -- columns 0-63 are rows 0-7 of the eight pages, columns 64-127 rows 8-15 --
+   * and P, the mask and the PV k-steps follow that column order. */
+  constexpr bool WIDE = HD == 128;
+  constexpr uint32_t kDescHiWide = (4096u >> 4) | (1u << 14) | (2u << 29);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
@@ -1172,21 +1181,22 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
     /* nothing to do: fall through to the common exit */
   } else if (warp == TMA_WARP) {
     /* ------------------------------------------------------ TMA producer.
-     * A 128-position tile of a paged cache is sixteen 2 KB boxes for K and sixteen for
-     * V (eight 16-token pages x two 128-byte halves at head_dim 128).  The whole warp
-     * issues them: lanes 0-15 own the K boxes, lanes 16-31 the V boxes, one box per
-     * lane, and the two half-warps run their rings independently (K is wanted a tile
-     * earlier than V).  Each lane fetches its page id one tile ahead, so no tile waits
-     * for a page-table load. */
+     * A 128-position tile of a paged cache is eight pages for K and eight for V, one
+     * box per page and operand (4 KB at head_dim 128, 2 KB at 64).  The whole warp
+     * issues them: lanes 0-15 own the K boxes, lanes 16-31 the V boxes,
+     * one box per lane, and the two half-warps run their rings independently (K is
+     * wanted a tile earlier than V).  Each lane fetches its page id one tile ahead, so
+     * no tile waits for a page-table load. */
     {
-      constexpr int BOXES = (BN / 16) * NH; /* per operand */
+      constexpr int BOXES = WIDE ? BN / 16 : (BN / 16) * NH; /* per operand */
       const int which = lane >> 4, sub = lane & 15;
       const bool active = sub < BOXES;
-      const int pg = sub / NH, h = sub % NH;
+      const int pg = WIDE ? sub : sub / NH, h = WIDE ? 0 : sub % NH;
       const unsigned halfmask = which ? 0xffff0000u : 0x0000ffffu;
       const int FULL = which ? V_FULL : K_FULL, EMPTY = which ? V_EMPTY : K_EMPTY;
       const CUtensorMap *map = which ? &vmap : &kmap;
-      const uint32_t dst0 = sbase + (which ? C::OFF_V : C::OFF_K) + h * HALF_BYTES + pg * 16 * 128;
+      const uint32_t dst0 = sbase + (which ? C::OFF_V : C::OFF_K) +
+                            (WIDE ? pg * 4096 : h * HALF_BYTES + pg * 16 * 128);
       auto page_of = [&](int seq, int jt) {
         const int slot = jt * (BN / 16) + pg;
         int page = (active && slot < a.max_pages)
@@ -1213,7 +1223,12 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
           }
           if (sub == 0) mbar_arrive_expect_tx(bar(FULL + st), KV_BYTES);
           __syncwarp(halfmask);
-          if (active) tma_load_4d(dst0 + st * KV_BYTES, map, bar(FULL + st), h * 64, 0, pc.kvh, page);
+          if (active) {
+            if constexpr (WIDE)
+              tma_load_5d(dst0 + st * KV_BYTES, map, bar(FULL + st), 0, 0, 0, pc.kvh, page);
+            else
+              tma_load_4d(dst0 + st * KV_BYTES, map, bar(FULL + st), h * 64, 0, pc.kvh, page);
+          }
         }
       }
     }
@@ -1225,9 +1240,10 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
      * starts a new accumulation and waits until the epilogue of the piece before has
      * read O. */
     constexpr uint32_t idesc_qk = umma_idesc(128, BN, 0);
+    constexpr uint32_t idesc_qk_half = umma_idesc(128, BN / 2, 0);
     constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
     const uint32_t k_lo0 = umma_desc_lo(sbase + C::OFF_K, 16);
-    const uint32_t v_lo0 = umma_desc_lo(sbase + C::OFF_V, HALF_BYTES);
+    const uint32_t v_lo0 = umma_desc_lo(sbase + C::OFF_V, WIDE ? 2048 : HALF_BYTES);
     /* two walkers: one for the S stream (two tiles ahead), one for the PV stream */
     SpanWalk ws = walk, wp = walk;
     SpanPiece ps, pp;
@@ -1252,9 +1268,17 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
       if (lane == 0) {
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (g % NSTAGE) * KV_BYTES + (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_ts_f16_lohi(tmem + C::COL_S + (g & 1) * BN, tmem + C::COL_Q + ks * 8,
-                           k_lo0 + (off >> 4), kDescHi, idesc_qk, ks > 0);
+          if constexpr (WIDE) {
+            const uint32_t off = (g % NSTAGE) * KV_BYTES + (ks >> 2) * 2048 + (ks & 3) * 32;
+            umma_ts_f16_lohi(tmem + C::COL_S + (g & 1) * BN, tmem + C::COL_Q + ks * 8,
+                             k_lo0 + (off >> 4), kDescHiWide, idesc_qk_half, ks > 0);
+            umma_ts_f16_lohi(tmem + C::COL_S + (g & 1) * BN + 64, tmem + C::COL_Q + ks * 8,
+                             k_lo0 + ((off + 1024) >> 4), kDescHiWide, idesc_qk_half, ks > 0);
+          } else {
+            const uint32_t off = (g % NSTAGE) * KV_BYTES + (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+            umma_ts_f16_lohi(tmem + C::COL_S + (g & 1) * BN, tmem + C::COL_Q + ks * 8,
+                             k_lo0 + (off >> 4), kDescHi, idesc_qk, ks > 0);
+          }
         }
         umma_commit(bar(S_FULL + (g & 1)));
         umma_commit(bar(K_EMPTY + g % NSTAGE));
@@ -1282,9 +1306,10 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
         const int first_dead = pp.kv_end - jt * BN;
         for (int idx = first_dead * (NH * 8) + lane; idx < BN * NH * 8; idx += 32) {
           const int row = idx / (NH * 8), rest = idx % (NH * 8);
-          asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(
-                           vb + (rest >> 3) * HALF_BYTES + row * 128 + (rest & 7) * 16),
-                       "r"(0u)
+          const uint32_t where =
+              WIDE ? (row >> 4) * 4096 + (rest >> 3) * 2048 + (row & 15) * 128 + (rest & 7) * 16
+                   : (rest >> 3) * HALF_BYTES + row * 128 + (rest & 7) * 16;
+          asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(vb + where), "r"(0u)
                        : "memory");
         }
         fence_async_smem();
@@ -1295,9 +1320,11 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
       if (lane == 0) {
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint32_t off = st * KV_BYTES + kk * 2048;
-          umma_ts_f16_lohi(tmem + C::COL_O, tmem + C::COL_P + kk * 8, v_lo0 + (off >> 4), kDescHi,
-                           idesc_pv, (p_pos > 0 || kk > 0) ? 1u : 0u);
+          /* P columns 16kk .. 16kk+15: (WIDE) rows 0-7 or 8-15 of two neighbouring pages */
+          const uint32_t off = WIDE ? st * KV_BYTES + (kk & 3) * 8192 + (kk >> 2) * 1024
+                                    : st * KV_BYTES + kk * 2048;
+          umma_ts_f16_lohi(tmem + C::COL_O, tmem + C::COL_P + kk * 8, v_lo0 + (off >> 4),
+                           WIDE ? kDescHiWide : kDescHi, idesc_pv, (p_pos > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(bar(PV_DONE));
         umma_commit(bar(V_EMPTY + st));
@@ -1385,10 +1412,17 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
           tc_fence_before_sync();
           mbar_arrive(bar(S_FREE + (G & 1)));
           if (jt * BN + BN > lim_min) { /* causal edge / end of sequence */
-            const int lim_local = lim - jt * BN - half * HB;
+            if constexpr (WIDE) { /* column c of this half is row 8*half + c%8 of page c/8 */
+              const int lim_tile = lim - jt * BN - 8 * half;
 #pragma unroll
-            for (int c = 0; c < HB; ++c)
-              if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
+              for (int c = 0; c < HB; ++c)
+                if (16 * (c >> 3) + (c & 7) >= lim_tile) sv[c] = 0xff800000u; /* -inf */
+            } else {
+              const int lim_local = lim - jt * BN - half * HB;
+#pragma unroll
+              for (int c = 0; c < HB; ++c)
+                if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
+            }
           }
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -1604,7 +1638,7 @@ wst_status_t launch_verify_span(const PrefillLaunch &P) {
   key.d2 = static_cast<uint64_t>(P.n_kv);
   key.d3 = static_cast<uint64_t>(P.n_pool_pages);
   key.b1 = 16;
-  key.rank = 4;
+  key.rank = P.hd == 128 ? 5 : 4; /* head_dim 128: both halves of a page in one box */
   key.base = P.k;
   wst_status_t st = cached_kv_tensor_map(&kmap, key);
   if (st != WST_OK) return st;

@@ -71,10 +71,21 @@ wst_status_t cached_kv_tensor_map(CUtensorMap *out, const KvMapKey &key) {
     *out = s.map;
     return WST_OK;
   }
-  uint64_t dims[4] = {key.d0, key.d1, key.d2, key.d3};
-  uint64_t strides[3] = {key.d0 * 2, key.d0 * key.d1 * 2, key.d0 * key.d1 * key.d2 * 2};
-  uint32_t box[4] = {64, key.b1, 1, 1};
-  wst_status_t st = make_kv_tensor_map(out, key.base, static_cast<int>(key.rank), dims, strides, box);
+  wst_status_t st;
+  if (key.rank == 5) {
+    /* page pool [pages][n_kv][16][128] seen as (64 columns, 16 rows, 2 column halves,
+     * n_kv, pages): one box is both 128-byte halves of a page's 16 rows of one KV head,
+     * 4 KB per request, laid down as [half][16 rows][128 B] */
+    uint64_t dims[5] = {64, 16, 2, key.d2, key.d3};
+    uint64_t strides[4] = {256, 128, 4096, key.d2 * 4096};
+    uint32_t box[5] = {64, 16, 2, 1, 1};
+    st = make_kv_tensor_map(out, key.base, 5, dims, strides, box);
+  } else {
+    uint64_t dims[4] = {key.d0, key.d1, key.d2, key.d3};
+    uint64_t strides[3] = {key.d0 * 2, key.d0 * key.d1 * 2, key.d0 * key.d1 * key.d2 * 2};
+    uint32_t box[4] = {64, key.b1, 1, 1};
+    st = make_kv_tensor_map(out, key.base, static_cast<int>(key.rank), dims, strides, box);
+  }
   if (st != WST_OK) return st;
   std::memset(&s.key, 0, sizeof(KvMapKey));
   s.key = key;

@@ -104,6 +104,16 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3), "r"(c4)
+      : "memory");
+}
+
 /* Untiled bulk copy global -> this CTA's shared memory, completion counted in bytes
  * on `bar`.  Both addresses 16-byte aligned, `bytes` a multiple of 16. */
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes,
