@@ -12,7 +12,9 @@
 
 namespace wst {
 
+#ifndef WST_DROPIN
 thread_local char g_error_text[512] = "no error";
+#endif
 static thread_local cudaStream_t t_stream = cudaStreamPerThread;
 
 cudaStream_t current_stream() { return t_stream; }
@@ -80,7 +82,9 @@ unsigned int *device_error_word() {
 
 using namespace wst;
 
+#ifndef WST_DROPIN
 extern "C" const char *wst_last_error(void) { return g_error_text; }
+#endif
 
 extern "C" const char *wst_b200_version(void) { return "0.1.0"; }
 
@@ -101,6 +105,10 @@ extern "C" wst_status_t wst_b200_device_error(uint32_t *out_code) {
   return WST_OK;
 }
 
+/* Everything from here to the next #endif is the engine's own runtime half of the ABI
+ * (cuda/runtime.cu:80-190): present so that a host can run on this library alone,
+ * left out of the drop-in archive, where the engine's objects define it. */
+#ifndef WST_DROPIN
 /* ----------------------------------------------------- device and memory */
 
 extern "C" wst_status_t wst_device_count(int32_t *out_count) {
@@ -158,6 +166,8 @@ extern "C" wst_status_t wst_memset(void *dst, int32_t value, size_t bytes) {
   return WST_OK;
 }
 
+#endif /* !WST_DROPIN */
+
 /* Sharing one device allocation with the other processes of the box (one process
  * per GPU): the owner exports a 64-byte handle of a buffer it got from wst_malloc,
  * another process imports it WITH ITS OWN DEVICE CURRENT, so that the mapping
@@ -188,6 +198,8 @@ extern "C" wst_status_t wst_b200_ipc_close(void *dev_ptr) {
   return WST_OK;
 }
 
+/* the rest of the engine's runtime, graph (cuda/graph.cu:47-145) and cursor entry points */
+#ifndef WST_DROPIN
 extern "C" wst_status_t wst_memcpy_h2d(void *dst, const void *src_host, size_t bytes) {
   if (bytes == 0) return WST_OK;
   WST_CHECK_ARG(dst && src_host, "wst_memcpy_h2d: null pointer");
@@ -287,6 +299,8 @@ extern "C" wst_status_t wst_advance_pos(void *pos, int32_t max_seq) {
   WST_LAUNCHED("wst_advance_pos");
   return WST_OK;
 }
+
+#endif /* !WST_DROPIN */
 
 /* ----------------------------------------------------------- RoPE table */
 

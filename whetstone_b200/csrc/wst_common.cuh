@@ -17,13 +17,28 @@ namespace wst {
 
 /* ---- error reporting --------------------------------------------------- */
 
+}  // namespace wst
+
+#ifdef WST_DROPIN
+/* Linked INTO the engine's kernel library (make DROPIN=1): messages go to the engine's
+ * own per-thread buffer, the one its wst_last_error returns
+ * (cuda/common.cuh:16, cuda/runtime.cu:5-7), so the Rust side's check() reads them. */
+extern __attribute__((visibility("default"))) thread_local char wst_err_buf[512];
+#define WST_ERROR_TEXT ::wst_err_buf
+#else
+namespace wst {
 /* 512 bytes per thread, like the engine's own buffer; wst_last_error returns it. */
 extern thread_local char g_error_text[512];
+}
+#define WST_ERROR_TEXT ::wst::g_error_text
+#endif
+
+namespace wst {
 
 inline wst_status_t fail(wst_status_t code, const char *fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
-  vsnprintf(g_error_text, sizeof(g_error_text), fmt, ap);
+  vsnprintf(WST_ERROR_TEXT, sizeof(WST_ERROR_TEXT), fmt, ap);
   va_end(ap);
   return code;
 }
