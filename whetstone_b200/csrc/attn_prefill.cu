@@ -989,11 +989,20 @@ struct SpanPiece {
   int pos0, tok_begin, ntok, kv_end;
 };
 
-/* Walks the pieces of a span; every role of the CTA runs its own copy. */
+/* What starting a piece costs a CTA, in tiles: the next unit's q has to be fetched and
+ * staged and the pipeline refilled while the finished piece's rows are stored (measured:
+ * 4 to 5 us per unit boundary against 1.8 us per tile).  The span arithmetic counts every
+ * unit as kUnitPad + tiles "slots", so a span with many short units gets fewer real
+ * tiles than one inside a long unit, and all CTAs finish together. */
+constexpr int kUnitPad = 3;
+
+/* Walks the pieces of a span; every role of the CTA runs its own copy.  Positions are
+ * slots: unit u owns slots [start_u, start_u + kUnitPad + tiles_u); the first kUnitPad
+ * of them are padding, slot kUnitPad + i is KV tile i. */
 struct SpanWalk {
-  int seq, kvh, tile; /* where the next piece starts */
-  long long g, hi;    /* global tile index of that point, end of the span */
-  long long before;   /* tiles of all units of earlier sequences */
+  int seq, kvh, slot; /* where the next piece starts: slot index inside the unit */
+  long long g, hi;    /* global slot index of that point, end of the span */
+  long long before;   /* slots of all units of earlier sequences */
   int span, cta;
   const SpanArgs *a;
 
@@ -1009,6 +1018,8 @@ struct SpanWalk {
     *kv_end = end;
     return (end + 127) / 128;
   }
+  /* slots of one unit of a sequence with t tiles (0 for a sequence without tokens) */
+  __device__ __forceinline__ static int unit_slots(int t) { return t > 0 ? t + kUnitPad : 0; }
 
   __device__ __forceinline__ bool next(SpanPiece *p) {
     while (g < hi && seq < a->n_seq) {
@@ -1017,26 +1028,36 @@ struct SpanWalk {
         ++seq;
         continue;
       }
+      const int us = unit_slots(t);
       const long long left = hi - g;
-      const int n = static_cast<int>(min(static_cast<long long>(t - tile), left));
-      const long long unit_start = before + static_cast<long long>(kvh) * t;
+      const int n_slots = static_cast<int>(min(static_cast<long long>(us - slot), left));
+      const long long unit_start = before + static_cast<long long>(kvh) * us;
+      /* the real tiles among slots [slot, slot + n_slots) */
+      const int first = max(slot - kUnitPad, 0);
+      const int last = slot + n_slots - kUnitPad; /* one past */
+      const int n = max(last - first, 0);
+      /* slices are numbered by the CTAs that hold real tiles of the unit: the first real
+       * tile sits at unit_start + kUnitPad */
+      const long long first_real = unit_start + kUnitPad;
       p->seq = seq;
       p->kvh = kvh;
-      p->first = tile;
+      p->first = first;
       p->n = n;
-      p->slice = cta - static_cast<int>(unit_start / span);
-      p->count = tile == 0 ? static_cast<int>((unit_start + t - 1) / span - unit_start / span) + 1 : 0;
-      g += n;
-      tile += n;
-      if (tile == t) {
-        tile = 0;
+      p->slice = cta - static_cast<int>(first_real / span);
+      p->count = (n > 0 && first == 0)
+                     ? static_cast<int>((first_real + t - 1) / span - first_real / span) + 1
+                     : 0;
+      g += n_slots;
+      slot += n_slots;
+      if (slot == us) {
+        slot = 0;
         if (++kvh == a->n_kv) {
           kvh = 0;
-          before += static_cast<long long>(a->n_kv) * t;
+          before += static_cast<long long>(a->n_kv) * us;
           ++seq;
         }
       }
-      return true;
+      if (n > 0) return true; /* a stretch of padding only is no piece */
     }
     return false;
   }
@@ -1101,6 +1122,12 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
     tmem_relinquish();
   }
   grid_launch_dependents();
+  if (warp == 0) { /* towards L2 while the dependency is open: no architectural effect */
+    for (int i = lane * 32; i <= a.n_seq; i += 32 * 32) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a.cu_tokens + i));
+      if (i < a.n_seq) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.pos0_dev + i));
+    }
+  }
   grid_dependency_wait();
 
   /* ---- where does this CTA's span start?  warp 0: total tiles, span length, and the
@@ -1110,7 +1137,7 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
     long long total = 0;
     for (int s0 = 0; s0 < a.n_seq; s0 += 32) {
       const int s = s0 + lane;
-      long long t = s < a.n_seq ? SpanWalk::seq_tiles(a, s, &pos0, &tb, &nt, &ke) : 0;
+      long long t = s < a.n_seq ? SpanWalk::unit_slots(SpanWalk::seq_tiles(a, s, &pos0, &tb, &nt, &ke)) : 0;
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
       total += t;
@@ -1126,9 +1153,10 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
     if (lo < total) {
       for (int s0 = 0; s0 < a.n_seq && seq == a.n_seq; s0 += 32) {
         const int s = s0 + lane;
-        const long long mine = s < a.n_seq
-                                   ? static_cast<long long>(a.n_kv) * SpanWalk::seq_tiles(a, s, &pos0, &tb, &nt, &ke)
-                                   : 0;
+        const long long mine =
+            s < a.n_seq ? static_cast<long long>(a.n_kv) *
+                              SpanWalk::unit_slots(SpanWalk::seq_tiles(a, s, &pos0, &tb, &nt, &ke))
+                        : 0;
         long long incl = mine;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
@@ -1168,14 +1196,19 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
   SpanWalk walk;
   walk.seq = static_cast<int>(walk0[0]);
   walk.kvh = static_cast<int>(walk0[1]);
-  walk.tile = static_cast<int>(walk0[2]);
+  walk.slot = static_cast<int>(walk0[2]);
   walk.span = static_cast<int>(walk0[3]);
   walk.g = walk0[4];
   walk.hi = walk0[5];
   walk.before = walk0[6];
   walk.cta = static_cast<int>(blockIdx.x);
   walk.a = &a;
-  const int n_total = walk.hi > walk.g ? static_cast<int>(walk.hi - walk.g) : 0; /* tiles of this CTA */
+  int n_total = 0; /* KV tiles of this CTA (its span minus the padding slots) */
+  {
+    SpanWalk count = walk;
+    SpanPiece pc;
+    while (count.next(&pc)) n_total += pc.n;
+  }
 
   if (n_total == 0) {
     /* nothing to do: fall through to the common exit */
