@@ -979,6 +979,9 @@ struct SpanArgs {
   int n_seq, n_q, n_kv, gqa, max_seq;
   int max_slices, rows_cap;
   int min_span; /* tiles: no unit may be cut into more than max_slices pieces */
+  int early;    /* the batch description and the cache rows below every sequence's new
+                 * tokens are not written by the launch ahead: read them before the grid
+                 * dependency resolves */
   float qscale;
   unsigned int *err_word;
 };
@@ -1128,7 +1131,13 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
       if (i < a.n_seq) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.pos0_dev + i));
     }
   }
-  grid_dependency_wait();
+  /* With `early`, the launch ahead of this one in the stream (the append of this step's
+   * tokens) writes only q and the cache rows at and above each sequence's seq_pos0, and
+   * nothing writes the batch description (seq_pos0, cu_tokens, page table) any more.  So
+   * the span arithmetic, the page ids and every K/V tile that lies wholly below seq_pos0
+   * are fetched while that launch and the merge before it are still running; each role
+   * waits for the dependency right before it first touches what the append writes. */
+  if (!a.early) grid_dependency_wait();
 
   /* ---- where does this CTA's span start?  warp 0: total tiles, span length, and the
    * (sequence, KV head, tile) at global tile index cta * span */
@@ -1241,10 +1250,15 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
       SpanPiece pc;
       int G = 0;
       bool ok = true;
+      bool waited = !a.early;
       while (ok && walk.next(&pc)) {
         int page_next = page_of(pc.seq, pc.first);
         for (int j = 0; j < pc.n; ++j, ++G) {
           const int st = G % NSTAGE, round = G / NSTAGE;
+          if (!waited && (pc.first + j) * BN + BN > pc.pos0) { /* this tile may hold new rows */
+            grid_dependency_wait();
+            waited = true;
+          }
           const int page = page_next;
           if (j + 1 < pc.n) page_next = page_of(pc.seq, pc.first + j + 1);
           if (G >= NSTAGE) {
@@ -1277,6 +1291,7 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
     constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
     const uint32_t k_lo0 = umma_desc_lo(sbase + C::OFF_K, 16);
     const uint32_t v_lo0 = umma_desc_lo(sbase + C::OFF_V, WIDE ? 2048 : HALF_BYTES);
+    if (a.early) grid_dependency_wait(); /* Q and P come from threads that waited; be ordered too */
     /* two walkers: one for the S stream (two tiles ahead), one for the PV stream */
     SpanWalk ws = walk, wp = walk;
     SpanPiece ps, pp;
@@ -1409,6 +1424,7 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
       mbar_arrive(bar(Q_READY));
     };
 
+    if (a.early) grid_dependency_wait(); /* q is what the append ahead of this launch wrote */
     SpanWalk wk = walk;
     SpanPiece pc, nxt;
     bool have = wk.next(&pc);
@@ -1661,6 +1677,7 @@ wst_status_t launch_verify_span(const PrefillLaunch &P) {
   a.min_span = (max_tiles + static_cast<int>(cap) - 2) / (static_cast<int>(cap) - 1);
   if (a.min_span < 1) a.min_span = 1;
   a.qscale = P.scale * kLog2e;
+  a.early = decode_overlap_allowed() ? 1 : 0;
   a.err_word = device_error_word();
   if (!a.err_word) return WST_ERR_CUDA;
 

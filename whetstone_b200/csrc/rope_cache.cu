@@ -160,8 +160,12 @@ rope_append_kernel(const RopeArgs a) {
   /* Under programmatic dependent launch: a single-token append lets the next
    * kernel in the stream (the decode attention, which re-reads the one row
    * written here after its own wait) start its prologue right away. */
-  if (a.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (a.trigger_early && !PAGED) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  /* paged (verify): the kernel behind reads the batch description and old cache rows
+   * before its own dependency resolves, so it is released only now, when everything ahead
+   * of this append in the stream has completed */
+  if (a.trigger_early && PAGED) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int HD = 64 * E;
   constexpr int HALF = HD / 2;
   const int lane = threadIdx.x & 31;
@@ -235,8 +239,9 @@ template <bool PAGED>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 rope_append_any_kernel(const RopeArgs a) {
   /* may be launched with programmatic stream serialization like the fast path */
-  if (a.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (a.trigger_early && !PAGED) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (a.trigger_early && PAGED) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int hd = a.hd, half = hd >> 1;
   const int lane = threadIdx.x & 31;
   const int heads = a.n_q + a.n_kv;
@@ -304,12 +309,15 @@ wst_status_t launch_rope(const RopeArgs &a, const char *name) {
   const bool vec_ok = aligned16(a.qkv) && aligned16(a.k_cache) && aligned16(a.v_cache) &&
                       aligned16(a.cos_tab) && aligned16(a.sin_tab) &&
                       (!a.q_gain || aligned16(a.q_gain)) && (!a.k_gain || aligned16(a.k_gain));
-  /* A single-token append (decode) is launched with programmatic stream
-   * serialization and lets its dependents start early; larger appends are
-   * ordinary launches, complete before anything after them starts. */
+  /* A single-token append (decode) and the ragged paged append (verify) are launched
+   * with programmatic stream serialization and let their dependents start early; other
+   * appends are ordinary launches, complete before anything after them starts. */
   RopeArgs args = a;
   args.trigger_early = 0;
   if (!PAGED && a.n_tokens == 1 && vec_ok && decode_overlap_allowed()) args.trigger_early = 1;
+  /* the ragged paged append: the verify kernel behind it reads, before its own
+   * dependency resolves, only what this kernel does not write */
+  if (PAGED && decode_overlap_allowed()) args.trigger_early = 1;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = block;
