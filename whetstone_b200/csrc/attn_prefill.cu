@@ -1383,10 +1383,22 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
       return true;
     };
 
-    for (int g = 0; ok && g < 2 && g < n_total; ++g) ok = issue_s(g);
+    /* A score tile that opens a new piece waits for that piece's Q, which the softmax
+     * warps stage only after the last tile of the piece before: such an S is held back
+     * behind the next PV (the old piece's last), so that PV and the old piece's epilogue
+     * run while Q is on its way instead of after it. */
+    int s_next = 0; /* next score tile to issue; runs up to two ahead of the PV stream */
+    auto s_opens_piece = [&]() { return s_left == 0; };
+    for (; ok && s_next < 2 && s_next < n_total; ++s_next) ok = issue_s(s_next);
     for (int g = 0; ok && g < n_total; ++g) {
       ok = issue_pv(g);
-      if (ok && g + 2 < n_total) ok = issue_s(g + 2);
+      while (ok && s_next < n_total && s_next <= g + 2) {
+        /* two ahead normally; a piece-opening S not before the PV of the tile right
+         * before it has been issued */
+        if (s_opens_piece() && s_next > g + 1) break;
+        ok = issue_s(s_next);
+        ++s_next;
+      }
     }
   } else {
     /* ---- softmax + partial output: two threads per query row, 64 score columns each */
@@ -1432,6 +1444,16 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
     int G = 0, piece = 0;
     bool ok = true; /* warp-uniform */
     while (have) {
+      /* the piece after this one: its q rows towards L2 now, staged when this piece's
+       * last score tile has been read */
+      const bool more = wk.next(&nxt);
+      if (more && r < nxt.ntok * a.gqa) {
+        const char *qn = reinterpret_cast<const char *>(
+            a.q + static_cast<long long>(nxt.tok_begin + r / a.gqa) * a.q_tok_stride +
+            static_cast<long long>(nxt.kvh * a.gqa + r % a.gqa) * HD + half * OC);
+#pragma unroll
+        for (int b = 0; b < OC * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(qn + b));
+      }
       const int rows_valid = pc.ntok * a.gqa;
       const int lim = r < rows_valid ? min(pc.pos0 + r / a.gqa + 1, a.max_seq) : pc.kv_end;
       const int lim_min = min(pc.pos0 + 1, a.max_seq);
@@ -1536,7 +1558,6 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
        * BEFORE this piece's epilogue -- the MMA warp issues the next piece's first score
        * tile ahead of this piece's last PV and would otherwise wait for Q while the
        * epilogue waits for that PV. */
-      const bool more = wk.next(&nxt);
       if (more) stage_q(nxt);
 
       /* ---- epilogue: this piece's (acc, m, l) rows for the merge kernel */
