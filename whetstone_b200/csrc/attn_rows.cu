@@ -864,6 +864,80 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
   }
 }
 
+/* The slice merge for launches with few slices per unit and many rows (the ragged
+ * verify: at most a handful of slices, tens of query rows per unit): one WARP per
+ * (unit, row) instead of one block, eight rows per block, lane = four output columns,
+ * up to eight slices' rows in flight per lane at once, folded with a running maximum.
+ * An eighth as many blocks as attn_merge_kernel would launch, all resident in one wave. */
+template <int HD>
+__global__ void __launch_bounds__(256) attn_merge_rows_kernel(const MergeArgs a) {
+  constexpr int DR = HD + 4;
+  constexpr int LPR = HD / 4;
+  grid_launch_dependents();
+  grid_dependency_wait();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp, unit = blockIdx.y;
+  const int rb = unit % a.n_rowblk;
+  const int kvh = (unit / a.n_rowblk) % a.n_kv;
+  const int s = unit / (a.n_rowblk * a.n_kv);
+  int tok_begin = s * a.tok_seq_stride, n_tok = a.n_tok;
+  if (a.cu_tokens) {
+    tok_begin = a.cu_tokens[s];
+    n_tok = a.cu_tokens[s + 1] - tok_begin;
+  }
+  const int tok0 = rb * a.tpb;
+  if (tok0 >= n_tok) return;
+  const int ntok_blk = min(a.tpb, n_tok - tok0);
+  if (row >= ntok_blk * a.gqa || lane >= LPR) return;
+
+  const int ns = a.slice_counts ? min(a.slice_counts[unit], a.n_splits) : a.n_splits;
+  const float *base = a.scratch + (static_cast<long long>(unit) * a.n_splits * a.rows_cap + row) * DR;
+  const long long sp_stride = static_cast<long long>(a.rows_cap) * DR;
+  float M = -INFINITY, den = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sp0 = 0; sp0 < ns; sp0 += 8) {
+    float4 v[8];
+    float2 ml[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (sp0 + i < ns) {
+        v[i] = __ldcg(reinterpret_cast<const float4 *>(base + (sp0 + i) * sp_stride) + lane);
+        ml[i] = __ldcg(reinterpret_cast<const float2 *>(base + (sp0 + i) * sp_stride + HD));
+      } else {
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        ml[i] = make_float2(-INFINITY, 0.f);
+      }
+    }
+    float top = M;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) top = fmaxf(top, ml[i].x);
+    const float use = top == -INFINITY ? 0.f : top;
+    const float keep = ex2(M - use); /* 0 while nothing has been folded in yet */
+    acc.x *= keep;
+    acc.y *= keep;
+    acc.z *= keep;
+    acc.w *= keep;
+    den *= keep;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float wgt = ex2(ml[i].x - use);
+      acc.x = fmaf(wgt, v[i].x, acc.x);
+      acc.y = fmaf(wgt, v[i].y, acc.y);
+      acc.z = fmaf(wgt, v[i].z, acc.z);
+      acc.w = fmaf(wgt, v[i].w, acc.w);
+      den = fmaf(wgt, ml[i].y, den);
+    }
+    M = top;
+  }
+  const int head = kvh * a.gqa + row % a.gqa;
+  const int tok = tok_begin + tok0 + row / a.gqa;
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  store_half4(static_cast<__half *>(a.out) + (static_cast<long long>(tok) * a.n_q + head) * HD +
+                  4 * lane,
+              acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+}
+
 /* ------------------------------------------------- portable fallback kernel */
 
 /* One warp per (token, query head); eight lanes share a cache position, each
@@ -1242,9 +1316,17 @@ wst_status_t launch_split_merge(const SplitMerge &S) {
   m.world = S.world;
   m.err_word = device_error_word();
   if (!m.err_word) return WST_ERR_CUDA;
-  const dim3 mgrid(static_cast<unsigned>(S.rows_cap), static_cast<unsigned>(S.n_units));
-  cudaError_t e = S.hd == 128 ? launch_pdl(attn_merge_kernel<128>, mgrid, dim3(128), 0, m)
-                              : launch_pdl(attn_merge_kernel<64>, mgrid, dim3(128), 0, m);
+  cudaError_t e;
+  if (S.slice_counts && !S.partial_out && S.world <= 1) {
+    /* few slices, many rows: a warp per row */
+    const dim3 rgrid(static_cast<unsigned>((S.rows_cap + 7) / 8), static_cast<unsigned>(S.n_units));
+    e = S.hd == 128 ? launch_pdl(attn_merge_rows_kernel<128>, rgrid, dim3(256), 0, m)
+                    : launch_pdl(attn_merge_rows_kernel<64>, rgrid, dim3(256), 0, m);
+  } else {
+    const dim3 mgrid(static_cast<unsigned>(S.rows_cap), static_cast<unsigned>(S.n_units));
+    e = S.hd == 128 ? launch_pdl(attn_merge_kernel<128>, mgrid, dim3(128), 0, m)
+                    : launch_pdl(attn_merge_kernel<64>, mgrid, dim3(128), 0, m);
+  }
   if (e != cudaSuccess)
     return fail(WST_ERR_CUDA, "%s (merge launch): %s (%s)", S.name, cudaGetErrorString(e),
                 cudaGetErrorName(e));
