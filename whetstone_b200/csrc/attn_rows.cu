@@ -1317,8 +1317,8 @@ wst_status_t launch_split_merge(const SplitMerge &S) {
   m.err_word = device_error_word();
   if (!m.err_word) return WST_ERR_CUDA;
   cudaError_t e;
-  if (S.slice_counts && !S.partial_out && S.world <= 1) {
-    /* few slices, many rows: a warp per row */
+  if ((S.slice_counts || (S.n_splits <= 16 && S.rows_cap >= 16)) && !S.partial_out && S.world <= 1) {
+    /* few slices, many rows (ragged verify, a sliced chunk): a warp per row */
     const dim3 rgrid(static_cast<unsigned>((S.rows_cap + 7) / 8), static_cast<unsigned>(S.n_units));
     e = S.hd == 128 ? launch_pdl(attn_merge_rows_kernel<128>, rgrid, dim3(256), 0, m)
                     : launch_pdl(attn_merge_rows_kernel<64>, rgrid, dim3(256), 0, m);
