@@ -61,8 +61,7 @@ struct RowsArgs {
   int n_splits, n_rowblk, tpb, rows_cap;
   int nstage;      /* ring stages in use, 2 .. Cfg::NSTAGE */
   int early_depth; /* 0: nothing is requested before the grid dependency resolves; else the
-                    * number of tiles requested at once ahead of it (the rest of the ring
-                    * follows one tile at a time) */
+                    * number of tiles kept in flight ahead of it */
   int via_scratch; /* a single slice still writes its row to scratch: the merge kernel
                     * follows (it carries the cross-GPU exchange) */
 };
@@ -195,10 +194,10 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
    * newest cache row; every row in a tile below that one was written by launches
    * that finished long ago.  So the slice's first tiles are requested right here,
    * before the dependency is resolved, and their latency hides behind the tail of
-   * the previous kernel: `early_depth` of them at once, the rest of the ring one at
-   * a time (tile i+1 when tile i has landed, or as soon as a consumer thread
-   * reports the dependency resolved, whichever comes first), so that the kernel
-   * ahead keeps getting its own last loads out in between.  The newest row of a
+   * the previous kernel: `early_depth` of them at once, then one more whenever one
+   * has landed (so that many stay in flight; all of the ring as soon as a consumer
+   * thread reports the dependency resolved), so that the kernel ahead keeps getting
+   * its own last loads out in between.  The newest row of a
    * tile requested this early is read again after the wait, with plain loads, and
    * stored over the copy in shared memory. */
   /* Let the kernels behind this one in the stream be scheduled as early as there is
@@ -220,11 +219,11 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
     }
     if (warp == C::CWARPS) {
       if (lane == 0 && spec > 0) {
-        const int burst = a.early_depth < spec ? a.early_depth : spec;
-        for (int i = 0; i < burst; ++i) issue(i);
-        for (int i = burst; i < spec; ++i) {
+        const int window = a.early_depth < spec ? a.early_depth : spec;
+        for (int i = 0; i < window; ++i) issue(i);
+        for (int i = window; i < spec; ++i) { /* `window` tiles in flight at a time */
           const long long t0 = clock64();
-          while (!mbar_try_wait(full_u32 + 8 * (i - 1), 0) && ld_shared_volatile(go_u32) == 0u)
+          while (!mbar_try_wait(full_u32 + 8 * (i - window), 0) && ld_shared_volatile(go_u32) == 0u)
             if (clock64() - t0 > kWaitCycleLimit) break; /* only a hint: go on */
           issue(i);
         }
