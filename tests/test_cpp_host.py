@@ -15,6 +15,14 @@ def test_cpp_host_layer_compiles():
     assert BIN.exists()
 
 
+def test_cpp_paged_kv_manager_tests_pass():
+    """tests/cpp/paged_kv_tests.cpp: the page manager and scheduler used from C++ (no GPU)."""
+    subprocess.run(["make", "-C", str(ROOT / "tests" / "cpp")], check=True, capture_output=True)
+    proc = subprocess.run([str(BIN.parent / "paged_kv_tests")], capture_output=True, text=True,
+                          timeout=60)
+    assert proc.returncode == 0 and "0 failed" in proc.stdout, proc.stdout + proc.stderr
+
+
 @pytest.mark.gpu
 def test_cpp_kernel_tests_pass():
     if not BIN.exists():

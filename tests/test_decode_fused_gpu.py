@@ -221,3 +221,94 @@ def test_sharded_decode_wait_runs_out_and_reports():
     torch.cuda.synchronize()
     assert decode.device_error() == 0
     assert torch.equal(out1, ref) or (out1.float() - ref.float()).abs().max().item() <= 1e-3
+
+
+# ------------------------------------------------ switches and the chunk workspace
+
+def test_decode_with_the_early_requests_switched_off():
+    """wst_b200_set_decode_overlap(0): no cache row is asked for before everything ahead
+    in the stream has finished (for hosts that cannot keep the stream-order rule); the
+    results do not change."""
+    from whetstone_b200._ffi import check, lib
+    check(lib.wst_b200_set_decode_overlap(0))
+    try:
+        n_q, n_kv, hd, theta, prefix, steps = 28, 4, 128, 1e6, 900, 8
+        rng = np.random.default_rng(77)
+        max_seq = prefix + steps + 3
+        width = (n_q + 2 * n_kv) * hd
+        table = decode.RopeTable(max_seq, hd, theta)
+        cache = decode.KvCache(n_kv, n_q, hd, max_seq)
+        pre, rows = workloads.f16_values(rng, (prefix, width)), workloads.f16_values(rng, (steps, width))
+        rows_d = dev(rows)
+        outs = torch.zeros(steps, n_q * hd, dtype=torch.float16, device="cuda")
+        cur = decode.DeviceCursor(prefix)
+        chunk.rope_cache(dev(pre), cache, table, n_q, 0, prefix)
+        for j in range(steps):
+            decode.rope_cache(rows_d[j], cache, table, n_q, cur)
+            decode.attn_decode(rows_d[j], cache, outs[j], n_q, cur)
+            cur.advance(max_seq)
+        torch.cuda.synchronize()
+        _, k_pre, v_pre = orc.rope_append(pre, np.arange(prefix), n_q, n_kv, hd, theta)
+        qr, k_new, v_new = orc.rope_append(rows, prefix + np.arange(steps), n_q, n_kv, hd, theta)
+        want = orc.attention_blocked(qr, np.concatenate([k_pre, k_new]), np.concatenate([v_pre, v_new]),
+                                     prefix + 1 + np.arange(steps))
+        assert_close_per_head(host(outs).astype(np.float64).reshape(steps, n_q, hd), want,
+                              "decode without early requests")
+    finally:
+        check(lib.wst_b200_set_decode_overlap(1))
+
+
+def test_chunk_call_without_a_workspace_runs_unsplit_and_says_so():
+    """A thread's first wst_attn_chunk that wants to split the KV range, made under
+    stream capture: no workspace can be allocated, so the launch runs unsplit, returns
+    WST_OK and leaves a note in the thread's error text; the captured graph still
+    computes the right thing.  After wst_b200_reserve_chunk_workspace the same call
+    leaves no note."""
+    import ctypes
+    import threading
+
+    from whetstone_b200._ffi import lib
+
+    n_q, n_kv, hd, pos0, n = 28, 4, 128, 3000, 6
+    rng = np.random.default_rng(41)
+    max_seq = pos0 + n + 10
+    k, v = rand16(rng, (n_kv, pos0 + n, hd)), rand16(rng, (n_kv, pos0 + n, hd))
+    cache = decode.KvCache(n_kv, n_q, hd, max_seq)
+    cache.k[:, :pos0 + n], cache.v[:, :pos0 + n] = dev(k), dev(v)
+    width = (n_q + 2 * n_kv) * hd
+    qkv = np.zeros((n, width), np.float32)
+    q = workloads.f16_values(rng, (n, n_q, hd))
+    qkv[:, : n_q * hd] = q.reshape(n, -1)
+    qd = dev(qkv)
+    out = torch.zeros(n * n_q * hd, dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+    notes = {}
+
+    def worker():
+        P = ctypes.c_void_p
+        args = (P(qd.data_ptr()), P(cache.k.data_ptr()), P(cache.v.data_ptr()), P(out.data_ptr()),
+                n_q, n_kv, hd, pos0, n, max_seq, ctypes.c_float(1.0 / np.sqrt(hd)))
+        assert lib.wst_device_set(torch.cuda.current_device()) == 0
+        assert lib.wst_b200_set_stream(None) == 0          # this thread's own default stream
+        assert lib.wst_graph_capture_begin() == 0, lib.wst_last_error()
+        status = lib.wst_attn_chunk(*args)
+        notes["captured"] = (status, lib.wst_last_error().decode())
+        graph = ctypes.c_void_p()
+        assert lib.wst_graph_capture_end(ctypes.byref(graph)) == 0, lib.wst_last_error()
+        assert lib.wst_graph_launch(graph) == 0 and lib.wst_stream_sync() == 0
+        assert lib.wst_graph_destroy(graph) == 0
+        notes["reserve"] = lib.wst_b200_reserve_chunk_workspace()
+        lib.wst_attn_decode_noscratch(None, None, None, None, 1, 1, 64, None, 1, 0.0)  # resets the text
+        status = lib.wst_attn_chunk(*args)
+        notes["eager"] = (status, lib.wst_last_error().decode())
+        assert lib.wst_stream_sync() == 0
+
+    t = threading.Thread(target=worker)
+    t.start()
+    t.join()
+    assert notes["captured"][0] == 0 and "without splitting" in notes["captured"][1], notes
+    assert notes["reserve"] == 0
+    assert notes["eager"][0] == 0 and "without splitting" not in notes["eager"][1], notes
+    want = orc.chunk_attention(q.astype(np.float64), k, v, pos0, 1.0 / np.sqrt(hd))
+    assert_close_per_head(host(out).astype(np.float64).reshape(n, n_q, hd), want,
+                          "chunk through the unsplit and the split launch")

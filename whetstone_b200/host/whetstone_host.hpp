@@ -15,7 +15,8 @@
  *   chunk::attn              src/chunk.rs:207-254
  *   Graph, Event             src/decode.rs:543-655
  * PagedKvCache and the paged:: / sharded decode wrappers have no counterpart in
- * the engine (it has one contiguous sequence on one GPU).
+ * the engine (it has one contiguous sequence on one GPU).  The host-side page manager
+ * and batch scheduler that produce the paged entry points' arrays are in paged_kv.hpp.
  */
 #pragma once
 
@@ -401,6 +402,21 @@ class PeerMailbox {
       a[g] = reinterpret_cast<uint64_t>(addr_[g]);
     }
     table_ = DeviceBuffer<uint64_t>::from_slice(a);
+  }
+  /* Attention over this rank's shard (rows [0, *len) of `shard`) and the exchange as one
+   * call: wst_attn_decode_sharded.  q replicated on every rank; every rank gets `out`. */
+  void decode(const DeviceBuffer<float> &qkv, KvCache &shard, DeviceBuffer<uint16_t> &out,
+              const DeviceCursor &len) {
+    const size_t hd = shard.head_dim;
+    if (hd != head_dim_ || qkv.len() < n_q_ * hd || out.len() != n_q_ * hd)
+      throw Error::shape("PeerMailbox::decode: qkv must hold n_q*head_dim queries, out exactly that");
+    check(wst_attn_decode_sharded(qkv.as_ptr(), shard.k.as_ptr(), shard.v.as_ptr(),
+                                  shard.partials.as_mut_ptr(), out.as_mut_ptr(),
+                                  static_cast<int32_t>(n_q_), static_cast<int32_t>(shard.n_kv),
+                                  static_cast<int32_t>(hd), len.buf.as_ptr(),
+                                  static_cast<int32_t>(shard.max_seq),
+                                  1.0f / std::sqrt(static_cast<float>(hd)), table_.as_ptr(),
+                                  state_.as_mut_ptr(), rank_, world_));
   }
   void merge(const DeviceBuffer<float> &my_triples, DeviceBuffer<uint16_t> &out) {
     if (my_triples.len() != n_q_ * (head_dim_ + 2) || out.len() != n_q_ * head_dim_)
