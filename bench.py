@@ -179,12 +179,14 @@ class Timing(float):
         return obj
 
 
-def timed_graph(torch, fn, steps, warmup, dist=None, min_region_s=MIN_REGION_S):
+def timed_graph(torch, fn, steps, warmup, dist=None, min_region_s=None):
     """Captures fn() into a CUDA graph (after eager warm-up) and replays it in blocks
     of `steps` between CUDA events on the launching stream, block after block with no
     gap, until at least `min_region_s` of device time have passed; a barrier and a
     synchronize bracket the whole region.  Returns seconds per step (mean over the
     region, max over ranks) with the per-block statistics attached."""
+    if min_region_s is None:
+        min_region_s = MIN_REGION_S
     for _ in range(2):
         fn()
     torch.cuda.synchronize()
@@ -853,10 +855,15 @@ def main():
     ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "refcuda"],
                     help="run one workload only (c3 = the headline line without 'also')")
     ap.add_argument("--no-long", action="store_true", help="skip the 262144-row decode leg")
+    ap.add_argument("--min-region-s", type=float, default=0.25,
+                    help="repeat the --steps block until this much device time has passed "
+                         "(0: one block; for runs under a profiler)")
     ap.add_argument("--long-layers", type=int, default=8)
     ap.add_argument("--c4-layers", type=int, default=4)
     ap.add_argument("--c5-layers", type=int, default=4)
     args = ap.parse_args()
+    global MIN_REGION_S
+    MIN_REGION_S = args.min_region_s
     if args.impl == "reference":
         run_reference(args)
     else:
