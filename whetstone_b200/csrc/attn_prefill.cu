@@ -311,7 +311,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
     for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
       if (!mbar_wait(bar(K_FULL + j), 0, a.err_word, 0x214u)) { ok = false; break; }
       tc_fence_after_sync();
-      if (lane == 0) {
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) s_step(j, ks);
         umma_commit(bar(S_FULL + j));
@@ -349,7 +349,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       if (!mbar_wait(bar(P_READY), i & 1, a.err_word, 0x211u)) { ok = false; break; }
       tc_fence_after_sync();
-      if (lane == 0) {
+      if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) pv_step(i, k);
         umma_commit(bar(PV_DONE));
@@ -359,7 +359,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
       if (has_s) {
         if (!mbar_wait(bar(S_FREE + (j & 1)), ((j >> 1) - 1) & 1, a.err_word, 0x215u)) { ok = false; break; }
         tc_fence_after_sync();
-        if (lane == 0) {
+        if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) s_step(j, k);
           umma_commit(bar(S_FULL + (j & 1)));
@@ -719,7 +719,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     tc_fence_after_sync();
 
     auto issue_s = [&](int t, int j) { /* S_t = Q_t K(j)^T */
-      if (lane == 0) {
+      if (elect_one()) {
         const uint32_t q_lo = umma_desc_lo(sbase + C::OFF_Q + t * C::Q_BYTES, 16);
         const uint32_t k_lo = umma_desc_lo(sbase + C::OFF_RING + ((2 * j) % NSLOT) * KV_BYTES, 16);
 #pragma unroll
@@ -755,7 +755,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       if (!mbar_wait(bar(P_READY + t), j & 1, a.err_word, 0x311u)) return false;
       tc_fence_after_sync();
-      if (lane == 0) {
+      if (elect_one()) {
         const uint32_t v_lo = umma_desc_lo(vb, HALF_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
@@ -775,12 +775,12 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
       if (j < n_tiles[0]) issue_s(0, j);
       if (j >= 1 && j - 1 < n_tiles[1]) {
         if (!issue_pv(1, j - 1)) break;
-        if (lane == 0) umma_commit(bar(EMPTY + (2 * j - 1) % NSLOT)); /* last reader of V(j-1) */
+        if (elect_one()) umma_commit(bar(EMPTY + (2 * j - 1) % NSLOT)); /* last reader of V(j-1) */
         __syncwarp();
       }
       if (j < n_tiles[1]) {
         issue_s(1, j);
-        if (lane == 0) umma_commit(bar(EMPTY + (2 * j) % NSLOT)); /* last reader of K(j) */
+        if (elect_one()) umma_commit(bar(EMPTY + (2 * j) % NSLOT)); /* last reader of K(j) */
         __syncwarp();
       }
       if (j < n_tiles[0] && !issue_pv(0, j)) break;
@@ -1313,7 +1313,7 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
       if (g >= 2 && !mbar_wait(bar(S_FREE + (g & 1)), ((g >> 1) - 1) & 1, a.err_word, 0x515u))
         return false;
       tc_fence_after_sync();
-      if (lane == 0) {
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           if constexpr (WIDE) {
@@ -1365,7 +1365,7 @@ attn_verify_span_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       if (!mbar_wait(bar(P_READY), g & 1, a.err_word, 0x511u)) return false;
       tc_fence_after_sync();
-      if (lane == 0) {
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           /* P columns 16kk .. 16kk+15: (WIDE) rows 0-7 or 8-15 of two neighbouring pages */

@@ -214,6 +214,18 @@ __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+/* True in exactly one lane of a converged warp (the same lane every time).  The
+ * issuer of tcgen05.mma and tcgen05.commit is chosen with this and not with
+ * `lane == 0`: behind a comparison of the lane index the compiler has to carry the
+ * descriptors from ordinary registers to the uniform ones instruction by instruction,
+ * and one MMA then costs the warp 70 clocks to issue -- more than the 64 the tensor
+ * pipe needs for 128 x 128 x 16 -- against some 40 behind the election. */
+__device__ __forceinline__ bool elect_one() {
+  uint32_t p;
+  asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\tselp.u32 %0, 1, 0, e;\n\t}" : "=r"(p));
+  return p != 0;
+}
+
 /* D[tmem] (+)= A[smem desc] * B[smem desc]; issued by ONE thread. */
 __device__ __forceinline__ void umma_ss_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                             uint32_t idesc, uint32_t accumulate) {
