@@ -587,22 +587,35 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
 
 
 /* ------------------------------------------------------------------------
- * Two query tiles per CTA.
+ * Two query tiles per CTA: attn_prefill_pair_kernel.
  *
- * Alternative schedule, selected with wst_b200_set_kernel_choice(4).
- * With one tile per CTA the softmax of a tile (16384 exponentials at 16 per
- * clock and SM, plus loads, max, pack, stores) is a longer critical path than
- * the tile's two MMAs, and the tensor core waits for P.  Here a CTA owns TWO
- * 128-row tiles of the same KV head, each with its own softmax warpgroup, and
- * the MMA warp alternates between them:
+ * A CTA owns TWO 128-row tiles of the same KV head, so every K/V tile fetched from
+ * L2 serves 256 query rows.  Each tile has its own softmax warpgroup AND its own
+ * MMA-issuing warp; the two tiles share only the K/V ring and the tensor pipe.
  *
- *     S0(j)  PV1(j-1)  S1(j)  PV0(j)  S0(j+1)  PV1(j)  ...
+ * Tensor memory is exactly full -- S0 S1 O0 O1 at 128 fp32 columns each -- and P_t
+ * (fp16) goes over columns 0..63 of S_t, so the scores of tile j+1 cannot be written
+ * where P(j) still waits for its MMA.  Were S(j+1) issued whole, after PV(j), every
+ * tile would run the chain  softmax -> PV -> S -> softmax  end to end (measured: 4100
+ * clocks per KV tile for 2048 clocks of tensor work).  The score MMA is therefore cut
+ * in two along the keys:
  *
- * so one tile's MMAs run while the other tile's softmax is in flight, and every
- * K/V tile fetched from L2 serves 256 query rows.  Tensor memory is exactly
- * full: S0 S1 O0 O1 at 128 fp32 columns each; P_i is written over the first 64
- * columns of S_i once the scores are in registers (the next S_i is issued after
- * PV_i, and the tensor pipe executes in order).  Q_i stay in shared memory.
+ *   S_hi(j+1) = Q K(j+1)[64..127]^T -> columns 64..127, issued as soon as the softmax
+ *               of tile j has read those columns into registers (HI_FREE);
+ *   S_lo(j+1) = Q K(j+1)[0..63]^T   -> columns 0..63, issued behind PV(j), which the
+ *               tensor pipe finishes first since it executes in order.
+ *
+ * The softmax of tile j+1 starts on the upper keys the moment it is done with tile j,
+ * and the lower keys arrive while it works; each half is one step of the online
+ * softmax (its own maximum, offset kept unless a row grows by more than 2^8).
+ * An N = 64 MMA with both operands in shared memory costs 48 clocks, not 32 (the
+ * 4 KB Q operand alone takes 32 at 128 bytes per clock), so the scores cost 768
+ * clocks per tile where one N = 128 instruction stream costs 512: the tensor pipe
+ * has 2560 clocks of work per KV tile and CTA, and that is the new bound.
+ *
+ * The issuing warps matter as much as the pipe: every wait, election, fence and
+ * commit costs the issuing warp 50 to 100 clocks with nothing to overlap it, and one
+ * warp driving both tiles spent more time on those than the pipe spent on the MMAs.
  * ---------------------------------------------------------------------- */
 template <int HD>
 struct P2Cfg {
@@ -611,22 +624,53 @@ struct P2Cfg {
   static constexpr int HALF_BYTES = BN * 128;
   static constexpr int Q_BYTES = NH * HALF_BYTES;   /* one query tile */
   static constexpr int KV_BYTES = NH * HALF_BYTES;
-  /* K and V tiles go through ONE ring in the order they are consumed, K(0) V(0)
+  /* K and V tiles go through ONE ring in the order they are fetched, K(0) V(0)
    * K(1) V(1) ...: next to the two query tiles shared memory has room for five
-   * 32 KB slots (head_dim 128), and five slots in one ring keep two and a half
-   * KV tiles in flight where separate K and V rings could hold two each at most;
-   * a tile takes some 2500 clocks to arrive from L2. */
+   * 32 KB slots (head_dim 128).  K(j+1) and V(j) are in use during step j, the
+   * other three slots are in flight; a tile takes some 2500 clocks to arrive from L2. */
   static constexpr int NSLOT = HD == 128 ? 5 : 8;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_RING = OFF_Q + 2 * Q_BYTES;
   static constexpr int OFF_BAR = OFF_RING + NSLOT * KV_BYTES;
-  static constexpr int NBAR = 2 * NSLOT + 2 + 2 + 2 + 1;
+  static constexpr int NBAR = 2 * NSLOT + 2 * 6;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
-  static constexpr int THREADS = 320; /* 2 x 4 softmax warps, MMA warp, TMA warp: 204 registers each */
-  static constexpr int COL_S = 0;     /* S_i at COL_S + i*128, P_i over its first 64 columns */
-  static constexpr int COL_O = 256;   /* O_i at COL_O + i*128 */
+  static constexpr int THREADS = 352; /* 2 x 4 softmax warps, 2 MMA warps, TMA warp */
+  static constexpr int COL_S = 0;     /* S_t at COL_S + t*128, P_t over its first 64 columns */
+  static constexpr int COL_O = 256;   /* O_t at COL_O + t*128 */
   static constexpr int TMEM_COLS = 512;
 };
+
+/* One half (64 keys) of a score row as a step of the online softmax: the offset
+ * m_cur moves only if some row of the warp grows by more than 2^8 (or `force`);
+ * p = 2^(s - offset) packed to fp16 pairs, returns their fp32 sum.  Subtraction and
+ * summation run two lanes wide (f32x2); the 64 exponentials are what bounds it. */
+__device__ __forceinline__ float softmax_half(uint32_t (&sv)[64], uint32_t (&pk)[32], float &m_cur,
+                                              bool force) {
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 64; c += 8)
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
+  const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+  const bool grow = force || mx > m_cur + 8.f;
+  if (__any_sync(0xffffffffu, grow)) m_cur = fmaxf(m_cur, mx);
+  const float m_use = m_cur == -INFINITY ? 0.f : m_cur;
+  const uint64_t mm = pack_f32x2(m_use, m_use);
+  uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float x0, x1;
+    unpack_f32x2(sub_f32x2(pack_f32x2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), mm),
+                 x0, x1);
+    const float p0 = ex2(x0), p1 = ex2(x1);
+    acc[i & 3] = add_f32x2(acc[i & 3], pack_f32x2(p0, p1));
+    pk[i] = pack_half2(p0, p1);
+  }
+  float s0, s1;
+  unpack_f32x2(add_f32x2(add_f32x2(acc[0], acc[1]), add_f32x2(acc[2], acc[3])), s0, s1);
+  return s0 + s1;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(P2Cfg<HD>::THREADS, 1)
@@ -644,8 +688,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
   auto bar = [bar0](int i) { return bar0 + 8u * i; };
   /* ring item 2j is K(j), item 2j+1 is V(j); item i lives in slot i % NSLOT */
   constexpr int FULL = 0, EMPTY = NSLOT;
-  constexpr int S_FULL = 2 * NSLOT, P_READY = S_FULL + 2, O_DONE = P_READY + 2;
-  constexpr int Q_READY = O_DONE + 2;
+  constexpr int SHI_FULL = 2 * NSLOT, SLO_FULL = SHI_FULL + 2, HI_FREE = SLO_FULL + 2;
+  constexpr int P_READY = HI_FREE + 2, O_DONE = P_READY + 2, Q_READY = O_DONE + 2;
+  constexpr int MMA_WARP0 = 8, TMA_WARP = 10;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + C::OFF_BAR + C::NBAR * 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -657,19 +702,21 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSLOT; ++i) {
       mbar_init(bar(FULL + i), 1);
-      mbar_init(bar(EMPTY + i), 1);
+      mbar_init(bar(EMPTY + i), 2); /* one arrival per MMA warp */
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(SHI_FULL + i), 1);
+      mbar_init(bar(SLO_FULL + i), 1);
+      mbar_init(bar(HI_FREE + i), 128);
       mbar_init(bar(P_READY + i), 128);
       mbar_init(bar(O_DONE + i), 1);
+      mbar_init(bar(Q_READY + i), 128);
     }
-    mbar_init(bar(Q_READY), 256);
     mbar_init_fence();
     tma_prefetch_desc(&kmap);
     tma_prefetch_desc(&vmap);
   }
-  if (warp == 8) {
+  if (warp == MMA_WARP0) {
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -682,22 +729,26 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
 
   const int pos0 = a.pos0_dev ? max(a.pos0_dev[seq], 0) : a.pos0;
   const int plane = seq * a.n_kv + kvh;
-  /* tile t of the pair: tokens [tok0[t], tok0[t] + ntok[t]); a missing second tile
+  /* tile t of the pair: tokens tok0_[t] .. tok0_[t] + ntok_[t] - 1; a missing second tile
    * (odd tile count) runs with zero rows over the first tile's range */
-  int tok0[2], ntok[2], kv_end[2], n_tiles[2];
+  int tok0_[2], ntok_[2], kv_end_[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int qt = 2 * pair + t;
-    tok0[t] = qt * a.tpt;
-    ntok[t] = qt < a.n_qtiles ? min(a.tpt, a.n - tok0[t]) : 0;
-    kv_end[t] = ntok[t] > 0 ? min(pos0 + tok0[t] + ntok[t], a.max_seq) : 0;
+    tok0_[t] = qt * a.tpt;
+    ntok_[t] = qt < a.n_qtiles ? min(a.tpt, a.n - tok0_[t]) : 0;
+    kv_end_[t] = ntok_[t] > 0 ? min(pos0 + tok0_[t] + ntok_[t], a.max_seq) : 0;
   }
-  if (ntok[1] == 0) kv_end[1] = kv_end[0];
-  n_tiles[0] = (kv_end[0] + BN - 1) / BN;
-  n_tiles[1] = (kv_end[1] + BN - 1) / BN; /* >= n_tiles[0] */
-  const int T = n_tiles[1];
+  if (ntok_[1] == 0) kv_end_[1] = kv_end_[0];
+  const int kv_end_all = kv_end_[1];
+  /* this warp's tile (warps 0-3 and 8: tile 0; warps 4-7 and 9: tile 1) */
+  const int my_t = warp < 8 ? warp >> 2 : (warp - 8) & 1;
+  const int my_tok0 = my_t ? tok0_[1] : tok0_[0], my_ntok = my_t ? ntok_[1] : ntok_[0];
+  const int my_kv_end = my_t ? kv_end_[1] : kv_end_[0];
+  const int my_tiles = (my_kv_end + BN - 1) / BN;
+  const int T = (kv_end_all + BN - 1) / BN; /* tile 1 sees at least as far as tile 0 */
 
-  if (warp == 9) {
+  if (warp == TMA_WARP) {
     /* ------------------------------------------------------ TMA producer */
     if (lane == 0) {
       for (int i = 0; i < 2 * T; ++i) {
@@ -711,38 +762,59 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
                       bar(FULL + slot), h * 64, j * BN, plane);
       }
     }
-  } else if (warp == 8) {
-    /* -------------------------------------------------------- MMA issuer */
-    constexpr uint32_t idesc_qk = umma_idesc(128, BN, 0);
+  } else if (warp >= MMA_WARP0) {
+    /* ------------------------------------- MMA issuer of tile t = warp - 8 */
+    const int t = my_t;
+    const int nt = my_tiles;
+    constexpr uint32_t idesc_qk = umma_idesc(128, BN / 2, 0);
     constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
-    bool ok = mbar_wait(bar(Q_READY), 0, a.err_word, 0x310u);
+    bool ok = mbar_wait(bar(Q_READY + t), 0, a.err_word, 0x310u);
     tc_fence_after_sync();
+    const uint32_t q_lo = umma_desc_lo(sbase + C::OFF_Q + t * C::Q_BYTES, 16);
+    const uint32_t s_col = tmem + C::COL_S + t * 128;
 
-    auto issue_s = [&](int t, int j) { /* S_t = Q_t K(j)^T */
+    auto full_wait = [&](int item, unsigned code) {
+      return mbar_wait(bar(FULL + item % NSLOT), (item / NSLOT) & 1, a.err_word, code);
+    };
+    /* S_t(j), keys 64*part .. 64*part+63, into columns 64*part .. of the score buffer */
+    auto issue_s = [&](int j, int part) {
+      const uint32_t k_lo =
+          umma_desc_lo(sbase + C::OFF_RING + ((2 * j) % NSLOT) * KV_BYTES + part * (64 * 128), 16);
       if (elect_one()) {
-        const uint32_t q_lo = umma_desc_lo(sbase + C::OFF_Q + t * C::Q_BYTES, 16);
-        const uint32_t k_lo = umma_desc_lo(sbase + C::OFF_RING + ((2 * j) % NSLOT) * KV_BYTES, 16);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
-          umma_ss_f16_lohi(tmem + C::COL_S + t * 128, q_lo + off, k_lo + off, kDescHi, idesc_qk,
-                           ks > 0);
+          umma_ss_f16_lohi(s_col + part * 64, q_lo + off, k_lo + off, kDescHi, idesc_qk, ks > 0);
         }
-        umma_commit(bar(S_FULL + t));
+        umma_commit(bar((part ? SHI_FULL : SLO_FULL) + t));
+        if (part == 0) umma_commit(bar(EMPTY + (2 * j) % NSLOT)); /* this warp is done with K(j) */
       }
       __syncwarp();
     };
-    auto issue_pv = [&](int t, int j) -> bool { /* O_t += P_t V(j) */
+
+    if (ok && nt > 0) {
+      ok = full_wait(0, 0x314u);
+      tc_fence_after_sync();
+      if (ok) {
+        issue_s(0, 1);
+        issue_s(0, 0);
+      }
+    }
+    for (int j = 0; ok && j < nt; ++j) {
+      const bool more = j + 1 < nt;
+      if (more) {
+        if (!full_wait(2 * j + 2, 0x314u) ||
+            !mbar_wait(bar(HI_FREE + t), j & 1, a.err_word, 0x313u)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_s(j + 1, 1);
+      }
       const int item = 2 * j + 1;
-      /* the first PV that reads this tile waits for it (the second finds it there) ... */
-      const bool first_use = t == 0 || j >= n_tiles[0];
-      if (first_use &&
-          !mbar_wait(bar(FULL + item % NSLOT), (item / NSLOT) & 1, a.err_word, 0x312u)) return false;
+      if (!full_wait(item, 0x312u)) { ok = false; break; }
       const uint32_t vb = sbase + C::OFF_RING + (item % NSLOT) * KV_BYTES;
-      /* ... and clears its rows past the live data, which may hold anything, and
-       * 0 * NaN is NaN */
-      if (first_use && j * BN + BN > kv_end[1]) {
-        const int first = kv_end[1] - j * BN;
+      /* rows past the live data may hold anything, and 0 * NaN is NaN: clear them
+       * (both MMA warps do, whichever comes first; the second writes zeros over zeros) */
+      if (j * BN + BN > kv_end_all) {
+        const int first = kv_end_all - j * BN;
         for (int idx = first * (NH * 8) + lane; idx < BN * NH * 8; idx += 32) {
           const int row = idx / (NH * 8), rest = idx % (NH * 8);
           asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(
@@ -753,44 +825,32 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
         fence_async_smem();
         __syncwarp();
       }
-      if (!mbar_wait(bar(P_READY + t), j & 1, a.err_word, 0x311u)) return false;
+      if (!mbar_wait(bar(P_READY + t), j & 1, a.err_word, 0x311u)) { ok = false; break; }
       tc_fence_after_sync();
-      if (elect_one()) {
+      if (elect_one()) { /* O_t += P_t V(j) */
         const uint32_t v_lo = umma_desc_lo(vb, HALF_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          umma_ts_f16_lohi(tmem + C::COL_O + t * 128, tmem + C::COL_S + t * 128 + kk * 8,
-                           v_lo + ((kk * 2048) >> 4), kDescHi, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-        if (j == n_tiles[t] - 1) umma_commit(bar(O_DONE + t));
+          umma_ts_f16_lohi(tmem + C::COL_O + t * 128, s_col + kk * 8, v_lo + ((kk * 2048) >> 4),
+                           kDescHi, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        if (!more) umma_commit(bar(O_DONE + t));
+        umma_commit(bar(EMPTY + item % NSLOT)); /* this warp is done with V(j) */
       }
       __syncwarp();
-      return true;
-    };
-
-    for (int j = 0; ok && j <= T; ++j) {
-      if (j < T) {
-        if (!mbar_wait(bar(FULL + (2 * j) % NSLOT), ((2 * j) / NSLOT) & 1, a.err_word, 0x314u)) break;
-        tc_fence_after_sync();
-      }
-      if (j < n_tiles[0]) issue_s(0, j);
-      if (j >= 1 && j - 1 < n_tiles[1]) {
-        if (!issue_pv(1, j - 1)) break;
-        if (elect_one()) umma_commit(bar(EMPTY + (2 * j - 1) % NSLOT)); /* last reader of V(j-1) */
-        __syncwarp();
-      }
-      if (j < n_tiles[1]) {
-        issue_s(1, j);
-        if (elect_one()) umma_commit(bar(EMPTY + (2 * j) % NSLOT)); /* last reader of K(j) */
-        __syncwarp();
-      }
-      if (j < n_tiles[0] && !issue_pv(0, j)) break;
+      if (more) issue_s(j + 1, 0); /* behind PV(j) in the pipe: P(j) has been read */
+    }
+    /* tiles that only the other query tile reads: pass their slots on */
+    for (int i = 2 * nt; ok && i < 2 * T; ++i) {
+      if (!full_wait(i, 0x315u)) break;
+      if (elect_one()) mbar_arrive(bar(EMPTY + i % NSLOT));
+      __syncwarp();
     }
   } else {
     /* --------------------------- softmax + output: warpgroup t owns tile t */
-    const int t = warp >> 2;
+    const int t = my_t;
     const int r = (warp & 3) * 32 + lane; /* query row == TMEM lane */
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int rows_valid = ntok[t] * a.gqa;
+    const int rows_valid = my_ntok * a.gqa;
     const uint32_t s_col = tmem + lane_base + C::COL_S + t * 128;
     const uint32_t o_col = tmem + lane_base + C::COL_O + t * 128;
 
@@ -798,7 +858,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     {
       const bool valid = r < rows_valid;
       const float *src = a.q +
-                         static_cast<long long>(seq * a.n + tok0[t] + r / a.gqa) * a.q_tok_stride +
+                         static_cast<long long>(seq * a.n + my_tok0 + r / a.gqa) * a.q_tok_stride +
                          static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD;
 #pragma unroll 4
       for (int ch = 0; ch < HD / 8; ++ch) {
@@ -815,83 +875,66 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
                                    swz128(r, ch & 7)) = packed;
       }
       fence_async_smem();
-      mbar_arrive(bar(Q_READY));
+      mbar_arrive(bar(Q_READY + t));
     }
 
-    const int lim = r < rows_valid ? min(pos0 + tok0[t] + r / a.gqa + 1, a.max_seq) : kv_end[t];
-    const int lim_min = min(pos0 + tok0[t] + 1, a.max_seq);
+    const int lim = r < rows_valid ? min(pos0 + my_tok0 + r / a.gqa + 1, a.max_seq) : my_kv_end;
+    const int lim_min = min(pos0 + my_tok0 + 1, a.max_seq);
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    for (int j = 0; j < n_tiles[t]; ++j) {
-      if (!mbar_wait(bar(S_FULL + t), j & 1, a.err_word, 0x320u)) { ok = false; break; }
-      tc_fence_after_sync();
+    for (int j = 0; j < my_tiles; ++j) {
       const bool masked = j * BN + BN > lim_min;
       const int lim_local = lim - j * BN;
+      uint32_t sv[64], p_hi[32], p_lo[32];
+      float m_cur = m_ref;
 
-      /* The whole score row into registers: one read of tensor memory, and P can
-       * then go over the first 64 columns of S at once.
-       * After the first tile the row maximum is not computed: the exponentials are
-       * taken against the offset in use, and only if some row of the warp comes out
-       * with a sum of 2^15 or more (so that a probability might leave fp16's range;
-       * infinities and NaNs land here too) is the tile done again the exact way --
-       * maximum, new offset, O rescaled -- from the scores still in tensor memory.
-       * 64 three-input maxima and their dependency chain per tile, a seventh of the
-       * softmax, are saved; offsets move as rarely as with the 2^8 rule. */
-      uint32_t sv[BN];
-      bool exact = j == 0;
-      bool warp_grow;
-      float m_new, m_use, psum;
-      for (;;) {
+      /* keys 64..127: computed while this warpgroup was busy with tile j-1 */
+      if (!mbar_wait(bar(SHI_FULL + t), j & 1, a.err_word, 0x320u)) { ok = false; break; }
+      tc_fence_after_sync();
+      tmem_ld_32x32(s_col + 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld_32x32(s_col + 96, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(bar(HI_FREE + t)); /* S_hi(j+1) may overwrite them now */
+      if (masked) {
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32)
-          tmem_ld_32x32(s_col + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
-        tmem_ld_wait();
-        if (masked) {
-#pragma unroll
-          for (int c = 0; c < BN; ++c)
-            if (c >= lim_local) sv[c] = 0xff800000u; /* -inf */
-        }
-        if (exact) {
-          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-          for (int c = 0; c < BN; c += 8)
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
-          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-          const bool grow = j == 0 || mx > m_ref + 8.f; /* rows that are fine keep their offset */
-          warp_grow = __any_sync(0xffffffffu, grow);
-          m_new = warp_grow ? fmaxf(m_ref, mx) : m_ref;
-        } else {
-          warp_grow = false;
-          m_new = m_ref;
-        }
-        m_use = m_new == -INFINITY ? 0.f : m_new;
-
-        float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < BN; c += 8)
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const float p = ex2(__uint_as_float(sv[c + k]) - m_use);
-            ps8[k] += p;
-            sv[c + k] = __float_as_uint(p);
-          }
-        psum = ((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7]));
-        if (exact || !__any_sync(0xffffffffu, !(psum < 32768.f))) break;
-        exact = true;
+        for (int c = 0; c < 64; ++c)
+          if (64 + c >= lim_local) sv[c] = 0xff800000u; /* -inf */
       }
-#pragma unroll
-      for (int c = 0; c < BN / 2; ++c)
-        sv[c] = pack_half2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1]));
-#pragma unroll
-      for (int c0 = 0; c0 < BN / 2; c0 += 32)
-        tmem_st_32x32(s_col + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+      float sum_hi = softmax_half(sv, p_hi, m_cur, j == 0);
+      const float m_mid = m_cur;
 
-      /* S_t(j) is complete, and it was issued after PV_t(j-1): O_t is quiescent */
-      if (warp_grow && j > 0) {
-        const float factor = ex2(m_ref - m_use);
+      /* keys 0..63: issued behind PV(j-1), so O_t is quiescent once they are here */
+      if (!mbar_wait(bar(SLO_FULL + t), j & 1, a.err_word, 0x321u)) { ok = false; break; }
+      tc_fence_after_sync();
+      tmem_ld_32x32(s_col, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld_32x32(s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_wait();
+      if (masked) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          if (c >= lim_local) sv[c] = 0xff800000u;
+      }
+      const float sum_lo = softmax_half(sv, p_lo, m_cur, false);
+      const float m_use = m_cur == -INFINITY ? 0.f : m_cur;
+      if (m_cur != m_mid) {
+        /* the offset moved between the halves: bring the upper keys' probabilities
+         * to the new one (they are all zero if the upper half was masked out) */
+        const float f = m_mid == -INFINITY ? 0.f : ex2(m_mid - m_use);
+        const __half2 f2 = __float2half2_rn(f);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const __half2 v = __hmul2(*reinterpret_cast<const __half2 *>(&p_hi[i]), f2);
+          p_hi[i] = *reinterpret_cast<const uint32_t *>(&v);
+        }
+        sum_hi *= f;
+      }
+      tmem_st_32x32(s_col, p_lo);
+      tmem_st_32x32(s_col + 32, p_hi);
+
+      if (__any_sync(0xffffffffu, m_cur != m_ref) && j > 0) {
+        const float factor = ex2(m_ref - m_use); /* 1 for rows that did not move */
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t v[32];
@@ -903,20 +946,20 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
         }
         l_run *= factor;
       }
-      m_ref = m_new;
-      l_run += psum;
+      m_ref = m_cur;
+      l_run += sum_hi + sum_lo;
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(bar(P_READY + t));
     }
     grid_launch_dependents();
 
-    if (ok && n_tiles[t] > 0) ok = mbar_wait(bar(O_DONE + t), 0, a.err_word, 0x323u);
+    if (ok && my_tiles > 0) ok = mbar_wait(bar(O_DONE + t), 0, a.err_word, 0x323u);
     if (ok && rows_valid > 0) {
       tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __half *dst = a.out +
-                    (static_cast<long long>(seq * a.n + tok0[t] + r / a.gqa) * a.n_q +
+                    (static_cast<long long>(seq * a.n + my_tok0 + r / a.gqa) * a.n_q +
                      (kvh * a.gqa + r % a.gqa)) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -940,7 +983,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == MMA_WARP0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, C::TMEM_COLS);
   }
