@@ -854,25 +854,35 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
     const uint32_t s_col = tmem + lane_base + C::COL_S + t * 128;
     const uint32_t o_col = tmem + lane_base + C::COL_O + t * 128;
 
-    /* q row -> fp16 * scale * log2(e), in the K-major swizzled operand layout */
+    /* q rows -> fp16 * scale * log2(e), in the K-major swizzled operand layout.  A warp
+     * stages its 32 rows with whole-row loads (one row of 128 fp32 = one float4 per
+     * lane), eight rows in flight; a thread walking its own row alone took several
+     * microseconds per CTA before the first MMA could be issued. */
     {
-      const bool valid = r < rows_valid;
-      const float *src = a.q +
-                         static_cast<long long>(seq * a.n + my_tok0 + r / a.gqa) * a.q_tok_stride +
-                         static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD;
-#pragma unroll 4
-      for (int ch = 0; ch < HD / 8; ++ch) {
-        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-        if (valid) {
-          const float4 lo = __ldg(reinterpret_cast<const float4 *>(src + ch * 8));
-          const float4 hi = __ldg(reinterpret_cast<const float4 *>(src + ch * 8 + 4));
-          packed.x = pack_half2(lo.x * a.qscale, lo.y * a.qscale);
-          packed.y = pack_half2(lo.z * a.qscale, lo.w * a.qscale);
-          packed.z = pack_half2(hi.x * a.qscale, hi.y * a.qscale);
-          packed.w = pack_half2(hi.z * a.qscale, hi.w * a.qscale);
+      constexpr int LPR = HD / 4;   /* lanes per row */
+      constexpr int RPI = 32 / LPR; /* rows per load instruction */
+      const int l = lane % LPR;
+      int row = (warp & 3) * 32 + lane / LPR;
+      int tok = row / a.gqa, head = row % a.gqa;
+      const float *q_tile = a.q + static_cast<long long>(seq * a.n + my_tok0) * a.q_tok_stride +
+                            static_cast<long long>(kvh * a.gqa) * HD + 4 * l;
+      uint8_t *q_smem = smem + C::OFF_Q + t * C::Q_BYTES + ((l >> 1) >> 3) * HALF_BYTES + (l & 1) * 8;
+#pragma unroll 8
+      for (int i = 0; i < 32 / RPI; ++i) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < rows_valid)
+          v = __ldg(reinterpret_cast<const float4 *>(q_tile + tok * a.q_tok_stride + head * HD));
+        uint2 h;
+        h.x = pack_half2(v.x * a.qscale, v.y * a.qscale);
+        h.y = pack_half2(v.z * a.qscale, v.w * a.qscale);
+        *reinterpret_cast<uint2 *>(q_smem + swz128(row, (l >> 1) & 7)) = h;
+        row += RPI;
+        head += RPI;
+        if (head >= a.gqa) { /* RPI <= 2: one step at most when gqa >= RPI */
+          head -= a.gqa;
+          ++tok;
+          if (head >= a.gqa) { head -= a.gqa; ++tok; }
         }
-        *reinterpret_cast<uint4 *>(smem + C::OFF_Q + t * C::Q_BYTES + (ch >> 3) * HALF_BYTES +
-                                   swz128(r, ch & 7)) = packed;
       }
       fence_async_smem();
       mbar_arrive(bar(Q_READY + t));
