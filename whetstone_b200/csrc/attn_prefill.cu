@@ -1872,16 +1872,16 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   st = cached_kv_tensor_map(&vmap, key);
   if (st != WST_OK) return st;
 
-  /* Two query tiles per CTA whenever there are two: the tiles' softmax warpgroups
-   * and MMAs overlap (835 against 729 TFLOP/s on the 4 x 8192-token, 32-head
-   * shape) and every K/V tile fetched from L2 serves 256 query rows.  The one-tile
-   * kernel takes what is left: launches that finish sooner with one tile per CTA
-   * (few tiles), paged caches, ragged batches and the sliced form. */
-  /* waves x measured clocks per KV tile: about 2250 for a CTA with one query tile,
-   * 3700 for one with two */
+  /* Two query tiles per CTA whenever there are two: every K/V tile fetched from L2
+   * serves 256 query rows and one tile's MMAs run under the other's softmax (1117
+   * against 841 TFLOP/s on the last chunk of the 4 x 8192-token, 32-head shape).
+   * The one-tile kernel takes what is left: launches that finish sooner with one
+   * tile per CTA (few tiles), paged caches, ragged batches and the sliced form. */
+  /* waves x measured time per KV tile: a CTA with two query tiles takes 1.5 times as
+   * long per KV tile as a CTA with one (1.86 against 1.24 us) */
   const long long tiles = units * a.n_qtiles, pairs = units * ((a.n_qtiles + 1) / 2);
   const long long sm = facts.sm_count;
-  const bool pays = (pairs + sm - 1) / sm * 3700 < (tiles + sm - 1) / sm * 2250;
+  const bool pays = (pairs + sm - 1) / sm * 3 < (tiles + sm - 1) / sm * 2;
   const bool pair = P.force_pair >= 0 && (P.force_pair > 0 || (a.n_qtiles >= 2 && pays)) &&
                     splits == 1 && !P.page_table && !P.cu_tokens;
   const unsigned gx = splits > 1 ? a.n_qtiles * splits : (pair ? (a.n_qtiles + 1) / 2 : a.n_qtiles);
