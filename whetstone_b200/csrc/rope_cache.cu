@@ -234,6 +234,88 @@ rope_append_kernel(const RopeArgs a) {
   store_half_vec<E>(a.v_cache + slot + HALF + i0, v2);
 }
 
+/* Chunks: one warp takes G consecutive heads of one token.  With one (token, head)
+ * per warp a warp moves 1 KB and leaves, and a chunk of 2048 tokens x 40 heads is
+ * 12,288 blocks of 8 KB each: the launch ran at two thirds of the HBM rate, bound
+ * by block turnover and by a single dependent load -> reduce -> store chain per warp.
+ * Here the loads of all G heads (and of the V rows that go with K heads) are in
+ * flight together and the token's cos/sin row is fetched once. */
+template <int E, int G>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rope_append_group_kernel(const RopeArgs a) {
+  constexpr int HD = 64 * E;
+  constexpr int HALF = HD / 2;
+  const int lane = threadIdx.x & 31;
+  const int heads = a.n_q + a.n_kv;
+  const int groups = heads / G; /* the launcher checked heads % G == 0 */
+  const long long grp =
+      static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (grp >= static_cast<long long>(a.n_tokens) * groups) return;
+  const int tok = static_cast<int>(grp / groups);
+  const int head0 = static_cast<int>(grp % groups) * G;
+
+  const TokenPlace place = place_token<false>(a, tok);
+  const int tpos = place.pos < a.table_len - 1 ? place.pos : a.table_len - 1;
+  float *row = a.qkv + static_cast<long long>(tok) * (a.n_q + 2 * a.n_kv) * HD;
+  const int i0 = lane * E;
+
+  float x1[G][E], x2[G][E], v1[G][E], v2[G][E], c[E], s[E];
+#pragma unroll
+  for (int g = 0; g < G; ++g) { /* q heads and k heads are consecutive in the row */
+    load_vec<E>(row + (head0 + g) * HD + i0, x1[g]);
+    load_vec<E>(row + (head0 + g) * HD + HALF + i0, x2[g]);
+  }
+  load_vec<E>(a.cos_tab + static_cast<long long>(tpos) * HALF + i0, c);
+  load_vec<E>(a.sin_tab + static_cast<long long>(tpos) * HALF + i0, s);
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (head0 + g >= a.n_q) {
+      const float *vsrc = row + (head0 + g + a.n_kv) * HD;
+      load_vec<E>(vsrc + i0, v1[g]);
+      load_vec<E>(vsrc + HALF + i0, v2[g]);
+    }
+  }
+
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const int head = head0 + g;
+    const bool is_q = head < a.n_q;
+    const __half *gain = is_q ? a.q_gain : a.k_gain;
+    if (gain) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) ss = fmaf(x1[g][e], x1[g][e], fmaf(x2[g][e], x2[g][e], ss));
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / static_cast<float>(HD) + a.eps);
+      float g1[E], g2[E];
+      load_gain<E>(gain + i0, g1);
+      load_gain<E>(gain + HALF + i0, g2);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        x1[g][e] = x1[g][e] * inv * g1[e];
+        x2[g][e] = x2[g][e] * inv * g2[e];
+      }
+    }
+    float y1[E], y2[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      y1[e] = x1[g][e] * c[e] - x2[g][e] * s[e];
+      y2[e] = x2[g][e] * c[e] + x1[g][e] * s[e];
+    }
+    if (is_q) {
+      store_vec<E>(row + head * HD + i0, y1);
+      store_vec<E>(row + head * HD + HALF + i0, y2);
+    } else if (place.kv_base >= 0) {
+      const long long slot =
+          place.kv_base + static_cast<long long>(head - a.n_q) * place.kv_head_stride;
+      store_half_vec<E>(a.k_cache + slot + i0, y1);
+      store_half_vec<E>(a.k_cache + slot + HALF + i0, y2);
+      store_half_vec<E>(a.v_cache + slot + i0, v1[g]);
+      store_half_vec<E>(a.v_cache + slot + HALF + i0, v2[g]);
+    }
+  }
+}
+
 /* Any even head_dim: two passes over the vector (the second hits L1). */
 template <bool PAGED>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -328,7 +410,16 @@ wst_status_t launch_rope(const RopeArgs &a, const char *name) {
   cfg.attrs = attr;
   cfg.numAttrs = args.trigger_early ? 1 : 0;
   cudaError_t e;
-  if (vec_ok && a.hd == 64) {
+  constexpr int kGroup = 4;
+  const bool grouped = !PAGED && vec_ok && a.n_tokens >= 32 && (a.n_q + a.n_kv) % kGroup == 0 &&
+                       (a.hd == 64 || a.hd == 128 || a.hd == 256);
+  if (grouped) {
+    const long long groups = units / kGroup;
+    cfg.gridDim = dim3(static_cast<unsigned>((groups + kWarpsPerBlock - 1) / kWarpsPerBlock));
+    e = a.hd == 64    ? cudaLaunchKernelEx(&cfg, rope_append_group_kernel<1, kGroup>, args)
+        : a.hd == 128 ? cudaLaunchKernelEx(&cfg, rope_append_group_kernel<2, kGroup>, args)
+                      : cudaLaunchKernelEx(&cfg, rope_append_group_kernel<4, kGroup>, args);
+  } else if (vec_ok && a.hd == 64) {
     e = cudaLaunchKernelEx(&cfg, rope_append_kernel<1, PAGED>, args);
   } else if (vec_ok && a.hd == 128) {
     e = cudaLaunchKernelEx(&cfg, rope_append_kernel<2, PAGED>, args);
