@@ -157,6 +157,23 @@ WST_API wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache, const 
                             void *out, int32_t n_q, int32_t n_kv, int32_t head_dim,
                             int32_t pos0, int32_t n, int32_t max_seq, float scale);
 
+/* ---- the projection either side of the attention path ------------------------ */
+
+/* y[j][r] = sum_c x[j][c] * w[r][c] (+ bias[r]) for j < n, r < out_f; with accum != 0
+ * the result is added to what y holds (the o_proj form: straight into the residual).
+ * whetstone.h:313-317, cuda/chunk_gemm.cu:178-258 and :340-365.
+ *   w     [out_f][in_f] half        x  [n][in_f] half, token-major
+ *   bias  [out_f] half or null      y  [n][out_f] float
+ * Any n is one launch.  Products and sums are fp32 (the engine's kernel rounds groups
+ * of four products to fp16 first), so results agree with the engine's to its own
+ * rounding, inside the 2e-3 relative bound of its tests. */
+WST_API wst_status_t wst_gemm_fp16(const void *w, const void *x, const void *bias, void *y,
+                           int32_t in_f, int32_t out_f, int32_t n, int32_t accum);
+
+/* Tokens per weight pass, which the engine takes as its prefill chunk width
+ * (whetstone.h:311, src/chunk.rs:20): 512 here, 16 in the engine's kernels. */
+WST_API int32_t wst_chunk_max_tokens(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,5 +1,5 @@
 """The integration recipe carried out: all of the engine's own kernel objects with the
-five attention entry points weakened, linked with this repository's drop-in archive
+entry points this repository replaces weakened, linked with this repository's drop-in archive
 (`make -C whetstone_b200/csrc DROPIN=1`) into oracle/_ref/libwhetstone_dropin.so by
 `make -C oracle dropin`.  One library must export every symbol the engine's Rust crate
 binds (crates/whetstone-kernels/src/ffi.rs:134-473, listed in
@@ -42,8 +42,8 @@ def test_the_archive_leaves_the_engines_runtime_symbols_out():
     names = {name for _, name in defined(ARCHIVE)}
     assert not names & set(ENGINE_RUNTIME), names & set(ENGINE_RUNTIME)
     for name in ("wst_rope_cache", "wst_attn_decode", "wst_attn_partial_floats",
-                 "wst_rope_cache_chunk", "wst_attn_chunk", "wst_attn_verify_paged",
-                 "wst_b200_set_stream"):
+                 "wst_rope_cache_chunk", "wst_attn_chunk", "wst_gemm_fp16",
+                 "wst_chunk_max_tokens", "wst_attn_verify_paged", "wst_b200_set_stream"):
         assert name in names
 
 

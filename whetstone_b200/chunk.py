@@ -57,6 +57,34 @@ def attn(qkv: torch.Tensor, cache: KvCache, out: torch.Tensor, n_q: int, pos0: i
                              cache.n_kv, hd, pos0, n, cache.max_seq, scale))
 
 
+def gemm_fp16(w: torch.Tensor, x: torch.Tensor, bias: torch.Tensor | None, y: torch.Tensor,
+              in_features: int, out_features: int, n: int, accumulate: bool = False) -> None:
+    """``y[j] = W x[j] + b`` for every ``j < n``, or ``+=`` when ``accumulate``
+    (src/chunk.rs:55-99): w ``[out][in]`` and x ``[n][in]`` fp16, y ``[n][out]`` fp32."""
+    _require_cuda(w, "gemm_fp16: w", torch.float16)
+    _require_cuda(x, "gemm_fp16: x", torch.float16)
+    _require_cuda(y, "gemm_fp16: y", torch.float32)
+    if x.numel() != n * in_features or y.numel() != n * out_features:
+        raise ShapeError(5, f"gemm_fp16: x[{x.numel()}], y[{y.numel()}] do not match n={n}, "
+                            f"in={in_features}, out={out_features}")
+    if w.numel() != in_features * out_features:
+        raise ShapeError(5, f"gemm_fp16: weights have {w.numel()} elements, expected "
+                            f"{in_features}*{out_features}")
+    if bias is not None:
+        _require_cuda(bias, "gemm_fp16: bias", torch.float16)
+        if bias.numel() != out_features:
+            raise ShapeError(5, f"gemm_fp16: bias has {bias.numel()} elements, expected "
+                                f"{out_features}")
+    use_torch_stream()
+    check(lib.wst_gemm_fp16(_ptr(w), _ptr(x), _ptr(bias) if bias is not None else None, _ptr(y),
+                            in_features, out_features, n, int(accumulate)))
+
+
+def max_tokens() -> int:
+    """Tokens one weight pass serves (src/chunk.rs:20)."""
+    return max(1, lib.wst_chunk_max_tokens())
+
+
 class KvCacheBatch:
     """Caches of n_seq sequences in one allocation, ``[n_seq][n_kv][max_seq][head_dim]``
     fp16 for K and V: what the batched chunk entry points take."""

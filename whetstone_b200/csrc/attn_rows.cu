@@ -91,12 +91,6 @@ struct Cfg {
   static_assert(smem_bytes(NSTAGE) <= 232448, "shared memory of one CTA");
 };
 
-__device__ __forceinline__ void grid_dependency_wait() {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-__device__ __forceinline__ void grid_launch_dependents() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
 
 __device__ __forceinline__ void store_half4(__half *dst, float a, float b, float c, float d) {
   __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);

@@ -1,0 +1,336 @@
+/* The multi-token projection either side of the attention path:
+ *
+ *     y[j][r] (+)= sum_c x[j][c] * w[r][c] + bias[r]        j < n tokens, r < out_f
+ *
+ * x [n][in_f] and w [out_f][in_f] fp16, y [n][out_f] fp32 -- wst_gemm_fp16 of the
+ * engine (cuda/chunk_gemm.cu:178-258, dispatch :340-365).  The engine's kernel keeps
+ * the weights outermost and covers at most 16 tokens per pass; every weight row is a
+ * warp's dot product in half2.  Here any number of tokens is one launch:
+ *
+ *   both operands are K-major, so a 128-token x BN-feature tile is
+ *   tcgen05.mma.kind::f16 M128 x N(BN) x K16 straight from the TMA-filled,
+ *   128-byte-swizzled stages (x tile 16 KB + w tile BN*128 B per 64 columns of K);
+ *   fp32 accumulators in tensor memory, TWO of them, so the epilogue of one tile
+ *   (tensor memory -> registers -> + bias (+ y) -> global) runs under the main loop
+ *   of the next; persistent CTAs, one per SM, walk the tiles token-tile fastest so
+ *   that the CTAs running at the same time share a weight tile in L2.
+ *
+ *   BN = 256 for real chunks (A 4 KB + B 8 KB of shared memory per 128-clock MMA,
+ *   96 bytes per clock); BN = 64 when the token count is small and the launch is a
+ *   stream of the weights: four times as many CTAs pull on HBM.
+ *
+ * Products are exact in fp32 and accumulated in fp32 (the engine's kernel rounds
+ * every group of four products to fp16 first): results differ from the engine's by
+ * its own rounding, well inside the 2e-3 relative bound its tests use
+ * (tests/chunk_kernels.rs:44-49).
+ *
+ * Shapes the tensor maps cannot describe (in_f not a multiple of 8, unaligned
+ * bases) go to a plain warp-per-output kernel.
+ */
+
+#include "tensor_map.cuh"
+#include "wst_common.cuh"
+#include "wst_ptx.cuh"
+
+namespace wst {
+namespace {
+
+using namespace ptx;
+
+template <int BN>
+struct GCfg {
+  static constexpr int BM = 128, BK = 64;
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int NSTAGE = BN == 256 ? 4 : 8;
+  static constexpr int OFF_BAR = NSTAGE * STAGE_BYTES;
+  static constexpr int NBAR = 2 * NSTAGE + 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
+  static constexpr int THREADS = 192; /* 4 epilogue warps, MMA warp, TMA warp */
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+};
+
+struct GemmArgs {
+  const __half *bias;
+  float *y;
+  int in_f, out_f, n, accum;
+  int m_tiles, n_tiles;
+  unsigned int *err_word;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GCfg<BN>::THREADS, 1)
+gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+                const GemmArgs a) {
+  using C = GCfg<BN>;
+  constexpr int NSTAGE = C::NSTAGE;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  auto bar = [bar0](int i) { return bar0 + 8u * i; };
+  constexpr int FULL = 0, EMPTY = NSTAGE, ACC_FULL = 2 * NSTAGE, ACC_EMPTY = ACC_FULL + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + C::OFF_BAR + C::NBAR * 8);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSTAGE; ++i) {
+      mbar_init(bar(FULL + i), 1);
+      mbar_init(bar(EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(ACC_FULL + i), 1);
+      mbar_init(bar(ACC_EMPTY + i), 128);
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&xmap);
+    tma_prefetch_desc(&wmap);
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  grid_dependency_wait();
+
+  const int n_tiles_total = a.m_tiles * a.n_tiles;
+  const int k_blocks = (a.in_f + C::BK - 1) / C::BK;
+  /* tile i of this CTA is global tile blockIdx.x + i * gridDim.x: token tile fastest */
+
+  if (warp == 5) {
+    /* ------------------------------------------------------ TMA producer */
+    if (lane == 0) {
+      int it = 0; /* stage uses so far */
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
+        const int m0 = (tile % a.m_tiles) * C::BM, n0 = (tile / a.m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % NSTAGE;
+          if (it >= NSTAGE &&
+              !mbar_wait(bar(EMPTY + st), ((it / NSTAGE) - 1) & 1, a.err_word, 0x601u)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(bar(FULL + st), C::STAGE_BYTES);
+          tma_load_3d(sbase + st * C::STAGE_BYTES, &xmap, bar(FULL + st), kb * C::BK, m0, 0);
+          tma_load_3d(sbase + st * C::STAGE_BYTES + C::A_BYTES, &wmap, bar(FULL + st), kb * C::BK,
+                      n0, 0);
+        }
+      }
+    }
+  } else if (warp == 4) {
+    /* -------------------------------------------------------- MMA issuer */
+    constexpr uint32_t idesc = umma_idesc(128, BN, 0);
+    int it = 0, local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      /* the epilogue of the tile two back has emptied this accumulator */
+      if (local >= 2 &&
+          !mbar_wait(bar(ACC_EMPTY + buf), ((local >> 1) - 1) & 1, a.err_word, 0x602u)) break;
+      tc_fence_after_sync();
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int st = it % NSTAGE;
+        if (!mbar_wait(bar(FULL + st), (it / NSTAGE) & 1, a.err_word, 0x603u)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a_lo = umma_desc_lo(sbase + st * C::STAGE_BYTES, 16);
+        const uint32_t b_lo = umma_desc_lo(sbase + st * C::STAGE_BYTES + C::A_BYTES, 16);
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < C::BK / 16; ++ks)
+            umma_ss_f16_lohi(tmem + buf * BN, a_lo + ((ks * 32) >> 4), b_lo + ((ks * 32) >> 4), kDescHi,
+                             idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(bar(EMPTY + st));
+          if (kb == k_blocks - 1) umma_commit(bar(ACC_FULL + buf));
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    /* --------------------------------------- epilogue: thread r owns token row r */
+    const int r = warp * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const bool vec = (a.out_f & 3) == 0;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile % a.m_tiles) * C::BM, n0 = (tile / a.m_tiles) * BN;
+      if (!mbar_wait(bar(ACC_FULL + buf), (local >> 1) & 1, a.err_word, 0x604u)) break;
+      tc_fence_after_sync();
+      const int row = m0 + r;
+      float *yrow = a.y + static_cast<long long>(row) * a.out_f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + lane_base + buf * BN + c0, v);
+        tmem_ld_wait();
+        const int col0 = n0 + c0;
+        if (row < a.n && col0 < a.out_f) {
+          if (vec && col0 + 32 <= a.out_f) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              float4 o = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                     __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+              if (a.bias) {
+                const uint2 b = __ldg(reinterpret_cast<const uint2 *>(a.bias + col0 + e));
+                const float2 b0 = __half22float2(*reinterpret_cast<const __half2 *>(&b.x));
+                const float2 b1 = __half22float2(*reinterpret_cast<const __half2 *>(&b.y));
+                o.x += b0.x; o.y += b0.y; o.z += b1.x; o.w += b1.y;
+              }
+              float4 *dst = reinterpret_cast<float4 *>(yrow + col0 + e);
+              if (a.accum) {
+                const float4 old = *dst;
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *dst = o;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (col0 + e < a.out_f) {
+                float o = __uint_as_float(v[e]);
+                if (a.bias) o += __half2float(a.bias[col0 + e]);
+                if (a.accum) o += yrow[col0 + e];
+                yrow[col0 + e] = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar(ACC_EMPTY + buf));
+    }
+    grid_launch_dependents();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+/* Any shape: one warp per (token, output feature), fp32 accumulation. */
+__global__ void __launch_bounds__(256)
+gemm_f16_plain_kernel(const __half *w, const __half *x, const __half *bias, float *y, int in_f,
+                      int out_f, int n, int accum) {
+  const long long unit = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (unit >= static_cast<long long>(n) * out_f) return;
+  const int lane = threadIdx.x & 31;
+  const int j = static_cast<int>(unit / out_f), r = static_cast<int>(unit % out_f);
+  const __half *wr = w + static_cast<long long>(r) * in_f;
+  const __half *xr = x + static_cast<long long>(j) * in_f;
+  float acc = 0.f;
+  for (int c = lane; c < in_f; c += 32) acc = fmaf(__half2float(wr[c]), __half2float(xr[c]), acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    if (bias) acc += __half2float(bias[r]);
+    float *dst = y + static_cast<long long>(j) * out_f + r;
+    *dst = accum ? *dst + acc : acc;
+  }
+}
+
+template <int BN>
+wst_status_t launch_gemm(const CUtensorMap &xmap, const CUtensorMap &wmap, GemmArgs a, int sm_count) {
+  using C = GCfg<BN>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  WST_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    WST_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  C::SMEM_BYTES));
+    configured_dev = dev;
+  }
+  a.m_tiles = (a.n + C::BM - 1) / C::BM;
+  a.n_tiles = (a.out_f + BN - 1) / BN;
+  const long long tiles = static_cast<long long>(a.m_tiles) * a.n_tiles;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count ? tiles : sm_count));
+  cfg.blockDim = dim3(C::THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = current_stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_f16_kernel<BN>, xmap, wmap, a);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("wst_gemm_fp16 (launch)", e);
+  return WST_OK;
+}
+
+}  // namespace
+}  // namespace wst
+
+using namespace wst;
+
+extern "C" wst_status_t wst_gemm_fp16(const void *w, const void *x, const void *bias, void *y,
+                                      int32_t in_f, int32_t out_f, int32_t n, int32_t accum) {
+  WST_CHECK_ARG(w && x && y, "wst_gemm_fp16: null pointer");
+  WST_CHECK_ARG(in_f > 0 && out_f > 0, "wst_gemm_fp16: non-positive dimension");
+  WST_CHECK_ARG(n > 0, "wst_gemm_fp16: n must be positive");
+  DeviceFacts facts;
+  if (!device_facts(&facts)) return WST_ERR_CUDA;
+
+  const bool tma_ok = in_f % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+                      (!bias || (reinterpret_cast<uintptr_t>(bias) & 7) == 0) && facts.cc_major >= 10;
+  if (!tma_ok) {
+    const long long units = static_cast<long long>(n) * out_f;
+    const long long blocks = (units + 7) / 8;
+    WST_CHECK_ARG(blocks <= 0x7fffffffLL, "wst_gemm_fp16: too many outputs");
+    gemm_f16_plain_kernel<<<static_cast<unsigned>(blocks), 256, 0, current_stream()>>>(
+        static_cast<const __half *>(w), static_cast<const __half *>(x),
+        static_cast<const __half *>(bias), static_cast<float *>(y), in_f, out_f, n, accum);
+    WST_LAUNCHED("wst_gemm_fp16");
+    return WST_OK;
+  }
+
+  unsigned int *err_word = device_error_word();
+  if (!err_word) return WST_ERR_CUDA;
+  GemmArgs a{};
+  a.bias = static_cast<const __half *>(bias);
+  a.y = static_cast<float *>(y);
+  a.in_f = in_f;
+  a.out_f = out_f;
+  a.n = n;
+  a.accum = accum;
+  a.err_word = err_word;
+
+  /* few tokens: the launch streams the weights once, and 64-feature tiles give HBM
+   * four times as many SMs to feed; else 256-feature tiles for the tensor pipe */
+  const bool narrow = n <= 128 && (out_f + 255) / 256 < facts.sm_count;
+  CUtensorMap xmap, wmap;
+  KvMapKey key{};
+  key.rank = 3;
+  key.d0 = static_cast<uint64_t>(in_f);
+  key.d2 = 1;
+  key.d3 = 1;
+  key.base = x;
+  key.d1 = static_cast<uint64_t>(n);
+  key.b1 = 128;
+  wst_status_t st = cached_kv_tensor_map(&xmap, key);
+  if (st != WST_OK) return st;
+  key.base = w;
+  key.d1 = static_cast<uint64_t>(out_f);
+  key.b1 = narrow ? 64 : 256;
+  st = cached_kv_tensor_map(&wmap, key);
+  if (st != WST_OK) return st;
+  return narrow ? launch_gemm<64>(xmap, wmap, a, facts.sm_count)
+                : launch_gemm<256>(xmap, wmap, a, facts.sm_count);
+}
+
+/* The engine sizes its prefill chunks by this (cuda/chunk_gemm.cu:367 returns 16, the
+ * widest pass of its kernels; src/chunk.rs:20, engine.rs:682-693).  A pass here takes
+ * any width; 512 tokens is the chunk the prefill kernels of this library are tuned on. */
+extern "C" int32_t wst_chunk_max_tokens(void) { return 512; }

@@ -234,6 +234,32 @@ __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+/* Shared-memory matrix descriptor for tcgen05.mma: 128-byte swizzle, tile base
+ * 1024-byte aligned, 8-row groups 1024 bytes apart.  It is built in halves: the
+ * high word is fixed by the layout (group stride, version 1, 128-byte swizzle); the
+ * low word holds the address and the leading-dimension offset, both in 16-byte
+ * units, so moving the start by `bytes` adds bytes / 16 to it (shared-memory
+ * addresses stay below 2^18). */
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+
+/* Instruction descriptor, kind::f16: fp16 A and B, fp32 D, M x N tile. */
+__device__ __forceinline__ constexpr uint32_t umma_idesc(int m, int n, int b_mn_major) {
+  return (1u << 4) | (static_cast<uint32_t>(b_mn_major) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+/* Programmatic dependent launch: wait for everything ahead of this grid in the stream;
+ * let the grid behind this one start its prologue. */
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 /* True in exactly one lane of a converged warp (the same lane every time).  The
  * issuer of tcgen05.mma and tcgen05.commit is chosen with this and not with
  * `lane == 0`: behind a comparison of the lane index the compiler has to carry the
