@@ -552,6 +552,45 @@ def bench_also(torch, args):
             **sec.stats}
         del caches, pool, rope_src
 
+    # ---- the projections either side of the attention path (wst_gemm_fp16): the qkv and
+    # o_proj GEMMs of a c4 chunk step (4 x 512 tokens, Qwen3-8B widths) on the tensor
+    # pipe, and the qkv projection of a c5 verify step (80 tokens, Qwen2.5-7B widths),
+    # which is a stream of the weights.  Weights rotate through more than L2 holds.
+    if want("gemm"):
+        s4, s5 = wl.QWEN3_8B, wl.QWEN25_7B
+        hid4, hid5 = s4.n_q * s4.head_dim, 3584
+        n_big, n_small = wl.C4["chunk"] * wl.C4["n_seq"], len(wl.c5_lengths()) * wl.C5["drafts"]
+        legs = {}
+        for tag, in_f, out_f, n, accum in (("c4_qkv_proj", hid4, s4.qkv_width, n_big, False),
+                                           ("c4_o_proj", hid4, hid4, n_big, True),
+                                           ("c5_qkv_proj", hid5, s5.qkv_width, n_small, False)):
+            copies = max(2, int(300e6 // (2 * in_f * out_f)) + 1)
+            ws = [(randn16((out_f, in_f)).float() / in_f ** 0.5).half() for _ in range(copies)]
+            x = randn16((n, in_f))
+            y = torch.zeros((n, out_f), dtype=torch.float32, device="cuda")
+            chunk.gemm_fp16(ws[0], x, None, y, in_f, out_f, n, False)
+            want_y = x.float() @ ws[0].float().T
+            err = float((y - want_y).abs().max())
+            if not err <= 2e-3:
+                raise SystemExit(f"[bench] {tag}: wst_gemm_fp16 differs from the fp32 product by {err}")
+
+            def step(ws=ws, x=x, y=y, in_f=in_f, out_f=out_f, n=n, accum=accum):
+                for w in ws:
+                    chunk.gemm_fp16(w, x, None, y, in_f, out_f, n, accum)
+            sec = timed_graph(torch, step, max(1, min(args.steps, 20) // 4), 3)
+            require_clean(torch, decode, None, tag)
+            per = sec / copies
+            flops = 2.0 * in_f * out_f * n
+            byts = 2.0 * in_f * out_f + 2.0 * n * in_f + (8.0 if accum else 4.0) * n * out_f
+            legs[tag] = {"in_features": in_f, "out_features": out_f, "tokens": n,
+                         "us_per_launch": per * 1e6, "tflops": flops / per / 1e12,
+                         "frac_of_tensor_peak": flops / per / 1e12 / pk["tf_burst"],
+                         "frac_of_sustained_tensor_peak": flops / per / 1e12 / pk["tf_sustained"],
+                         "gbs": byts / per / 1e9, "frac_of_hbm_peak": byts / per / 1e9 / pk["hbm"],
+                         "max_abs_err_vs_fp32_product": err, **sec.stats}
+            del ws
+        out["projection_gemm_fp16"] = legs
+
     # ---- c5: speculative verify, 16 sequences x 5 drafts, paged cache, 28 layers
     if want("c5"):
         s5 = wl.QWEN25_7B
@@ -852,7 +891,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip configs c1, c2, c4, c5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "refcuda"],
+    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "gemm", "refcuda"],
                     help="run one workload only (c3 = the headline line without 'also')")
     ap.add_argument("--no-long", action="store_true", help="skip the 262144-row decode leg")
     ap.add_argument("--min-region-s", type=float, default=0.25,

@@ -16,8 +16,8 @@
  *   that the CTAs running at the same time share a weight tile in L2.
  *
  *   BN = 256 for real chunks (A 4 KB + B 8 KB of shared memory per 128-clock MMA,
- *   96 bytes per clock); BN = 64 when the token count is small and the launch is a
- *   stream of the weights: four times as many CTAs pull on HBM.
+ *   96 bytes per clock); BN = 32, 48 or 64 when the token count is small and the
+ *   launch is a stream of the weights: as many CTAs as there are SMs pull on HBM.
  *
  * Products are exact in fp32 and accumulated in fp32 (the engine's kernel rounds
  * every group of four products to fp16 first): results differ from the engine's by
@@ -28,6 +28,8 @@
  * bases) go to a plain warp-per-output kernel.
  */
 
+#include <initializer_list>
+
 #include "tensor_map.cuh"
 #include "wst_common.cuh"
 #include "wst_ptx.cuh"
@@ -37,18 +39,27 @@ namespace {
 
 using namespace ptx;
 
-template <int BN>
+/* BN feature rows per tile; KS 64-column slabs of K per pipeline stage; RB token rows
+ * fetched per tile (the MMA is always M = 128: with RB < 128 the tensor core reads
+ * whatever follows the fetched rows in shared memory, and the accumulator rows that
+ * come of it belong to tokens that do not exist and are never stored). */
+template <int BN, int KS, int RB>
 struct GCfg {
-  static constexpr int BM = 128, BK = 64;
-  static constexpr int A_BYTES = BM * 128;
-  static constexpr int B_BYTES = BN * 128;
+  static constexpr int BM = 128, BK = 64 * KS;
+  static constexpr int A_SLAB = RB * 128, B_SLAB = BN * 128;
+  static constexpr int A_BYTES = KS * A_SLAB;
+  static constexpr int B_BYTES = KS * B_SLAB;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int NSTAGE = BN == 256 ? 4 : 8;
+  static constexpr int NSTAGE = (200 * 1024) / STAGE_BYTES < 8 ? (200 * 1024) / STAGE_BYTES : 8;
   static constexpr int OFF_BAR = NSTAGE * STAGE_BYTES;
   static constexpr int NBAR = 2 * NSTAGE + 4;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
   static constexpr int THREADS = 192; /* 4 epilogue warps, MMA warp, TMA warp */
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int ACC_STRIDE = BN <= 32 ? 32 : BN <= 64 ? 64 : 256; /* columns per accumulator */
+  static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
+  static_assert(RB % 8 == 0 && NSTAGE >= 2, "stage geometry");
+  /* the M = 128 read of the last slab of the last stage stays inside the ring */
+  static_assert(KS == 1 ? RB == 128 : 128 * 128 <= A_SLAB + B_BYTES, "over-read leaves the ring");
 };
 
 struct GemmArgs {
@@ -59,11 +70,11 @@ struct GemmArgs {
   unsigned int *err_word;
 };
 
-template <int BN>
-__global__ void __launch_bounds__(GCfg<BN>::THREADS, 1)
+template <int BN, int KS, int RB>
+__global__ void __launch_bounds__(GCfg<BN, KS, RB>::THREADS, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                 const GemmArgs a) {
-  using C = GCfg<BN>;
+  using C = GCfg<BN, KS, RB>;
   constexpr int NSTAGE = C::NSTAGE;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
@@ -118,9 +129,15 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             break;
           }
           mbar_arrive_expect_tx(bar(FULL + st), C::STAGE_BYTES);
-          tma_load_3d(sbase + st * C::STAGE_BYTES, &xmap, bar(FULL + st), kb * C::BK, m0, 0);
-          tma_load_3d(sbase + st * C::STAGE_BYTES + C::A_BYTES, &wmap, bar(FULL + st), kb * C::BK,
-                      n0, 0);
+          if constexpr (KS == 1) { /* maps over [rows][in_f]: columns past in_f read as zero */
+            tma_load_3d(sbase + st * C::STAGE_BYTES, &xmap, bar(FULL + st), kb * C::BK, m0, 0);
+            tma_load_3d(sbase + st * C::STAGE_BYTES + C::A_BYTES, &wmap, bar(FULL + st), kb * C::BK,
+                        n0, 0);
+          } else { /* maps over [in_f / 64][rows][64]: KS slabs per request */
+            tma_load_3d(sbase + st * C::STAGE_BYTES, &xmap, bar(FULL + st), 0, m0, kb * KS);
+            tma_load_3d(sbase + st * C::STAGE_BYTES + C::A_BYTES, &wmap, bar(FULL + st), 0, n0,
+                        kb * KS);
+          }
         }
       }
     }
@@ -143,9 +160,12 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
         const uint32_t b_lo = umma_desc_lo(sbase + st * C::STAGE_BYTES + C::A_BYTES, 16);
         if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < C::BK / 16; ++ks)
-            umma_ss_f16_lohi(tmem + buf * BN, a_lo + ((ks * 32) >> 4), b_lo + ((ks * 32) >> 4), kDescHi,
-                             idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < C::BK / 16; ++ks) {
+            const uint32_t a_off = ((ks >> 2) * C::A_SLAB + (ks & 3) * 32) >> 4;
+            const uint32_t b_off = ((ks >> 2) * C::B_SLAB + (ks & 3) * 32) >> 4;
+            umma_ss_f16_lohi(tmem + buf * C::ACC_STRIDE, a_lo + a_off, b_lo + b_off, kDescHi, idesc,
+                             (kb > 0 || ks > 0) ? 1u : 0u);
+          }
           umma_commit(bar(EMPTY + st));
           if (kb == k_blocks - 1) umma_commit(bar(ACC_FULL + buf));
         }
@@ -168,11 +188,11 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + buf * BN + c0, v);
+        tmem_ld_32x32(tmem + lane_base + buf * C::ACC_STRIDE + c0, v);
         tmem_ld_wait();
         const int col0 = n0 + c0;
         if (row < a.n && col0 < a.out_f) {
-          if (vec && col0 + 32 <= a.out_f) {
+          if (vec && c0 + 32 <= BN && col0 + 32 <= a.out_f) {
 #pragma unroll
             for (int e = 0; e < 32; e += 4) {
               float4 o = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
@@ -193,7 +213,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-              if (col0 + e < a.out_f) {
+              if (c0 + e < BN && col0 + e < a.out_f) {
                 float o = __uint_as_float(v[e]);
                 if (a.bias) o += __half2float(a.bias[col0 + e]);
                 if (a.accum) o += yrow[col0 + e];
@@ -238,15 +258,59 @@ gemm_f16_plain_kernel(const __half *w, const __half *x, const __half *bias, floa
   }
 }
 
-template <int BN>
-wst_status_t launch_gemm(const CUtensorMap &xmap, const CUtensorMap &wmap, GemmArgs a, int sm_count) {
-  using C = GCfg<BN>;
+/* The operand maps.  KS == 1: [rows][in_f] as it lies, box 64 columns x `box_rows`.
+ * KS > 1 (in_f a multiple of 64): the same memory as [in_f / 64][rows][64] -- slab,
+ * row, column -- so that one request brings KS slabs. */
+wst_status_t operand_map(CUtensorMap *out, const void *base, int in_f, int rows, int box_rows,
+                         int ks) {
+  if (ks == 1) {
+    KvMapKey key{};
+    key.rank = 3;
+    key.base = base;
+    key.d0 = static_cast<uint64_t>(in_f);
+    key.d1 = static_cast<uint64_t>(rows);
+    key.d2 = 1;
+    key.d3 = 1;
+    key.b1 = static_cast<uint32_t>(box_rows);
+    return cached_kv_tensor_map(out, key);
+  }
+  struct Slot {
+    const void *base;
+    int in_f, rows, box_rows, ks;
+    CUtensorMap map;
+    bool used;
+  };
+  static thread_local Slot slots[16];
+  const uint64_t h = (reinterpret_cast<uint64_t>(base) >> 8) ^ (static_cast<uint64_t>(rows) * 0x9E3779B97F4A7C15ull);
+  Slot &sl = slots[(h ^ (h >> 31)) % 16];
+  if (sl.used && sl.base == base && sl.in_f == in_f && sl.rows == rows && sl.box_rows == box_rows &&
+      sl.ks == ks) {
+    *out = sl.map;
+    return WST_OK;
+  }
+  const uint64_t dims[3] = {64, static_cast<uint64_t>(rows), static_cast<uint64_t>(in_f / 64)};
+  const uint64_t strides[2] = {static_cast<uint64_t>(in_f) * 2, 128};
+  const uint32_t box[3] = {64, static_cast<uint32_t>(box_rows), static_cast<uint32_t>(ks)};
+  const wst_status_t st = make_kv_tensor_map(out, base, 3, dims, strides, box);
+  if (st != WST_OK) return st;
+  sl = Slot{base, in_f, rows, box_rows, ks, *out, true};
+  return WST_OK;
+}
+
+template <int BN, int KS, int RB>
+wst_status_t launch_gemm(const void *w, const void *x, GemmArgs a, int sm_count) {
+  using C = GCfg<BN, KS, RB>;
+  CUtensorMap xmap, wmap;
+  wst_status_t st = operand_map(&xmap, x, a.in_f, a.n, RB, KS);
+  if (st != WST_OK) return st;
+  st = operand_map(&wmap, w, a.in_f, a.out_f, BN, KS);
+  if (st != WST_OK) return st;
   static thread_local int configured_dev = -1;
   int dev = 0;
   WST_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    WST_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  C::SMEM_BYTES));
+    WST_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<BN, KS, RB>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured_dev = dev;
   }
   a.m_tiles = (a.n + C::BM - 1) / C::BM;
@@ -262,10 +326,19 @@ wst_status_t launch_gemm(const CUtensorMap &xmap, const CUtensorMap &wmap, GemmA
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_f16_kernel<BN>, xmap, wmap, a);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_f16_kernel<BN, KS, RB>, xmap, wmap, a);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("wst_gemm_fp16 (launch)", e);
   return WST_OK;
+}
+
+template <int KS, int RB>
+wst_status_t launch_narrow(int bn, const void *w, const void *x, const GemmArgs &a, int sm_count) {
+  switch (bn) {
+    case 32: return launch_gemm<32, KS, RB>(w, x, a, sm_count);
+    case 48: return launch_gemm<48, KS, RB>(w, x, a, sm_count);
+    default: return launch_gemm<64, KS, RB>(w, x, a, sm_count);
+  }
 }
 
 }  // namespace
@@ -307,27 +380,26 @@ extern "C" wst_status_t wst_gemm_fp16(const void *w, const void *x, const void *
   a.accum = accum;
   a.err_word = err_word;
 
-  /* few tokens: the launch streams the weights once, and 64-feature tiles give HBM
-   * four times as many SMs to feed; else 256-feature tiles for the tensor pipe */
-  const bool narrow = n <= 128 && (out_f + 255) / 256 < facts.sm_count;
-  CUtensorMap xmap, wmap;
-  KvMapKey key{};
-  key.rank = 3;
-  key.d0 = static_cast<uint64_t>(in_f);
-  key.d2 = 1;
-  key.d3 = 1;
-  key.base = x;
-  key.d1 = static_cast<uint64_t>(n);
-  key.b1 = 128;
-  wst_status_t st = cached_kv_tensor_map(&xmap, key);
-  if (st != WST_OK) return st;
-  key.base = w;
-  key.d1 = static_cast<uint64_t>(out_f);
-  key.b1 = narrow ? 64 : 256;
-  st = cached_kv_tensor_map(&wmap, key);
-  if (st != WST_OK) return st;
-  return narrow ? launch_gemm<64>(xmap, wmap, a, facts.sm_count)
-                : launch_gemm<256>(xmap, wmap, a, facts.sm_count);
+  /* Few tokens: the launch streams the weights once and is bound by how many SMs pull on
+   * HBM, so the feature tile is the one of 32, 48 or 64 rows that gives a CTA the least
+   * to stream (6144 features: 128 tiles of 48; 4096: 128 tiles of 32).  Else 256-feature
+   * tiles for the tensor pipe. */
+  int bn = 256;
+  if (n <= 128) {
+    long long best = -1;
+    for (int cand : {64, 48, 32}) {
+      const long long tiles = (out_f + cand - 1) / cand;
+      const long long per_cta = (tiles + facts.sm_count - 1) / facts.sm_count * cand;
+      if (best < 0 || per_cta < best) { best = per_cta; bn = cand; }
+    }
+  }
+  if (n > 128) return launch_gemm<256, 1, 128>(w, x, a, facts.sm_count);
+  /* a handful of tokens (decode-side chunks, speculative verification): four slabs of K
+   * per request, and only the token rows that exist are fetched */
+  if (in_f % 64 == 0 && n <= 16) return launch_narrow<4, 16>(bn, w, x, a, facts.sm_count);
+  if (in_f % 64 == 0 && n <= 64) return launch_narrow<4, 64>(bn, w, x, a, facts.sm_count);
+  if (in_f % 64 == 0) return launch_narrow<4, 128>(bn, w, x, a, facts.sm_count);
+  return launch_narrow<1, 128>(bn, w, x, a, facts.sm_count);
 }
 
 /* The engine sizes its prefill chunks by this (cuda/chunk_gemm.cu:367 returns 16, the
