@@ -211,6 +211,39 @@ WST_API wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
                                           int32_t head_dim, int32_t n, int32_t max_seq,
                                           float scale);
 
+/* ---- the projection fused with kernel set 1 ------------------------------------ */
+
+/* The qkv projection of a chunk step with the rotation, the head norm and the cache
+ * append in its epilogue: what wst_gemm_fp16 + wst_rope_cache_chunk_batch do in two
+ * launches with a [tokens][(n_q + 2 n_kv) * head_dim] fp32 buffer written and read back
+ * in between.  Here an accumulator tile of 128 tokens x 256 features is whole heads of
+ * whole tokens (two heads of 128, four of 64): a thread holds a head of its token in
+ * registers, norms it (q and k heads, if gains are given), rotates it at the token's
+ * cache position and stores fp16 -- q heads to q_out, k and v heads to the token's row
+ * of the batched cache.  No counterpart in the engine, which runs the two steps one
+ * after the other (engine.rs:796-809).
+ *   w         [(n_q + 2 n_kv) * head_dim][in_f] half     x  [n_seq * n][in_f] half
+ *   bias      [(n_q + 2 n_kv) * head_dim] half or null
+ *   q_out     [n_seq * n][n_q * head_dim] half: the rotated (and normed) queries, the
+ *             input of wst_b200_attn_chunk_batch_q16
+ *   k_cache, v_cache, cos_tab, sin_tab, seq_pos0, gains, eps: as for
+ *             wst_rope_cache_chunk_batch; table_len = rows of cos/sin
+ * head_dim 64 or 128; in_f a multiple of 8; 16-byte aligned buffers. */
+WST_API wst_status_t wst_b200_qkv_rope_append_batch(
+    const void *w, const void *x, const void *bias, void *q_out, void *k_cache, void *v_cache,
+    const void *cos_tab, const void *sin_tab, const void *seq_pos0, int32_t in_f, int32_t n_seq,
+    int32_t n, int32_t n_q, int32_t n_kv, int32_t head_dim, int32_t max_seq, int32_t table_len,
+    const void *q_norm_w, const void *k_norm_w, float eps);
+
+/* wst_attn_chunk_batch over fp16 query rows [n_seq * n][n_q * head_dim] (q_out above)
+ * instead of the fp32 projection buffer.  Taken by the tensor-core kernels only: chunks
+ * of at least 64 query rows per KV head, else WST_ERR_SHAPE. */
+WST_API wst_status_t wst_b200_attn_chunk_batch_q16(const void *q16, const void *k_cache,
+                                                   const void *v_cache, void *out,
+                                                   const void *seq_pos0, int32_t n_seq, int32_t n_q,
+                                                   int32_t n_kv, int32_t head_dim, int32_t n,
+                                                   int32_t max_seq, float scale);
+
 /* ------------------------------------------------ paged cache, many sequences */
 
 /* Paged KV pool: [n_pool_pages][n_kv][page_size][head_dim] half for K and for V.

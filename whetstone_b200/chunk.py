@@ -139,3 +139,59 @@ def attn_batch(qkv: torch.Tensor, cache: KvCacheBatch, out: torch.Tensor, n_q: i
 
 
 __all__ = ["rope_cache", "attn", "KvCacheBatch", "rope_cache_batch", "attn_batch"]
+
+
+def qkv_rope_append_batch(w: torch.Tensor, x: torch.Tensor, bias: torch.Tensor | None,
+                          q_out: torch.Tensor, cache: KvCacheBatch, table: RopeTable, n_q: int,
+                          seq_pos0: torch.Tensor, n: int, qk_norm: QkNorm | None = None) -> None:
+    """The qkv projection of n tokens per sequence with RoPE, head norm and cache append in
+    its epilogue: x [n_seq * n][in] fp16, w [(n_q + 2 n_kv) * hd][in] fp16; the rotated
+    queries land in q_out [n_seq * n][n_q * hd] fp16, k and v in the batched cache."""
+    hd = cache.head_dim
+    width = (n_q + 2 * cache.n_kv) * hd
+    tokens = cache.n_seq * n
+    _require_cuda(w, "qkv_rope_append_batch: w", torch.float16)
+    _require_cuda(x, "qkv_rope_append_batch: x", torch.float16)
+    _require_cuda(q_out, "qkv_rope_append_batch: q_out", torch.float16)
+    _require_cuda(seq_pos0, "qkv_rope_append_batch: seq_pos0", torch.int32)
+    if x.numel() % tokens != 0:
+        raise ShapeError(5, f"qkv_rope_append_batch: x[{x.numel()}] is not {tokens} rows")
+    in_f = x.numel() // tokens
+    if w.numel() != width * in_f:
+        raise ShapeError(5, f"qkv_rope_append_batch: w[{w.numel()}] needs {width} * {in_f}")
+    if q_out.numel() < tokens * n_q * hd:
+        raise ShapeError(5, f"qkv_rope_append_batch: q_out[{q_out.numel()}] needs {tokens} * {n_q} * {hd}")
+    if bias is not None:
+        _require_cuda(bias, "qkv_rope_append_batch: bias", torch.float16)
+        if bias.numel() != width:
+            raise ShapeError(5, f"qkv_rope_append_batch: bias has {bias.numel()} elements, expected {width}")
+    if seq_pos0.numel() != cache.n_seq:
+        raise ShapeError(5, "qkv_rope_append_batch: seq_pos0 needs one entry per sequence")
+    if table.half_dim != hd // 2:
+        raise ShapeError(5, "qkv_rope_append_batch: rotary table does not match the head width")
+    if qk_norm is not None:
+        qk_norm.check(hd)
+    qw, kw, eps = norm_ptrs(qk_norm)
+    use_torch_stream()
+    check(lib.wst_b200_qkv_rope_append_batch(
+        _ptr(w), _ptr(x), _ptr(bias) if bias is not None else None, _ptr(q_out), _ptr(cache.k),
+        _ptr(cache.v), _ptr(table.cos), _ptr(table.sin), _ptr(seq_pos0), in_f, cache.n_seq, n, n_q,
+        cache.n_kv, hd, cache.max_seq, table.max_seq, qw, kw, eps))
+
+
+def attn_batch_q16(q16: torch.Tensor, cache: KvCacheBatch, out: torch.Tensor, n_q: int,
+                   seq_pos0: torch.Tensor, n: int) -> None:
+    """attn_batch over fp16 query rows [n_seq * n][n_q * head_dim] (what
+    qkv_rope_append_batch leaves)."""
+    hd = cache.head_dim
+    _require_cuda(q16, "attn_chunk_batch_q16: q", torch.float16)
+    _require_cuda(out, "attn_chunk_batch_q16: out", torch.float16)
+    _require_cuda(seq_pos0, "attn_chunk_batch_q16: seq_pos0", torch.int32)
+    need = cache.n_seq * n * n_q * hd
+    if q16.numel() < need or out.numel() < need:
+        raise ShapeError(5, f"attn_chunk_batch_q16: q[{q16.numel()}] and out[{out.numel()}] need {need}")
+    use_torch_stream()
+    check(lib.wst_b200_attn_chunk_batch_q16(_ptr(q16), _ptr(cache.k), _ptr(cache.v), _ptr(out),
+                                            _ptr(seq_pos0), cache.n_seq, n_q, cache.n_kv, hd, n,
+                                            cache.max_seq, 1.0 / math.sqrt(hd)))
+

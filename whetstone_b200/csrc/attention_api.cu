@@ -535,11 +535,12 @@ extern "C" wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache,
   return launch_rows(L);
 }
 
-extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
-                                             const void *v_cache, void *out,
-                                             const void *seq_pos0, int32_t n_seq, int32_t n_q,
-                                             int32_t n_kv, int32_t head_dim, int32_t n,
-                                             int32_t max_seq, float scale) {
+/* wst_attn_chunk_batch and its form with fp16 query rows (q16: `qkv` is a packed
+ * [tokens][n_q * head_dim] half buffer, as the fused projection leaves it). */
+static wst_status_t chunk_batch_common(const void *qkv, bool q16, const void *k_cache,
+                                       const void *v_cache, void *out, const void *seq_pos0,
+                                       int32_t n_seq, int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                       int32_t n, int32_t max_seq, float scale) {
   WST_CHECK_ARG(qkv && k_cache && v_cache && out && seq_pos0, "wst_attn_chunk_batch: null pointer");
   WST_CHECK_ARG(n_q > 0 && n_kv > 0 && head_dim > 0 && n > 0 && n_seq > 0,
                 "wst_attn_chunk_batch: non-positive shape");
@@ -551,17 +552,23 @@ extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cach
     return fail(WST_ERR_SHAPE,
                 "wst_attn_chunk_batch: needs head_dim 64 or 128, at most 64 query heads per KV "
                 "head and 16-byte aligned buffers");
-  const long long q_stride = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
+  const long long q_stride =
+      q16 ? static_cast<long long>(n_q) * head_dim : static_cast<long long>(n_q + 2 * n_kv) * head_dim;
   const int choice = g_kernel_choice.load();
   bool use_prefill = choice != 2 && prefill_kernel_supports(n_q, n_kv, head_dim, n);
-  if (use_prefill && choice != 3 && choice != 4) {
+  if (use_prefill && choice != 3 && choice != 4 && !q16) {
     const int gqa = n_q / n_kv;
     use_prefill = (static_cast<long long>(n) * gqa + 127) / 128 * n_kv * n_seq >= 32;
   }
+  if (q16 && !use_prefill)
+    return fail(WST_ERR_SHAPE,
+                "wst_b200_attn_chunk_batch_q16: fp16 query rows are taken by the tensor-core "
+                "kernels only (chunks of at least 128 query rows per KV head)");
   if (use_prefill) {
     PrefillLaunch P;
     P.name = "wst_attn_chunk_batch";
     P.qkv = static_cast<const float *>(qkv);
+    P.q16 = q16;
     P.q_tok_stride = q_stride;
     P.k = static_cast<const __half *>(k_cache);
     P.v = static_cast<const __half *>(v_cache);
@@ -618,6 +625,24 @@ extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cach
     if (!L.scratch && max_seq > 2 * kRowsTile) note_unsplit("wst_attn_chunk_batch", why);
   }
   return launch_rows(L);
+}
+
+extern "C" wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
+                                             const void *v_cache, void *out,
+                                             const void *seq_pos0, int32_t n_seq, int32_t n_q,
+                                             int32_t n_kv, int32_t head_dim, int32_t n,
+                                             int32_t max_seq, float scale) {
+  return chunk_batch_common(qkv, false, k_cache, v_cache, out, seq_pos0, n_seq, n_q, n_kv, head_dim,
+                            n, max_seq, scale);
+}
+
+extern "C" wst_status_t wst_b200_attn_chunk_batch_q16(const void *q16, const void *k_cache,
+                                                      const void *v_cache, void *out,
+                                                      const void *seq_pos0, int32_t n_seq,
+                                                      int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                                      int32_t n, int32_t max_seq, float scale) {
+  return chunk_batch_common(q16, true, k_cache, v_cache, out, seq_pos0, n_seq, n_q, n_kv, head_dim,
+                            n, max_seq, scale);
 }
 
 extern "C" int64_t wst_attn_verify_scratch_floats(int32_t n_seq, int32_t max_tokens_per_seq,

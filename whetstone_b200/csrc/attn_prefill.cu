@@ -76,6 +76,7 @@ struct PCfg {
 struct PrefillArgs {
   const float *q;            /* [token][q_tok_stride], sequence s owns tokens s*n .. or cu_tokens */
   long long q_tok_stride;
+  int q16;                   /* q is fp16: the pointer is reinterpreted, the stride is in halves */
   __half *out;               /* [token][n_q*hd] */
   float *scratch;            /* split mode: [unit][slice][rows_cap][hd+4] */
   const int32_t *pos0_dev;   /* per-sequence chunk start, or null: pos0 for all */
@@ -372,10 +373,22 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap,
                          static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD + half * OC;
       constexpr int QC = OC / 2; /* 32-bit columns this thread writes */
       uint32_t packed[QC];
+      const __half *src16 = reinterpret_cast<const __half *>(a.q) +
+                            static_cast<long long>(tok_base + r / a.gqa) * a.q_tok_stride +
+                            static_cast<long long>(kvh * a.gqa + r % a.gqa) * HD + half * OC;
 #pragma unroll
       for (int e = 0; e < QC; e += 2) {
         float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (valid) f = __ldg(reinterpret_cast<const float4 *>(src + 2 * e));
+        if (valid) {
+          if (a.q16) {
+            const uint2 h = __ldg(reinterpret_cast<const uint2 *>(src16 + 2 * e));
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&h.y));
+            f = make_float4(lo.x, lo.y, hi.x, hi.y);
+          } else {
+            f = __ldg(reinterpret_cast<const float4 *>(src + 2 * e));
+          }
+        }
         packed[e] = pack_half2(f.x * a.qscale, f.y * a.qscale);
         packed[e + 1] = pack_half2(f.z * a.qscale, f.w * a.qscale);
       }
@@ -843,12 +856,24 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap kmap,
       int tok = row / a.gqa, head = row % a.gqa;
       const float *q_tile = a.q + static_cast<long long>(seq * a.n + my_tok0) * a.q_tok_stride +
                             static_cast<long long>(kvh * a.gqa) * HD + 4 * l;
+      const __half *q16_tile = reinterpret_cast<const __half *>(a.q) +
+                               static_cast<long long>(seq * a.n + my_tok0) * a.q_tok_stride +
+                               static_cast<long long>(kvh * a.gqa) * HD + 4 * l;
       uint8_t *q_smem = smem + C::OFF_Q + t * C::Q_BYTES + ((l >> 1) >> 3) * HALF_BYTES + (l & 1) * 8;
 #pragma unroll 8
       for (int i = 0; i < 32 / RPI; ++i) {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row < rows_valid)
-          v = __ldg(reinterpret_cast<const float4 *>(q_tile + tok * a.q_tok_stride + head * HD));
+        if (row < rows_valid) {
+          if (a.q16) {
+            const uint2 h =
+                __ldg(reinterpret_cast<const uint2 *>(q16_tile + tok * a.q_tok_stride + head * HD));
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&h.y));
+            v = make_float4(lo.x, lo.y, hi.x, hi.y);
+          } else {
+            v = __ldg(reinterpret_cast<const float4 *>(q_tile + tok * a.q_tok_stride + head * HD));
+          }
+        }
         uint2 h;
         h.x = pack_half2(v.x * a.qscale, v.y * a.qscale);
         h.y = pack_half2(v.z * a.qscale, v.w * a.qscale);
@@ -1708,6 +1733,7 @@ wst_status_t launch_verify_span(const PrefillLaunch &P) {
   if (cap < 2) return fail(WST_ERR_INVALID_ARG, "%s: scratch too small", P.name);
   const int max_tiles = (P.max_len > 0 ? P.max_len : P.max_seq) / 128 + 1;
 
+  if (P.q16) return fail(WST_ERR_SHAPE, "%s: fp16 query rows are not taken by the paged verify", P.name);
   SpanArgs a{};
   a.q = P.qkv;
   a.q_tok_stride = P.q_tok_stride;
@@ -1795,6 +1821,7 @@ wst_status_t launch_prefill(const PrefillLaunch &P) {
   PrefillArgs a{};
   a.q = P.qkv;
   a.q_tok_stride = P.q_tok_stride;
+  a.q16 = P.q16 ? 1 : 0;
   a.out = P.out;
   a.scratch = P.scratch;
   a.pos0_dev = P.pos0_dev;

@@ -11,6 +11,7 @@ namespace wst {
 struct PrefillLaunch {
   const float *qkv = nullptr;  /* [n][q_tok_stride] fp32, q of head h at h*hd */
   long long q_tok_stride = 0;
+  bool q16 = false;            /* the q rows are fp16 (stride in halves): qkv points at them */
   const __half *k = nullptr;   /* [n_kv][max_seq][hd] */
   const __half *v = nullptr;
   __half *out = nullptr;       /* [n][n_q*hd] */

@@ -68,9 +68,96 @@ struct GemmArgs {
   int in_f, out_f, n, accum;
   int m_tiles, n_tiles;
   unsigned int *err_word;
+  /* the fused form (ROPE): the tile's columns are whole heads of the qkv row; they are
+   * normed, rotated and stored where the attention reads them instead of going to y */
+  __half *q_out;         /* [n][n_q * hd] */
+  __half *k_cache;       /* [n_seq][n_kv][max_seq][hd] */
+  __half *v_cache;
+  const float *cos_tab;  /* [table_len][hd / 2] */
+  const float *sin_tab;
+  const __half *q_gain;  /* [hd] or null */
+  const __half *k_gain;
+  const int32_t *seq_pos0; /* [n_seq] */
+  int n_q, n_kv, hd, n_per_seq, max_seq, table_len;
+  float eps;
 };
 
-template <int BN, int KS, int RB>
+/* Epilogue of the fused form for one head of one token: HD accumulator columns from
+ * tensor memory (+ bias) -> per-head RMS norm with fp16 gains (q and k heads, if gains
+ * are given) -> half-rotation RoPE at the token's position -> fp16, to the q buffer or
+ * to the token's cache row; v heads are narrowed and stored as they are.  The
+ * arithmetic is that of rope_append_kernel (norm before rotation, x * inv * gain,
+ * cuda/decode.cu:112-178 and cuda/chunk_ops.cu:101-150 of the engine). */
+template <int HD>
+__device__ __forceinline__ void rope_head_epilogue(const GemmArgs &a, uint32_t tmem_head, int head,
+                                                   int tpos, long long kv_row, int tok, bool valid) {
+  float x[HD];
+#pragma unroll
+  for (int c0 = 0; c0 < HD; c0 += 32) {
+    uint32_t v[32];
+    tmem_ld_32x32(tmem_head + c0, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int e = 0; e < 32; ++e) x[c0 + e] = __uint_as_float(v[e]);
+  }
+  if (!valid) return;
+  if (a.bias) {
+#pragma unroll
+    for (int e = 0; e < HD; e += 2) {
+      const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(a.bias + head * HD + e));
+      x[e] += b.x;
+      x[e + 1] += b.y;
+    }
+  }
+  constexpr int HALF = HD / 2;
+  const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
+  __half *dst;
+  if (is_q) {
+    dst = a.q_out + (static_cast<long long>(tok) * a.n_q + head) * HD;
+  } else {
+    const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+    dst = (is_k ? a.k_cache : a.v_cache) + kv_row + static_cast<long long>(kvh) * a.max_seq * HD;
+  }
+  if (is_q || is_k) {
+    const __half *gain = is_q ? a.q_gain : a.k_gain;
+    if (gain) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < HALF; ++e) ss = fmaf(x[e], x[e], fmaf(x[e + HALF], x[e + HALF], ss));
+      const float inv = rsqrtf(ss / static_cast<float>(HD) + a.eps);
+#pragma unroll
+      for (int e = 0; e < HD; e += 2) {
+        const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(gain + e));
+        x[e] = x[e] * inv * g.x;
+        x[e + 1] = x[e + 1] * inv * g.y;
+      }
+    }
+    const float4 *ct = reinterpret_cast<const float4 *>(a.cos_tab + static_cast<long long>(tpos) * HALF);
+    const float4 *st = reinterpret_cast<const float4 *>(a.sin_tab + static_cast<long long>(tpos) * HALF);
+#pragma unroll
+    for (int e = 0; e < HALF; e += 4) {
+      const float4 c = __ldg(ct + e / 4), sn = __ldg(st + e / 4);
+      const float cc[4] = {c.x, c.y, c.z, c.w}, ss4[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float x1 = x[e + k], x2 = x[e + k + HALF];
+        x[e + k] = x1 * cc[k] - x2 * ss4[k];
+        x[e + k + HALF] = x2 * cc[k] + x1 * ss4[k];
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < HD; e += 8) {
+    uint4 o;
+    o.x = pack_half2(x[e], x[e + 1]);
+    o.y = pack_half2(x[e + 2], x[e + 3]);
+    o.z = pack_half2(x[e + 4], x[e + 5]);
+    o.w = pack_half2(x[e + 6], x[e + 7]);
+    *reinterpret_cast<uint4 *>(dst + e) = o;
+  }
+}
+
+template <int BN, int KS, int RB, bool ROPE>
 __global__ void __launch_bounds__(GCfg<BN, KS, RB>::THREADS, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                 const GemmArgs a) {
@@ -184,6 +271,36 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
       if (!mbar_wait(bar(ACC_FULL + buf), (local >> 1) & 1, a.err_word, 0x604u)) break;
       tc_fence_after_sync();
       const int row = m0 + r;
+      if constexpr (ROPE) {
+        /* the token's sequence, cache position (clamped, never trusted) and cache row */
+        const bool valid = row < a.n;
+        const int sq = valid ? row / a.n_per_seq : 0;
+        int pos = valid ? a.seq_pos0[sq] + (row - sq * a.n_per_seq) : 0;
+        pos = pos < 0 ? 0 : pos;
+        pos = pos < a.max_seq - 1 ? pos : a.max_seq - 1;
+        const int tpos = pos < a.table_len - 1 ? pos : a.table_len - 1;
+        const long long kv_row =
+            (static_cast<long long>(sq) * a.n_kv * a.max_seq + pos) * static_cast<long long>(a.hd);
+        const uint32_t acc = tmem + lane_base + buf * C::ACC_STRIDE;
+        if (a.hd == 128) {
+#pragma unroll 1
+          for (int h = 0; h < BN / 128; ++h) {
+            const int head = (n0 >> 7) + h;
+            rope_head_epilogue<128>(a, acc + h * 128, head, tpos, kv_row, row,
+                                    valid && head * 128 < a.out_f);
+          }
+        } else {
+#pragma unroll 1
+          for (int h = 0; h < BN / 64; ++h) {
+            const int head = (n0 >> 6) + h;
+            rope_head_epilogue<64>(a, acc + h * 64, head, tpos, kv_row, row,
+                                   valid && head * 64 < a.out_f);
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(bar(ACC_EMPTY + buf));
+        continue;
+      }
       float *yrow = a.y + static_cast<long long>(row) * a.out_f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -297,7 +414,7 @@ wst_status_t operand_map(CUtensorMap *out, const void *base, int in_f, int rows,
   return WST_OK;
 }
 
-template <int BN, int KS, int RB>
+template <int BN, int KS, int RB, bool ROPE = false>
 wst_status_t launch_gemm(const void *w, const void *x, GemmArgs a, int sm_count) {
   using C = GCfg<BN, KS, RB>;
   CUtensorMap xmap, wmap;
@@ -309,7 +426,7 @@ wst_status_t launch_gemm(const void *w, const void *x, GemmArgs a, int sm_count)
   int dev = 0;
   WST_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    WST_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<BN, KS, RB>,
+    WST_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<BN, KS, RB, ROPE>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured_dev = dev;
   }
@@ -326,7 +443,7 @@ wst_status_t launch_gemm(const void *w, const void *x, GemmArgs a, int sm_count)
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_f16_kernel<BN, KS, RB>, xmap, wmap, a);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_f16_kernel<BN, KS, RB, ROPE>, xmap, wmap, a);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("wst_gemm_fp16 (launch)", e);
   return WST_OK;
@@ -400,6 +517,62 @@ extern "C" wst_status_t wst_gemm_fp16(const void *w, const void *x, const void *
   if (in_f % 64 == 0 && n <= 64) return launch_narrow<4, 64>(bn, w, x, a, facts.sm_count);
   if (in_f % 64 == 0) return launch_narrow<4, 128>(bn, w, x, a, facts.sm_count);
   return launch_narrow<1, 128>(bn, w, x, a, facts.sm_count);
+}
+
+extern "C" wst_status_t wst_b200_qkv_rope_append_batch(
+    const void *w, const void *x, const void *bias, void *q_out, void *k_cache, void *v_cache,
+    const void *cos_tab, const void *sin_tab, const void *seq_pos0, int32_t in_f, int32_t n_seq,
+    int32_t n, int32_t n_q, int32_t n_kv, int32_t head_dim, int32_t max_seq, int32_t table_len,
+    const void *q_norm_w, const void *k_norm_w, float eps) {
+  const char *name = "wst_b200_qkv_rope_append_batch";
+  WST_CHECK_ARG(w && x && q_out && k_cache && v_cache && cos_tab && sin_tab && seq_pos0,
+                "wst_b200_qkv_rope_append_batch: null pointer");
+  WST_CHECK_ARG(in_f > 0 && n_seq > 0 && n > 0 && n_q > 0 && n_kv > 0 && max_seq > 0 &&
+                    table_len > 0,
+                "wst_b200_qkv_rope_append_batch: non-positive shape");
+  WST_CHECK_ARG(head_dim == 64 || head_dim == 128,
+                "wst_b200_qkv_rope_append_batch: head_dim must be 64 or 128");
+  WST_CHECK_ARG(in_f % 8 == 0, "wst_b200_qkv_rope_append_batch: in_features must be a multiple of 8");
+  const long long tokens = static_cast<long long>(n_seq) * n;
+  const long long out_f = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
+  WST_CHECK_ARG(tokens <= 0x7fffffffLL && out_f <= 0x7fffffffLL,
+                "wst_b200_qkv_rope_append_batch: shape overflows");
+  for (const void *ptr : {w, x, static_cast<const void *>(q_out), static_cast<const void *>(k_cache),
+                          static_cast<const void *>(v_cache), cos_tab, sin_tab})
+    WST_CHECK_ARG((reinterpret_cast<uintptr_t>(ptr) & 15) == 0,
+                  "wst_b200_qkv_rope_append_batch: buffers must be 16-byte aligned");
+  WST_CHECK_ARG((!bias || (reinterpret_cast<uintptr_t>(bias) & 3) == 0) &&
+                    (!q_norm_w || (reinterpret_cast<uintptr_t>(q_norm_w) & 3) == 0) &&
+                    (!k_norm_w || (reinterpret_cast<uintptr_t>(k_norm_w) & 3) == 0),
+                "wst_b200_qkv_rope_append_batch: bias and gains must be 4-byte aligned");
+  DeviceFacts facts;
+  if (!device_facts(&facts)) return WST_ERR_CUDA;
+  if (facts.cc_major < 10)
+    return fail(WST_ERR_UNSUPPORTED_ARCH, "%s: this library is built for sm_100a only", name);
+  unsigned int *err_word = device_error_word();
+  if (!err_word) return WST_ERR_CUDA;
+  GemmArgs a{};
+  a.bias = static_cast<const __half *>(bias);
+  a.in_f = in_f;
+  a.out_f = static_cast<int>(out_f);
+  a.n = static_cast<int>(tokens);
+  a.err_word = err_word;
+  a.q_out = static_cast<__half *>(q_out);
+  a.k_cache = static_cast<__half *>(k_cache);
+  a.v_cache = static_cast<__half *>(v_cache);
+  a.cos_tab = static_cast<const float *>(cos_tab);
+  a.sin_tab = static_cast<const float *>(sin_tab);
+  a.q_gain = static_cast<const __half *>(q_norm_w);
+  a.k_gain = static_cast<const __half *>(k_norm_w);
+  a.seq_pos0 = static_cast<const int32_t *>(seq_pos0);
+  a.n_q = n_q;
+  a.n_kv = n_kv;
+  a.hd = head_dim;
+  a.n_per_seq = n;
+  a.max_seq = max_seq;
+  a.table_len = table_len;
+  a.eps = eps;
+  return launch_gemm<256, 1, 128, true>(w, x, a, facts.sm_count);
 }
 
 /* The engine sizes its prefill chunks by this (cuda/chunk_gemm.cu:367 returns 16, the
