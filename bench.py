@@ -591,6 +591,63 @@ def bench_also(torch, args):
             del ws
         out["projection_gemm_fp16"] = legs
 
+        # The attention block of one c4 chunk step (chunk 8 of 16: rows 4096..4607), end to
+        # end, both ways: qkv projection -> RoPE/norm/append -> attention -> o_proj into the
+        # residual.  "fused": the projection's epilogue does the RoPE step and leaves fp16
+        # q rows (3 launches); "separate": the engine's sequence of entry points with the
+        # fp32 projection buffer in between (4 launches).
+        n4, nseq, prompt4 = wl.C4["chunk"], wl.C4["n_seq"], wl.C4["prompt"]
+        c_mid = (prompt4 // n4) // 2
+        table4 = decode.RopeTable(prompt4, s4.head_dim, s4.theta)
+        norm4 = decode.QkNorm((1 + 0.02 * randn16((s4.head_dim,)).float()).half(),
+                              (1 + 0.02 * randn16((s4.head_dim,)).float()).half(), wl.C4["eps"])
+        cache4 = chunk.KvCacheBatch(nseq, s4.n_kv, s4.head_dim, prompt4)
+        cache4.k.copy_(randn16(tuple(cache4.k.shape)))
+        cache4.v.copy_(randn16(tuple(cache4.v.shape)))
+        starts4 = torch.full((nseq,), c_mid * n4, dtype=torch.int32, device="cuda")
+        blocks = 4   # weight sets rotated: 4 x (50 + 34) MB > L2
+        wq = [(randn16((s4.qkv_width, hid4)).float() / hid4 ** 0.5).half() for _ in range(blocks)]
+        wo = [(randn16((hid4, hid4)).float() / hid4 ** 0.5).half() for _ in range(blocks)]
+        h4 = randn16((n_big, hid4))
+        resid = torch.zeros((n_big, hid4), dtype=torch.float32, device="cuda")
+        y4 = torch.zeros((n_big, s4.qkv_width), dtype=torch.float32, device="cuda")
+        q16 = torch.zeros((n_big, s4.n_q * s4.head_dim), dtype=torch.float16, device="cuda")
+        att = torch.zeros(n_big * s4.n_q * s4.head_dim, dtype=torch.float16, device="cuda")
+
+        def block_fused():
+            for i in range(blocks):
+                chunk.qkv_rope_append_batch(wq[i], h4, None, q16, cache4, table4, s4.n_q, starts4,
+                                            n4, norm4)
+                chunk.attn_batch_q16(q16, cache4, att, s4.n_q, starts4, n4)
+                chunk.gemm_fp16(wo[i], att, None, resid, hid4, hid4, n_big, True)
+
+        def block_separate():
+            for i in range(blocks):
+                chunk.gemm_fp16(wq[i], h4, None, y4, hid4, s4.qkv_width, n_big, False)
+                chunk.rope_cache_batch(y4, cache4, table4, s4.n_q, starts4, n4, norm4)
+                chunk.attn_batch(y4, cache4, att, s4.n_q, starts4, n4)
+                chunk.gemm_fp16(wo[i], att, None, resid, hid4, hid4, n_big, True)
+        block_fused()
+        att_fused = att.clone()
+        block_separate()
+        torch.cuda.synchronize()
+        dev_err = float((att.float() - att_fused.float()).abs().max())
+        if not dev_err <= 2e-3:
+            raise SystemExit(f"[bench] attention block: fused and separate chains differ by {dev_err}")
+        sec_f = timed_graph(torch, block_fused, max(1, min(args.steps, 20) // 4), 3)
+        require_clean(torch, decode, None, "attention block, fused")
+        sec_s = timed_graph(torch, block_separate, max(1, min(args.steps, 20) // 4), 3)
+        require_clean(torch, decode, None, "attention block, separate")
+        flops_blk = 2.0 * hid4 * s4.qkv_width * n_big + 2.0 * hid4 * hid4 * n_big + \
+            nseq * wl.prefill_flops(s4.n_q, s4.head_dim, c_mid * n4, n4)
+        out["c4_attention_block_chunk8"] = {
+            "fused_us": sec_f / blocks * 1e6, "separate_us": sec_s / blocks * 1e6,
+            "fused_tflops": flops_blk / (sec_f / blocks) / 1e12,
+            "separate_tflops": flops_blk / (sec_s / blocks) / 1e12,
+            "flops": flops_blk, "max_abs_diff_between_the_chains": dev_err,
+            "launches": {"fused": 3, "separate": 4}, **sec_f.stats}
+        del wq, wo, cache4
+
     # ---- c5: speculative verify, 16 sequences x 5 drafts, paged cache, 28 layers
     if want("c5"):
         s5 = wl.QWEN25_7B
