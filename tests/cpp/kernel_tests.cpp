@@ -3,7 +3,7 @@
  * written against the Rust one:
  *
  *   crates/whetstone-kernels/tests/decode_kernels.rs:91-410
- *   crates/whetstone-kernels/tests/chunk_kernels.rs:263-360
+ *   crates/whetstone-kernels/tests/chunk_kernels.rs:51-108 (the fp16 projection), :263-360
  *
  * Same closed-form inputs, same LCG, same tolerances.  Prints one line per test
  * and exits non-zero if any failed; needs a B200.
@@ -410,6 +410,36 @@ static void decode_step_replays_as_a_graph() {
   for (float x : o) REQUIRE(std::isfinite(x), "finite output");
 }
 
+/* chunk_kernels.rs:51-108.  The engine pins its chunk GEMM against its own GEMV; the
+ * GEMV is not part of this library, so the yardstick here is the same sum in double on
+ * the host, with the engine's tolerance. */
+static void gemm_case(size_t in_f, size_t out_f, size_t n, bool with_bias, bool accumulate,
+                      uint64_t sw, uint64_t sx, uint64_t sb) {
+  auto w = f16v(noise(in_f * out_f, sw)), x = f16v(noise(in_f * n, sx));
+  auto bias = f16v(noise(out_f, sb));
+  auto seed_y = noise(n * out_f, 66);
+  auto wd = DeviceBuffer<uint16_t>::from_slice(w), xd = DeviceBuffer<uint16_t>::from_slice(x);
+  auto bd = DeviceBuffer<uint16_t>::from_slice(bias);
+  auto yd = accumulate ? DeviceBuffer<float>::from_slice(seed_y) : DeviceBuffer<float>::zeros(n * out_f);
+  chunk::gemm_fp16(wd, xd, with_bias ? &bd : nullptr, yd, in_f, out_f, n, accumulate);
+  auto got = yd.to_vec();
+  auto wf = from_f16(w), xf = from_f16(x), bf = from_f16(bias);
+  for (size_t j = 0; j < n; ++j)
+    for (size_t r = 0; r < out_f; ++r) {
+      double want = accumulate ? seed_y[j * out_f + r] : 0.0;
+      for (size_t c = 0; c < in_f; ++c) want += static_cast<double>(xf[j * in_f + c]) * wf[r * in_f + c];
+      if (with_bias) want += bf[r];
+      const double scale = std::fmax(std::fabs(want), 1.0);
+      REQUIRE(std::fabs(got[j * out_f + r] - want) <= 2e-3 * scale, "gemm_fp16 output");
+    }
+}
+static void gemm_fp16_matches_the_sum_per_token() { gemm_case(896, 320, 7, true, false, 11, 22, 33); }
+static void gemm_fp16_accumulates_the_same_way() { gemm_case(256, 96, 5, false, true, 44, 55, 0); }
+static void gemm_fp16_takes_a_whole_chunk_in_one_pass() {
+  REQUIRE(chunk::max_tokens() >= 512, "one pass covers a 512-token chunk");
+  gemm_case(512, 384, 300, true, false, 7, 8, 9);
+}
+
 int main() {
   int32_t devices = 0;
   if (wst_device_count(&devices) != WST_OK || devices == 0) {
@@ -426,6 +456,9 @@ int main() {
       {"rope_and_attention_chunk_match_sequential_decode", rope_and_attention_chunk_match_sequential_decode},
       {"attention_chunk_resumes_mid_cache", attention_chunk_resumes_mid_cache},
       {"batched_chunk_matches_one_sequence_at_a_time", batched_chunk_matches_one_sequence_at_a_time},
+      {"gemm_fp16_matches_the_sum_per_token", gemm_fp16_matches_the_sum_per_token},
+      {"gemm_fp16_accumulates_the_same_way", gemm_fp16_accumulates_the_same_way},
+      {"gemm_fp16_takes_a_whole_chunk_in_one_pass", gemm_fp16_takes_a_whole_chunk_in_one_pass},
       {"shape_errors_are_typed_and_launch_nothing", shape_errors_are_typed_and_launch_nothing},
       {"decode_step_replays_as_a_graph", decode_step_replays_as_a_graph},
   };

@@ -359,6 +359,82 @@ inline void attn_batch(const DeviceBuffer<float> &qkv, const KvCacheBatch &cache
                              1.0f / std::sqrt(static_cast<float>(hd))));
 }
 
+/* y[j] = W x[j] + b for every j < n, or += when `accumulate` (src/chunk.rs:55-99). */
+inline void gemm_fp16(const DeviceBuffer<uint16_t> &w, const DeviceBuffer<uint16_t> &x,
+                      const DeviceBuffer<uint16_t> *bias, DeviceBuffer<float> &y, size_t in_features,
+                      size_t out_features, size_t n, bool accumulate) {
+  using detail::S;
+  if (x.len() != n * in_features || y.len() != n * out_features)
+    throw Error::shape("gemm_fp16: x[" + S(x.len()) + "], y[" + S(y.len()) + "] do not match n=" +
+                       S(n) + ", in=" + S(in_features) + ", out=" + S(out_features));
+  if (w.len() != in_features * out_features)
+    throw Error::shape("gemm_fp16: weights have " + S(w.len()) + " elements, expected " +
+                       S(in_features) + "*" + S(out_features));
+  if (bias && bias->len() != out_features)
+    throw Error::shape("gemm_fp16: bias has " + S(bias->len()) + " elements, expected " +
+                       S(out_features));
+  check(wst_gemm_fp16(w.as_ptr(), x.as_ptr(), bias ? bias->as_ptr() : nullptr, y.as_mut_ptr(),
+                      static_cast<int32_t>(in_features), static_cast<int32_t>(out_features),
+                      static_cast<int32_t>(n), accumulate ? 1 : 0));
+}
+
+/* Tokens one weight pass serves (src/chunk.rs:20). */
+inline size_t max_tokens() {
+  const int32_t m = wst_chunk_max_tokens();
+  return m < 1 ? 1 : static_cast<size_t>(m);
+}
+
+/* The qkv projection with RoPE, head norm and cache append in its epilogue; the rotated
+ * queries land in q_out [n_seq * n][n_q * head_dim] (no counterpart in the engine). */
+inline void qkv_rope_append_batch(const DeviceBuffer<uint16_t> &w, const DeviceBuffer<uint16_t> &x,
+                                  const DeviceBuffer<uint16_t> *bias, DeviceBuffer<uint16_t> &q_out,
+                                  KvCacheBatch &cache, const RopeTable &table, size_t n_q,
+                                  const DeviceBuffer<int32_t> &seq_pos0, size_t n,
+                                  const QkNorm *qk_norm = nullptr) {
+  using detail::S;
+  const size_t hd = cache.head_dim, width = (n_q + 2 * cache.n_kv) * hd, tokens = cache.n_seq * n;
+  if (tokens == 0 || x.len() % tokens != 0)
+    throw Error::shape("qkv_rope_append_batch: x[" + S(x.len()) + "] is not " + S(tokens) + " rows");
+  const size_t in_f = x.len() / tokens;
+  if (w.len() != width * in_f)
+    throw Error::shape("qkv_rope_append_batch: w[" + S(w.len()) + "] needs " + S(width) + " * " + S(in_f));
+  if (q_out.len() < tokens * n_q * hd)
+    throw Error::shape("qkv_rope_append_batch: q_out[" + S(q_out.len()) + "] needs " + S(tokens) +
+                       " * " + S(n_q) + " * " + S(hd));
+  if (bias && bias->len() != width)
+    throw Error::shape("qkv_rope_append_batch: bias has " + S(bias->len()) + " elements, expected " + S(width));
+  if (seq_pos0.len() != cache.n_seq)
+    throw Error::shape("qkv_rope_append_batch: seq_pos0 needs one entry per sequence");
+  if (table.half_dim != hd / 2)
+    throw Error::shape("qkv_rope_append_batch: rotary table does not match the head width");
+  if (qk_norm && (qk_norm->q->len() != hd || qk_norm->k->len() != hd))
+    throw Error::shape("qkv_rope_append_batch: gains must be head_dim " + S(hd));
+  const auto np = detail::norm_ptrs(qk_norm);
+  check(wst_b200_qkv_rope_append_batch(
+      w.as_ptr(), x.as_ptr(), bias ? bias->as_ptr() : nullptr, q_out.as_mut_ptr(), cache.k.as_mut_ptr(),
+      cache.v.as_mut_ptr(), table.cos.as_ptr(), table.sin.as_ptr(), seq_pos0.as_ptr(),
+      static_cast<int32_t>(in_f), static_cast<int32_t>(cache.n_seq), static_cast<int32_t>(n),
+      static_cast<int32_t>(n_q), static_cast<int32_t>(cache.n_kv), static_cast<int32_t>(hd),
+      static_cast<int32_t>(cache.max_seq), static_cast<int32_t>(table.max_seq), np.q, np.k, np.eps));
+}
+
+/* attn_batch over the fp16 query rows that qkv_rope_append_batch leaves. */
+inline void attn_batch_q16(const DeviceBuffer<uint16_t> &q16, const KvCacheBatch &cache,
+                           DeviceBuffer<uint16_t> &out, size_t n_q,
+                           const DeviceBuffer<int32_t> &seq_pos0, size_t n) {
+  using detail::S;
+  const size_t hd = cache.head_dim, need = cache.n_seq * n * n_q * hd;
+  if (q16.len() < need || out.len() < need)
+    throw Error::shape("attn_chunk_batch_q16: q[" + S(q16.len()) + "] and out[" + S(out.len()) +
+                       "] need " + S(need));
+  check(wst_b200_attn_chunk_batch_q16(q16.as_ptr(), cache.k.as_ptr(), cache.v.as_ptr(),
+                                      out.as_mut_ptr(), seq_pos0.as_ptr(),
+                                      static_cast<int32_t>(cache.n_seq), static_cast<int32_t>(n_q),
+                                      static_cast<int32_t>(cache.n_kv), static_cast<int32_t>(hd),
+                                      static_cast<int32_t>(n), static_cast<int32_t>(cache.max_seq),
+                                      1.0f / std::sqrt(static_cast<float>(hd))));
+}
+
 }  // namespace chunk
 
 /* --------------------------------------- one long sequence over several GPUs */
