@@ -170,6 +170,21 @@ WST_API wst_status_t wst_attn_chunk(const void *qkv, const void *k_cache, const 
 WST_API wst_status_t wst_gemm_fp16(const void *w, const void *x, const void *bias, void *y,
                            int32_t in_f, int32_t out_f, int32_t n, int32_t accum);
 
+/* The same projection with weights in the engine's hierarchical int4 format
+ * (whetstone.h:313-315, cuda/chunk_gemm.cu:61-176, cuda/hier.cuh:8-13):
+ *   qw  [out_f][in_f/32] 16-byte words: 32 nibbles q, weight c of a group in bits 4c..4c+3
+ *   si  [out_f][in_f/32] bytes: ls | lm << 4, two 4-bit scale indices per group
+ *   sb  [out_f] half2 (d, dmin)            w = q * (d * ls) - dmin * lm
+ * in_f a multiple of 32.  The engine's kernel covers 16 tokens per pass and re-reads the
+ * weights for every pass; here the weight tile is unpacked to fp16 in shared memory by
+ * eight warps of the CTA and the contraction runs on the tensor cores for any n.  Each
+ * weight is rounded to fp16 once (the engine keeps q exact and rounds partial dot
+ * products to fp16 instead); results agree within the 3e-3 relative bound of the
+ * engine's test (tests/chunk_kernels.rs:114-167). */
+WST_API wst_status_t wst_gemm_int4_hier(const void *qw, const void *si, const void *sb,
+                                const void *x, const void *bias, void *y, int32_t in_f,
+                                int32_t out_f, int32_t n, int32_t accum);
+
 /* Tokens per weight pass, which the engine takes as its prefill chunk width
  * (whetstone.h:311, src/chunk.rs:20): 512 here, 16 in the engine's kernels. */
 WST_API int32_t wst_chunk_max_tokens(void);

@@ -42,7 +42,7 @@ def test_the_archive_leaves_the_engines_runtime_symbols_out():
     names = {name for _, name in defined(ARCHIVE)}
     assert not names & set(ENGINE_RUNTIME), names & set(ENGINE_RUNTIME)
     for name in ("wst_rope_cache", "wst_attn_decode", "wst_attn_partial_floats",
-                 "wst_rope_cache_chunk", "wst_attn_chunk", "wst_gemm_fp16",
+                 "wst_rope_cache_chunk", "wst_attn_chunk", "wst_gemm_fp16", "wst_gemm_int4_hier",
                  "wst_chunk_max_tokens", "wst_attn_verify_paged", "wst_b200_set_stream"):
         assert name in names
 

@@ -191,3 +191,20 @@ def test_error_stats():
     b = np.array([[1.0, 0.001], [0.0, 2.0]])
     mx, cs = orc.error_stats(b, a)
     assert abs(mx - 0.001) < 1e-15 and 0.9999 < cs <= 1.0
+
+
+def test_int4_hier_dequant_layout():
+    """One group by hand: nibble c of the 16-byte word is weight c; w = q * (d * ls) -
+    dmin * lm (cuda/hier.cuh:8-13)."""
+    in_f, out_f = 32, 1
+    q = np.arange(32) % 16
+    words = np.zeros(4, dtype=np.uint32)
+    for c in range(32):
+        words[c // 8] |= np.uint32(q[c]) << np.uint32(4 * (c % 8))
+    si = np.array([3 | (5 << 4)], dtype=np.uint8)
+    d, dmin = np.float16(0.25), np.float16(0.5)
+    sb = np.array([int(d.view(np.uint16)) | (int(dmin.view(np.uint16)) << 16)], dtype=np.uint32)
+    w = orc.dequant_int4_hier(words, si, sb, in_f, out_f)
+    assert np.array_equal(w[0], q * (0.25 * 3) - 0.5 * 5)
+    x = np.ones((2, 32), dtype=np.float16)
+    assert np.allclose(orc.gemm_int4_hier(words, si, sb, x, in_f, out_f), w.sum())

@@ -99,6 +99,7 @@ SIGNATURES: dict[str, tuple] = {
     "wst_rope_cache_chunk": (I, [P, P, P, P, P, I, I, I, I, I, I, P, P, F]),
     "wst_attn_chunk": (I, [P, P, P, P, I, I, I, I, I, I, F]),
     "wst_gemm_fp16": (I, [P, P, P, P, I, I, I, I]),
+    "wst_gemm_int4_hier": (I, [P, P, P, P, P, P, I, I, I, I]),
     "wst_chunk_max_tokens": (I, []),
     # extensions (whetstone_b200.h)
     "wst_b200_version": (c_char_p, []),

@@ -80,6 +80,35 @@ def gemm_fp16(w: torch.Tensor, x: torch.Tensor, bias: torch.Tensor | None, y: to
                             in_features, out_features, n, int(accumulate)))
 
 
+def gemm_int4_hier(qw: torch.Tensor, si: torch.Tensor, sb: torch.Tensor, x: torch.Tensor,
+                   bias: torch.Tensor | None, y: torch.Tensor, in_features: int,
+                   out_features: int, n: int, accumulate: bool = False) -> None:
+    """gemm_fp16 with weights in the hierarchical int4 format (QuantLinearHier::gemm_ex,
+    src/gemv.rs): qw ``[out][in/32]`` 16-byte words as int32 x 4, si ``[out][in/32]`` uint8,
+    sb ``[out]`` (d, dmin) fp16 pairs."""
+    _require_cuda(qw, "gemm_int4_hier: qw", torch.int32)
+    _require_cuda(si, "gemm_int4_hier: si", torch.uint8)
+    _require_cuda(sb, "gemm_int4_hier: sb", torch.float16)
+    _require_cuda(x, "gemm_int4_hier: x", torch.float16)
+    _require_cuda(y, "gemm_int4_hier: y", torch.float32)
+    if in_features % 32 != 0:
+        raise ShapeError(5, "gemm_int4_hier: in_features must be a multiple of 32")
+    groups = out_features * in_features // 32
+    if qw.numel() != groups * 4 or si.numel() != groups or sb.numel() != 2 * out_features:
+        raise ShapeError(5, f"gemm_int4_hier: qw[{qw.numel()}], si[{si.numel()}], sb[{sb.numel()}] "
+                            f"do not match in={in_features}, out={out_features}")
+    if x.numel() != n * in_features or y.numel() != n * out_features:
+        raise ShapeError(5, f"gemm_int4_hier: x[{x.numel()}], y[{y.numel()}] do not match n={n}")
+    if bias is not None:
+        _require_cuda(bias, "gemm_int4_hier: bias", torch.float16)
+        if bias.numel() != out_features:
+            raise ShapeError(5, f"gemm_int4_hier: bias has {bias.numel()} elements")
+    use_torch_stream()
+    check(lib.wst_gemm_int4_hier(_ptr(qw), _ptr(si), _ptr(sb), _ptr(x),
+                                 _ptr(bias) if bias is not None else None, _ptr(y), in_features,
+                                 out_features, n, int(accumulate)))
+
+
 def max_tokens() -> int:
     """Tokens one weight pass serves (src/chunk.rs:20)."""
     return max(1, lib.wst_chunk_max_tokens())

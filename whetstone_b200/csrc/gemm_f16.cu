@@ -54,7 +54,6 @@ struct GCfg {
   static constexpr int OFF_BAR = NSTAGE * STAGE_BYTES;
   static constexpr int NBAR = 2 * NSTAGE + 4;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
-  static constexpr int THREADS = 192; /* 4 epilogue warps, MMA warp, TMA warp */
   static constexpr int ACC_STRIDE = BN <= 32 ? 32 : BN <= 64 ? 64 : 256; /* columns per accumulator */
   static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
   static_assert(RB % 8 == 0 && NSTAGE >= 2, "stage geometry");
@@ -70,6 +69,11 @@ struct GemmArgs {
   unsigned int *err_word;
   /* the fused form (ROPE): the tile's columns are whole heads of the qkv row; they are
    * normed, rotated and stored where the attention reads them instead of going to y */
+  /* the int4 form (INT4): the weights come packed, one 16-byte word of 32 nibbles and one
+   * byte of two 4-bit scale indices per group of 32 along K, one (d, dmin) pair per row */
+  const uint4 *qw;       /* [out_f][in_f / 32] */
+  const uint8_t *si;     /* [out_f][in_f / 32]: ls | lm << 4 */
+  const __half2 *sb;     /* [out_f]: (d, dmin) */
   __half *q_out;         /* [n][n_q * hd] */
   __half *k_cache;       /* [n_seq][n_kv][max_seq][hd] */
   __half *v_cache;
@@ -157,8 +161,13 @@ __device__ __forceinline__ void rope_head_epilogue(const GemmArgs &a, uint32_t t
   }
 }
 
-template <int BN, int KS, int RB, bool ROPE>
-__global__ void __launch_bounds__(GCfg<BN, KS, RB>::THREADS, 1)
+/* Threads of a CTA: 4 epilogue warps, the MMA warp, the TMA warp, and for the int4 form
+ * eight warps that unpack the weight tile into shared memory. */
+constexpr int kUnpackThreads = 256;
+constexpr int gemm_threads(bool int4) { return int4 ? 192 + kUnpackThreads : 192; }
+
+template <int BN, int KS, int RB, bool ROPE, bool INT4>
+__global__ void __launch_bounds__(gemm_threads(INT4), 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                 const GemmArgs a) {
   using C = GCfg<BN, KS, RB>;
@@ -175,7 +184,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) {
-      mbar_init(bar(FULL + i), 1);
+      mbar_init(bar(FULL + i), INT4 ? 1 + kUnpackThreads : 1); /* the TMA lane (+ the unpacking threads) */
       mbar_init(bar(EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -184,7 +193,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     }
     mbar_init_fence();
     tma_prefetch_desc(&xmap);
-    tma_prefetch_desc(&wmap);
+    if constexpr (!INT4) tma_prefetch_desc(&wmap);
   }
   if (warp == 4) {
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
@@ -215,8 +224,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(bar(FULL + st), C::STAGE_BYTES);
-          if constexpr (KS == 1) { /* maps over [rows][in_f]: columns past in_f read as zero */
+          mbar_arrive_expect_tx(bar(FULL + st), INT4 ? C::A_BYTES : C::STAGE_BYTES);
+          if constexpr (INT4) { /* the weight tile comes from the unpacking warps */
+            tma_load_3d(sbase + st * C::STAGE_BYTES, &xmap, bar(FULL + st), kb * C::BK, m0, 0);
+          } else if constexpr (KS == 1) { /* maps over [rows][in_f]: columns past in_f read as zero */
             tma_load_3d(sbase + st * C::STAGE_BYTES, &xmap, bar(FULL + st), kb * C::BK, m0, 0);
             tma_load_3d(sbase + st * C::STAGE_BYTES + C::A_BYTES, &wmap, bar(FULL + st), kb * C::BK,
                         n0, 0);
@@ -225,6 +236,66 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             tma_load_3d(sbase + st * C::STAGE_BYTES + C::A_BYTES, &wmap, bar(FULL + st), 0, n0,
                         kb * KS);
           }
+        }
+      }
+    }
+  } else if (warp >= 6) {
+    /* ---------------------- int4 weights -> fp16 tile in the operand layout.
+     * w = q * (d * ls) - dmin * lm per weight (cuda/hier.cuh:8-13, the arithmetic of
+     * cuda/chunk_gemm.cu:121-132), evaluated in fp32 as (q - 8) * s + (8 s - dmin * lm)
+     * and rounded to fp16 ONCE: that rounding (2^-12 of a weight on average, random in
+     * sign) is the only difference from the exact product.  With the scale and the
+     * offset rounded to fp16 per group and a half2 fma per pair -- a third fewer
+     * instructions -- the worst error over a 300 x 1024 output at contraction length 4096
+     * was 9e-3, three times this form's.  A thread takes the groups g = tid, tid + 256, ...
+     * of the stage: row g / 2 of the tile, 32-column half g % 2 of the 64-column k-block =
+     * four 16-byte chunks of the row's 128 swizzled bytes. */
+    if constexpr (INT4) {
+      const int tid = threadIdx.x - 6 * 32;
+      const int vec_per_row = a.in_f / 32;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
+        const int n0 = (tile / a.m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % NSTAGE;
+          if (it >= NSTAGE &&
+              !mbar_wait(bar(EMPTY + st), ((it / NSTAGE) - 1) & 1, a.err_word, 0x605u)) {
+            ok = false;
+            break;
+          }
+          uint8_t *btile = smem + st * C::STAGE_BYTES + C::A_BYTES;
+#pragma unroll
+          for (int g = tid; g < 2 * BN; g += kUnpackThreads) {
+            const int row = g >> 1, half = g & 1;
+            const int grow = n0 + row, v = kb * 2 + half;
+            uint32_t words[4] = {0u, 0u, 0u, 0u};
+            float sc = 0.f, mt = 0.f;
+            if (grow < a.out_f && v < vec_per_row) {
+              const size_t at = static_cast<size_t>(grow) * vec_per_row + v;
+              const uint4 packed = __ldg(a.qw + at);
+              const unsigned idx = __ldg(a.si + at);
+              const float2 dd = __half22float2(__ldg(a.sb + grow));
+              sc = dd.x * static_cast<float>(idx & 0xFu);
+              mt = fmaf(8.0f, sc, -dd.y * static_cast<float>(idx >> 4));
+              words[0] = packed.x; words[1] = packed.y; words[2] = packed.z; words[3] = packed.w;
+            } /* else: past the last row or the last group, sc = mt = 0 gives zeros */
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) { /* 8 weights = one 16-byte chunk per word */
+              uint32_t o[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                /* 2^23 + q as a float (the step of fp32 is 1 there), minus 2^23 + 8 */
+                const float q0 = __uint_as_float(0x4B000000u | ((words[wi] >> (8 * i)) & 0xFu)) - 8388616.0f;
+                const float q1 = __uint_as_float(0x4B000000u | ((words[wi] >> (8 * i + 4)) & 0xFu)) - 8388616.0f;
+                o[i] = pack_half2(fmaf(q0, sc, mt), fmaf(q1, sc, mt));
+              }
+              *reinterpret_cast<uint4 *>(btile + swz128(row, half * 4 + wi)) =
+                  make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+          fence_async_smem();
+          mbar_arrive(bar(FULL + st));
         }
       }
     }
@@ -414,19 +485,23 @@ wst_status_t operand_map(CUtensorMap *out, const void *base, int in_f, int rows,
   return WST_OK;
 }
 
-template <int BN, int KS, int RB, bool ROPE = false>
+template <int BN, int KS, int RB, bool ROPE = false, bool INT4 = false>
 wst_status_t launch_gemm(const void *w, const void *x, GemmArgs a, int sm_count) {
   using C = GCfg<BN, KS, RB>;
   CUtensorMap xmap, wmap;
   wst_status_t st = operand_map(&xmap, x, a.in_f, a.n, RB, KS);
   if (st != WST_OK) return st;
-  st = operand_map(&wmap, w, a.in_f, a.out_f, BN, KS);
-  if (st != WST_OK) return st;
+  if (INT4) {
+    wmap = xmap; /* not used: the weight tile is unpacked by the CTA itself */
+  } else {
+    st = operand_map(&wmap, w, a.in_f, a.out_f, BN, KS);
+    if (st != WST_OK) return st;
+  }
   static thread_local int configured_dev = -1;
   int dev = 0;
   WST_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    WST_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<BN, KS, RB, ROPE>,
+    WST_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<BN, KS, RB, ROPE, INT4>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured_dev = dev;
   }
@@ -435,7 +510,7 @@ wst_status_t launch_gemm(const void *w, const void *x, GemmArgs a, int sm_count)
   const long long tiles = static_cast<long long>(a.m_tiles) * a.n_tiles;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count ? tiles : sm_count));
-  cfg.blockDim = dim3(C::THREADS);
+  cfg.blockDim = dim3(gemm_threads(INT4));
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = current_stream();
   cudaLaunchAttribute attr[1];
@@ -443,7 +518,7 @@ wst_status_t launch_gemm(const void *w, const void *x, GemmArgs a, int sm_count)
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_f16_kernel<BN, KS, RB, ROPE>, xmap, wmap, a);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_f16_kernel<BN, KS, RB, ROPE, INT4>, xmap, wmap, a);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("wst_gemm_fp16 (launch)", e);
   return WST_OK;
@@ -517,6 +592,40 @@ extern "C" wst_status_t wst_gemm_fp16(const void *w, const void *x, const void *
   if (in_f % 64 == 0 && n <= 64) return launch_narrow<4, 64>(bn, w, x, a, facts.sm_count);
   if (in_f % 64 == 0) return launch_narrow<4, 128>(bn, w, x, a, facts.sm_count);
   return launch_narrow<1, 128>(bn, w, x, a, facts.sm_count);
+}
+
+extern "C" wst_status_t wst_gemm_int4_hier(const void *qw, const void *si, const void *sb,
+                                           const void *x, const void *bias, void *y,
+                                           int32_t in_f, int32_t out_f, int32_t n, int32_t accum) {
+  WST_CHECK_ARG(qw && si && sb && x && y, "wst_gemm_int4_hier: null pointer");
+  WST_CHECK_ARG(in_f > 0 && out_f > 0, "wst_gemm_int4_hier: non-positive dimension");
+  WST_CHECK_ARG(n > 0, "wst_gemm_int4_hier: n must be positive");
+  WST_CHECK_ARG(in_f % 32 == 0, "wst_gemm_int4_hier: in_features must be a multiple of 32");
+  WST_CHECK_ARG((reinterpret_cast<uintptr_t>(qw) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(sb) & 3) == 0 &&
+                    (!bias || (reinterpret_cast<uintptr_t>(bias) & 7) == 0),
+                "wst_gemm_int4_hier: buffers must be 16-byte aligned");
+  DeviceFacts facts;
+  if (!device_facts(&facts)) return WST_ERR_CUDA;
+  if (facts.cc_major < 10)
+    return fail(WST_ERR_UNSUPPORTED_ARCH, "wst_gemm_int4_hier: this library is built for sm_100a only");
+  unsigned int *err_word = device_error_word();
+  if (!err_word) return WST_ERR_CUDA;
+  GemmArgs a{};
+  a.bias = static_cast<const __half *>(bias);
+  a.y = static_cast<float *>(y);
+  a.in_f = in_f;
+  a.out_f = out_f;
+  a.n = n;
+  a.accum = accum;
+  a.err_word = err_word;
+  a.qw = static_cast<const uint4 *>(qw);
+  a.si = static_cast<const uint8_t *>(si);
+  a.sb = static_cast<const __half2 *>(sb);
+  /* the token count decides the feature tile as for fp16 weights: 256 rows for the tensor
+   * pipe, 64 when the launch is a stream of the (four times smaller) weights */
+  if (n > 128) return launch_gemm<256, 1, 128, false, true>(nullptr, x, a, facts.sm_count);
+  return launch_gemm<64, 1, 128, false, true>(nullptr, x, a, facts.sm_count);
 }
 
 extern "C" wst_status_t wst_b200_qkv_rope_append_batch(
