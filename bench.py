@@ -591,6 +591,55 @@ def bench_also(torch, args):
             del ws
         out["projection_gemm_fp16"] = legs
 
+        # the same qkv projection with weights in the hierarchical int4 format
+        # (wst_gemm_int4_hier): unpacked to fp16 in shared memory, same tensor-core loop
+        legs4 = {}
+        for tag, in_f, out_f, n in (("c4_qkv_proj_int4", hid4, s4.qkv_width, n_big),
+                                    ("c5_qkv_proj_int4", hid5, s5.qkv_width, n_small)):
+            copies = max(2, int(300e6 // (in_f * out_f * 17 // 32)) + 1)
+            groups = out_f * in_f // 32
+            sets = []
+            for _ in range(copies):
+                qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (groups * 4,), generator=gen, device="cuda",
+                                   dtype=torch.int32)
+                si = (torch.randint(1, 9, (groups,), generator=gen, device="cuda") |
+                      (torch.randint(0, 16, (groups,), generator=gen, device="cuda") << 4)).to(torch.uint8)
+                sb = torch.stack([0.002 + 0.001 * torch.rand(out_f, generator=gen, device="cuda"),
+                                  0.01 + 0.005 * torch.rand(out_f, generator=gen, device="cuda")],
+                                 dim=1).half().contiguous()
+                sets.append((qw, si, sb))
+            x = (2 * torch.rand((n, in_f), generator=gen, device="cuda") - 1).half()
+            y = torch.zeros((n, out_f), dtype=torch.float32, device="cuda")
+            qw, si, sb = sets[0]
+            chunk.gemm_int4_hier(qw, si, sb, x, None, y, in_f, out_f, n)
+            # exact weights on the device in fp32 (nibble c of a word is weight c)
+            nib = (qw.view(out_f, in_f // 8, 1) >> (4 * torch.arange(8, device="cuda", dtype=torch.int32))) & 0xF
+            ls = (si & 0xF).view(out_f, in_f // 32, 1).float().expand(-1, -1, 32).reshape(out_f, in_f)
+            lm = (si >> 4).view(out_f, in_f // 32, 1).float().expand(-1, -1, 32).reshape(out_f, in_f)
+            wf = nib.reshape(out_f, in_f).float() * (sb[:, 0:1].float() * ls) - sb[:, 1:2].float() * lm
+            want_y = x.float() @ wf.T
+            err = float(((y - want_y).abs() / want_y.abs().clamp(min=1.0)).max())
+            if not err <= 8e-3:
+                raise SystemExit(f"[bench] {tag}: wst_gemm_int4_hier differs from the product by {err}")
+            del nib, ls, lm, wf, want_y
+
+            def step4(sets=sets, x=x, y=y, in_f=in_f, out_f=out_f, n=n):
+                for qw_, si_, sb_ in sets:
+                    chunk.gemm_int4_hier(qw_, si_, sb_, x, None, y, in_f, out_f, n)
+            sec = timed_graph(torch, step4, max(1, min(args.steps, 20) // 4), 3)
+            require_clean(torch, decode, None, tag)
+            per = sec / copies
+            flops = 2.0 * in_f * out_f * n
+            byts = in_f * out_f * 17.0 / 32 + 2.0 * n * in_f + 4.0 * n * out_f
+            legs4[tag] = {"in_features": in_f, "out_features": out_f, "tokens": n,
+                          "us_per_launch": per * 1e6, "tflops": flops / per / 1e12,
+                          "frac_of_tensor_peak": flops / per / 1e12 / pk["tf_burst"],
+                          "frac_of_sustained_tensor_peak": flops / per / 1e12 / pk["tf_sustained"],
+                          "gbs": byts / per / 1e9, "frac_of_hbm_peak": byts / per / 1e9 / pk["hbm"],
+                          "max_rel_err_vs_fp32_product": err, **sec.stats}
+            del sets
+        out["projection_gemm_int4_hier"] = legs4
+
         # The attention block of one c4 chunk step (chunk 8 of 16: rows 4096..4607), end to
         # end, both ways: qkv projection -> RoPE/norm/append -> attention -> o_proj into the
         # residual.  "fused": the projection's epilogue does the RoPE step and leaves fp16

@@ -184,7 +184,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) {
-      mbar_init(bar(FULL + i), INT4 ? 1 + kUnpackThreads : 1); /* the TMA lane (+ the unpacking threads) */
+      mbar_init(bar(FULL + i), INT4 ? 1 + kUnpackThreads / 32 : 1); /* the TMA lane (+ the unpacking warps) */
       mbar_init(bar(EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -240,62 +240,127 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
       }
     }
   } else if (warp >= 6) {
-    /* ---------------------- int4 weights -> fp16 tile in the operand layout.
-     * w = q * (d * ls) - dmin * lm per weight (cuda/hier.cuh:8-13, the arithmetic of
-     * cuda/chunk_gemm.cu:121-132), evaluated in fp32 as (q - 8) * s + (8 s - dmin * lm)
-     * and rounded to fp16 ONCE: that rounding (2^-12 of a weight on average, random in
-     * sign) is the only difference from the exact product.  With the scale and the
-     * offset rounded to fp16 per group and a half2 fma per pair -- a third fewer
-     * instructions -- the worst error over a 300 x 1024 output at contraction length 4096
-     * was 9e-3, three times this form's.  A thread takes the groups g = tid, tid + 256, ...
-     * of the stage: row g / 2 of the tile, 32-column half g % 2 of the 64-column k-block =
-     * four 16-byte chunks of the row's 128 swizzled bytes. */
+    /* ---------------------- int4 weights -> fp16 tile in the operand layout
+     * (cuda/hier.cuh:8-13, the arithmetic of cuda/chunk_gemm.cu:121-132).  A thread takes
+     * the groups g = tid, tid + 256, ... of the stage: row g / 2 of the tile, 32-column
+     * half g % 2 of the 64-column k-block = four 16-byte chunks of the row's 128 swizzled
+     * bytes. */
     if constexpr (INT4) {
+      /* The packed words of a group are one dependent load from DRAM; a thread that asked
+       * for them only when their stage fell free spent a memory latency per k-block (228 us
+       * for the projection that takes 101 with fp16 weights).  So each thread keeps the
+       * words of its groups for the next kAhead k-blocks in registers. */
+      constexpr int kAhead = 4;
+      constexpr int G = 2 * BN / kUnpackThreads > 0 ? 2 * BN / kUnpackThreads : 1;
       const int tid = threadIdx.x - 6 * 32;
       const int vec_per_row = a.in_f / 32;
-      int it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
-        const int n0 = (tile / a.m_tiles) * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int st = it % NSTAGE;
-          if (it >= NSTAGE &&
-              !mbar_wait(bar(EMPTY + st), ((it / NSTAGE) - 1) & 1, a.err_word, 0x605u)) {
-            ok = false;
-            break;
-          }
-          uint8_t *btile = smem + st * C::STAGE_BYTES + C::A_BYTES;
+      const int my_tiles = blockIdx.x < n_tiles_total
+                               ? (n_tiles_total - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1
+                               : 0;
+      const int total = my_tiles * k_blocks;
+      struct Raw { /* as loaded: nothing may depend on these before their stage is unpacked */
+        uint4 w;
+        unsigned idx;
+        __half2 dd;
+      };
+      Raw ahead[kAhead][G];
+      /* the fetch cursor walks (tile, k-block) in the order of the stages; everything that
+       * needs a division is recomputed once per tile (the unpacking warps are bound by the
+       * instructions they issue: with the tile and k-block derived from the stage counter
+       * by three divisions per k-block, the address arithmetic cost as much as the
+       * unpacking) */
+      int f_left = total, f_kb = 0, f_tile = blockIdx.x;
+      size_t f_at[G];   /* group index of (row, half) at k-block 0 of the cursor's tile */
+      bool f_row_ok[G];
+      int f_grow[G];
+      auto fetch_tile = [&]() {
+        const int n0 = (f_tile / a.m_tiles) * BN;
 #pragma unroll
-          for (int g = tid; g < 2 * BN; g += kUnpackThreads) {
+        for (int j = 0; j < G; ++j) {
+          const int g = tid + j * kUnpackThreads;
+          const int grow = n0 + (g >> 1);
+          f_row_ok[j] = g < 2 * BN && grow < a.out_f;
+          f_grow[j] = grow;
+          f_at[j] = static_cast<size_t>(grow) * vec_per_row + (g & 1);
+        }
+      };
+      fetch_tile();
+      auto fetch = [&](Raw (&dst)[G]) {
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          dst[j].w = make_uint4(0u, 0u, 0u, 0u);
+          dst[j].idx = 0u;
+          dst[j].dd = __float2half2_rn(0.f); /* past the last row or the last group: zeros */
+          const int v = f_kb * 2 + ((tid + j * kUnpackThreads) & 1);
+          if (f_left > 0 && f_row_ok[j] && v < vec_per_row) {
+            const size_t at = f_at[j] + 2 * f_kb;
+            dst[j].w = __ldg(a.qw + at);
+            dst[j].idx = __ldg(a.si + at);
+            dst[j].dd = __ldg(a.sb + f_grow[j]);
+          }
+        }
+        --f_left;
+        if (++f_kb == k_blocks) {
+          f_kb = 0;
+          f_tile += gridDim.x;
+          if (f_left > 0) fetch_tile();
+        }
+      };
+      auto unpack = [&](int it, const Raw (&src)[G]) -> bool {
+        const int st = it % NSTAGE;
+        if (it >= NSTAGE && !mbar_wait(bar(EMPTY + st), ((it / NSTAGE) - 1) & 1, a.err_word, 0x605u))
+          return false;
+        uint8_t *btile = smem + st * C::STAGE_BYTES + C::A_BYTES;
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          const int g = tid + j * kUnpackThreads;
+          if (g < 2 * BN) {
             const int row = g >> 1, half = g & 1;
-            const int grow = n0 + row, v = kb * 2 + half;
-            uint32_t words[4] = {0u, 0u, 0u, 0u};
-            float sc = 0.f, mt = 0.f;
-            if (grow < a.out_f && v < vec_per_row) {
-              const size_t at = static_cast<size_t>(grow) * vec_per_row + v;
-              const uint4 packed = __ldg(a.qw + at);
-              const unsigned idx = __ldg(a.si + at);
-              const float2 dd = __half22float2(__ldg(a.sb + grow));
-              sc = dd.x * static_cast<float>(idx & 0xFu);
-              mt = fmaf(8.0f, sc, -dd.y * static_cast<float>(idx >> 4));
-              words[0] = packed.x; words[1] = packed.y; words[2] = packed.z; words[3] = packed.w;
-            } /* else: past the last row or the last group, sc = mt = 0 gives zeros */
+            const uint32_t words[4] = {src[j].w.x, src[j].w.y, src[j].w.z, src[j].w.w};
+            /* A nibble q dropped into byte 2 of 0x3F000000 is the float 0.5 + q / 256, one
+             * byte permute per weight; then w = q s - dmin lm = (256 s) f - (128 s + dmin lm)
+             * with s = d * ls is ONE fp32 fma per weight, and the result is rounded to fp16
+             * once -- the only difference from the exact weight, random in sign.  (In half2
+             * arithmetic, (q * ls) * d - fp16(lm * dmin), the rounded offset is common to the
+             * 32 weights of a group and adds up along the group: 9.7e-3 from the exact
+             * product on the engine's test case where this form has 1.3e-3 and the engine's
+             * own kernel 7.7e-3, for 6 % less time.) */
+            const float2 dd = __half22float2(src[j].dd);
+            const float s1 = dd.x * static_cast<float>(src[j].idx & 0xFu); /* d * ls */
+            const float sc = 256.0f * s1;
+            const float mt = fmaf(-128.0f, s1, -dd.y * static_cast<float>(src[j].idx >> 4));
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) { /* 8 weights = one 16-byte chunk per word */
+              const uint32_t even = words[wi] & 0x0F0F0F0Fu, odd = (words[wi] >> 4) & 0x0F0F0F0Fu;
               uint32_t o[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                /* 2^23 + q as a float (the step of fp32 is 1 there), minus 2^23 + 8 */
-                const float q0 = __uint_as_float(0x4B000000u | ((words[wi] >> (8 * i)) & 0xFu)) - 8388616.0f;
-                const float q1 = __uint_as_float(0x4B000000u | ((words[wi] >> (8 * i + 4)) & 0xFu)) - 8388616.0f;
-                o[i] = pack_half2(fmaf(q0, sc, mt), fmaf(q1, sc, mt));
+              for (int i = 0; i < 4; ++i) { /* weights 2i (low nibble of byte i) and 2i + 1 */
+                const float f0 = __uint_as_float(__byte_perm(even, 0x3F000000u, 0x7044u | (i << 8)));
+                const float f1 = __uint_as_float(__byte_perm(odd, 0x3F000000u, 0x7044u | (i << 8)));
+                o[i] = pack_half2(fmaf(f0, sc, mt), fmaf(f1, sc, mt));
               }
               *reinterpret_cast<uint4 *>(btile + swz128(row, half * 4 + wi)) =
                   make_uint4(o[0], o[1], o[2], o[3]);
             }
           }
-          fence_async_smem();
-          mbar_arrive(bar(FULL + st));
+        }
+        /* one arrival per warp: 256 arrivals on one barrier word took longer than the
+         * unpacking itself */
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(FULL + st));
+        return true;
+      };
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) fetch(ahead[u]);
+      bool ok = true;
+      for (int it0 = 0; ok && it0 < total; it0 += kAhead) {
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+          if (it0 + u < total) {
+            ok = ok && unpack(it0 + u, ahead[u]);
+            fetch(ahead[u]);
+          }
         }
       }
     }
