@@ -177,7 +177,7 @@ WST_API wst_status_t wst_gemm_fp16(const void *w, const void *x, const void *bia
  *   sb  [out_f] half2 (d, dmin)            w = q * (d * ls) - dmin * lm
  * in_f a multiple of 32.  The engine's kernel covers 16 tokens per pass and re-reads the
  * weights for every pass; here the weight tile is unpacked to fp16 in shared memory by
- * eight warps of the CTA and the contraction runs on the tensor cores for any n.  Each
+ * sixteen warps of the CTA and the contraction runs on the tensor cores for any n.  Each
  * weight is evaluated in fp32 and rounded to fp16 once (the engine keeps q exact and
  * rounds partial dot products to fp16 instead, and sits three to six times further from
  * the exact product); inside the 3e-3 relative bound of the engine's test at its shape

@@ -162,8 +162,8 @@ __device__ __forceinline__ void rope_head_epilogue(const GemmArgs &a, uint32_t t
 }
 
 /* Threads of a CTA: 4 epilogue warps, the MMA warp, the TMA warp, and for the int4 form
- * eight warps that unpack the weight tile into shared memory. */
-constexpr int kUnpackThreads = 256;
+ * sixteen warps that unpack the weight tile into shared memory. */
+constexpr int kUnpackThreads = 512;
 constexpr int gemm_threads(bool int4) { return int4 ? 192 + kUnpackThreads : 192; }
 
 template <int BN, int KS, int RB, bool ROPE, bool INT4>
@@ -242,7 +242,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
   } else if (warp >= 6) {
     /* ---------------------- int4 weights -> fp16 tile in the operand layout
      * (cuda/hier.cuh:8-13, the arithmetic of cuda/chunk_gemm.cu:121-132).  A thread takes
-     * the groups g = tid, tid + 256, ... of the stage: row g / 2 of the tile, 32-column
+     * the groups g = tid, tid + 512, ... of the stage: row g / 2 of the tile, 32-column
      * half g % 2 of the 64-column k-block = four 16-byte chunks of the row's 128 swizzled
      * bytes. */
     if constexpr (INT4) {
