@@ -404,7 +404,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++local) {
       const int buf = local & 1;
       const int m0 = (tile % a.m_tiles) * C::BM, n0 = (tile / a.m_tiles) * BN;
-      if (!mbar_wait(bar(ACC_FULL + buf), (local >> 1) & 1, a.err_word, 0x604u)) break;
+      if (!mbar_wait_idle(bar(ACC_FULL + buf), (local >> 1) & 1, a.err_word, 0x604u)) break;
       tc_fence_after_sync();
       const int row = m0 + r;
       if constexpr (ROPE) {

@@ -67,6 +67,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
   return true;
 }
 
+/* The same wait for warps that expect to wait long (an epilogue waiting for a whole
+ * tile): they sleep between polls, so that their polling does not take issue slots from
+ * the warps of the same scheduler that are working. */
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, unsigned int *err_word,
+                                               unsigned int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(200);
+    if (clock64() - t0 > kWaitCycleLimit) {
+      if (err_word) atomicCAS(err_word, 0u, code);
+      return false;
+    }
+  }
+  return true;
+}
+
 __device__ __forceinline__ uint32_t ld_shared_volatile(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
