@@ -211,6 +211,35 @@ WST_API wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
                                           int32_t head_dim, int32_t n, int32_t max_seq,
                                           float scale);
 
+/* ---- 8-bit KV cache (the engine's roadmap, docs/ROADMAP.md:206) ------ */
+
+/* The cache holds e4m3 bytes, [n_kv][max_seq][head_dim]; a stored byte times k_scale
+ * (v_scale) is the key (value).  Half the bytes of the fp16 cache per decoded token.
+ *
+ * wst_b200_rope_cache_fp8: kernel set 1 with that cache -- norm, rotation and the q
+ * write-back exactly as wst_rope_cache / wst_rope_cache_chunk; k and v rows are stored as
+ * round-to-nearest-even e4m3 of value / scale, saturating at +-448.  `pos` non-null: one
+ * token at the device cursor (n = 1, pos0 ignored); `pos` null: n tokens at rows pos0...
+ * head_dim 64, 128 or 256.
+ *
+ * wst_b200_attn_decode_fp8: wst_attn_decode over that cache (head_dim 128, at most 16
+ * query heads per KV head).  The raw tiles are streamed by TMA; every consumer warp
+ * converts its 16 positions of a tile to fp16 in shared memory right before use (every
+ * e4m3 number is an fp16 number, so the attention arithmetic is that of the fp16 path on
+ * the dequantized cache); k_scale is folded into the query scale, v_scale into the
+ * output.  `partials`: wst_attn_partial_floats as for wst_attn_decode. */
+WST_API wst_status_t wst_b200_rope_cache_fp8(void *qkv, void *k_cache8, void *v_cache8,
+                                             const void *cos_tab, const void *sin_tab, int32_t n_q,
+                                             int32_t n_kv, int32_t head_dim, const void *pos,
+                                             int32_t pos0, int32_t n, int32_t max_seq,
+                                             const void *q_norm_w, const void *k_norm_w, float eps,
+                                             float k_scale, float v_scale);
+WST_API wst_status_t wst_b200_attn_decode_fp8(const void *q, const void *k_cache8,
+                                              const void *v_cache8, void *partials, void *out,
+                                              int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                              const void *pos, int32_t max_seq, float scale,
+                                              float k_scale, float v_scale);
+
 /* ---- the projection fused with kernel set 1 ------------------------------------ */
 
 /* The qkv projection of a chunk step with the rotation, the head norm and the cache

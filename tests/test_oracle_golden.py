@@ -208,3 +208,19 @@ def test_int4_hier_dequant_layout():
     assert np.array_equal(w[0], q * (0.25 * 3) - 0.5 * 5)
     x = np.ones((2, 32), dtype=np.float16)
     assert np.allclose(orc.gemm_int4_hier(words, si, sb, x, in_f, out_f), w.sum())
+
+
+def test_e4m3_rounding_matches_torch():
+    """oracle.e4m3_quantize against torch's float8_e4m3fn (round to nearest even) wherever the
+    value is inside the finite range; beyond it the oracle saturates at 448 like the device's
+    cvt.rn.satfinite."""
+    import torch
+    x = (np.random.default_rng(0).standard_normal(200000) * 40).astype(np.float32)
+    x = x[np.abs(x) <= 448]
+    want = torch.tensor(x).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(orc.e4m3_quantize(x), want)
+    assert list(orc.e4m3_quantize(np.array([500.0, -1000.0, 464.0], dtype=np.float32))) == [126, 254, 126]
+    table = orc.e4m3_values()
+    assert table[0x7E] == 448 and table[0x38] == 1 and table[0x01] == 2.0 ** -9 and np.isnan(table[0x7F])
+    back = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
+    assert np.array_equal(np.nan_to_num(table, nan=-1), np.nan_to_num(back, nan=-1))

@@ -337,6 +337,46 @@ extern "C" wst_status_t wst_attn_decode(const void *q, const void *k_cache, cons
                        head_dim, pos, max_seq, scale, false, false);
 }
 
+extern "C" wst_status_t wst_b200_attn_decode_fp8(const void *q, const void *k_cache8,
+                                                 const void *v_cache8, void *partials, void *out,
+                                                 int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                                 const void *pos, int32_t max_seq, float scale,
+                                                 float k_scale, float v_scale) {
+  const char *who = "wst_b200_attn_decode_fp8";
+  WST_CHECK_ARG(q && k_cache8 && v_cache8 && out && pos && partials,
+                "wst_b200_attn_decode_fp8: null pointer");
+  wst_status_t st = check_decode_shape(who, n_q, n_kv, head_dim, max_seq);
+  if (st != WST_OK) return st;
+  WST_CHECK_ARG(k_scale > 0.f && v_scale > 0.f, "wst_b200_attn_decode_fp8: scales must be positive");
+  if (head_dim != 128 || n_q / n_kv > 16 || !aligned16(q) || !aligned16(k_cache8) ||
+      !aligned16(v_cache8))
+    return fail(WST_ERR_SHAPE,
+                "%s: needs head_dim 128, at most 16 query heads per KV head and 16-byte aligned "
+                "buffers", who);
+  RowsLaunch L;
+  L.name = who;
+  L.q = static_cast<const float *>(q);
+  L.k = static_cast<const __half *>(k_cache8);
+  L.v = static_cast<const __half *>(v_cache8);
+  L.kv8 = true;
+  L.k_scale = k_scale;
+  L.v_scale = v_scale;
+  L.max_seq = max_seq;
+  L.pos0_dev = static_cast<const int32_t *>(pos);
+  L.clamp_pos0_nonneg = true; /* seq = max(*pos, 0) + 1 */
+  L.n_seq = 1;
+  L.n_tok = 1;
+  L.n_q = n_q;
+  L.n_kv = n_kv;
+  L.hd = head_dim;
+  L.scale = scale;
+  L.scratch = static_cast<float *>(partials);
+  L.scratch_floats = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 4);
+  L.max_len = max_seq;
+  L.out = out;
+  return launch_rows(L);
+}
+
 extern "C" wst_status_t wst_attn_decode_noscratch(const void *q, const void *k_cache,
                                                   const void *v_cache, void *out, int32_t n_q,
                                                   int32_t n_kv, int32_t head_dim,

@@ -64,9 +64,13 @@ struct RowsArgs {
                     * number of tiles kept in flight ahead of it */
   int via_scratch; /* a single slice still writes its row to scratch: the merge kernel
                     * follows (it carries the cross-GPU exchange) */
+  float out_scale; /* fp8 cache: the values' scale, applied to the accumulated rows */
 };
 
-template <int HD, int MT, int RG>
+/* KV8: the cache holds e4m3 bytes.  A stage is then the raw K and V tiles, [BN rows][HD
+ * bytes] each, and every consumer warp keeps a private fp16 copy of its own 16 positions
+ * of the tile in flight (PRIV_BYTES), converted from the stage right before use. */
+template <int HD, int MT, int RG, bool KV8 = false>
 struct Cfg {
   static constexpr int BN = kRowsTile;
   static constexpr int NH = HD / 64;             /* 64-column (128-byte) halves */
@@ -75,8 +79,10 @@ struct Cfg {
   static constexpr int CTHREADS = CWARPS * 32;
   static constexpr int THREADS = CTHREADS + 32;
   static constexpr int HALF_BYTES = BN * 128;
-  static constexpr int STAGE_BYTES = 2 * NH * HALF_BYTES;
-  static constexpr int NSTAGE = kRowsRingBytes / STAGE_BYTES; /* at most: 6 (head_dim 128) or 12 (64) */
+  static constexpr int STAGE_BYTES = KV8 ? 2 * BN * HD : 2 * NH * HALF_BYTES;
+  static constexpr int PRIV_WARP_BYTES = 2 * NH * 16 * 128; /* K then V, [NH][16 rows][128 B] */
+  static constexpr int PRIV_BYTES = KV8 ? CWARPS * PRIV_WARP_BYTES : 0;
+  static constexpr int NSTAGE = (kRowsRingBytes - PRIV_BYTES) / STAGE_BYTES; /* 6 (head_dim 128), 12 (64), 5 (fp8) */
   static constexpr int Q_BYTES = NH * ROWS * 128;
   /* the warp-combine dump [RG][4][16*MT][HD+4] floats reuses the ring */
   static constexpr int DUMP_BYTES = RG * 4 * 16 * MT * (HD + 4) * 4;
@@ -85,7 +91,7 @@ struct Cfg {
                                         : (DUMP_BYTES + STAGE_BYTES - 1) / STAGE_BYTES;
   /* ring of `stages` stages | q tile | barriers (full, empty per stage) and the flag word */
   static constexpr int smem_bytes(int stages) {
-    return stages * STAGE_BYTES + Q_BYTES + (2 * NSTAGE + 2) * 8 + 64 + 1024;
+    return stages * STAGE_BYTES + PRIV_BYTES + Q_BYTES + (2 * NSTAGE + 2) * 8 + 64 + 1024;
   }
   static_assert(MIN_STAGES <= NSTAGE, "combine buffer must fit the ring");
   static_assert(smem_bytes(NSTAGE) <= 232448, "shared memory of one CTA");
@@ -104,11 +110,22 @@ __device__ __forceinline__ void consumer_bar(int threads) {
   asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
-template <int HD, int MT, int RG, bool PAGED>
-__global__ void __launch_bounds__(Cfg<HD, MT, RG>::THREADS, 1)
+/* four e4m3 bytes -> four fp16 values (exact: every e4m3 number is an fp16 number) */
+__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t in, uint32_t &lo, uint32_t &hi) {
+  asm("{\n\t.reg .b16 a, b;\n\t"
+      "mov.b32 {a, b}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, a;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(in));
+}
+
+template <int HD, int MT, int RG, bool PAGED, bool KV8 = false>
+__global__ void __launch_bounds__(Cfg<HD, MT, RG, KV8>::THREADS, 1)
 attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap, const RowsArgs a) {
-  using C = Cfg<HD, MT, RG>;
+  using C = Cfg<HD, MT, RG, KV8>;
+  static_assert(!KV8 || (HD == 128 && !PAGED && MT == 1 && RG == 1), "fp8 cache: the decode shape");
   constexpr int BN = C::BN, NH = C::NH, ROWS = C::ROWS;
   constexpr int HALF_BYTES = C::HALF_BYTES, STAGE_BYTES = C::STAGE_BYTES;
 
@@ -122,7 +139,8 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t *qsm = smem + nst * STAGE_BYTES;
+  uint8_t *qsm = smem + nst * STAGE_BYTES + C::PRIV_BYTES;
+  const uint32_t priv_u32 = smem_u32(smem + nst * STAGE_BYTES); /* fp8 cache: the warps' fp16 copies */
   uint64_t *bars = reinterpret_cast<uint64_t *>(qsm + C::Q_BYTES);
   const uint32_t stages_u32 = smem_u32(smem);
   const uint32_t q_u32 = smem_u32(qsm);
@@ -150,8 +168,12 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   const int ns = a.n_splits;
   auto issue_to = [&](int tile, uint32_t full, uint32_t kdst) {
     mbar_arrive_expect_tx(full, STAGE_BYTES);
-    const uint32_t vdst = kdst + NH * HALF_BYTES;
-    if constexpr (!PAGED) {
+    const uint32_t vdst = kdst + (KV8 ? BN * HD : NH * HALF_BYTES);
+    if constexpr (KV8) { /* a row of 128 e4m3 bytes is one 128-byte swizzle row: one box per tile */
+      const int plane = s * a.n_kv + kvh;
+      tma_load_3d(kdst, &kmap, full, 0, tile * BN, plane);
+      tma_load_3d(vdst, &vmap, full, 0, tile * BN, plane);
+    } else if constexpr (!PAGED) {
       const int plane = s * a.n_kv + kvh;
 #pragma unroll
       for (int h = 0; h < NH; ++h) {
@@ -378,8 +400,49 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
   for (int i = 0; i < my_tiles; ++i) {
     if (!mbar_wait(full_u32 + 8 * stage, phase, a.err_word, 0x102u)) break;
     const int tile = split + i * ns;
-    const uint32_t kb = stages_u32 + stage * STAGE_BYTES;
-    const uint32_t vb = kb + NH * HALF_BYTES;
+    uint32_t kb = stages_u32 + stage * STAGE_BYTES;
+    uint32_t vb = kb + NH * HALF_BYTES;
+    /* K / V operand addresses: row `prow` of the tile, 16-byte chunk `chg` of its HD halves */
+    uint32_t row_off = 0, half_stride = HALF_BYTES;
+    if constexpr (KV8) {
+      /* this warp's 16 positions of the raw tile -> fp16 in its private buffer, in the
+       * layout the fragment loads below expect ([NH][16 rows][128 B], swizzled): a lane
+       * takes 4 of the 128 sixteen-byte chunks of K and of V; every chunk is 16 e4m3
+       * values = two chunks of fp16 */
+      const uint32_t kp = priv_u32 + warp * C::PRIV_WARP_BYTES, vp = kp + NH * 16 * 128;
+      const uint32_t kraw = kb, vraw = kb + BN * HD;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const uint32_t raw = t ? vraw : kraw, dst = t ? vp : kp;
+        uint4 in[4];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int c = lane + 32 * c4, row = c >> 3, ch8 = c & 7;
+          asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(in[c4].x), "=r"(in[c4].y), "=r"(in[c4].z), "=r"(in[c4].w)
+                       : "r"(raw + swz128(16 * w + row, ch8)));
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int c = lane + 32 * c4, row = c >> 3, ch8 = c & 7;
+          const uint32_t words[4] = {in[c4].x, in[c4].y, in[c4].z, in[c4].w};
+          uint32_t h[8];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) e4m3x4_to_f16x4(words[k], h[2 * k], h[2 * k + 1]);
+          const int ch = 2 * ch8; /* fp16 chunk index over the row's 16 chunks */
+          const uint32_t at = dst + (ch >> 3) * (16 * 128);
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at + swz128(row, ch & 7)),
+                       "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at + swz128(row, (ch + 1) & 7)),
+                       "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+        }
+      }
+      __syncwarp();
+      kb = kp;
+      vb = vp;
+      row_off = 16 * w; /* rows of the private copy count from the warp's first position */
+      half_stride = 16 * 128;
+    }
     if (i == patch) {
       if (patcher) {
         const int ch = lane % (NH * 8);
@@ -406,7 +469,7 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       const int prow = 16 * w + (mi >> 1) * 8 + (lane & 7);
       const int chg = 2 * ks + (mi & 1);
       uint32_t b0, b1, b2, b3;
-      ldsm_x4(kb + (chg >> 3) * HALF_BYTES + swz128(prow, chg & 7), b0, b1, b2, b3);
+      ldsm_x4(kb + (chg >> 3) * half_stride + swz128(prow - row_off, chg & 7), b0, b1, b2, b3);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         if constexpr (MT == 1) {
@@ -479,7 +542,7 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
         const int rest = idx % (NH * 8);
         if (tile * BN + prow >= kv_end) {
           asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(
-                           vb + (rest >> 3) * HALF_BYTES + prow * 128 + (rest & 7) * 16),
+                           vb + (rest >> 3) * half_stride + (prow - row_off) * 128 + (rest & 7) * 16),
                        "r"(0u)
                        : "memory");
         }
@@ -495,7 +558,7 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       const int prow = 16 * w + (mi & 1) * 8 + (lane & 7);
       const int chg = 2 * jj + (mi >> 1);
       uint32_t b0, b1, b2, b3;
-      ldsm_x4_trans(vb + (chg >> 3) * HALF_BYTES + swz128(prow, chg & 7), b0, b1, b2, b3);
+      ldsm_x4_trans(vb + (chg >> 3) * half_stride + swz128(prow - row_off, chg & 7), b0, b1, b2, b3);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         mma_16816(o[mt][2 * jj], pa[mt], b0, b1);
@@ -573,6 +636,9 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       acc.z = fmaf(wgt, v.z, acc.z);
       acc.w = fmaf(wgt, v.w, acc.w);
       den = fmaf(wgt, cell[static_cast<size_t>(k) * RPG * DR + HD + 1], den);
+    }
+    if constexpr (KV8) { /* the stored values times their scale are the values */
+      acc.x *= a.out_scale; acc.y *= a.out_scale; acc.z *= a.out_scale; acc.w *= a.out_scale;
     }
     const int head = kvh * a.gqa + r % a.gqa;
     if (direct && !a.partial_out) {
@@ -1065,11 +1131,11 @@ cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, Args... ar
   return e == cudaSuccess ? cudaGetLastError() : e;
 }
 
-template <int HD, int MT, int RG, bool PAGED>
+template <int HD, int MT, int RG, bool PAGED, bool KV8 = false>
 wst_status_t launch_cfg(const RowsLaunch &L, const RowsArgs &args, const CUtensorMap &kmap,
                         const CUtensorMap &vmap, dim3 grid) {
-  using C = Cfg<HD, MT, RG>;
-  auto kern = attn_rows_kernel<HD, MT, RG, PAGED>;
+  using C = Cfg<HD, MT, RG, KV8>;
+  auto kern = attn_rows_kernel<HD, MT, RG, PAGED, KV8>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   WST_CUDA(cudaGetDevice(&dev));
@@ -1194,6 +1260,11 @@ wst_status_t launch_rows(const RowsLaunch &L) {
                 "%s: the in-kernel exchange takes one token of one contiguous sequence with a "
                 "split scratch (head_dim 64 or 128)", L.name);
 
+  if (L.kv8 && !(L.hd == 128 && !L.paged && rows == 16))
+    return fail(WST_ERR_SHAPE,
+                "%s: the fp8 cache takes head_dim 128, a contiguous cache and at most 16 query "
+                "rows per KV head", L.name);
+
   RowsArgs a{};
   a.q = L.q;
   a.q_tok_stride = L.q_tok_stride;
@@ -1213,7 +1284,8 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   a.n_kv = L.n_kv;
   a.gqa = gqa;
   a.max_seq = L.max_seq;
-  a.qscale = L.scale * kLog2e;
+  a.qscale = L.scale * kLog2e * (L.kv8 ? L.k_scale : 1.f); /* keys = stored bytes * k_scale */
+  a.out_scale = L.kv8 ? L.v_scale : 1.f;
   a.scratch = L.scratch;
   a.out = L.out;
   a.partial_out = L.partial_out ? 1 : 0;
@@ -1226,10 +1298,11 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   a.nstage = max_stages;
   if (decode_shape) a.nstage = L.hd == 128 ? kDecodeStages : 2 * kDecodeStages;
   if (tune.ring_stages >= 2 && tune.ring_stages <= max_stages) a.nstage = tune.ring_stages;
+  if (L.kv8) a.nstage = Cfg<128, 1, 1, true>::NSTAGE;
   /* requests ahead of the grid dependency: decode only (the launch ahead writes at
    * most the newest row), one row group (the patch of that row is a warp's job) */
   a.early_depth = 0;
-  if (L.newest_row_only && decode_shape && rows <= 32 && decode_overlap_allowed()) {
+  if (L.newest_row_only && decode_shape && rows <= 32 && decode_overlap_allowed() && !L.kv8) {
     a.early_depth = tune.early_depth >= 0 ? tune.early_depth : kDefaultEarlyDepth;
     if (a.early_depth > a.nstage) a.early_depth = a.nstage;
   }
@@ -1237,7 +1310,7 @@ wst_status_t launch_rows(const RowsLaunch &L) {
   if (!a.err_word) return WST_ERR_CUDA;
   CUtensorMap kmap, vmap;
   KvMapKey key{};
-  key.d0 = static_cast<uint64_t>(L.hd);
+  key.d0 = static_cast<uint64_t>(L.kv8 ? L.hd / 2 : L.hd); /* fp8 rows described as 64 two-byte elements */
   if (L.paged) {
     key.d1 = 16; key.d2 = static_cast<uint64_t>(L.n_kv); key.d3 = static_cast<uint64_t>(L.n_pool_pages);
     key.b1 = 16; key.rank = 4;
@@ -1255,7 +1328,9 @@ wst_status_t launch_rows(const RowsLaunch &L) {
 
   const dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(L.n_kv * n_rowblk),
                   static_cast<unsigned>(L.n_seq));
-  if (L.hd == 128) {
+  if (L.kv8) {
+    st = launch_cfg<128, 1, 1, false, true>(L, a, kmap, vmap, grid);
+  } else if (L.hd == 128) {
     st = L.paged ? launch_shape<128, true>(L, a, kmap, vmap, grid, rows)
                  : launch_shape<128, false>(L, a, kmap, vmap, grid, rows);
   } else {

@@ -69,6 +69,11 @@ struct RowsLaunch {
   const void *mailboxes = nullptr; /* device array of `world` mailbox addresses */
   void *xstate = nullptr;          /* this rank's per-head call counters */
   int rank = 0, world = 1;
+  /* fp8 cache (contiguous, head_dim 128, one row block of at most 16 rows): k and v point
+   * at e4m3 bytes [n_seq][n_kv][max_seq][hd]; a stored value times k_scale / v_scale is
+   * the key / value */
+  bool kv8 = false;
+  float k_scale = 1.f, v_scale = 1.f;
   const char *name = "attention";
 };
 

@@ -45,6 +45,9 @@ struct RopeArgs {
   int n_per_seq; /* contiguous batch: tokens per sequence (0 = single sequence) */
   float eps;
   int trigger_early; /* set by the launcher: single-token append under programmatic launch */
+  /* fp8 cache: k_cache / v_cache are e4m3 bytes; a row is stored as value * inv_scale */
+  int kv8;
+  float k_inv_scale, v_inv_scale;
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -90,6 +93,25 @@ __device__ __forceinline__ void store_half_vec(__half *p, const float (&x)[E]) {
     *reinterpret_cast<__half2 *>(p) = __floats2half2_rn(x[0], x[1]);
   } else {
     *p = __float2half_rn(x[0]);
+  }
+}
+
+/* E values -> e4m3 (round to nearest, saturating) at byte offset `at` of an fp8 cache */
+template <int E>
+__device__ __forceinline__ void store_fp8_vec(__half *cache, long long at, const float (&x)[E],
+                                              float inv_scale) {
+  uint8_t *dst = reinterpret_cast<uint8_t *>(cache) + at;
+  if constexpr (E >= 2) {
+#pragma unroll
+    for (int e = 0; e < E; e += 2) {
+      unsigned short two;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(two) : "f"(x[e] * inv_scale), "f"(x[e + 1] * inv_scale));
+      *reinterpret_cast<unsigned short *>(dst + e) = two;
+    }
+  } else {
+    unsigned short two;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(two) : "f"(x[0] * inv_scale), "f"(0.f));
+    dst[0] = static_cast<uint8_t>(two & 0xFF);
   }
 }
 
@@ -223,13 +245,19 @@ rope_append_kernel(const RopeArgs a) {
 
   if (place.kv_base < 0) return;
   const long long slot = place.kv_base + static_cast<long long>(kvh) * place.kv_head_stride;
-  store_half_vec<E>(a.k_cache + slot + i0, y1);
-  store_half_vec<E>(a.k_cache + slot + HALF + i0, y2);
-
   const float *vsrc = row + (a.n_q + a.n_kv + kvh) * HD;
   float v1[E], v2[E];
   load_vec<E>(vsrc + i0, v1);
   load_vec<E>(vsrc + HALF + i0, v2);
+  if (a.kv8) { /* element offsets are byte offsets in an e4m3 cache */
+    store_fp8_vec<E>(a.k_cache, slot + i0, y1, a.k_inv_scale);
+    store_fp8_vec<E>(a.k_cache, slot + HALF + i0, y2, a.k_inv_scale);
+    store_fp8_vec<E>(a.v_cache, slot + i0, v1, a.v_inv_scale);
+    store_fp8_vec<E>(a.v_cache, slot + HALF + i0, v2, a.v_inv_scale);
+    return;
+  }
+  store_half_vec<E>(a.k_cache + slot + i0, y1);
+  store_half_vec<E>(a.k_cache + slot + HALF + i0, y2);
   store_half_vec<E>(a.v_cache + slot + i0, v1);
   store_half_vec<E>(a.v_cache + slot + HALF + i0, v2);
 }
@@ -308,10 +336,17 @@ rope_append_group_kernel(const RopeArgs a) {
     } else if (place.kv_base >= 0) {
       const long long slot =
           place.kv_base + static_cast<long long>(head - a.n_q) * place.kv_head_stride;
-      store_half_vec<E>(a.k_cache + slot + i0, y1);
-      store_half_vec<E>(a.k_cache + slot + HALF + i0, y2);
-      store_half_vec<E>(a.v_cache + slot + i0, v1[g]);
-      store_half_vec<E>(a.v_cache + slot + HALF + i0, v2[g]);
+      if (a.kv8) {
+        store_fp8_vec<E>(a.k_cache, slot + i0, y1, a.k_inv_scale);
+        store_fp8_vec<E>(a.k_cache, slot + HALF + i0, y2, a.k_inv_scale);
+        store_fp8_vec<E>(a.v_cache, slot + i0, v1[g], a.v_inv_scale);
+        store_fp8_vec<E>(a.v_cache, slot + HALF + i0, v2[g], a.v_inv_scale);
+      } else {
+        store_half_vec<E>(a.k_cache + slot + i0, y1);
+        store_half_vec<E>(a.k_cache + slot + HALF + i0, y2);
+        store_half_vec<E>(a.v_cache + slot + i0, v1[g]);
+        store_half_vec<E>(a.v_cache + slot + HALF + i0, v2[g]);
+      }
     }
   }
 }
@@ -409,6 +444,9 @@ wst_status_t launch_rope(const RopeArgs &a, const char *name) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = args.trigger_early ? 1 : 0;
+  if (a.kv8 && !(vec_ok && (a.hd == 64 || a.hd == 128 || a.hd == 256)))
+    return fail(WST_ERR_SHAPE, "%s: the fp8 cache needs head_dim 64, 128 or 256 and aligned buffers",
+                name);
   cudaError_t e;
   constexpr int kGroup = 4;
   const bool grouped = !PAGED && vec_ok && a.n_tokens >= 32 && (a.n_q + a.n_kv) % kGroup == 0 &&
@@ -558,4 +596,42 @@ extern "C" wst_status_t wst_rope_cache_chunk_batch(void *qkv, void *k_cache, voi
   a.n_seq = n_seq; a.n_per_seq = n;
   a.eps = eps;
   return launch_rope<false>(a, "wst_rope_cache_chunk_batch");
+}
+
+
+/* wst_rope_cache / wst_rope_cache_chunk with an e4m3 cache: k and v rows are stored as
+ * round-to-nearest e4m3 of value / scale (saturating at 448); q is written back as fp32
+ * exactly as by the fp16 entry points.  No counterpart in the engine (its roadmap names
+ * an 8-bit cache, docs/ROADMAP.md:206). */
+extern "C" wst_status_t wst_b200_rope_cache_fp8(void *qkv, void *k_cache8, void *v_cache8,
+                                                const void *cos_tab, const void *sin_tab,
+                                                int32_t n_q, int32_t n_kv, int32_t head_dim,
+                                                const void *pos, int32_t pos0, int32_t n,
+                                                int32_t max_seq, const void *q_norm_w,
+                                                const void *k_norm_w, float eps, float k_scale,
+                                                float v_scale) {
+  WST_CHECK_ARG(qkv && k_cache8 && v_cache8 && cos_tab && sin_tab,
+                "wst_b200_rope_cache_fp8: null pointer");
+  WST_CHECK_ARG(n_q > 0 && n_kv > 0 && head_dim > 0 && n > 0 && max_seq > 0,
+                "wst_b200_rope_cache_fp8: non-positive shape");
+  WST_CHECK_ARG(k_scale > 0.f && v_scale > 0.f, "wst_b200_rope_cache_fp8: scales must be positive");
+  WST_CHECK_ARG(pos != nullptr ? n == 1
+                               : (pos0 >= 0 && static_cast<long long>(pos0) + n <= max_seq),
+                "wst_b200_rope_cache_fp8: one token at the device cursor, or a chunk inside the cache");
+  RopeArgs a{};
+  a.qkv = static_cast<float *>(qkv);
+  a.k_cache = static_cast<__half *>(k_cache8);
+  a.v_cache = static_cast<__half *>(v_cache8);
+  a.cos_tab = static_cast<const float *>(cos_tab);
+  a.sin_tab = static_cast<const float *>(sin_tab);
+  a.q_gain = static_cast<const __half *>(q_norm_w);
+  a.k_gain = static_cast<const __half *>(k_norm_w);
+  a.pos_dev = static_cast<const int32_t *>(pos);
+  a.n_q = n_q; a.n_kv = n_kv; a.hd = head_dim;
+  a.n_tokens = n; a.pos0 = pos0; a.max_seq = max_seq; a.table_len = max_seq;
+  a.eps = eps;
+  a.kv8 = 1;
+  a.k_inv_scale = 1.f / k_scale;
+  a.v_inv_scale = 1.f / v_scale;
+  return launch_rope<false>(a, "wst_b200_rope_cache_fp8");
 }

@@ -255,6 +255,55 @@ def set_tuning(key: int, value: int) -> None:
     check(lib.wst_b200_set_tuning(key, value))
 
 
+class KvCacheFp8:
+    """One layer's cache in e4m3 bytes, ``[n_kv][max_seq][head_dim]`` uint8 for K and V, with
+    the two scales (a stored byte times the scale is the value) and the split scratch."""
+
+    def __init__(self, n_kv: int, n_q: int, head_dim: int, max_seq: int, k_scale: float = 1.0,
+                 v_scale: float = 1.0, device: str = "cuda"):
+        floats = lib.wst_attn_partial_floats(n_q, head_dim, max_seq)
+        self.k = torch.zeros((n_kv, max_seq, head_dim), dtype=torch.uint8, device=device)
+        self.v = torch.zeros((n_kv, max_seq, head_dim), dtype=torch.uint8, device=device)
+        self.partials = torch.zeros(max(floats, 1), dtype=torch.float32, device=device)
+        self.n_kv, self.head_dim, self.max_seq = n_kv, head_dim, max_seq
+        self.k_scale, self.v_scale = float(k_scale), float(v_scale)
+
+
+def rope_cache_fp8(qkv: torch.Tensor, cache: KvCacheFp8, table: "RopeTable", n_q: int,
+                   pos: "DeviceCursor | None" = None, pos0: int = 0, n: int = 1,
+                   qk_norm: "QkNorm | None" = None) -> None:
+    """rope_cache (``pos`` given: one token at the cursor) or its chunk form (``pos0``,
+    ``n``) into an e4m3 cache."""
+    hd = cache.head_dim
+    _require_cuda(qkv, "rope_cache_fp8: qkv", torch.float32)
+    if qkv.numel() < n * (n_q + 2 * cache.n_kv) * hd:
+        raise ShapeError(5, f"rope_cache_fp8: qkv[{qkv.numel()}] is too short")
+    if table.half_dim != hd // 2 or table.max_seq < cache.max_seq:
+        raise ShapeError(5, "rope_cache_fp8: rotary table does not match the cache geometry")
+    if qk_norm is not None:
+        qk_norm.check(hd)
+    qw, kw, eps = norm_ptrs(qk_norm)
+    use_torch_stream()
+    check(lib.wst_b200_rope_cache_fp8(_ptr(qkv), _ptr(cache.k), _ptr(cache.v), _ptr(table.cos),
+                                      _ptr(table.sin), n_q, cache.n_kv, hd,
+                                      _ptr(pos.buf) if pos is not None else None, pos0, n,
+                                      cache.max_seq, qw, kw, eps, cache.k_scale, cache.v_scale))
+
+
+def attn_decode_fp8(qkv: torch.Tensor, cache: KvCacheFp8, out: torch.Tensor, n_q: int,
+                    pos: "DeviceCursor") -> None:
+    """attn_decode over an e4m3 cache."""
+    hd = cache.head_dim
+    _require_cuda(qkv, "attn_decode_fp8: q", torch.float32)
+    _require_cuda(out, "attn_decode_fp8: out", torch.float16)
+    if qkv.numel() < n_q * hd or out.numel() != n_q * hd:
+        raise ShapeError(5, f"attn_decode_fp8: q[{qkv.numel()}], out[{out.numel()}] need {n_q} * {hd}")
+    use_torch_stream()
+    check(lib.wst_b200_attn_decode_fp8(_ptr(qkv), _ptr(cache.k), _ptr(cache.v), _ptr(cache.partials),
+                                       _ptr(out), n_q, cache.n_kv, hd, _ptr(pos.buf), cache.max_seq,
+                                       1.0 / math.sqrt(hd), cache.k_scale, cache.v_scale))
+
+
 def device_error() -> int:
     """Read and clear the device watchdog word (0 = no kernel gave up a wait)."""
     use_torch_stream()
