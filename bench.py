@@ -697,6 +697,45 @@ def bench_also(torch, args):
             "launches": {"fused": 3, "separate": 4}, **sec_f.stats}
         del wq, wo, cache4
 
+    # ---- c3 with an 8-bit (e4m3) KV cache: the same decode step over half the bytes
+    if want("fp8"):
+        s7 = wl.QWEN25_7B
+        ctx8, lay8 = wl.C3["context"], s7.layers
+        cur8 = decode.DeviceCursor(ctx8 - 1)
+        caches8, qs8, outs8 = [], [], []
+        for _ in range(lay8):
+            c8 = decode.KvCacheFp8(s7.n_kv, s7.n_q, s7.head_dim, ctx8, k_scale=0.0625, v_scale=0.0625)
+            c8.k.copy_((randn16(tuple(c8.k.shape)).float() / c8.k_scale).to(torch.float8_e4m3fn).view(torch.uint8))
+            c8.v.copy_((randn16(tuple(c8.v.shape)).float() / c8.v_scale).to(torch.float8_e4m3fn).view(torch.uint8))
+            caches8.append(c8)
+            qs8.append(randn16((s7.qkv_width,)).float())
+            outs8.append(torch.zeros(s7.n_q * s7.head_dim, dtype=torch.float16, device="cuda"))
+        # layer 0 against plain fp32 attention over the dequantized cache (outside any timing)
+        decode.attn_decode_fp8(qs8[0], caches8[0], outs8[0], s7.n_q, cur8)
+        kf = caches8[0].k.view(torch.float8_e4m3fn).float() * caches8[0].k_scale
+        vf = caches8[0].v.view(torch.float8_e4m3fn).float() * caches8[0].v_scale
+        qf = qs8[0][: s7.n_q * s7.head_dim].view(s7.n_kv, s7.n_q // s7.n_kv, s7.head_dim)
+        att = torch.softmax(torch.einsum("kgd,ksd->kgs", qf, kf) / s7.head_dim ** 0.5, dim=-1)
+        want8 = torch.einsum("kgs,ksd->kgd", att, vf).reshape(-1)
+        err8 = float((outs8[0].float() - want8).abs().max())
+        if not err8 <= 2e-3:
+            raise SystemExit(f"[bench] fp8 decode differs from fp32 attention over the same cache by {err8}")
+        del kf, vf, att
+
+        def step8():
+            for i in range(lay8):
+                decode.attn_decode_fp8(qs8[i], caches8[i], outs8[i], s7.n_q, cur8)
+        sec = timed_graph(torch, step8, args.steps, args.warmup)
+        require_clean(torch, decode, None, "c3 fp8")
+        bytes8 = 2 * s7.n_kv * ctx8 * s7.head_dim + s7.n_q * s7.head_dim * 6
+        out["c3_fp8_kv_cache"] = {"us_per_layer": sec / lay8 * 1e6,
+                                  "hbm_gbs": bytes8 * lay8 / sec / 1e9,
+                                  "frac_of_hbm_peak": bytes8 * lay8 / sec / 1e9 / pk["hbm"],
+                                  "bytes_per_layer": bytes8, "max_abs_err_layer0": err8,
+                                  "note": "attention only, as the headline; e4m3 cache, half the bytes",
+                                  **sec.stats}
+        del caches8
+
     # ---- c5: speculative verify, 16 sequences x 5 drafts, paged cache, 28 layers
     if want("c5"):
         s5 = wl.QWEN25_7B
@@ -997,7 +1036,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip configs c1, c2, c4, c5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "gemm", "refcuda"],
+    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "gemm", "fp8", "refcuda"],
                     help="run one workload only (c3 = the headline line without 'also')")
     ap.add_argument("--no-long", action="store_true", help="skip the 262144-row decode leg")
     ap.add_argument("--min-region-s", type=float, default=0.25,
