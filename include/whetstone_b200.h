@@ -211,7 +211,7 @@ WST_API wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
                                           int32_t head_dim, int32_t n, int32_t max_seq,
                                           float scale);
 
-/* ---- 8-bit KV cache (the engine's roadmap, docs/ROADMAP.md:206) ------ */
+/* ---- 8-bit KV cache (on the engine's roadmap, docs/ROADMAP.md:206) ---------------- */
 
 /* The cache holds e4m3 bytes, [n_kv][max_seq][head_dim]; a stored byte times k_scale
  * (v_scale) is the key (value).  Half the bytes of the fp16 cache per decoded token.
