@@ -151,3 +151,42 @@ def test_bad_arguments_launch_nothing():
     with pytest.raises(ShapeError):
         chunk.gemm_fp16(w, w, None, y, 4, 4, 1)
     assert chunk.max_tokens() == 512
+
+
+def test_random_shapes_against_the_exact_product():
+    """Seeded random shapes through all feature-tile choices (few tokens: 32, 48, 64 rows
+    and one or four slabs of K per request; many tokens: 256 rows), bias and accumulate at
+    random."""
+    rng = np.random.default_rng(2026)
+    for case in range(24):
+        n = int(rng.choice([1, 3, 16, 17, 64, 65, 128, 129, 200, 600]))
+        in_f = int(rng.choice([64, 72, 128, 320, 1000, 1024, 2048]))
+        out_f = int(rng.integers(1, 40)) * int(rng.choice([1, 7, 32, 48]))
+        bias, accum = bool(rng.integers(2)), bool(rng.integers(2))
+        w = (rng.standard_normal((out_f, in_f)) / np.sqrt(in_f)).astype(np.float16)
+        x = rng.standard_normal((n, in_f)).astype(np.float16)
+        b = rng.standard_normal(out_f).astype(np.float16) if bias else None
+        y0 = rng.standard_normal((n, out_f)).astype(np.float32) if accum else None
+        got = run(w, x, b, y0, accum)
+        close(got, orc.gemm_fp16(w, x, b, y0), 2e-4, f"case {case}: {in_f} x {out_f} x {n}")
+
+
+def test_projection_replays_in_a_graph():
+    """The entry point under stream capture (after one ordinary call): same result on replay
+    with new activations."""
+    in_f, out_f, n = 512, 768, 300
+    rng = np.random.default_rng(3)
+    w = dev((rng.standard_normal((out_f, in_f)) / np.sqrt(in_f)).astype(np.float16))
+    x = dev(rng.standard_normal((n, in_f)).astype(np.float16))
+    y = torch.zeros((n, out_f), dtype=torch.float32, device="cuda")
+    chunk.gemm_fp16(w, x, None, y, in_f, out_f, n)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        chunk.gemm_fp16(w, x, None, y, in_f, out_f, n)
+    x2 = rng.standard_normal((n, in_f)).astype(np.float16)
+    x.copy_(dev(x2))
+    g.replay()
+    torch.cuda.synchronize()
+    close(host(y), orc.gemm_fp16(host(w), x2), 2e-4, "graph replay")
+    assert decode.device_error() == 0
