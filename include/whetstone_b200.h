@@ -264,6 +264,14 @@ WST_API wst_status_t wst_b200_qkv_rope_append_batch(
     int32_t n, int32_t n_q, int32_t n_kv, int32_t head_dim, int32_t max_seq, int32_t table_len,
     const void *q_norm_w, const void *k_norm_w, float eps);
 
+/* The same with the qkv weights in the engine's hierarchical int4 format (qw, si, sb as
+ * for wst_gemm_int4_hier in whetstone.h; in_f a multiple of 32). */
+WST_API wst_status_t wst_b200_qkv_int4_rope_append_batch(
+    const void *qw, const void *si, const void *sb, const void *x, const void *bias, void *q_out,
+    void *k_cache, void *v_cache, const void *cos_tab, const void *sin_tab, const void *seq_pos0,
+    int32_t in_f, int32_t n_seq, int32_t n, int32_t n_q, int32_t n_kv, int32_t head_dim,
+    int32_t max_seq, int32_t table_len, const void *q_norm_w, const void *k_norm_w, float eps);
+
 /* wst_attn_chunk_batch over fp16 query rows [n_seq * n][n_q * head_dim] (q_out above)
  * instead of the fp32 projection buffer.  Taken by the tensor-core kernels only: chunks
  * of at least 64 query rows per KV head, else WST_ERR_SHAPE. */

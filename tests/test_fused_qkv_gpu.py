@@ -135,3 +135,39 @@ def test_q16_needs_the_tensor_core_kernels():
     with pytest.raises(Exception) as err:
         chunk.attn_batch_q16(q16, cache, out, 4, starts, 4)
     assert "fp16 query rows" in str(err.value)
+
+
+def test_fused_projection_with_int4_weights():
+    """wst_b200_qkv_int4_rope_append_batch against the oracle: dequantized weights
+    (cuda/hier.cuh:8-13) -> exact projection -> RoPE / norm / append."""
+    from tests.test_gemm_int4_gpu import fast_packed_weights
+    n_seq, n, in_f, n_q, n_kv, hd, max_seq = 2, 140, 512, 4, 2, 128, 400
+    theta, eps = 1e6, 1e-6
+    width = (n_q + 2 * n_kv) * hd
+    rng = np.random.default_rng(41)
+    qw, si, sb = fast_packed_weights(in_f, width, 41)
+    x = rng.uniform(-1, 1, (n_seq * n, in_f)).astype(np.float16)
+    gq = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float16)
+    gk = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float16)
+    starts_np = np.array([7, 200], dtype=np.int32)
+    table = decode.RopeTable(max_seq, hd, theta)
+    cache = chunk.KvCacheBatch(n_seq, n_kv, hd, max_seq)
+    fill_bits(cache.k, NAN16)
+    fill_bits(cache.v, NAN16)
+    q16 = torch.zeros((n_seq * n, n_q * hd), dtype=torch.float16, device="cuda")
+    chunk.qkv_int4_rope_append_batch(dev(qw.view(np.int32)), dev(si), dev(sb.view(np.float16)), dev(x),
+                                     None, q16, cache, table, n_q, dev(starts_np), n,
+                                     decode.QkNorm(dev(gq), dev(gk), eps))
+    torch.cuda.synchronize()
+    assert decode.device_error() == 0
+    y = orc.gemm_int4_hier(qw, si, sb, x, in_f, width)
+    k_bits, v_bits = bits16(cache.k), bits16(cache.v)
+    for s in range(n_seq):
+        pos = starts_np[s] + np.arange(n)
+        q_rot, k_rot, v = orc.rope_append(y[s * n:(s + 1) * n], pos, n_q, n_kv, hd, theta, gq, gk, eps)
+        # the weights are rounded to fp16 once (3e-3 of the engine's test at this length)
+        for got, want, what in ((bits16(q16[s * n:(s + 1) * n]).reshape(n, n_q, hd), q_rot, "q"),
+                                (k_bits[s][:, pos], k_rot.transpose(1, 0, 2), "k"),
+                                (v_bits[s][:, pos], v.transpose(1, 0, 2), "v")):
+            diff = np.abs(got.view(np.float16).astype(np.float64) - want)
+            assert (diff <= 3e-3 * np.maximum(np.abs(want), 1.0)).all(), f"{what}, sequence {s}: {diff.max()}"

@@ -122,6 +122,7 @@ SIGNATURES: dict[str, tuple] = {
     "wst_rope_cache_chunk_batch": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P, P, F]),
     "wst_attn_chunk_batch": (I, [P, P, P, P, P, I, I, I, I, I, I, F]),
     "wst_b200_qkv_rope_append_batch": (I, [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, F]),
+    "wst_b200_qkv_int4_rope_append_batch": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, F]),
     "wst_b200_attn_chunk_batch_q16": (I, [P, P, P, P, P, I, I, I, I, I, I, F]),
     "wst_b200_rope_cache_fp8": (I, [P, P, P, P, P, I, I, I, P, I, I, I, P, P, F, F, F]),
     "wst_b200_attn_decode_fp8": (I, [P, P, P, P, P, I, I, I, P, I, F, F, F]),

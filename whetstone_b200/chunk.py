@@ -208,6 +208,38 @@ def qkv_rope_append_batch(w: torch.Tensor, x: torch.Tensor, bias: torch.Tensor |
         cache.n_kv, hd, cache.max_seq, table.max_seq, qw, kw, eps))
 
 
+def qkv_int4_rope_append_batch(qw: torch.Tensor, si: torch.Tensor, sb: torch.Tensor, x: torch.Tensor,
+                               bias: torch.Tensor | None, q_out: torch.Tensor, cache: KvCacheBatch,
+                               table: RopeTable, n_q: int, seq_pos0: torch.Tensor, n: int,
+                               qk_norm: QkNorm | None = None) -> None:
+    """qkv_rope_append_batch with the qkv weights in the hierarchical int4 format
+    (gemm_int4_hier's qw, si, sb)."""
+    hd = cache.head_dim
+    width = (n_q + 2 * cache.n_kv) * hd
+    tokens = cache.n_seq * n
+    _require_cuda(qw, "qkv_int4_rope_append_batch: qw", torch.int32)
+    _require_cuda(si, "qkv_int4_rope_append_batch: si", torch.uint8)
+    _require_cuda(sb, "qkv_int4_rope_append_batch: sb", torch.float16)
+    _require_cuda(x, "qkv_int4_rope_append_batch: x", torch.float16)
+    _require_cuda(q_out, "qkv_int4_rope_append_batch: q_out", torch.float16)
+    if x.numel() % tokens != 0:
+        raise ShapeError(5, f"qkv_int4_rope_append_batch: x[{x.numel()}] is not {tokens} rows")
+    in_f = x.numel() // tokens
+    groups = width * in_f // 32
+    if in_f % 32 != 0 or qw.numel() != groups * 4 or si.numel() != groups or sb.numel() != 2 * width:
+        raise ShapeError(5, "qkv_int4_rope_append_batch: packed weights do not match the shape")
+    if q_out.numel() < tokens * n_q * hd:
+        raise ShapeError(5, f"qkv_int4_rope_append_batch: q_out[{q_out.numel()}] is too short")
+    if qk_norm is not None:
+        qk_norm.check(hd)
+    qwp, kwp, eps = norm_ptrs(qk_norm)
+    use_torch_stream()
+    check(lib.wst_b200_qkv_int4_rope_append_batch(
+        _ptr(qw), _ptr(si), _ptr(sb), _ptr(x), _ptr(bias) if bias is not None else None, _ptr(q_out),
+        _ptr(cache.k), _ptr(cache.v), _ptr(table.cos), _ptr(table.sin), _ptr(seq_pos0), in_f,
+        cache.n_seq, n, n_q, cache.n_kv, hd, cache.max_seq, table.max_seq, qwp, kwp, eps))
+
+
 def attn_batch_q16(q16: torch.Tensor, cache: KvCacheBatch, out: torch.Tensor, n_q: int,
                    seq_pos0: torch.Tensor, n: int) -> None:
     """attn_batch over fp16 query rows [n_seq * n][n_q * head_dim] (what

@@ -693,25 +693,26 @@ extern "C" wst_status_t wst_gemm_int4_hier(const void *qw, const void *si, const
   return launch_gemm<64, 1, 128, false, true>(nullptr, x, a, facts.sm_count);
 }
 
-extern "C" wst_status_t wst_b200_qkv_rope_append_batch(
-    const void *w, const void *x, const void *bias, void *q_out, void *k_cache, void *v_cache,
+static wst_status_t qkv_rope_append_common(
+    const char *name, const void *w, const void *qw, const void *si, const void *sb, const void *x, const void *bias, void *q_out, void *k_cache, void *v_cache,
     const void *cos_tab, const void *sin_tab, const void *seq_pos0, int32_t in_f, int32_t n_seq,
     int32_t n, int32_t n_q, int32_t n_kv, int32_t head_dim, int32_t max_seq, int32_t table_len,
     const void *q_norm_w, const void *k_norm_w, float eps) {
-  const char *name = "wst_b200_qkv_rope_append_batch";
-  WST_CHECK_ARG(w && x && q_out && k_cache && v_cache && cos_tab && sin_tab && seq_pos0,
+  WST_CHECK_ARG((w || (qw && si && sb)) && x && q_out && k_cache && v_cache && cos_tab && sin_tab &&
+                    seq_pos0,
                 "wst_b200_qkv_rope_append_batch: null pointer");
   WST_CHECK_ARG(in_f > 0 && n_seq > 0 && n > 0 && n_q > 0 && n_kv > 0 && max_seq > 0 &&
                     table_len > 0,
                 "wst_b200_qkv_rope_append_batch: non-positive shape");
   WST_CHECK_ARG(head_dim == 64 || head_dim == 128,
                 "wst_b200_qkv_rope_append_batch: head_dim must be 64 or 128");
-  WST_CHECK_ARG(in_f % 8 == 0, "wst_b200_qkv_rope_append_batch: in_features must be a multiple of 8");
+  WST_CHECK_ARG(in_f % (qw ? 32 : 8) == 0,
+                "wst_b200_qkv_rope_append_batch: in_features must be a multiple of 8 (32 for int4 weights)");
   const long long tokens = static_cast<long long>(n_seq) * n;
   const long long out_f = static_cast<long long>(n_q + 2 * n_kv) * head_dim;
   WST_CHECK_ARG(tokens <= 0x7fffffffLL && out_f <= 0x7fffffffLL,
                 "wst_b200_qkv_rope_append_batch: shape overflows");
-  for (const void *ptr : {w, x, static_cast<const void *>(q_out), static_cast<const void *>(k_cache),
+  for (const void *ptr : {w ? w : qw, x, static_cast<const void *>(q_out), static_cast<const void *>(k_cache),
                           static_cast<const void *>(v_cache), cos_tab, sin_tab})
     WST_CHECK_ARG((reinterpret_cast<uintptr_t>(ptr) & 15) == 0,
                   "wst_b200_qkv_rope_append_batch: buffers must be 16-byte aligned");
@@ -746,7 +747,35 @@ extern "C" wst_status_t wst_b200_qkv_rope_append_batch(
   a.max_seq = max_seq;
   a.table_len = table_len;
   a.eps = eps;
+  if (qw) {
+    a.qw = static_cast<const uint4 *>(qw);
+    a.si = static_cast<const uint8_t *>(si);
+    a.sb = static_cast<const __half2 *>(sb);
+    return launch_gemm<256, 1, 128, true, true>(nullptr, x, a, facts.sm_count);
+  }
   return launch_gemm<256, 1, 128, true>(w, x, a, facts.sm_count);
+}
+
+extern "C" wst_status_t wst_b200_qkv_rope_append_batch(
+    const void *w, const void *x, const void *bias, void *q_out, void *k_cache, void *v_cache,
+    const void *cos_tab, const void *sin_tab, const void *seq_pos0, int32_t in_f, int32_t n_seq,
+    int32_t n, int32_t n_q, int32_t n_kv, int32_t head_dim, int32_t max_seq, int32_t table_len,
+    const void *q_norm_w, const void *k_norm_w, float eps) {
+  return qkv_rope_append_common("wst_b200_qkv_rope_append_batch", w, nullptr, nullptr, nullptr, x, bias,
+                                q_out, k_cache, v_cache, cos_tab, sin_tab, seq_pos0, in_f, n_seq, n, n_q,
+                                n_kv, head_dim, max_seq, table_len, q_norm_w, k_norm_w, eps);
+}
+
+/* The same with the qkv weights in the hierarchical int4 format of wst_gemm_int4_hier. */
+extern "C" wst_status_t wst_b200_qkv_int4_rope_append_batch(
+    const void *qw, const void *si, const void *sb, const void *x, const void *bias, void *q_out,
+    void *k_cache, void *v_cache, const void *cos_tab, const void *sin_tab, const void *seq_pos0,
+    int32_t in_f, int32_t n_seq, int32_t n, int32_t n_q, int32_t n_kv, int32_t head_dim,
+    int32_t max_seq, int32_t table_len, const void *q_norm_w, const void *k_norm_w, float eps) {
+  WST_CHECK_ARG(qw && si && sb, "wst_b200_qkv_int4_rope_append_batch: null pointer");
+  return qkv_rope_append_common("wst_b200_qkv_int4_rope_append_batch", nullptr, qw, si, sb, x, bias,
+                                q_out, k_cache, v_cache, cos_tab, sin_tab, seq_pos0, in_f, n_seq, n, n_q,
+                                n_kv, head_dim, max_seq, table_len, q_norm_w, k_norm_w, eps);
 }
 
 /* The engine sizes its prefill chunks by this (cuda/chunk_gemm.cu:367 returns 16, the
