@@ -25,10 +25,32 @@ def random_e4m3(rng, shape, scale):
     return orc.e4m3_quantize(rng.standard_normal(shape) / scale)
 
 
+@pytest.fixture(params=[1, 2], ids=["row-block kernel", "tensor-memory kernel"])
+def fp8_kernel(request):
+    """Both decode kernels of the e4m3 cache, whatever the cache's capacity would pick."""
+    decode.set_tuning(6, request.param)
+    yield request.param
+    decode.set_tuning(6, 0)
+
+
 @pytest.mark.parametrize("n_q,n_kv", [(28, 4), (8, 8), (32, 2)])
 @pytest.mark.parametrize("seq", [1, 17, 128, 129, 1000, 4097, 20000])
-def test_decode_over_an_fp8_cache(n_q, n_kv, seq):
-    hd, max_seq = 128, seq + 7
+def test_decode_over_an_fp8_cache(n_q, n_kv, seq, fp8_kernel):
+    run_decode_case(n_q, n_kv, seq, seq + 7)
+
+
+@pytest.mark.parametrize("seq,max_seq", [(300, 50000), (1, 16384), (70000, 70016), (16385, 40000)])
+def test_decode_picks_a_kernel_by_capacity(seq, max_seq):
+    """No tuning: the capacity decides, and slices past the live rows hold nothing."""
+    run_decode_case(28, 4, seq, max_seq)
+
+
+def test_sixteen_heads_per_kv_head(fp8_kernel):
+    run_decode_case(16, 1, 2500, 2560)
+
+
+def run_decode_case(n_q, n_kv, seq, max_seq):
+    hd = 128
     rng = np.random.default_rng(seq * 31 + n_q)
     cache = decode.KvCacheFp8(n_kv, n_q, hd, max_seq, k_scale=0.0625, v_scale=0.5)
     kb = random_e4m3(rng, (n_kv, max_seq, hd), cache.k_scale)
@@ -83,7 +105,7 @@ def test_append_into_an_fp8_cache(gains):
     assert (kb[:, untouched] == 0x7F).all() and (vb[:, untouched] == 0x7F).all()
 
 
-def test_decode_steps_through_both_entry_points():
+def test_decode_steps_through_both_entry_points(fp8_kernel):
     """Append + attend for a few tokens, the oracle reading back what the cache holds."""
     n_q, n_kv, hd, max_seq, theta = 28, 4, 128, 300, 1e6
     rng = np.random.default_rng(9)

@@ -302,6 +302,7 @@ extern "C" wst_status_t wst_b200_set_tuning(int32_t key, int32_t value) {
     case 2: t.early_depth = value; break;
     case 4: t.ring_stages = value; break;
     case 5: t.verify_ctas = value; break;
+    case 6: t.fp8_kernel = value; break;
     default: return fail(WST_ERR_INVALID_ARG, "wst_b200_set_tuning: unknown key %d", key);
   }
   return WST_OK;
@@ -374,6 +375,11 @@ extern "C" wst_status_t wst_b200_attn_decode_fp8(const void *q, const void *k_ca
   L.scratch_floats = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 4);
   L.max_len = max_seq;
   L.out = out;
+  /* The tensor-memory kernel pays about 1.3 us more per launch and 1.3 us per 128-row tile
+   * and slice where the row-block kernel pays 1.6: it wins from a few tiles per slice on.
+   * The cursor lives on the device, so the choice goes by the cache's capacity. */
+  const int pick = rows_tuning().fp8_kernel;
+  if (pick == 2 || (pick == 0 && max_seq >= 16384)) return launch_decode_fp8_tc(L);
   return launch_rows(L);
 }
 

@@ -18,6 +18,8 @@ struct RowsTuning {
   int early_depth = -1;   /* tiles requested at once ahead of the grid dependency */
   int ring_stages = 0;    /* ring depth in use (0: all the shared memory holds) */
   int verify_ctas = 0;    /* persistent CTAs of the ragged verify kernel (0: one per SM) */
+  int fp8_kernel = 0;     /* decode over the e4m3 cache: 0 by cache length, 1 row-block kernel,
+                             2 tensor-memory kernel */
 };
 RowsTuning &rows_tuning();
 
@@ -108,6 +110,10 @@ struct SplitMerge {
   const char *name = "attention";
 };
 wst_status_t launch_split_merge(const SplitMerge &m);
+
+/* Decode over the e4m3 cache with both contractions on tcgen05 (attn_decode_tc.cu):
+ * head_dim 128, one token, at most 16 query heads per KV head, contiguous cache. */
+wst_status_t launch_decode_fp8_tc(const RowsLaunch &L);
 
 /* Portable CUDA-core kernel for head widths the tensor-core kernel does not
  * take (any head_dim % 32 == 0 up to 256, contiguous cache, no split). */
