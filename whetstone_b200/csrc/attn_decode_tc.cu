@@ -1,26 +1,21 @@
 /* Decode attention over the 8-bit (e4m3) cache on the tensor-memory path.
  *
  * The row-block kernel (attn_rows.cu) spends 32 mma.sync per 64-row tile and warp on
- * the seven valid query rows of a 16-row fragment; over the fp16 cache that is just
- * under the time HBM needs for the tile, over the e4m3 cache -- half the bytes -- it is
- * the bound (1540 clocks per tile where HBM needs 620).  Here a tile is 128 keys and both
- * contractions are tcgen05.mma with M = 128: 1024 clocks of tensor pipe per tile, under
- * the 1240 in which HBM delivers 128 e4m3 rows of K and V.
+ * the seven valid query rows of a 16-row fragment and converts every tile once per
+ * consumer warp; over the e4m3 cache -- half the bytes of the fp16 cache -- that work, not
+ * HBM, is its bound.  Here a tile is 128 keys, it is converted once per block, and both
+ * contractions are tcgen05.mma with M = 128.
  *
  * One CTA per (KV head, slice of the sequence); a slice owns tiles split, split + n, ...
  *
  *   TMA warp        raw e4m3 tiles [128 keys][128 bytes] of K and of V into a ring of four
- *                   16 KB slots: 64 KB per SM on their way from HBM
- *   8 converter     e4m3 -> fp16 (exact) from the raw ring into two K and three V slots of 32 KB
- *     warps         laid out as UMMA operands ([2 halves][128 rows][128 B], 128-byte
- *                   swizzle); V rows past the live data are written as zeros.  (Plain
- *                   loads into registers instead of the raw ring were tried: sixteen
- *                   loads per thread in flight share six scoreboards, so every wait for a
- *                   tile also waited for the newest request, and a tile took 3400 clocks.)
- *                   A tile moves 192 KB through shared memory (32 in, 32 + 64 through the
- *                   converters, 64 read by the tensor core): 1536 clocks at 128 bytes per
- *                   clock, which is the bound of this kernel; HBM delivers the tile's
- *                   32 KB in about 1300.
+ *                   16 KB slots; the first four are requested before the launch ahead in
+ *                   the stream has finished (see the kernel)
+ *   4 + 4           e4m3 -> fp16 (exact) from the raw ring into two K and three V slots of
+ *     converter     32 KB laid out as K-major UMMA operands ([2 halves][128 rows][128 B],
+ *     warps         128-byte swizzle): four warps take the K tiles, four the V tiles, which
+ *                   they store TRANSPOSED ([head_dim][keys], through ldmatrix and
+ *                   stmatrix.trans) with the rows past the live data as zeros.
  *   MMA warp        S(j) = Q K(j)^T (Q in tensor memory) into one of two score buffers,
  *                   O += P(j-1) V(j-1)
  *   4 softmax       The GQA group's rows (at most 16) are REPLICATED in the four lane
@@ -33,6 +28,22 @@
  *                   memory, and a warp can reach only its quadrant: without the replicas
  *                   one warp would take the exponentials of all 128 keys of the seven
  *                   rows and the other three would idle.)
+ *
+ * What was measured on the way (SM clocks per tile and slice, 131072 rows, 28 tiles):
+ *   - Plain loads into registers instead of the raw ring: sixteen loads per thread in
+ *     flight share six scoreboards, so every wait for a tile also waited for the newest
+ *     request: 3400.
+ *   - TMA ring, eight warps converting K and V in turn, cvt only: 2400.  The same with
+ *     integer operations only: 2400.  Either way one pipe of each scheduler (the one cvt
+ *     and ex2 share, or the integer one) carried about 1300 clocks of work per tile, and
+ *     every warp paid its waits, loads and stores twice per tile.
+ *   - Eight lanes of a 16-byte store along one fp16 row collide in pairs (the row's halves
+ *     lie 16 KB apart): eight lanes down eight rows do not.  2330.
+ *   - Separate K and V quartets: 1930 (with cvt for half of the pairs and integer
+ *     operations for the other half: 1900 -> 1750 at 131072 rows).
+ * A tile moves 192 KB through shared memory (32 in, 32 + 64 through the converters, 64 read
+ * by the tensor core), 1536 clocks at 128 bytes per clock, and about 900 clocks through
+ * each of the two pipes named above; HBM delivers its 32 KB in about 1300.
  *
  * Each slice leaves one (acc, m, l) row per query head in the scratch layout of the
  * row-block kernel; attn_merge_kernel finishes.  All waits are bounded (codes 0x7xx).
@@ -77,11 +88,13 @@ static_assert(TcCfg::SMEM_BYTES <= 232448, "shared memory of one CTA");
 
 struct TcArgs {
   const float *q;        /* [n_q][128] fp32 */
+  const uint8_t *k8, *v8; /* [n_kv][max_seq][128] e4m3 (the tensor maps describe the same bytes) */
   float *scratch;        /* [n_kv][n_splits][gqa][132] */
   const int32_t *pos;    /* device cursor */
   int n_q, n_kv, gqa, max_seq, n_splits;
   float qscale;          /* scale * log2(e) * k_scale */
   float out_scale;       /* v_scale */
+  int early;             /* request the first tiles before the launch ahead has finished */
   unsigned int *err_word;
 };
 
@@ -135,14 +148,34 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, ns = a.n_splits;
 
+  /* The launch right before this one in the stream -- still running under programmatic
+   * dependent launch -- can only be writing the newest cache row; every older row was
+   * written by launches that finished long ago.  So the slice's first tiles are requested
+   * first of all, by the thread that sets up the raw ring's barriers, while the rest of the
+   * block is still being set up and before the dependency resolves (without the cursor,
+   * which is not known yet: tiles past the live rows are requested and never read).  The
+   * newest row is read again with plain loads after the wait, by the converter threads that
+   * own its pieces. */
+  grid_launch_dependents();
+  auto request = [&](int i) {
+    mbar_arrive_expect_tx(bar(RAW_FULL + i % NRAW), C::RAW_SLOT);
+    tma_load_3d(sbase + C::OFF_RAW + (i % NRAW) * C::RAW_SLOT, (i & 1) ? &vmap : &kmap, bar(RAW_FULL + i % NRAW), 0,
+                (split + (i >> 1) * ns) * BN, kvh);
+  };
+  int n_early = 0;
+  if (warp == 5 && lane == 0) {
+    for (int i = 0; i < NRAW; ++i) {
+      mbar_init(bar(RAW_FULL + i), 1);
+      mbar_init(bar(RAW_EMPTY + i), C::CONV_WARPS / 2);
+    }
+    mbar_init_fence();
+    if (a.early)
+      while (n_early < NRAW && (split + (n_early >> 1) * ns) * BN < a.max_seq) request(n_early++);
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < NCV; ++i) {
       mbar_init(bar(C_FULL + i), C::CONV_WARPS / 2);
       mbar_init(bar(C_EMPTY + i), 1);
-    }
-    for (int i = 0; i < NRAW; ++i) {
-      mbar_init(bar(RAW_FULL + i), 1);
-      mbar_init(bar(RAW_EMPTY + i), C::CONV_WARPS / 2);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(S_FULL + i), 1);
@@ -165,7 +198,6 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
-  grid_launch_dependents();
   grid_dependency_wait();
 
   int pos0 = *a.pos;
@@ -177,23 +209,22 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
   if (warp == 5) {
     /* ------- TMA producer: item i is the K (even) or V (odd) tile of the slice's tile i / 2 */
     if (lane == 0) {
-      for (int i = 0; i < 2 * T; ++i) {
-        const int st = i % NRAW;
-        if (i >= NRAW && !mbar_wait(bar(RAW_EMPTY + st), ((i / NRAW) - 1) & 1, a.err_word, 0x701u)) break;
-        mbar_arrive_expect_tx(bar(RAW_FULL + st), C::RAW_SLOT);
-        tma_load_3d(sbase + C::OFF_RAW + st * C::RAW_SLOT, (i & 1) ? &vmap : &kmap, bar(RAW_FULL + st), 0,
-                    (split + (i >> 1) * ns) * BN, kvh);
+      for (int i = n_early; i < 2 * T; ++i) {
+        if (i >= NRAW && !mbar_wait(bar(RAW_EMPTY + i % NRAW), ((i / NRAW) - 1) & 1, a.err_word, 0x701u)) break;
+        request(i);
       }
+      /* tiles requested early that turned out to lie past the live rows: let them land
+       * before the block may leave */
+      for (int i = 2 * T; i < n_early; ++i) mbar_wait(bar(RAW_FULL + i), 0, a.err_word, 0x704u);
     }
   } else if (warp >= 6) {
-    /* ------- converters: a thread takes four 16-byte pieces of an item.  Eight neighbouring
-     * lanes take the same piece of eight consecutive rows: under the 128-byte swizzle those
-     * are eight different bank groups in the raw tile and in the fp16 tile alike, so every
-     * 16-byte load and store of a warp is four wavefronts.  (Eight lanes along one row
-     * collide in pairs in the fp16 tile, whose halves lie 16 KB apart.) */
-    /* Warps 6..9 convert the K tiles and warps 10..13 the V tiles, a whole tile per warp
-     * quartet: one round of waits, loads and stores per tile and warp, and the two tiles of
-     * a step are converted side by side. */
+    /* ------- converters.  Warps 6..9 convert the K tiles and warps 10..13 the V tiles, a
+     * whole tile per warp quartet: one round of waits, loads and stores per tile and warp,
+     * and the two tiles of a step are converted side by side.  A K thread takes eight
+     * 16-byte pieces; eight neighbouring lanes take the same piece of eight consecutive
+     * rows: under the 128-byte swizzle those are eight different bank groups in the raw tile
+     * and in the fp16 tile alike, so every 16-byte load and store of a warp is four
+     * wavefronts. */
     const bool v_side = warp >= 10;
     const int cw = (warp - 6) & 3;
     const int row0 = 8 * cw + (lane & 7);  /* K piece n: row row0 + 32 (n / 2), 16-byte column lane / 8 + 4 (n % 2) */
@@ -224,6 +255,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
           asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                        : "=r"(w[n][0]), "=r"(w[n][1]), "=r"(w[n][2]), "=r"(w[n][3])
                        : "r"(src + swz128(8 * kb + vi, 4 * (n & 1) + vm)));
+          if (live <= BN && 8 * kb + (lane >> 2) == live - 1) { /* the newest row: the copy in shared memory may be stale */
+            const uint8_t *rowp = a.v8 + (static_cast<long long>(kvh) * a.max_seq + kv_end - 1) * HD +
+                                  64 * (n & 1) + 4 * (lane & 3);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) w[n][m] = *reinterpret_cast<const uint32_t *>(rowp + 16 * m);
+          }
           /* dead rows may hold anything, and 0 * NaN is NaN */
           if (8 * kb + (lane >> 2) >= live) w[n][0] = w[n][1] = w[n][2] = w[n][3] = 0u;
         }
@@ -255,6 +292,14 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
           asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
                        : "=r"(r[n].x), "=r"(r[n].y), "=r"(r[n].z), "=r"(r[n].w)
                        : "r"(src + swz128(row0 + 32 * (n >> 1), col + 4 * (n & 1))));
+        const int newest = kv_end - 1 - (split + j * ns) * BN; /* the newest row, if it is in this tile */
+        if (newest < BN) {
+#pragma unroll
+          for (int n = 0; n < 8; ++n)
+            if (row0 + 32 * (n >> 1) == newest) /* the copy in shared memory may be stale */
+              r[n] = *reinterpret_cast<const uint4 *>(
+                  a.k8 + (static_cast<long long>(kvh) * a.max_seq + kv_end - 1) * HD + 16 * (col + 4 * (n & 1)));
+        }
         if (use > 0 && !mbar_wait(bar(C_EMPTY + cs), (use - 1) & 1, a.err_word, 0x703u)) break;
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
@@ -502,6 +547,9 @@ wst_status_t launch_decode_fp8_tc(const RowsLaunch &L) {
 
   TcArgs a{};
   a.q = L.q;
+  a.k8 = reinterpret_cast<const uint8_t *>(L.k);
+  a.v8 = reinterpret_cast<const uint8_t *>(L.v);
+  a.early = decode_overlap_allowed() ? 1 : 0;
   a.scratch = L.scratch;
   a.pos = L.pos0_dev;
   a.n_q = L.n_q;
