@@ -727,14 +727,49 @@ def bench_also(torch, args):
                 decode.attn_decode_fp8(qs8[i], caches8[i], outs8[i], s7.n_q, cur8)
         sec = timed_graph(torch, step8, args.steps, args.warmup)
         require_clean(torch, decode, None, "c3 fp8")
+        decode.set_tuning(6, 1)      # the same step on the row-block kernel (mma.sync, a conversion per warp)
+        sec_rows = timed_graph(torch, step8, args.steps, args.warmup)
+        decode.set_tuning(6, 0)
+        require_clean(torch, decode, None, "c3 fp8, row-block kernel")
         bytes8 = 2 * s7.n_kv * ctx8 * s7.head_dim + s7.n_q * s7.head_dim * 6
         out["c3_fp8_kv_cache"] = {"us_per_layer": sec / lay8 * 1e6,
                                   "hbm_gbs": bytes8 * lay8 / sec / 1e9,
                                   "frac_of_hbm_peak": bytes8 * lay8 / sec / 1e9 / pk["hbm"],
                                   "bytes_per_layer": bytes8, "max_abs_err_layer0": err8,
+                                  "kernel": "attn_decode_tc_kernel (tcgen05) + attn_merge_kernel",
+                                  "row_block_kernel_us_per_layer": sec_rows / lay8 * 1e6,
                                   "note": "attention only, as the headline; e4m3 cache, half the bytes",
                                   **sec.stats}
         del caches8
+
+    if want("fp8") and not args.no_long:
+        # the same pair of caches at four times the context, where the tiles outweigh the launch
+        ctxl, layl = 4 * ctx8, 8
+        curl = decode.DeviceCursor(ctxl - 1)
+        long8 = [decode.KvCacheFp8(s7.n_kv, s7.n_q, s7.head_dim, ctxl, k_scale=0.0625, v_scale=0.0625)
+                 for _ in range(layl)]
+        long16 = [decode.KvCache(s7.n_kv, s7.n_q, s7.head_dim, ctxl) for _ in range(layl)]
+        for c8, c16 in zip(long8, long16):
+            c16.k.copy_(randn16(tuple(c16.k.shape)))
+            c16.v.copy_(randn16(tuple(c16.v.shape)))
+            c8.k.copy_((c16.k.float() / c8.k_scale).to(torch.float8_e4m3fn).view(torch.uint8))
+            c8.v.copy_((c16.v.float() / c8.v_scale).to(torch.float8_e4m3fn).view(torch.uint8))
+
+        def long_step8():
+            for i in range(layl):
+                decode.attn_decode_fp8(qs8[i], long8[i], outs8[i], s7.n_q, curl)
+
+        def long_step16():
+            for i in range(layl):
+                decode.attn_decode(qs8[i], long16[i], outs8[i], s7.n_q, curl)
+        sec_l8 = timed_graph(torch, long_step8, args.steps, args.warmup)
+        sec_l16 = timed_graph(torch, long_step16, args.steps, args.warmup)
+        require_clean(torch, decode, None, "long-context fp8")
+        out["c3_fp8_kv_cache"]["context_%d" % ctxl] = {
+            "fp8_us_per_layer": sec_l8 / layl * 1e6, "fp16_us_per_layer": sec_l16 / layl * 1e6,
+            "fp8_frac_of_hbm_peak": (2 * s7.n_kv * ctxl * s7.head_dim) * layl / sec_l8 / 1e9 / pk["hbm"],
+            "layers": layl}
+        del long8, long16
 
     # ---- c5: speculative verify, 16 sequences x 5 drafts, paged cache, 28 layers
     if want("c5"):

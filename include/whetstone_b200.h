@@ -51,7 +51,9 @@ WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
  *   key 2  cache tiles requested at once before the launch ahead has finished
  *   key 4  stages of the shared-memory ring in use (head_dim 128: 2..6; at 3 or
  *          fewer, two blocks of consecutive launches share an SM)
- *   key 5  persistent CTAs of wst_attn_verify_paged (default: one per SM) */
+ *   key 5  persistent CTAs of wst_attn_verify_paged (default: one per SM)
+ *   key 6  kernel of wst_b200_attn_decode_fp8: 0 by the cache's capacity, 1 the row-block
+ *          kernel (mma.sync), 2 the tensor-memory kernel (tcgen05) */
 WST_API wst_status_t wst_b200_set_tuning(int32_t key, int32_t value);
 
 /* 0: wst_attn_decode waits for everything ahead of it in the stream before it asks
@@ -223,11 +225,15 @@ WST_API wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
  * head_dim 64, 128 or 256.
  *
  * wst_b200_attn_decode_fp8: wst_attn_decode over that cache (head_dim 128, at most 16
- * query heads per KV head).  The raw tiles are streamed by TMA; every consumer warp
- * converts its 16 positions of a tile to fp16 in shared memory right before use (every
- * e4m3 number is an fp16 number, so the attention arithmetic is that of the fp16 path on
- * the dequantized cache); k_scale is folded into the query scale, v_scale into the
- * output.  `partials`: wst_attn_partial_floats as for wst_attn_decode. */
+ * query heads per KV head).  The raw tiles are streamed by TMA and converted to fp16 in
+ * shared memory (every e4m3 number is an fp16 number, so the attention arithmetic is that
+ * of the fp16 path on the dequantized cache); k_scale is folded into the query scale,
+ * v_scale into the output.  A cache of 16384 rows or more goes to the tensor-memory kernel
+ * (tcgen05.mma for both contractions, a block-wide conversion by dedicated warps), a
+ * smaller one to the row-block kernel, where every consumer warp converts its own 16
+ * positions of a tile.  Like wst_attn_decode, the call assumes that the launch right
+ * before it in the stream writes no cache row but the one at *pos.  `partials`:
+ * wst_attn_partial_floats as for wst_attn_decode. */
 WST_API wst_status_t wst_b200_rope_cache_fp8(void *qkv, void *k_cache8, void *v_cache8,
                                              const void *cos_tab, const void *sin_tab, int32_t n_q,
                                              int32_t n_kv, int32_t head_dim, const void *pos,
