@@ -375,11 +375,11 @@ extern "C" wst_status_t wst_b200_attn_decode_fp8(const void *q, const void *k_ca
   L.scratch_floats = static_cast<long long>(n_q) * max_splits_for(max_seq) * (head_dim + 4);
   L.max_len = max_seq;
   L.out = out;
-  /* The tensor-memory kernel pays about 1.3 us more per launch and 1.3 us per 128-row tile
-   * and slice where the row-block kernel pays 1.6: it wins from a few tiles per slice on.
+  /* The tensor-memory kernel pays about a microsecond more per launch and 0.9 us per 128-row
+   * tile and slice where the row-block kernel pays 1.6: level at 8192 rows, ahead beyond.
    * The cursor lives on the device, so the choice goes by the cache's capacity. */
   const int pick = rows_tuning().fp8_kernel;
-  if (pick == 2 || (pick == 0 && max_seq >= 16384)) return launch_decode_fp8_tc(L);
+  if (pick == 2 || (pick == 0 && max_seq >= 8192)) return launch_decode_fp8_tc(L);
   return launch_rows(L);
 }
 

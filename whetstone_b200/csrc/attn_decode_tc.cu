@@ -537,8 +537,18 @@ wst_status_t launch_decode_fp8_tc(const RowsLaunch &L) {
   DeviceFacts facts;
   if (!device_facts(&facts)) return WST_ERR_CUDA;
   const int gqa = L.n_q / L.n_kv;
-  int splits = facts.sm_count / L.n_kv;
+  /* Slices: one CTA per SM when a slice has many tiles; with few, a tenth of the SMs is left
+   * to the merge kernel and to the first blocks of the next launch, which then request their
+   * tiles and set themselves up while this launch streams (33 against 37 slices per KV head
+   * at 32768 rows and 4 KV heads: 14.4 against 15.2 us per layer; at 131072 rows: 40.2
+   * against 37.2). */
   const int tiles = (L.max_seq + C::BN - 1) / C::BN;
+  int splits = facts.sm_count / L.n_kv;
+  if (splits > 1 && tiles <= 14 * splits) {
+    const int fewer = (facts.sm_count - facts.sm_count / 10) / L.n_kv;
+    if (fewer >= 1) splits = fewer;
+  }
+  if (rows_tuning().decode_splits > 0) splits = rows_tuning().decode_splits;
   if (splits > tiles) splits = tiles;
   if (splits > kRowsMaxSplits) splits = kRowsMaxSplits;
   while (splits > 1 && rows_scratch_floats(L.n_kv * gqa, splits, L.hd) > L.scratch_floats) --splits;
