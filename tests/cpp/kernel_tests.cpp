@@ -410,6 +410,60 @@ static void decode_step_replays_as_a_graph() {
   for (float x : o) REQUIRE(std::isfinite(x), "finite output");
 }
 
+/* e4m3 (1-4-3, bias 7, no infinities): the value of a byte */
+static float e4m3_to_f32(uint8_t b) {
+  const int e = (b >> 3) & 15, m = b & 7;
+  const float mag = e == 0 ? std::ldexp(static_cast<float>(m) / 8.f, -6)
+                           : std::ldexp(1.f + static_cast<float>(m) / 8.f, e - 7);
+  return (b & 0x80) ? -mag : mag;
+}
+
+/* The 8-bit cache against the fp16 cache holding the same numbers: every e4m3 value times
+ * a power-of-two scale is an fp16 number, so both caches describe the same keys and values
+ * and the two decode paths must agree to fp16 rounding of the output.  Capacity 600 goes
+ * to the row-block kernel, 9000 to the tensor-memory kernel. */
+static void fp8_cache_case(size_t max_seq, size_t seq) {
+  const size_t n_q = 28, n_kv = 4, hd = 128;
+  const float k_scale = 0.25f, v_scale = 0.5f;
+  KvCache c16(n_kv, n_q, hd, max_seq);
+  KvCacheFp8 c8(n_kv, n_q, hd, max_seq, k_scale, v_scale);
+  std::vector<uint8_t> kb(n_kv * max_seq * hd, 0x7F), vb(kb.size(), 0x7F); /* dead rows: NaN bytes */
+  std::vector<uint16_t> kh(kb.size(), 0x7E00), vh(kb.size(), 0x7E00);     /* and fp16 NaN */
+  uint64_t x = 0x9E3779B97F4A7C15ull;
+  auto next = [&x] { x ^= x << 13; x ^= x >> 7; x ^= x << 17; return x; };
+  for (size_t h = 0; h < n_kv; ++h)
+    for (size_t p = 0; p < seq; ++p)
+      for (size_t d = 0; d < hd; ++d) {
+        const size_t at = (h * max_seq + p) * hd + d;
+        const uint64_t r = next();
+        /* sign, exponent field 0..8 (magnitudes below 4), mantissa */
+        kb[at] = static_cast<uint8_t>(((r & 1) << 7) | (((r >> 1) % 9) << 3) | ((r >> 8) & 7));
+        vb[at] = static_cast<uint8_t>((((r >> 16) & 1) << 7) | (((r >> 17) % 9) << 3) | ((r >> 24) & 7));
+        kh[at] = f32_to_f16(e4m3_to_f32(kb[at]) * k_scale);
+        vh[at] = f32_to_f16(e4m3_to_f32(vb[at]) * v_scale);
+      }
+  c8.k = DeviceBuffer<uint8_t>::from_slice(kb);
+  c8.v = DeviceBuffer<uint8_t>::from_slice(vb);
+  c16.k = DeviceBuffer<uint16_t>::from_slice(kh);
+  c16.v = DeviceBuffer<uint16_t>::from_slice(vh);
+  auto qd = DeviceBuffer<float>::from_slice(noise((n_q + 2 * n_kv) * hd, 91));
+  auto o8 = DeviceBuffer<uint16_t>::zeros(n_q * hd), o16 = DeviceBuffer<uint16_t>::zeros(n_q * hd);
+  DeviceCursor cursor(static_cast<int32_t>(seq - 1));
+  decode::attn_decode(qd, c16, o16, n_q, cursor);
+  decode::attn_decode_fp8(qd, c8, o8, n_q, cursor);
+  auto a = from_f16(o8.to_vec()), b = from_f16(o16.to_vec());
+  for (size_t i = 0; i < a.size(); ++i) {
+    REQUIRE(std::isfinite(a[i]) && std::isfinite(b[i]), "finite output");
+    REQUIRE(std::fabs(a[i] - b[i]) <= 2e-3f, "the two caches hold the same numbers");
+  }
+}
+static void fp8_cache_decodes_like_the_fp16_cache_holding_the_same_numbers() {
+  fp8_cache_case(600, 600);
+  fp8_cache_case(600, 77);
+  fp8_cache_case(9000, 9000);
+  fp8_cache_case(9000, 1031);
+}
+
 /* chunk_kernels.rs:51-108.  The engine pins its chunk GEMM against its own GEMV; the
  * GEMV is not part of this library, so the yardstick here is the same sum in double on
  * the host, with the engine's tolerance. */
@@ -459,6 +513,8 @@ int main() {
       {"gemm_fp16_matches_the_sum_per_token", gemm_fp16_matches_the_sum_per_token},
       {"gemm_fp16_accumulates_the_same_way", gemm_fp16_accumulates_the_same_way},
       {"gemm_fp16_takes_a_whole_chunk_in_one_pass", gemm_fp16_takes_a_whole_chunk_in_one_pass},
+      {"fp8_cache_decodes_like_the_fp16_cache_holding_the_same_numbers",
+       fp8_cache_decodes_like_the_fp16_cache_holding_the_same_numbers},
       {"shape_errors_are_typed_and_launch_nothing", shape_errors_are_typed_and_launch_nothing},
       {"decode_step_replays_as_a_graph", decode_step_replays_as_a_graph},
   };

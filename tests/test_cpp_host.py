@@ -29,4 +29,4 @@ def test_cpp_kernel_tests_pass():
         subprocess.run(["make", "-C", str(ROOT / "tests" / "cpp")], check=True, capture_output=True)
     proc = subprocess.run([str(BIN)], capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stdout + proc.stderr
-    assert "0 failed" in proc.stdout and proc.stdout.count("ok ") == 13, proc.stdout
+    assert "0 failed" in proc.stdout and proc.stdout.count("ok ") == 14, proc.stdout

@@ -173,6 +173,29 @@ struct KvCache {
   size_t bytes() const { return k.bytes() + v.bytes() + partials.bytes(); }
 };
 
+/* One layer's cache in e4m3 bytes (the engine's roadmap names an 8-bit cache,
+ * docs/ROADMAP.md:206; it has no type for it yet): a stored byte times k_scale / v_scale is
+ * the key / value.  Same shape and scratch as KvCache. */
+struct KvCacheFp8 {
+  DeviceBuffer<uint8_t> k, v;    /* [n_kv][max_seq][head_dim] e4m3 */
+  DeviceBuffer<float> partials;  /* split scratch, sized by the library */
+  size_t n_kv, head_dim, max_seq;
+  float k_scale, v_scale;
+
+  KvCacheFp8(size_t n_kv_, size_t n_q, size_t head_dim_, size_t max_seq_, float k_scale_ = 1.f,
+             float v_scale_ = 1.f)
+      : n_kv(n_kv_), head_dim(head_dim_), max_seq(max_seq_), k_scale(k_scale_), v_scale(v_scale_) {
+    const size_t n = n_kv * max_seq * head_dim;
+    const int32_t floats = wst_attn_partial_floats(static_cast<int32_t>(n_q),
+                                                   static_cast<int32_t>(head_dim),
+                                                   static_cast<int32_t>(max_seq));
+    k = DeviceBuffer<uint8_t>::zeros(n);
+    v = DeviceBuffer<uint8_t>::zeros(n);
+    partials = DeviceBuffer<float>::zeros(static_cast<size_t>(floats > 1 ? floats : 1));
+  }
+  size_t bytes() const { return k.bytes() + v.bytes() + partials.bytes(); }
+};
+
 struct DeviceCursor {
   DeviceBuffer<int32_t> buf;
   explicit DeviceCursor(int32_t value) : buf(DeviceBuffer<int32_t>::from_slice({value})) {}
@@ -231,6 +254,42 @@ inline void attn_decode(const DeviceBuffer<float> &qkv, KvCache &cache, DeviceBu
                         static_cast<int32_t>(cache.n_kv), static_cast<int32_t>(hd),
                         pos.buf.as_ptr(), static_cast<int32_t>(cache.max_seq),
                         1.0f / std::sqrt(static_cast<float>(hd))));
+}
+
+/* The same two steps over an 8-bit cache: the append stores round-to-nearest-even e4m3 of
+ * value / scale, the attention reads the bytes back times the scale (head_dim 128, at most
+ * 16 query heads per KV head). */
+inline void rope_cache_fp8(DeviceBuffer<float> &qkv, KvCacheFp8 &cache, const RopeTable &table,
+                           size_t n_q, const DeviceCursor &pos, const QkNorm *qk_norm = nullptr) {
+  using detail::S;
+  const size_t hd = cache.head_dim, want = (n_q + 2 * cache.n_kv) * hd;
+  if (qkv.len() != want)
+    throw Error::shape("rope_cache_fp8: qkv[" + S(qkv.len()) + "] should be (" + S(n_q) + " + 2*" +
+                       S(cache.n_kv) + ") * " + S(hd) + " = " + S(want));
+  if (table.half_dim != hd / 2 || table.max_seq < cache.max_seq)
+    throw Error::shape("rope_cache_fp8: rotary table does not match the cache geometry");
+  const auto n = detail::norm_ptrs(qk_norm);
+  check(wst_b200_rope_cache_fp8(qkv.as_mut_ptr(), cache.k.as_mut_ptr(), cache.v.as_mut_ptr(),
+                                table.cos.as_ptr(), table.sin.as_ptr(), static_cast<int32_t>(n_q),
+                                static_cast<int32_t>(cache.n_kv), static_cast<int32_t>(hd),
+                                pos.buf.as_ptr(), 0, 1, static_cast<int32_t>(cache.max_seq), n.q, n.k,
+                                n.eps, cache.k_scale, cache.v_scale));
+}
+
+inline void attn_decode_fp8(const DeviceBuffer<float> &qkv, KvCacheFp8 &cache,
+                            DeviceBuffer<uint16_t> &out, size_t n_q, const DeviceCursor &pos) {
+  using detail::S;
+  const size_t hd = cache.head_dim;
+  if (qkv.len() < n_q * hd || out.len() != n_q * hd)
+    throw Error::shape("attn_decode_fp8: qkv[" + S(qkv.len()) + "] must hold at least " + S(n_q) +
+                       "*" + S(hd) + " queries and out[" + S(out.len()) + "] exactly that");
+  check(wst_b200_attn_decode_fp8(qkv.as_ptr(), cache.k.as_ptr(), cache.v.as_ptr(),
+                                 cache.partials.as_mut_ptr(), out.as_mut_ptr(),
+                                 static_cast<int32_t>(n_q), static_cast<int32_t>(cache.n_kv),
+                                 static_cast<int32_t>(hd), pos.buf.as_ptr(),
+                                 static_cast<int32_t>(cache.max_seq),
+                                 1.0f / std::sqrt(static_cast<float>(hd)), cache.k_scale,
+                                 cache.v_scale));
 }
 
 /* One shard of a KV sequence split over GPUs: (m, l, acc) per head over rows [0, *len). */
