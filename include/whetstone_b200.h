@@ -232,8 +232,10 @@ WST_API wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
  * (tcgen05.mma for both contractions, a block-wide conversion by dedicated warps), a
  * smaller one to the row-block kernel, where every consumer warp converts its own 16
  * positions of a tile.  Like wst_attn_decode, the call assumes that the launch right
- * before it in the stream writes no cache row but the one at *pos.  `partials`:
- * wst_attn_partial_floats as for wst_attn_decode. */
+ * before it in the stream writes no cache row but the one at *pos.  The two NaN bytes of
+ * e4m3 (0x7f, 0xff) must not occur in rows [0, *pos]: the append never writes them (it
+ * saturates), and the kernels do not agree on what they read them as.  Rows past *pos may
+ * hold anything.  `partials`: wst_attn_partial_floats as for wst_attn_decode. */
 WST_API wst_status_t wst_b200_rope_cache_fp8(void *qkv, void *k_cache8, void *v_cache8,
                                              const void *cos_tab, const void *sin_tab, int32_t n_q,
                                              int32_t n_kv, int32_t head_dim, const void *pos,

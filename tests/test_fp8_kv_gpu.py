@@ -130,6 +130,41 @@ def test_decode_steps_through_both_entry_points(fp8_kernel):
     assert decode.device_error() == 0
 
 
+def test_the_row_just_appended_is_the_row_attended_to(fp8_kernel):
+    """The attention may request its tiles while the append ahead of it is still running;
+    whatever it fetched that early, the newest row must be the appended one.  Queries
+    aligned with the new key put nearly all of the weight on that row, so a stale copy
+    (the zeros the row held before) would show in every head."""
+    n_q, n_kv, hd, max_seq, theta = 28, 4, 128, 8300, 1e6
+    rng = np.random.default_rng(21)
+    table = decode.RopeTable(max_seq, hd, theta)
+    cache = decode.KvCacheFp8(n_kv, n_q, hd, max_seq, k_scale=0.0625, v_scale=0.0625)
+    start = 8100
+    cache.k[:, :start] = dev(random_e4m3(rng, (n_kv, start, hd), cache.k_scale * 4))   # small keys
+    cache.v[:, :start] = dev(random_e4m3(rng, (n_kv, start, hd), cache.v_scale))
+    cur = decode.DeviceCursor(start)
+    out = torch.zeros(n_q * hd, dtype=torch.float16, device="cuda")
+    group = n_q // n_kv
+    for step in range(8):
+        k_new = rng.standard_normal((n_kv, hd)).astype(np.float32)
+        v_new = rng.standard_normal((n_kv, hd)).astype(np.float32)
+        q = np.repeat(k_new, group, axis=0) * 3.0            # head h looks for its group's new key
+        qkv = dev(np.concatenate([q.reshape(-1), k_new.reshape(-1), v_new.reshape(-1)]))
+        decode.rope_cache_fp8(qkv, cache, table, n_q, pos=cur)   # no synchronisation in between
+        decode.attn_decode_fp8(qkv, cache, out, n_q, cur)
+        torch.cuda.synchronize()
+        seq = start + step + 1
+        k = orc.e4m3_dequantize(host(cache.k)[:, :seq], cache.k_scale)
+        v = orc.e4m3_dequantize(host(cache.v)[:, :seq], cache.v_scale)
+        got = host(out).astype(np.float64).reshape(n_q, hd)
+        want = orc.decode_attention(host(qkv)[: n_q * hd].reshape(n_q, hd), k, v, seq)
+        assert_close_per_head(got, want, f"step {step}")
+        newest = np.repeat(v[:, seq - 1], group, axis=0)
+        assert np.abs(got - newest).max() < 0.05, "the output is the appended value row"
+        cur.advance(max_seq)
+    assert decode.device_error() == 0
+
+
 def test_shapes_the_fp8_path_does_not_take():
     cache = decode.KvCacheFp8(2, 4, 64, 32)
     out = torch.zeros(4 * 64, dtype=torch.float16, device="cuda")
