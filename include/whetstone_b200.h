@@ -228,7 +228,7 @@ WST_API wst_status_t wst_attn_chunk_batch(const void *qkv, const void *k_cache,
  * query heads per KV head).  The raw tiles are streamed by TMA and converted to fp16 in
  * shared memory (every e4m3 number is an fp16 number, so the attention arithmetic is that
  * of the fp16 path on the dequantized cache); k_scale is folded into the query scale,
- * v_scale into the output.  A cache of 8192 rows or more goes to the tensor-memory kernel
+ * v_scale into the output.  A cache of 12288 rows or more goes to the tensor-memory kernel
  * (tcgen05.mma for both contractions, a block-wide conversion by dedicated warps), a
  * smaller one to the row-block kernel, where every consumer warp converts its own 16
  * positions of a tile.  Like wst_attn_decode, the call assumes that the launch right

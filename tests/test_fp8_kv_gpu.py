@@ -39,7 +39,7 @@ def test_decode_over_an_fp8_cache(n_q, n_kv, seq, fp8_kernel):
     run_decode_case(n_q, n_kv, seq, seq + 7)
 
 
-@pytest.mark.parametrize("seq,max_seq", [(300, 50000), (1, 8192), (8191, 8191), (70000, 70016), (16385, 40000)])
+@pytest.mark.parametrize("seq,max_seq", [(300, 50000), (1, 12288), (12287, 12287), (70000, 70016), (16385, 40000)])
 def test_decode_picks_a_kernel_by_capacity(seq, max_seq):
     """No tuning: the capacity decides, and slices past the live rows hold nothing."""
     run_decode_case(28, 4, seq, max_seq)

@@ -376,10 +376,10 @@ extern "C" wst_status_t wst_b200_attn_decode_fp8(const void *q, const void *k_ca
   L.max_len = max_seq;
   L.out = out;
   /* The tensor-memory kernel pays about a microsecond more per launch and 0.9 us per 128-row
-   * tile and slice where the row-block kernel pays 1.6: level at 8192 rows, ahead beyond.
+   * tile and slice where the row-block kernel pays 1.4: level at 12288 rows, ahead beyond.
    * The cursor lives on the device, so the choice goes by the cache's capacity. */
   const int pick = rows_tuning().fp8_kernel;
-  if (pick == 2 || (pick == 0 && max_seq >= 8192)) return launch_decode_fp8_tc(L);
+  if (pick == 2 || (pick == 0 && max_seq >= 12288)) return launch_decode_fp8_tc(L);
   return launch_rows(L);
 }
 

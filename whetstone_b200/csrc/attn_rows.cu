@@ -408,7 +408,10 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
       /* this warp's 16 positions of the raw tile -> fp16 in its private buffer, in the
        * layout the fragment loads below expect ([NH][16 rows][128 B], swizzled): a lane
        * takes 4 of the 128 sixteen-byte chunks of K and of V; every chunk is 16 e4m3
-       * values = two chunks of fp16 */
+       * values = two chunks of fp16.  Eight neighbouring lanes take the same chunk of eight
+       * consecutive rows: eight different bank groups under the swizzle, in the raw tile
+       * and in the copy (eight lanes along one row collide in pairs in the copy, whose
+       * halves lie 2 KB apart). */
       const uint32_t kp = priv_u32 + warp * C::PRIV_WARP_BYTES, vp = kp + NH * 16 * 128;
       const uint32_t kraw = kb, vraw = kb + BN * HD;
 #pragma unroll
@@ -417,14 +420,14 @@ attn_rows_kernel(const __grid_constant__ CUtensorMap kmap,
         uint4 in[4];
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {
-          const int c = lane + 32 * c4, row = c >> 3, ch8 = c & 7;
+          const int row = (lane & 7) + 8 * (c4 >> 1), ch8 = (lane >> 3) + 4 * (c4 & 1);
           asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
                        : "=r"(in[c4].x), "=r"(in[c4].y), "=r"(in[c4].z), "=r"(in[c4].w)
                        : "r"(raw + swz128(16 * w + row, ch8)));
         }
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {
-          const int c = lane + 32 * c4, row = c >> 3, ch8 = c & 7;
+          const int row = (lane & 7) + 8 * (c4 >> 1), ch8 = (lane >> 3) + 4 * (c4 & 1);
           const uint32_t words[4] = {in[c4].x, in[c4].y, in[c4].z, in[c4].w};
           uint32_t h[8];
 #pragma unroll
