@@ -56,9 +56,9 @@ WST_API wst_status_t wst_b200_set_kernel_choice(int32_t choice);
  *          kernel (mma.sync), 2 the tensor-memory kernel (tcgen05) */
 WST_API wst_status_t wst_b200_set_tuning(int32_t key, int32_t value);
 
-/* 0: wst_attn_decode waits for everything ahead of it in the stream before it asks
- * for any cache row (no stream-order precondition, see whetstone.h); 1 (default):
- * it asks for the rows below the cursor early.  Process-wide. */
+/* 0: wst_attn_decode (and wst_b200_attn_decode_fp8) waits for everything ahead of it in
+ * the stream before it asks for any cache row (no stream-order precondition, see
+ * whetstone.h); 1 (default): it asks for the rows below the cursor early.  Process-wide. */
 WST_API wst_status_t wst_b200_set_decode_overlap(int32_t on);
 
 /* Allocates the calling thread's 16 MiB split workspace of wst_attn_chunk /
